@@ -1,0 +1,266 @@
+"""Cache manager: the host-side bookkeeping (native, `csrc/host/cache_manager.cpp`) and the
+device memory it describes.
+
+Layers are sorted into groups by what they must keep: all keys, or a window of them.  Each
+group has its own pool of pages and its own block table per request; layers of a group share
+the table, each with K and V planes of its own laid out [page][kv_head][slot][head_dim].
+Beside the pages, every live request owns one slot; layers that keep fixed-size state get a
+tensor [slots, *shape] indexed by it.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..csrc import build as _build
+from ..parts.base import CacheSpec, FixedStateSpec, PagedKVSpec
+
+
+class CacheError(RuntimeError):
+    pass
+
+
+class OutOfPages(CacheError):
+    pass
+
+
+_host = None
+
+
+def host_library() -> ctypes.CDLL:
+    """The native host runtime (cache manager and scheduler), built on first use."""
+    global _host
+    if _host is None:
+        lib = ctypes.CDLL(_build.build_host())
+        vp, i, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        ip = ctypes.POINTER(ctypes.c_int)
+        llp = ctypes.POINTER(ctypes.c_longlong)
+        sig = {
+            "kcache_create": (vp, [i, ip, ip, i, i, i]), "kcache_destroy": (None, [vp]),
+            "kcache_admit": (i, [vp, ll]), "kcache_can_reserve": (i, [vp, ll, i]),
+            "kcache_reserve": (i, [vp, ll, i]), "kcache_commit": (i, [vp, ll, i]),
+            "kcache_release": (i, [vp, ll]), "kcache_length": (i, [vp, ll]), "kcache_slot": (i, [vp, ll]),
+            "kcache_num_blocks": (i, [vp, ll, i]), "kcache_block_table": (i, [vp, ll, i, vp, i]),
+            "kcache_free_pages": (i, [vp, i]), "kcache_num_pages": (i, [vp, i]),
+            "kcache_num_groups": (i, [vp]), "kcache_page_size": (i, [vp]),
+            "kcache_live_requests": (i, [vp]), "kcache_free_slots": (i, [vp]),
+            "kcache_pages_handed_out": (ll, [vp]), "kcache_pages_given_back": (ll, [vp]),
+            "kcache_check": (i, [vp]),
+            "ksched_create": (vp, [vp, i, i, i, i, i]), "ksched_destroy": (None, [vp]),
+            "ksched_add": (i, [vp, ll, i, i]), "ksched_schedule": (i, [vp, llp, ip, ip, ip, i]),
+            "ksched_preempted": (i, [vp, llp, i]), "ksched_step_done": (i, [vp]),
+            "ksched_on_token": (i, [vp, ll]), "ksched_finish": (i, [vp, ll]),
+            "ksched_num_running": (i, [vp]), "ksched_num_waiting": (i, [vp]),
+            "ksched_num_preemptions": (ll, [vp]), "ksched_known": (i, [vp, ll]),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _host = lib
+    return _host
+
+
+@dataclass(frozen=True)
+class GroupInfo:
+    window: int              # 0 = all keys
+    num_pages: int
+    layers: Tuple[int, ...]  # cache layers that share this group's block tables
+
+
+class LayerCache:
+    """What one layer call sees of the cache."""
+
+    __slots__ = ("index", "group", "page_size", "k", "v", "state", "writable", "spec")
+
+    def __init__(self, index, group, page_size, k, v, state, writable, spec):
+        self.index, self.group, self.page_size = index, group, page_size
+        self.k, self.v, self.state, self.writable, self.spec = k, v, state, writable, spec
+
+
+class PageTable:
+    """The native bookkeeping alone (no device memory): groups, pages, block tables, slots."""
+
+    def __init__(self, windows: Sequence[int], num_pages: Sequence[int], page_size: int,
+                 max_requests: int, max_blocks_per_request: int):
+        self._lib = host_library()
+        n = len(windows)
+        W = (ctypes.c_int * max(1, n))(*windows)
+        P = (ctypes.c_int * max(1, n))(*num_pages)
+        self._h = self._lib.kcache_create(n, W, P, page_size, max_requests, max_blocks_per_request)
+        if not self._h:
+            raise CacheError("cache manager: bad sizes")
+        self.page_size = page_size
+        self.num_groups = n
+        self.max_requests = max_requests
+        self.max_blocks = max_blocks_per_request
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.kcache_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def admit(self, rid: int) -> int:
+        slot = self._lib.kcache_admit(self._h, rid)
+        if slot == -1:
+            raise CacheError(f"no free state slot for request {rid} ({self.max_requests} live)")
+        if slot == -2:
+            raise CacheError(f"request {rid} is live already")
+        return slot
+
+    def can_reserve(self, rid: int, n_new: int) -> bool:
+        rc = self._lib.kcache_can_reserve(self._h, rid, n_new)
+        if rc < 0:
+            raise CacheError(self._explain(rc, rid))
+        return rc == 1
+
+    def reserve(self, rid: int, n_new: int) -> None:
+        rc = self._lib.kcache_reserve(self._h, rid, n_new)
+        if rc == -1:
+            raise OutOfPages(f"request {rid}: no pages left for {n_new} more tokens "
+                             f"(free per group: {[self.free_pages(g) for g in range(self.num_groups)]})")
+        if rc != 0:
+            raise CacheError(self._explain(rc, rid))
+
+    def commit(self, rid: int, n_new: int) -> None:
+        rc = self._lib.kcache_commit(self._h, rid, n_new)
+        if rc != 0:
+            raise CacheError(self._explain(rc, rid))
+
+    def release(self, rid: int) -> None:
+        rc = self._lib.kcache_release(self._h, rid)
+        if rc != 0:
+            raise CacheError(self._explain(rc, rid))
+
+    def length(self, rid: int) -> int:
+        n = self._lib.kcache_length(self._h, rid)
+        if n < 0:
+            raise CacheError(self._explain(n, rid))
+        return n
+
+    def slot(self, rid: int) -> int:
+        s = self._lib.kcache_slot(self._h, rid)
+        if s < 0:
+            raise CacheError(self._explain(s, rid))
+        return s
+
+    def is_live(self, rid: int) -> bool:
+        return self._lib.kcache_slot(self._h, rid) >= 0
+
+    def num_blocks(self, rid: int, group: int) -> int:
+        return self._lib.kcache_num_blocks(self._h, rid, group)
+
+    def block_table_into(self, rid: int, group: int, row: np.ndarray) -> int:
+        """Fill ``row`` (int32, contiguous) with the request's pages, -1 beyond them."""
+        return self._lib.kcache_block_table(self._h, rid, group, row.ctypes.data, row.shape[0])
+
+    def block_table(self, rid: int, group: int) -> List[int]:
+        n = self.num_blocks(rid, group)
+        row = np.empty(max(n, 1), dtype=np.int32)
+        self.block_table_into(rid, group, row)
+        return row[:n].tolist()
+
+    def free_pages(self, group: int) -> int:
+        return self._lib.kcache_free_pages(self._h, group)
+
+    def num_pages(self, group: int) -> int:
+        return self._lib.kcache_num_pages(self._h, group)
+
+    def live_requests(self) -> int:
+        return self._lib.kcache_live_requests(self._h)
+
+    def free_slots(self) -> int:
+        return self._lib.kcache_free_slots(self._h)
+
+    def pages_handed_out(self) -> int:
+        return self._lib.kcache_pages_handed_out(self._h)
+
+    def check(self) -> None:
+        rc = self._lib.kcache_check(self._h)
+        if rc != 0:
+            what = {-10: "page id out of range", -11: "page both free and owned", -12: "page free twice",
+                    -13: "page held but not marked", -14: "page held twice", -15: "page lost",
+                    -16: "slot free twice", -17: "slot held twice", -18: "slot lost"}.get(rc, str(rc))
+            raise CacheError(f"cache manager invariant broken: {what}")
+
+    @staticmethod
+    def _explain(rc: int, rid: int) -> str:
+        return {-3: f"request {rid} is not live", -4: f"request {rid} would exceed the longest request the "
+                "block table holds", -5: f"request {rid}: commit beyond what was reserved",
+                -6: "no such cache group"}.get(rc, f"cache manager error {rc} for request {rid}")
+
+
+class CacheManager(PageTable):
+    """Bookkeeping plus the device memory of every cache layer.
+
+    ``specs[i]`` is what cache layer i keeps (a `PagedKVSpec`, a `FixedStateSpec` or None).
+    ``num_pages`` pages go to every group."""
+
+    def __init__(self, specs: Sequence[CacheSpec], dtype: torch.dtype, device, page_size: int,
+                 num_pages: int, max_requests: int, max_model_len: int):
+        windows: List[int] = []
+        members: List[List[int]] = []
+        self.layer_group: List[int] = []
+        for i, sp in enumerate(specs):
+            if isinstance(sp, PagedKVSpec):
+                if sp.window not in windows:
+                    windows.append(sp.window)
+                    members.append([])
+                g = windows.index(sp.window)
+                members[g].append(i)
+                self.layer_group.append(g)
+            else:
+                self.layer_group.append(-1)
+        max_blocks = (max_model_len + page_size - 1) // page_size
+        super().__init__(windows, [num_pages] * len(windows), page_size, max_requests, max_blocks)
+        self.groups = [GroupInfo(w, num_pages, tuple(m)) for w, m in zip(windows, members)]
+        self.specs = list(specs)
+        self.dtype, self.device = dtype, torch.device(device)
+        self.k: List[Optional[torch.Tensor]] = []
+        self.v: List[Optional[torch.Tensor]] = []
+        self.state: List[Optional[torch.Tensor]] = []
+        for sp in specs:
+            if isinstance(sp, PagedKVSpec):
+                shape = (num_pages, sp.kv_heads, page_size, sp.head_dim)
+                self.k.append(torch.zeros(shape, dtype=dtype, device=device))
+                self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+                self.state.append(None)
+            elif isinstance(sp, FixedStateSpec):
+                self.k.append(None)
+                self.v.append(None)
+                self.state.append(torch.zeros((max_requests,) + tuple(sp.shape), dtype=sp.dtype, device=device))
+            else:
+                self.k.append(None)
+                self.v.append(None)
+                self.state.append(None)
+
+    def admit(self, rid: int) -> int:
+        slot = super().admit(rid)
+        for st in self.state:                 # a new request starts from zero state
+            if st is not None:
+                st[slot].zero_()
+        return slot
+
+    def layer(self, index: int, writable: bool = True) -> LayerCache:
+        return LayerCache(index, self.layer_group[index], self.page_size, self.k[index], self.v[index],
+                          self.state[index], writable, self.specs[index])
+
+    def bytes_per_token(self) -> int:
+        n = 0
+        for sp in self.specs:
+            if isinstance(sp, PagedKVSpec):
+                n += 2 * sp.kv_heads * sp.head_dim * torch.empty((), dtype=self.dtype).element_size()
+        return n

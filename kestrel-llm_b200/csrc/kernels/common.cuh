@@ -1,0 +1,43 @@
+// Shared declarations of the sm_100a kernel library: storage types, error reporting and the
+// conventions of the exported C entry points.
+//
+// Every entry point is `extern "C"`, takes raw device pointers, sizes and a CUDA stream,
+// launches on that stream without synchronising, and returns 0 or a negative code; the
+// message of the last failure on the calling thread is read with kestrel_last_error().
+// Storage type codes: 0 = float32, 1 = bfloat16.  Sums, norms, softmax, rotation angles and
+// the residual stream are float32 whatever the storage type.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define KESTREL_API extern "C" __attribute__((visibility("default")))
+
+enum { KESTREL_F32 = 0, KESTREL_BF16 = 1 };
+
+int kestrel_fail(int code, const char *fmt, ...);
+int kestrel_check_launch(const char *what);
+
+#define KESTREL_REQUIRE(cond, ...)                       \
+    do {                                                 \
+        if (!(cond)) return kestrel_fail(-2, __VA_ARGS__); \
+    } while (0)
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}

@@ -1,0 +1,305 @@
+// Row-wise kernels of the decoder: embedding gather, residual-add + RMSNorm, gated
+// activation, and the step between the QKV projection and attention (bias, per-head RMSNorm,
+// rotary position encoding, write of K and V into cache pages).
+//
+// A projection's output reaches these kernels as `S` float32 partial results of shape
+// [S, T, N] (split-K slices of a matrix product; S = 1 for an unsplit product).  The consumer
+// sums the slices in ascending s, so the result does not depend on scheduling, and the sum
+// never makes a round trip through memory.  Formulas follow the reference's float32 path:
+// RMSNorm st.c:8811-8827, per-head norm st.c:9541-9561, rotation st.c:8950-8991, SiLU
+// st.c:3605-3607 (st.c = src/model/vllm_safetensors.c).
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------
+// embedding: out[t, :] = table[ids[t], :] widened to float32 (st.c:16392-16393)
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T *__restrict__ table, const int *__restrict__ ids,
+                             float *__restrict__ out, int d) {
+    int t = blockIdx.x;
+    const T *row = table + (size_t)ids[t] * d;
+    float *o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32<T>(row[i]);
+}
+
+KESTREL_API int kestrel_embed(const void *table, int dtype, const int *ids, float *out, int T,
+                              int d, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && d > 0, "embed: bad sizes T=%d d=%d", T, d);
+    if (dtype == KESTREL_F32)
+        embed_kernel<float><<<T, 256, 0, stream>>>((const float *)table, ids, out, d);
+    else if (dtype == KESTREL_BF16)
+        embed_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16 *)table, ids, out, d);
+    else
+        return kestrel_fail(-2, "embed: unknown dtype %d", dtype);
+    return kestrel_check_launch("embed");
+}
+
+// ------------------------------------------------------------------------------------------
+// residual add + RMSNorm
+//   src row t = rows ? rows[r] : r
+//   x = residual[t] + (sum_s partial[s, t] + bias)      (partial may be null: x = residual[t])
+//   if write_back: residual[t] = x
+//   out[r] = (x * rsqrt(mean(x^2) + eps)) * w
+// One block of 256 threads per row; the sum of squares is reduced in a fixed tree, so a
+// row's result does not depend on what else is in the batch.
+// ------------------------------------------------------------------------------------------
+#define NORM_THREADS 256
+
+template <typename TOut>
+__global__ void add_rmsnorm_kernel(float *__restrict__ residual, const float *__restrict__ partial,
+                                   int S, size_t slice_stride, const float *__restrict__ bias,
+                                   const int *__restrict__ rows, const float *__restrict__ w,
+                                   float eps, TOut *__restrict__ out, int d, int write_back) {
+    extern __shared__ float xs[];
+    __shared__ float red[NORM_THREADS / 32];
+    int r = blockIdx.x;
+    int t = rows ? rows[r] : r;
+    float *res = residual + (size_t)t * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += NORM_THREADS) {
+        float x = res[i];
+        if (partial) {
+            float delta = 0.f;
+            for (int s = 0; s < S; ++s) delta += partial[(size_t)s * slice_stride + (size_t)t * d + i];
+            if (bias) delta += bias[i];
+            x += delta;
+            if (write_back) res[i] = x;
+        }
+        xs[i] = x;
+        ss += x * x;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_THREADS / 32; ++k) tot += red[k];
+    float rinv = 1.0f / sqrtf(tot / (float)d + eps);
+    TOut *o = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += NORM_THREADS) o[i] = from_f32<TOut>((xs[i] * rinv) * w[i]);
+}
+
+KESTREL_API int kestrel_add_rmsnorm(float *residual, const float *partial, int S,
+                                    long long slice_stride, const float *bias, const int *rows,
+                                    const float *w, float eps, void *out, int out_dtype, int R,
+                                    int d, int write_back, cudaStream_t stream) {
+    if (R == 0) return 0;
+    KESTREL_REQUIRE(R > 0 && d > 0, "add_rmsnorm: bad sizes R=%d d=%d", R, d);
+    KESTREL_REQUIRE(!(rows && write_back), "add_rmsnorm: write_back with gathered rows");
+    size_t smem = (size_t)d * sizeof(float);
+    KESTREL_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: width %d exceeds the 51200 the kernel holds in shared memory", d);
+    if (out_dtype == KESTREL_F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<float><<<R, NORM_THREADS, smem, stream>>>(
+            residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, (float *)out, d, write_back);
+    } else if (out_dtype == KESTREL_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<__nv_bfloat16><<<R, NORM_THREADS, smem, stream>>>(
+            residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, (__nv_bfloat16 *)out, d, write_back);
+    } else {
+        return kestrel_fail(-2, "add_rmsnorm: unknown dtype %d", out_dtype);
+    }
+    return kestrel_check_launch("add_rmsnorm");
+}
+
+// ------------------------------------------------------------------------------------------
+// gated activation: out[t, i] = silu(g) * u,  g = sum_s P[s, t, i],  u = sum_s P[s, t, ff + i]
+// ------------------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void swiglu_kernel(const float *__restrict__ partial, int S, size_t slice_stride,
+                              TOut *__restrict__ out, int T, int ff) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)T * ff) return;
+    int t = (int)(idx / ff), i = (int)(idx % ff);
+    const float *row = partial + (size_t)t * 2 * ff;
+    float g = 0.f, u = 0.f;
+    for (int s = 0; s < S; ++s) {
+        g += row[(size_t)s * slice_stride + i];
+        u += row[(size_t)s * slice_stride + ff + i];
+    }
+    float a = g / (1.0f + expf(-g));
+    out[idx] = from_f32<TOut>(a * u);
+}
+
+KESTREL_API int kestrel_swiglu(const float *partial, int S, long long slice_stride, void *out,
+                               int out_dtype, int T, int ff, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && ff > 0, "swiglu: bad sizes T=%d ff=%d", T, ff);
+    size_t n = (size_t)T * ff;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_dtype == KESTREL_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>(partial, S, (size_t)slice_stride, (float *)out, T, ff);
+    else if (out_dtype == KESTREL_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(partial, S, (size_t)slice_stride, (__nv_bfloat16 *)out, T, ff);
+    else
+        return kestrel_fail(-2, "swiglu: unknown dtype %d", out_dtype);
+    return kestrel_check_launch("swiglu");
+}
+
+// ------------------------------------------------------------------------------------------
+// between the QKV projection and attention
+//   input  : partial [S, T, nq*hd + 2*nkv*hd] float32 (q heads, then k heads, then v heads),
+//            optional bias of the same width
+//   q head : + bias, per-head RMSNorm (if q_norm_w), rotation, -> q_out [T, nq*hd]
+//   k head : + bias, per-head RMSNorm (if k_norm_w), rotation, -> K page slot of the token
+//   v head : + bias                                           -> V page slot of the token
+// Rotation pairs dimension j with j + rot/2 inside the first `rot` dimensions of a head
+// (rot = head size for Qwen3); angle = (float)pos * inv_freq[j], cosf/sinf in float32.
+// The page of a token is block_table[seq, pos / page_size]; cache planes are laid out
+// [page][kv_head][slot][hd].  One warp per (token, head).
+// ------------------------------------------------------------------------------------------
+#define PREP_MAX_PER_LANE 8   // head size up to 512
+
+template <typename T>
+__global__ void attn_prepare_kernel(const float *__restrict__ partial, int S, size_t slice_stride,
+                                    const float *__restrict__ bias, const float *__restrict__ q_norm_w,
+                                    const float *__restrict__ k_norm_w, float norm_eps,
+                                    const float *__restrict__ inv_freq, int rot,
+                                    const int *__restrict__ positions, const int *__restrict__ seq_of_token,
+                                    const int *__restrict__ block_table, int table_stride, int page_size,
+                                    T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out,
+                                    int Tn, int nq, int nkv, int hd, int write_kv) {
+    int warp = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    int lane = threadIdx.x & 31;
+    int heads = nq + 2 * nkv;
+    if (warp >= Tn * heads) return;
+    int t = warp / heads, h = warp % heads;
+    bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    if (!is_q && !write_kv) return;
+    int width = heads * hd;
+    const float *row = partial + (size_t)t * width + (size_t)h * hd;
+    const float *b = bias ? bias + (size_t)h * hd : nullptr;
+
+    float x[PREP_MAX_PER_LANE];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
+        int i = lane + 32 * c;
+        float v = 0.f;
+        if (i < hd) {
+            for (int s = 0; s < S; ++s) v += row[(size_t)s * slice_stride + i];
+            if (b) v += b[i];
+        }
+        x[c] = v;
+        ss += v * v;
+    }
+    const float *nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    if (nw) {
+        ss = warp_sum(ss);
+        float rinv = 1.0f / sqrtf(ss / (float)hd + norm_eps);
+#pragma unroll
+        for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
+            int i = lane + 32 * c;
+            if (i < hd) x[c] = (x[c] * rinv) * nw[i];
+        }
+    }
+    int pos = positions[t];
+    if ((is_q || is_k) && rot > 0) {
+        // The partner of element i lives in another lane/register; exchange through shared
+        // memory is avoided by recomputing: each lane fetches its partner with a shuffle
+        // when half is a multiple of 32, else through a per-warp shared row.
+        __shared__ float stage[4][PREP_MAX_PER_LANE * 32];
+        float *st = stage[threadIdx.x >> 5];
+#pragma unroll
+        for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
+            int i = lane + 32 * c;
+            if (i < hd) st[i] = x[c];
+        }
+        __syncwarp();
+        int half = rot >> 1;
+#pragma unroll
+        for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
+            int i = lane + 32 * c;
+            if (i < rot) {
+                int j = i < half ? i : i - half;
+                float ang = (float)pos * inv_freq[j];
+                float cs = cosf(ang), sn = sinf(ang);
+                float lo = st[j], hi = st[j + half];
+                x[c] = i < half ? lo * cs - hi * sn : hi * cs + lo * sn;
+            }
+        }
+    }
+    if (is_q) {
+        T *o = q_out + (size_t)t * nq * hd + (size_t)h * hd;
+#pragma unroll
+        for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
+            int i = lane + 32 * c;
+            if (i < hd) o[i] = from_f32<T>(x[c]);
+        }
+    } else {
+        int kvh = is_k ? h - nq : h - nq - nkv;
+        int seq = seq_of_token[t];
+        int page = block_table[(size_t)seq * table_stride + pos / page_size];
+        int slot = pos % page_size;
+        T *plane = is_k ? k_cache : v_cache;
+        T *o = plane + (((size_t)page * nkv + kvh) * page_size + slot) * hd;
+#pragma unroll
+        for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
+            int i = lane + 32 * c;
+            if (i < hd) o[i] = from_f32<T>(x[c]);
+        }
+    }
+}
+
+KESTREL_API int kestrel_attn_prepare(const float *partial, int S, long long slice_stride,
+                                     const float *bias, const float *q_norm_w, const float *k_norm_w,
+                                     float norm_eps, const float *inv_freq, int rot,
+                                     const int *positions, const int *seq_of_token,
+                                     const int *block_table, int table_stride, int page_size,
+                                     void *k_cache, void *v_cache, void *q_out, int dtype, int T,
+                                     int nq, int nkv, int hd, int write_kv, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0, "attn_prepare: bad sizes");
+    KESTREL_REQUIRE(hd <= 32 * PREP_MAX_PER_LANE, "attn_prepare: head size %d exceeds %d", hd, 32 * PREP_MAX_PER_LANE);
+    KESTREL_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "attn_prepare: rotary size %d does not fit head size %d", rot, hd);
+    KESTREL_REQUIRE(page_size > 0, "attn_prepare: page size %d", page_size);
+    long long warps = (long long)T * (nq + 2 * nkv);
+    unsigned blocks = (unsigned)((warps + 3) / 4);
+    if (dtype == KESTREL_F32)
+        attn_prepare_kernel<float><<<blocks, 128, 0, stream>>>(
+            partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, positions,
+            seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache,
+            (float *)q_out, T, nq, nkv, hd, write_kv);
+    else if (dtype == KESTREL_BF16)
+        attn_prepare_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(
+            partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, positions,
+            seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)k_cache,
+            (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, T, nq, nkv, hd, write_kv);
+    else
+        return kestrel_fail(-2, "attn_prepare: unknown dtype %d", dtype);
+    return kestrel_check_launch("attn_prepare");
+}
+
+// ------------------------------------------------------------------------------------------
+// sum of partial slices (+ bias) into a tensor of the storage type; for consumers that have
+// no fused form of their own
+// ------------------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void reduce_partials_kernel(const float *__restrict__ partial, int S, size_t slice_stride,
+                                       const float *__restrict__ bias, TOut *__restrict__ out,
+                                       size_t n, int width) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    float v = 0.f;
+    for (int s = 0; s < S; ++s) v += partial[(size_t)s * slice_stride + idx];
+    if (bias) v += bias[idx % width];
+    out[idx] = from_f32<TOut>(v);
+}
+
+KESTREL_API int kestrel_reduce_partials(const float *partial, int S, long long slice_stride,
+                                        const float *bias, void *out, int out_dtype, int T, int width,
+                                        cudaStream_t stream) {
+    if (T == 0) return 0;
+    size_t n = (size_t)T * width;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_dtype == KESTREL_F32)
+        reduce_partials_kernel<float><<<blocks, 256, 0, stream>>>(partial, S, (size_t)slice_stride, bias, (float *)out, n, width);
+    else if (out_dtype == KESTREL_BF16)
+        reduce_partials_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(partial, S, (size_t)slice_stride, bias, (__nv_bfloat16 *)out, n, width);
+    else
+        return kestrel_fail(-2, "reduce_partials: unknown dtype %d", out_dtype);
+    return kestrel_check_launch("reduce_partials");
+}

@@ -1,0 +1,300 @@
+"""Python face of the sm_100a kernel library: one function per exported entry point.
+
+Tensors are torch CUDA tensors used as typed device memory; every function checks dtypes,
+shapes and contiguity, then launches on torch's current stream.  There is no CPU fallback and
+no other implementation behind these names: if the library cannot be built or loaded, the
+first call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library, built on first use."""
+    global _lib
+    if _lib is None:
+        path = _build.build_cuda()
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load {path}: {e}") from None
+        lib.kestrel_last_error.restype = ctypes.c_char_p
+        _declare(lib)
+        _lib = lib
+    return _lib
+
+
+def library_path() -> str:
+    library()
+    return _build.build_cuda(verbose=False)
+
+
+_vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+def _declare(lib) -> None:
+    sig = {
+        "kestrel_device_arch": [],
+        "kestrel_embed": [_vp, _i, _vp, _vp, _i, _i, _vp],
+        "kestrel_add_rmsnorm": [_vp, _vp, _i, _ll, _vp, _vp, _vp, _f, _vp, _i, _i, _i, _i, _vp],
+        "kestrel_swiglu": [_vp, _i, _ll, _vp, _i, _i, _i, _vp],
+        "kestrel_attn_prepare": [_vp, _i, _ll, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _vp, _i, _i,
+                                 _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+        "kestrel_reduce_partials": [_vp, _i, _ll, _vp, _vp, _i, _i, _i, _vp],
+        "kestrel_gemm_plain": [_vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
+        "kestrel_attention_plain": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _i,
+                                    _f, _vp],
+        "kestrel_argmax": [_vp, _ll, _i, _i, _vp, _vp],
+        "kestrel_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    }
+    for name, args in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = _i
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise KernelError(library().kestrel_last_error().decode("utf-8", "replace"))
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name}: tensor is on {t.device}; the kernels run on a CUDA device only")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name}: expected {dims} dimensions, got shape {tuple(t.shape)}")
+
+
+def _code(t: torch.Tensor, name: str) -> int:
+    if t.dtype not in _DT:
+        raise KernelError(f"{name}: dtype {t.dtype} is neither float32 nor bfloat16")
+    return _DT[t.dtype]
+
+
+def device_arch() -> int:
+    return library().kestrel_device_arch()
+
+
+class Partials:
+    """A projection's output before its consumer: ``data`` float32 [S, T, N] whose slices sum to
+    the result, plus an optional float32 bias [N] still to be added."""
+
+    __slots__ = ("data", "bias")
+
+    def __init__(self, data: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        if data.dim() == 2:
+            data = data.unsqueeze(0)
+        _need(data, "partials", torch.float32, 3)
+        self.data = data
+        self.bias = bias
+
+    @property
+    def slices(self) -> int:
+        return self.data.shape[0]
+
+    @property
+    def tokens(self) -> int:
+        return self.data.shape[1]
+
+    @property
+    def width(self) -> int:
+        return self.data.shape[2]
+
+    @property
+    def slice_stride(self) -> int:
+        return self.data.stride(0)
+
+    def reduce(self, dtype: torch.dtype) -> torch.Tensor:
+        """The summed result [T, N] in ``dtype``, for consumers without a fused form."""
+        out = torch.empty((self.tokens, self.width), dtype=dtype, device=self.data.device)
+        _check(library().kestrel_reduce_partials(self.data.data_ptr(), self.slices, self.slice_stride,
+                                                 _p(self.bias), out.data_ptr(), _code(out, "reduce"),
+                                                 self.tokens, self.width, _stream()))
+        return out
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] widened to float32."""
+    _need(table, "embed.table", dims=2)
+    _need(ids, "embed.ids", torch.int32, 1)
+    _need(out, "embed.out", torch.float32, 2)
+    T, d = out.shape
+    if ids.shape[0] != T or table.shape[1] != d:
+        raise KernelError(f"embed: ids {tuple(ids.shape)}, table {tuple(table.shape)}, out {tuple(out.shape)}")
+    _check(library().kestrel_embed(table.data_ptr(), _code(table, "embed.table"), ids.data_ptr(),
+                                   out.data_ptr(), T, d, _stream()))
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[Partials], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
+    """x = residual[t] + delta[t]; residual[t] = x if write_back; out[r] = rmsnorm(x) * weight,
+    where t = rows[r] if rows is given, else r."""
+    _need(residual, "add_rmsnorm.residual", torch.float32, 2)
+    _need(weight, "add_rmsnorm.weight", torch.float32, 1)
+    _need(out, "add_rmsnorm.out", dims=2)
+    T, d = residual.shape
+    R = out.shape[0]
+    if weight.shape[0] != d or out.shape[1] != d:
+        raise KernelError("add_rmsnorm: widths differ")
+    if rows is not None:
+        _need(rows, "add_rmsnorm.rows", torch.int32, 1)
+        if rows.shape[0] != R:
+            raise KernelError("add_rmsnorm: rows and out differ in length")
+        write_back = False
+    elif R != T:
+        raise KernelError("add_rmsnorm: out and residual differ in rows")
+    if delta is not None and (delta.tokens != T or delta.width != d):
+        raise KernelError(f"add_rmsnorm: delta [{delta.tokens},{delta.width}] against residual [{T},{d}]")
+    _check(library().kestrel_add_rmsnorm(
+        residual.data_ptr(), _p(delta.data) if delta else None, delta.slices if delta else 0,
+        delta.slice_stride if delta else 0, _p(delta.bias) if delta else None, _p(rows),
+        weight.data_ptr(), float(eps), out.data_ptr(), _code(out, "add_rmsnorm.out"), R, d,
+        1 if (write_back and delta is not None) else 0, _stream()))
+
+
+def swiglu(gate_up: Partials, out: torch.Tensor) -> None:
+    """out[t, i] = silu(g[t, i]) * u[t, i] with g, u the two halves of gate_up's width."""
+    _need(out, "swiglu.out", dims=2)
+    T, ff = out.shape
+    if gate_up.tokens != T or gate_up.width != 2 * ff or gate_up.bias is not None:
+        raise KernelError("swiglu: shapes differ, or a bias is pending")
+    _check(library().kestrel_swiglu(gate_up.data.data_ptr(), gate_up.slices, gate_up.slice_stride,
+                                    out.data_ptr(), _code(out, "swiglu.out"), T, ff, _stream()))
+
+
+def attn_prepare(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor],
+                 norm_eps: float, inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                 positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                 page_size: int, k_cache: torch.Tensor, v_cache: torch.Tensor, q_out: torch.Tensor,
+                 nq: int, nkv: int, hd: int, write_kv: bool = True) -> None:
+    """Bias, per-head RMSNorm, rotation; q to q_out, K and V into their cache pages."""
+    _need(q_out, "attn_prepare.q_out", dims=2)
+    _need(positions, "attn_prepare.positions", torch.int32, 1)
+    _need(seq_of_token, "attn_prepare.seq_of_token", torch.int32, 1)
+    _need(block_table, "attn_prepare.block_table", torch.int32, 2)
+    _need(k_cache, "attn_prepare.k_cache", q_out.dtype)
+    _need(v_cache, "attn_prepare.v_cache", q_out.dtype)
+    T = q_out.shape[0]
+    if qkv.tokens != T or qkv.width != (nq + 2 * nkv) * hd or q_out.shape[1] != nq * hd:
+        raise KernelError("attn_prepare: shapes differ")
+    if rotary_dim and inv_freq is None:
+        raise KernelError("attn_prepare: rotation asked for without frequencies")
+    _check(library().kestrel_attn_prepare(
+        qkv.data.data_ptr(), qkv.slices, qkv.slice_stride, _p(qkv.bias), _p(q_norm_w), _p(k_norm_w),
+        float(norm_eps), _p(inv_freq), int(rotary_dim), positions.data_ptr(), seq_of_token.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), int(page_size), k_cache.data_ptr(),
+        v_cache.data_ptr(), q_out.data_ptr(), _code(q_out, "attn_prepare.q_out"), T, nq, nkv, hd,
+        1 if write_kv else 0, _stream()))
+
+
+def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, n] = sum_k x[t, k] w[n, k] on the CUDA cores, float32 accumulation in ascending k."""
+    _need(x, "gemm.x", dims=2)
+    _need(w, "gemm.w", x.dtype, 2)
+    _need(out, "gemm.out", torch.float32, 2)
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (T, N):
+        raise KernelError(f"gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check(library().kestrel_gemm_plain(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(x, "gemm.x"),
+                                        T, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()))
+
+
+def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                    page_size: int, out: torch.Tensor, nq: int, nkv: int, hd: int, window: int,
+                    scale: float) -> None:
+    _need(q, "attention.q", dims=2)
+    _need(out, "attention.out", q.dtype, 2)
+    _need(k_cache, "attention.k_cache", q.dtype)
+    _need(v_cache, "attention.v_cache", q.dtype)
+    _need(block_table, "attention.block_table", torch.int32, 2)
+    T = q.shape[0]
+    if q.shape[1] != nq * hd or out.shape != q.shape:
+        raise KernelError("attention: shapes differ")
+    _check(library().kestrel_attention_plain(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
+        seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size),
+        out.data_ptr(), _code(q, "attention.q"), T, nq, nkv, hd, int(window), float(scale), _stream()))
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the first maximum of logits[r]."""
+    _need(logits, "argmax.logits", torch.float32, 2)
+    _need(out, "argmax.out", torch.int32, 1)
+    R, V = logits.shape
+    _check(library().kestrel_argmax(logits.data_ptr(), logits.stride(0), R, V, out.data_ptr(), _stream()))
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
+    """One token per row; per-row options; rows with temperature <= 0 take the first maximum."""
+    _need(logits, "sample.logits", torch.float32, 2)
+    R, V = logits.shape
+    for t, name, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
+                        (top_p, "top_p", torch.float32), (min_p, "min_p", torch.float32),
+                        (uniform, "uniform", torch.float32), (out, "out", torch.int32)):
+        _need(t, f"sample.{name}", dt, 1)
+        if t.shape[0] != R:
+            raise KernelError(f"sample.{name}: {t.shape[0]} entries for {R} rows")
+    _check(library().kestrel_sample(logits.data_ptr(), logits.stride(0), R, V, temperature.data_ptr(),
+                                    top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(),
+                                    uniform.data_ptr(), out.data_ptr(), _stream()))
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x w^T as float32 slices [S, T, N] (S = 1 unless a split-K kernel ran).
+
+    float32 operands always take the CUDA-core product; bfloat16 operands take the tcgen05
+    product when its tiling rules hold (see `gemm_tc_supported`) and the CUDA-core one
+    otherwise."""
+    T, N = x.shape[0], w.shape[0]
+    if out is None:
+        out = torch.empty((1, T, N), dtype=torch.float32, device=x.device)
+    elif out.dim() == 2:
+        out = out.unsqueeze(0)
+    gemm_plain(x, w, out[0])
+    return out
+
+
+def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) in x's dtype, Wg and Wu being the two halves of w_gate_up's rows."""
+    out = torch.empty((x.shape[0], ff), dtype=x.dtype, device=x.device)
+    swiglu(Partials(linear(x, w_gate_up)), out)
+    return out
+
+
+def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch, block_table: torch.Tensor,
+              page_size: int, out: torch.Tensor, nq: int, nkv: int, hd: int, window: int, scale: float) -> None:
+    """Causal attention of this step's queries over their requests' cache pages.  ``batch``
+    gives positions, seq_of_token and the per-request lengths."""
+    attention_plain(q, k_cache, v_cache, batch.positions, batch.seq_of_token, block_table, page_size,
+                    out, nq, nkv, hd, window, scale)

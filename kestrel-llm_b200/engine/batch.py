@@ -1,0 +1,105 @@
+"""The description of one step's tokens, on the host and on the device.
+
+A step runs a flat list of T tokens from ``nseq`` requests: prompt portions (several tokens of
+one request, in order) beside single decoded tokens.  Everything a kernel needs to place a
+token - its id, its position in its request, which request, that request's pages - is packed
+into one int32 buffer on the host and copied to the device in one transfer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class Entry:
+    """Tokens [start, start + len(tokens)) of request ``rid``; ``want`` lists the offsets among
+    these tokens whose logits are asked for."""
+    rid: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepBatch:
+    def __init__(self, entries: Sequence[Entry], cache, device, table_width: Optional[int] = None):
+        """``cache`` is the `CacheManager`; pages for every entry must be reserved already."""
+        nseq = len(entries)
+        counts = [len(e.tokens) for e in entries]
+        T = int(sum(counts))
+        self.num_tokens, self.num_seqs = T, nseq
+        self.entries = list(entries)
+        starts = [cache.length(e.rid) for e in entries]
+        self.starts = starts
+        self.kv_lens_host = [s + c for s, c in zip(starts, counts)]
+        rows: List[int] = []
+        off = 0
+        for e, c in zip(entries, counts):
+            for w in e.want:
+                if not 0 <= w < c:
+                    raise ValueError(f"request {e.rid}: wanted place {w} outside its {c} tokens of this step")
+                rows.append(off + w)
+            off += c
+        R = len(rows)
+        self.num_logit_rows = R
+        n_groups = cache.num_groups
+        if table_width is None:
+            need = 1
+            for g in range(n_groups):
+                for e in entries:
+                    need = max(need, cache.num_blocks(e.rid, g))
+            table_width = (need + 7) // 8 * 8
+        self.table_width = table_width
+        # layout of the packed buffer
+        o_tok, o_pos, o_seq = 0, T, 2 * T
+        o_cu = 3 * T
+        o_kv = o_cu + nseq + 1
+        o_slot = o_kv + nseq
+        o_rows = o_slot + nseq
+        o_tab = o_rows + R
+        total = o_tab + n_groups * nseq * table_width
+        host = np.empty(max(total, 1), dtype=np.int32)
+        cu = 0
+        for i, (e, c, s) in enumerate(zip(entries, counts, starts)):
+            host[o_tok + cu:o_tok + cu + c] = np.asarray(e.tokens, dtype=np.int64)
+            host[o_pos + cu:o_pos + cu + c] = np.arange(s, s + c, dtype=np.int32)
+            host[o_seq + cu:o_seq + cu + c] = i
+            host[o_cu + i] = cu
+            host[o_kv + i] = s + c
+            host[o_slot + i] = cache.slot(e.rid)
+            cu += c
+        host[o_cu + nseq] = cu
+        host[o_rows:o_rows + R] = rows
+        for g in range(n_groups):
+            for i, e in enumerate(entries):
+                b = o_tab + (g * nseq + i) * table_width
+                cache.block_table_into(e.rid, g, host[b:b + table_width])
+        self.host = host
+        pinned = torch.from_numpy(host)
+        if torch.device(device).type == "cuda":
+            pinned = pinned.pin_memory()
+        dev = pinned.to(device, non_blocking=True)
+        self._pinned = pinned            # keep alive until the copy has run
+        self.device_buffer = dev
+        self.token_ids = dev[o_tok:o_tok + T]
+        self.positions = dev[o_pos:o_pos + T]
+        self.seq_of_token = dev[o_seq:o_seq + T]
+        self.cu_seqlens = dev[o_cu:o_cu + nseq + 1]
+        self.kv_lens = dev[o_kv:o_kv + nseq]
+        self.slots = dev[o_slot:o_slot + nseq]
+        self.logit_rows = dev[o_rows:o_rows + R]
+        self._tables = [dev[o_tab + g * nseq * table_width: o_tab + (g + 1) * nseq * table_width]
+                        .view(nseq, table_width) for g in range(n_groups)]
+        self.counts = counts
+        self.max_count = max(counts) if counts else 0
+        self.max_kv_len = max(self.kv_lens_host) if counts else 0
+        self.bytes_h2d = int(host.nbytes)
+
+    def block_table(self, group: int) -> torch.Tensor:
+        return self._tables[group]
+
+    @property
+    def is_decode_only(self) -> bool:
+        return self.max_count == 1

@@ -1,0 +1,95 @@
+"""The engine: a model, its cache, and ONE step function.
+
+``step(entries)`` takes a batch of (request, its next tokens) - portions of prompts beside
+single decoded tokens, cut anywhere - reserves pages, runs exactly these tokens through the
+model from the cache that earlier steps left, commits the cache, and returns the float32
+logits at the wanted places.  The reference has three separate forward entry points
+(src/model/vllm_safetensors.c:16356 single token, :17926 one request's prompt, :17041 one
+token of each of n requests) and never mixes them; this one function covers all three and
+their mixtures.  Generation (`LLM`), trace replay (`bin/trace_run`) and the benchmark all
+call it.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages
+from ..config.engine_options import EngineOptions
+from ..csrc import ops
+from .batch import Entry, StepBatch
+
+
+class Engine:
+    def __init__(self, model, options: EngineOptions):
+        self.model = model
+        self.options = options
+        dev = model.device
+        if dev.type != "cuda":
+            raise RuntimeError(f"the engine runs on a CUDA device, not on '{dev}': there is no CPU path")
+        arch = ops.device_arch()
+        if arch < 100:
+            raise RuntimeError(f"this engine is written for sm_100a (B200); the device reports sm_{arch}")
+        cfg = model.config
+        self.max_model_len = options.max_model_len or cfg.max_position_embeddings
+        page = options.page_size
+        if options.num_pages:
+            num_pages = options.num_pages
+        else:
+            max_tokens = options.max_tokens or options.batch_max * self.max_model_len
+            num_pages = (max_tokens + page - 1) // page
+        self.cache = CacheManager(model.cache_specs(), model.dtype, dev, page, num_pages,
+                                  options.batch_max, self.max_model_len)
+        self.vocab_size = model.vocab_size
+        self.steps_run = 0
+
+    # ---- requests -----------------------------------------------------------------------
+    def admit(self, rid: int) -> int:
+        """Gives a new request its state slot."""
+        return self.cache.admit(rid)
+
+    def release(self, rid: int) -> None:
+        """Ends a request: its pages and its slot are given back."""
+        self.cache.release(rid)
+
+    # ---- the step -----------------------------------------------------------------------
+    def step(self, entries: Sequence[Entry], reserved: bool = False) -> Optional[torch.Tensor]:
+        """Runs one batch.  Unknown requests are admitted.  Returns float32 logits
+        [number of wanted places, vocab] on the device, in the order of entries and of each
+        entry's ``want``; None if nothing was wanted.  If pages run out, `OutOfPages` is raised
+        before anything runs; no request's length changes (pages that earlier entries of
+        the same call had reserved stay with those requests for their next step)."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return None
+        seen = set()
+        for e in entries:
+            if e.rid in seen:
+                raise ValueError(f"request {e.rid} appears twice in one step")
+            seen.add(e.rid)
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise ValueError(f"request {e.rid}: token id {t} outside the vocabulary of {self.vocab_size}")
+        admitted: List[int] = []
+        try:
+            for e in entries:
+                if not self.cache.is_live(e.rid):
+                    self.cache.admit(e.rid)
+                    admitted.append(e.rid)
+                if self.cache.length(e.rid) + len(e.tokens) > self.max_model_len:
+                    raise ValueError(f"request {e.rid} would grow beyond max_model_len {self.max_model_len}")
+            if not reserved:
+                for e in entries:
+                    self.cache.reserve(e.rid, len(e.tokens))
+        except Exception:
+            for rid in admitted:
+                self.cache.release(rid)
+            raise
+        batch = StepBatch(entries, self.cache, self.model.device)
+        logits = self.model.forward(batch, self.cache)
+        for e in entries:
+            self.cache.commit(e.rid, len(e.tokens))
+        self.steps_run += 1
+        self.last_batch = batch
+        return logits

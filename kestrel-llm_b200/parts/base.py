@@ -1,0 +1,117 @@
+"""What a layer is built from, and what each kind of part must offer.
+
+A model is a list of blocks and a list that says in which order they run.  A block arranges a
+mixer, a feed-forward and norms around the residual stream; a mixer may use a position
+encoding.  Every part takes its sizes and constants as constructor arguments, allocates its
+own weights on the device it is given, names the checkpoint tensors that fill them
+(`weight_slots`), and says what it needs from the cache (`cache_spec`).  No part knows which
+model it is in; a model is assembled layer by layer from a configuration.
+
+Activations: the residual stream is float32 [T, width].  A norm turns it into the storage
+dtype (bfloat16 or float32).  A mixer or feed-forward takes that and returns `Partials`
+(float32 slices of a projection's output, still to be summed), which the next norm adds to
+the residual stream in the same kernel that normalises it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple, Union
+
+import torch
+
+
+@dataclass
+class WeightSlot:
+    """One checkpoint tensor and the device memory it fills.
+
+    ``dest`` may be a slice of a larger fused tensor (rows of a fused QKV matrix).  ``init`` is
+    the distribution used by the random-weights mode: "linear" N(0, 0.02), "norm"
+    1 + N(0, 0.02), "bias" N(0, 0.02)."""
+    name: str
+    dest: torch.Tensor
+    init: str = "linear"
+
+
+@dataclass(frozen=True)
+class PagedKVSpec:
+    """Keys and values of every token, or of the last ``window`` tokens, in pages."""
+    kv_heads: int
+    head_dim: int
+    window: int = 0          # 0 = all keys
+
+
+@dataclass(frozen=True)
+class FixedStateSpec:
+    """A region of constant size per live request (recurrent state and the like)."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+CacheSpec = Union[PagedKVSpec, FixedStateSpec, None]
+
+
+class Part:
+    """Base of all parts: weights by checkpoint name."""
+
+    def weight_slots(self) -> List[WeightSlot]:
+        return []
+
+
+class PositionEncoding(Part):
+    """How positions enter the model.
+
+    ``rotary()`` returns (inv_freq float32 [rot/2] on the device, rot) for mixers that rotate
+    queries and keys, or None.  ``add_to_embedding(x, batch)`` lets an absolute encoding add
+    to the embedded tokens; the default does nothing."""
+
+    def rotary(self) -> Optional[Tuple[torch.Tensor, int]]:
+        return None
+
+    def add_to_embedding(self, x: torch.Tensor, batch) -> None:
+        return None
+
+
+class Norm(Part):
+    """``add_forward(residual, delta, out_dtype, rows=None)``: residual += delta (a Partials or
+    None), in place unless ``rows`` selects a subset; returns norm(residual) in out_dtype."""
+
+    def add_forward(self, residual: torch.Tensor, delta, out_dtype: torch.dtype,
+                    rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    """Mixes information between the tokens of a request (attention, recurrence ...).
+
+    ``cache_spec()`` says what it keeps per request.  ``forward(x, batch, cache)`` takes the
+    normed activations [T, width] of this step's tokens and the layer's `LayerCache`, reads and
+    updates the cache for exactly these tokens, and returns Partials [S, T, width]."""
+
+    def cache_spec(self) -> CacheSpec:
+        return None
+
+    def forward(self, x: torch.Tensor, batch, cache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """Token-wise transformation: ``forward(x, batch)`` -> Partials [S, T, width]."""
+
+    def forward(self, x: torch.Tensor, batch):
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of parts around the residual stream.
+
+    ``forward(residual, pending, batch, cache)`` -> (residual, pending): ``pending`` is a
+    Partials not yet added to the residual stream (the previous block's last output), so that
+    the add is fused into the first norm of the next block."""
+
+    mixer: Mixer
+
+    def cache_spec(self) -> CacheSpec:
+        return self.mixer.cache_spec()
+
+    def forward(self, residual: torch.Tensor, pending, batch, cache):
+        raise NotImplementedError

@@ -1,0 +1,29 @@
+"""Pre-norm residual block: x += mixer(norm1(x)); x += ffn(norm2(x))
+(reference: st.c:16412-16413 and 16622-16626 for the attention half, st.c:16704-16705 and
+16796-16797 for the feed-forward half).  The output of the feed-forward is handed on unadded,
+so that the next block's first norm (or the final norm) adds it while normalising.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .base import Block, FeedForward, Mixer, Norm, WeightSlot
+
+
+class PreNormBlock(Block):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward, dtype: torch.dtype):
+        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+        self.dtype = dtype
+
+    def weight_slots(self) -> List[WeightSlot]:
+        return (self.norm1.weight_slots() + self.mixer.weight_slots() + self.norm2.weight_slots()
+                + self.ffn.weight_slots())
+
+    def forward(self, residual: torch.Tensor, pending, batch, cache):
+        n = self.norm1.add_forward(residual, pending, self.dtype)
+        a = self.mixer.forward(n, batch, cache)
+        n = self.norm2.add_forward(residual, a, self.dtype)
+        f = self.ffn.forward(n, batch)
+        return residual, f

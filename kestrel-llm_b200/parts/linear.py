@@ -1,0 +1,28 @@
+"""A weight matrix [out, in] and the product with it, y = x W^T (st.c:8880-8892 of the
+reference: weights are used in checkpoint layout, without transposing).
+
+The kernel is chosen by dtype and size: float32 always runs the CUDA-core product with
+ascending-k FMA accumulation (the true 32-bit path); bfloat16 runs the tcgen05 tensor-core
+product when the sizes fit its tiling rules and the CUDA-core product otherwise.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..csrc import ops
+from .base import Part, WeightSlot
+
+
+class Linear(Part):
+    def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device,
+                 bias: bool = False):
+        self.in_features = in_features
+        self.out_features = out_features
+        self.weight = torch.empty((out_features, in_features), dtype=dtype, device=device)
+        self.bias = torch.empty((out_features,), dtype=torch.float32, device=device) if bias else None
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> ops.Partials:
+        """x [T, in] in the weight's dtype -> Partials [S, T, out]."""
+        return ops.Partials(ops.linear(x, self.weight, out), self.bias)

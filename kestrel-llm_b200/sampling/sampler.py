@@ -1,0 +1,61 @@
+"""Picks the next token of every request whose logits a step returned, on the device.
+
+Greedy rows take the first maximum.  Other rows are sampled by one kernel with their own
+temperature, top-k, min-p and top-p (meanings: src/core/vllm_transformer.c:357-479 of the
+reference).  The uniform number of a draw is a function of (request seed, index of the token
+being generated) only - the reference draws from the process-wide, never seeded ``rand()``
+(vllm_transformer.c:464) - so a request's output does not depend on what it was batched with
+and can be repeated.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+from .params import SamplingParams
+
+_MASK = (1 << 64) - 1
+
+
+def _mix(z: int) -> int:
+    z = (z + 0x9E3779B97F4A7C15) & _MASK
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+    return z ^ (z >> 31)
+
+
+def uniform_for(seed: int, index: int) -> float:
+    """Uniform number in (0, 1] for the ``index``-th generated token of a request with ``seed``
+    (two rounds of the splitmix64 finaliser; 24 bits, so the value is exact in float32)."""
+    z = _mix(_mix(seed & _MASK) ^ (index & _MASK))
+    return ((z >> 40) + 1) / float(1 << 24)
+
+
+class Sampler:
+    def __init__(self, device):
+        self.device = torch.device(device)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               indices: Sequence[int]) -> torch.Tensor:
+        """logits float32 [R, V]; row r belongs to a request with ``params[r]``, ``seeds[r]``,
+        generating its ``indices[r]``-th token.  Returns int32 [R] on the device."""
+        R = logits.shape[0]
+        out = torch.empty((R,), dtype=torch.int32, device=self.device)
+        if all(p.greedy for p in params):
+            ops.argmax(logits, out)
+            return out
+        host = np.empty((5, R), dtype=np.float32)
+        ks = np.empty((R,), dtype=np.int32)
+        for r, (p, s, i) in enumerate(zip(params, seeds, indices)):
+            host[0, r] = p.temperature if not p.greedy else 0.0
+            host[1, r] = p.top_p
+            host[2, r] = p.min_p
+            host[3, r] = uniform_for(s, i)
+            ks[r] = p.top_k
+        host[4] = ks.view(np.float32)
+        dev = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
+        ops.sample(logits, dev[0], dev[4].view(torch.int32), dev[1], dev[2], dev[3], out)
+        return out

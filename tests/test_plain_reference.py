@@ -1,0 +1,57 @@
+"""The plain implementation against the reference's own compiled float32 forward pass.
+
+tests/golden/reference_logits.npy was written once by tests/golden/make_reference_golden.py,
+which builds six of the reference's C files on the CPU and runs st_qwen_model_forward token by
+token on tests/golden/tiny_model.  This test needs neither the reference nor a GPU."""
+import json
+import os
+
+import numpy as np
+
+import plain_qwen3 as P
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def test_plain_matches_reference_code():
+    cfg, W = P.read_model(os.path.join(GOLD, "tiny_model"))
+    tokens = json.load(open(os.path.join(GOLD, "reference_tokens.json")))
+    ref = np.load(os.path.join(GOLD, "reference_logits.npy"))
+    mine = P.forward_logits(cfg, W, tokens)
+    assert mine.shape == ref.shape
+    assert np.abs(mine - ref).max() <= 2e-6 * max(1.0, np.abs(ref).max())
+    assert (mine.argmax(1) == ref.argmax(1)).all()
+    # the comparison can fail: a different rope base must show
+    cfg2 = dict(cfg, rope_theta=10000.0)
+    assert np.abs(P.forward_logits(cfg2, W, tokens) - ref).max() > 1e-4
+
+
+def test_plain_parts():
+    x = np.array([[3.0, 4.0]], dtype=np.float32)
+    out = P.rms_norm(x, np.ones(2, np.float32), 0.0)
+    np.testing.assert_allclose(out, x / np.sqrt(12.5), rtol=1e-6)
+    cos, sin = P.rope_angles([0, 1], 4, 10000.0)
+    assert cos.shape == (2, 2) and np.allclose(cos[0], 1) and np.allclose(sin[0], 0)
+    v = np.arange(8, dtype=np.float32).reshape(1, 2, 4)
+    r = P.rope(np.repeat(v, 2, 0), cos, sin)
+    np.testing.assert_allclose(r[0], v[0])                      # position 0 rotates nothing
+    np.testing.assert_allclose(np.linalg.norm(r[1], axis=-1), np.linalg.norm(v[0], axis=-1), rtol=1e-6)
+    assert P.greedy(np.array([1.0, 5.0, 5.0, 2.0], np.float32)) == 1
+    q = np.random.default_rng(0).normal(size=(5, 2, 4)).astype(np.float32)
+    k = np.random.default_rng(1).normal(size=(5, 1, 4)).astype(np.float32)
+    a = P.causal_attention(q, k, k)
+    np.testing.assert_allclose(a[0, 0], k[0, 0], rtol=1e-6)     # the first token sees itself only
+    w = P.causal_attention(q, k, k, window=1)
+    np.testing.assert_allclose(w[:, 0], k[:, 0], rtol=1e-6)     # window 1: every token sees itself only
+
+
+def test_plain_sampling_filters():
+    l = np.log(np.array([0.5, 0.2, 0.15, 0.1, 0.05], dtype=np.float32))
+    p = P.sample_probs(l, 1.0, top_k=3)
+    assert (p > 0).tolist() == [True, True, True, False, False]
+    p = P.sample_probs(l, 1.0, top_p=0.6)
+    assert (p > 0).tolist() == [True, True, False, False, False]
+    p = P.sample_probs(l, 1.0, min_p=0.25)
+    assert (p > 0).tolist() == [True, True, True, False, False]
+    p = P.sample_probs(l, 1.0)
+    assert P.sample_from(p, 0.49) == 0 and P.sample_from(p, 0.51) == 1 and P.sample_from(p, 1.0) == 4

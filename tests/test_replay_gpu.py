@@ -1,0 +1,108 @@
+"""The engine against the plain implementation under every way of cutting the work, in
+float32 and in bfloat16, for three tiny configurations (GPU)."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import replay_util as R
+import tiny_configs
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": (5, 11, 17, 40, 70), "B": (1, 33, 70, 129, 47, 90), "C": (3, 50, 97, 130, 64, 81)}
+DTYPES = ("float32", "bfloat16")
+
+
+def _requests(name):
+    return R.random_requests(tiny_configs.CONFIGS[name][0]["vocab_size"], LENGTHS[name], seed=1 + ord(name))
+
+
+def _run(model_dirs, name, dtype, family, record_property, **kw):
+    reqs = _requests(name)
+    steps, max_tokens = family(reqs, **kw)
+    engine = R.make_engine(model_dirs[name][dtype], dtype, max_tokens)
+    got = R.run_trace(engine, steps)
+    assert engine.cache.live_requests() == 0
+    engine.cache.check()
+    worst = R.compare_with_plain(model_dirs[name]["float32"], reqs, got, dtype, f"{name}/{dtype}/{family.__name__}")
+    record_property("worst_relative_error", worst)
+    print(f"[replay] {name} {dtype} {family.__name__}: worst {worst:.3e}")
+    return engine
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_prompts(model_dirs, name, dtype, record_property):
+    _run(model_dirs, name, dtype, R.trace_whole, record_property)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_tokens_one_by_one(model_dirs, name, dtype, record_property):
+    _run(model_dirs, name, dtype, R.trace_tail_decode, record_property)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_portions_of_changing_size(model_dirs, name, dtype, record_property):
+    _run(model_dirs, name, dtype, R.trace_portions, record_property)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_with_page_reuse(model_dirs, name, dtype, record_property):
+    engine = _run(model_dirs, name, dtype, R.trace_mixed, record_property)
+    # the pool was so small that pages were handed out more often than there are pages
+    assert engine.cache.pages_handed_out() > engine.cache.num_pages(0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cuttings_agree_with_each_other(model_dirs, dtype):
+    """Beyond the comparison with the plain implementation: the same position's logits from
+    different cuttings differ by rounding only."""
+    name = "B"
+    reqs = _requests(name)
+    results = []
+    for family in (R.trace_whole, R.trace_tail_decode, R.trace_portions, R.trace_mixed):
+        steps, max_tokens = family(reqs)
+        results.append(R.run_trace(R.make_engine(model_dirs[name][dtype], dtype, max_tokens), steps))
+    tol = {"float32": 1e-5, "bfloat16": 4e-2}[dtype]
+    for other in results[1:]:
+        for rname, toks in reqs.items():
+            scale = max(float(np.abs(results[0][rname][p]).max()) for p in range(len(toks)))
+            for p in range(len(toks)):
+                err = float(np.abs(other[rname][p] - results[0][rname][p]).max()) / scale
+                assert err <= tol, f"request {rname} position {p}: cuttings differ by {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program(model_dirs, dtype, tmp_path):
+    """bin/trace_run as a user calls it: JSON lines in, <step>.f32 files and `done` lines out."""
+    name = "A"
+    reqs = _requests(name)
+    steps, max_tokens = R.trace_mixed(reqs, seed=3)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lines = "".join(json.dumps(dict(step=i, **s)) + "\n" for i, s in enumerate(steps))
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model_dirs[name][dtype],
+                        "--dtype", dtype, "--out", str(out), "--max-tokens", str(max_tokens)],
+                       input=lines, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
+    V = tiny_configs.A["vocab_size"]
+    pos = {n: 0 for n in reqs}
+    got = {n: {} for n in reqs}
+    for i, s in enumerate(steps):
+        arr = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
+        r = 0
+        for e in s["entries"]:
+            for w in e["want"]:
+                got[e["id"]][pos[e["id"]] + w] = arr[r]
+                r += 1
+            pos[e["id"]] += len(e["tokens"])
+        assert r == arr.shape[0]
+    R.compare_with_plain(model_dirs[name]["float32"], reqs, got, dtype, f"trace_run/{dtype}")
