@@ -93,6 +93,8 @@ class StepBatch:
         self._tables = [dev[o_tab + g * nseq * table_width: o_tab + (g + 1) * nseq * table_width]
                         .view(nseq, table_width) for g in range(n_groups)]
         self.counts = counts
+        self.cu_seqlens_host = [int(x) for x in host[o_cu:o_cu + nseq + 1]]
+        self.slots_host = [int(x) for x in host[o_slot:o_slot + nseq]]
         self.max_count = max(counts) if counts else 0
         self.max_kv_len = max(self.kv_lens_host) if counts else 0
         self.bytes_h2d = int(host.nbytes)

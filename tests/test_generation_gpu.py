@@ -1,0 +1,154 @@
+"""Generation through the Python entry point, long decoding, the first tokens of a sequence,
+what happens when pages run out, and the command line (GPU)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_qwen3 as P
+import replay_util as R
+import tiny_configs
+
+pytestmark = pytest.mark.gpu
+
+
+def _check_greedy(model_dir_f32, prompt, generated, dtype):
+    cfg, W = P.read_model(model_dir_f32)
+    toks = list(prompt)
+    for got in generated:
+        logits = P.forward_logits(cfg, W, toks)[-1]
+        want = P.greedy(logits)
+        if got != want:     # only a tie within rounding may differ
+            assert float(logits[want] - logits[got]) <= R.TOL[dtype] * float(np.abs(logits).max()), \
+                f"token {got} instead of {want} after {len(toks)} tokens"
+        toks.append(got)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,lengths,n_new,chunk", [("A", (5, 11, 17), 8, 512), ("B", (1, 33, 70, 129), 16, 24)])
+def test_greedy_generation(model_dirs, name, lengths, n_new, chunk, dtype):
+    """The workloads of the two tiny baseline configurations, greedy, through LLM.generate."""
+    from kestrel_llm_b200 import LLM, SamplingParams
+    prompts = list(R.random_requests(tiny_configs.CONFIGS[name][0]["vocab_size"], lengths, seed=1 if name == "A" else 3).values())
+    page = 4 if name == "A" else 16
+    llm = LLM(model_dirs[name][dtype], dtype=dtype, page_size=page, batch_max=4, max_tokens=1024,
+              prefill_batch=chunk, max_step_tokens=64)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+    assert [len(o.token_ids) for o in outs] == [n_new] * len(prompts)
+    assert all(o.finish_reason == "length" for o in outs)
+    for p, o in zip(prompts, outs):
+        _check_greedy(model_dirs[name]["float32"], p, o.token_ids, dtype)
+    assert llm.engine.cache.live_requests() == 0
+    llm.engine.cache.check()
+    assert llm.stats.generated_tokens == n_new * len(prompts) and llm.stats.d2h_bytes == 4 * llm.stats.generated_tokens
+    # twice the same: token ids are stable from run to run
+    again = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+    assert [o.token_ids for o in again] == [o.token_ids for o in outs]
+
+
+def test_temperature_sampling_does_not_depend_on_the_batch(model_dirs):
+    """Config B's workload: temperature 0.8, seed 4, 16 tokens, portions of 24 beside decodes.
+    A request's tokens are the same alone and in company, and follow the plain sampler fed with
+    the plain logits and the same uniform numbers."""
+    from kestrel_llm_b200 import LLM, SamplingParams
+    from kestrel_llm_b200.sampling import uniform_for
+    prompts = list(R.random_requests(509, (1, 33, 70, 129), seed=3).values())
+    sp = [SamplingParams(temperature=0.8, max_tokens=16, seed=4 + i, ignore_eos=True) for i in range(4)]
+    together = LLM(model_dirs["B"]["float32"], dtype="float32", page_size=16, batch_max=4, max_tokens=1024,
+                   prefill_batch=24, max_step_tokens=48).generate(prompts, sp)
+    alone = [LLM(model_dirs["B"]["float32"], dtype="float32", page_size=16, batch_max=1, max_tokens=256)
+             .generate([p], s)[0] for p, s in zip(prompts, sp)]
+    assert [o.token_ids for o in together] == [o.token_ids for o in alone]
+    cfg, W = P.read_model(model_dirs["B"]["float32"])
+    for i in (0, 2):
+        toks = list(prompts[i])
+        for j, got in enumerate(together[i].token_ids):
+            p = P.sample_probs(P.forward_logits(cfg, W, toks)[-1], 0.8)
+            want = P.sample_from(p, uniform_for(4 + i, j))
+            if got != want:
+                c = np.cumsum(p.astype(np.float64))
+                assert abs(c[min(got, want)] - uniform_for(4 + i, j) * c[-1]) < 1e-4 * c[-1]
+            toks.append(got)
+    other = LLM(model_dirs["B"]["float32"], dtype="float32", max_tokens=256, batch_max=1).generate(
+        [prompts[1]], SamplingParams(temperature=0.8, max_tokens=16, seed=99, ignore_eos=True))[0]
+    assert other.token_ids != together[1].token_ids
+
+
+def test_stop_token_ends_a_request(model_dirs):
+    from kestrel_llm_b200 import LLM, SamplingParams
+    prompt = R.random_requests(256, (9,), seed=5)["r0"]
+    llm = LLM(model_dirs["A"]["float32"], dtype="float32", max_tokens=256, batch_max=2)
+    free = llm.generate([prompt], SamplingParams(max_tokens=8, ignore_eos=True))[0].token_ids
+    stop = free[3]
+    cut = llm.generate([prompt], SamplingParams(max_tokens=8, stop_token_ids=(stop,)))[0]
+    k = free.index(stop)
+    assert cut.finish_reason == "stop" and cut.token_ids == free[:k + 1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_dirs, dtype, record_property):
+    """Four prompt tokens, then 300 tokens one by one: every position against the plain
+    implementation, across many page edges."""
+    reqs = R.random_requests(509, (304,), seed=8)
+    steps, max_tokens = R.trace_tail_decode(reqs, tail=300)
+    assert len(steps) == 301
+    got = R.run_trace(R.make_engine(model_dirs["B"][dtype], dtype, max_tokens), steps)
+    R.compare_with_plain(model_dirs["B"]["float32"], reqs, got, dtype, "long decode")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
+    vocab = tiny_configs.CONFIGS[name][0]["vocab_size"]
+    reqs = R.random_requests(vocab, (1, 2, 3, 4), seed=6)
+    for family in (R.trace_whole, R.trace_tail_decode):
+        steps, max_tokens = family(reqs)
+        got = R.run_trace(R.make_engine(model_dirs[name][dtype], dtype, max_tokens, page_size=4), steps)
+        R.compare_with_plain(model_dirs[name]["float32"], reqs, got, dtype, f"first tokens {family.__name__}")
+
+
+@pytest.mark.parametrize("dtype", ["float32"])
+def test_when_pages_run_out_the_youngest_is_computed_again(model_dirs, dtype):
+    """A pool too small for all requests at their full length: requests are preempted and
+    recomputed, and still produce the tokens they produce undisturbed."""
+    from kestrel_llm_b200 import LLM, SamplingParams
+    prompts = list(R.random_requests(509, (30, 28, 33), seed=12).values())
+    sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    roomy = LLM(model_dirs["B"][dtype], dtype=dtype, page_size=16, batch_max=4, max_tokens=1024).generate(prompts, sp)
+    tight_llm = LLM(model_dirs["B"][dtype], dtype=dtype, page_size=16, batch_max=4, num_pages=9)   # 144 tokens
+    tight = tight_llm.generate(prompts, sp)
+    assert tight_llm.scheduler.num_preemptions > 0 and sum(o.preemptions for o in tight) > 0
+    assert [o.token_ids for o in tight] == [o.token_ids for o in roomy]
+    tight_llm.engine.cache.check()
+    assert tight_llm.engine.cache.live_requests() == 0
+
+
+def test_requests_that_cannot_run_are_refused(model_dirs):
+    from kestrel_llm_b200 import LLM, SamplingParams
+    from kestrel_llm_b200.engine import SchedulerError
+    llm = LLM(model_dirs["A"]["float32"], dtype="float32", num_pages=4, page_size=16, batch_max=2)
+    with pytest.raises(SchedulerError, match="exceed"):
+        llm.add_request(list(range(60)), SamplingParams(max_tokens=10))
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        llm.add_request([1, 2, 256])
+    from kestrel_llm_b200.engine import Entry
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        llm.engine.step([Entry(0, [999], [0])])
+    with pytest.raises(ValueError, match="outside its"):
+        llm.engine.step([Entry(0, [1, 2], [2])])
+    assert llm.engine.cache.live_requests() == 0
+
+
+def test_command_line(model_dirs):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "kestrel"), "--model", model_dirs["A"]["bfloat16"],
+                        "--stream-test", "--stream-n", "6", "--prompt-ids", "5,17,3,200", "--dtype", "float32"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    line = [l for l in p.stdout.splitlines() if l.startswith("[STREAM] TOKIDS:")]
+    assert len(line) == 1
+    ids = [int(t) for t in line[0].split(":", 1)[1].split()]
+    assert len(ids) == 6
+    _check_greedy(model_dirs["A"]["float32"], [5, 17, 3, 200], ids, "float32")

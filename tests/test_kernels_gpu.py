@@ -1,0 +1,324 @@
+"""Each kernel alone against a plain float32 (numpy/torch) statement of the same operation,
+at sizes other than the engine's tiny models: widths and vocabularies that are no power of
+two, head sizes in steps of 16, odd numbers of heads and groups (GPU)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def _ops():
+    from kestrel_llm_b200.csrc import ops
+    return ops
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    t = (torch.randn(shape, generator=g) * scale).to(dtype)
+    return t.to(DEV), t.float().numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,N,K", [(1, 509, 96), (37, 200, 96), (130, 96, 200), (65, 1000, 777), (3, 64, 1)])
+def test_gemm_plain(dtype, T, N, K):
+    ops = _ops()
+    x, xr = _rand((T, K), DT[dtype], 1)
+    w, wr = _rand((N, K), DT[dtype], 2, 0.05)
+    out = torch.full((T, N), float("nan"), device=DEV)
+    ops.gemm_plain(x, w, out)
+    ref = xr.astype(np.float64) @ wr.astype(np.float64).T
+    np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max() + 1e-7)
+
+
+def test_gemm_plain_is_the_same_for_any_batch():
+    ops = _ops()
+    x, _ = _rand((70, 333), torch.float32, 3)
+    w, _ = _rand((129, 333), torch.float32, 4)
+    full = torch.empty((70, 129), device=DEV)
+    ops.gemm_plain(x, w, full)
+    one = torch.empty((1, 129), device=DEV)
+    ops.gemm_plain(x[41:42].contiguous(), w, one)
+    assert torch.equal(one[0], full[41])            # bit-identical: the k order does not depend on T
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d", [96, 1000, 5120, 13000])
+def test_add_rmsnorm(out_dtype, d):
+    ops = _ops()
+    T, S = 7, 3
+    res, rr = _rand((T, d), torch.float32, 5)
+    part, pr = _rand((S, T, d), torch.float32, 6, 0.3)
+    bias, br = _rand((d,), torch.float32, 7, 0.1)
+    w, wr = _rand((d,), torch.float32, 8)
+    out = torch.empty((T, d), dtype=DT[out_dtype], device=DEV)
+    res_in = res.clone()
+    ops.add_rmsnorm(res, ops.Partials(part, bias), w, 1e-5, out)
+    x = rr + (pr.sum(0) + br)
+    np.testing.assert_allclose(res.cpu().numpy(), x, rtol=1e-6, atol=1e-6)
+    ref = P.rms_norm(x, wr, 1e-5)
+    tol = 1e-5 if out_dtype == "float32" else 1e-2
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=tol, atol=tol * np.abs(ref).max())
+    # gathered rows: the residual stays untouched
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    out2 = torch.empty((3, d), dtype=DT[out_dtype], device=DEV)
+    res2 = res_in.clone()
+    ops.add_rmsnorm(res2, ops.Partials(part, bias), w, 1e-5, out2, rows=rows)
+    assert torch.equal(res2, res_in)
+    assert torch.equal(out2[0], out[5]) and torch.equal(out2[1], out[0]) and torch.equal(out2[2], out[5])
+    # no delta: a plain norm
+    out3 = torch.empty((T, d), dtype=DT[out_dtype], device=DEV)
+    ops.add_rmsnorm(res_in.clone(), None, w, 1e-5, out3)
+    ref3 = P.rms_norm(rr, wr, 1e-5)
+    np.testing.assert_allclose(out3.float().cpu().numpy(), ref3, rtol=tol, atol=tol * np.abs(ref3).max())
+
+
+def test_add_rmsnorm_refuses_what_it_cannot_hold():
+    ops = _ops()
+    d = 60000
+    with pytest.raises(ops.KernelError, match="exceeds"):
+        ops.add_rmsnorm(torch.zeros((1, d), device=DEV), None, torch.ones(d, device=DEV), 1e-6,
+                        torch.empty((1, d), device=DEV))
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("ff", [200, 777])
+def test_swiglu(out_dtype, ff):
+    ops = _ops()
+    T, S = 5, 2
+    part, pr = _rand((S, T, 2 * ff), torch.float32, 9, 2.0)
+    out = torch.empty((T, ff), dtype=DT[out_dtype], device=DEV)
+    ops.swiglu(ops.Partials(part), out)
+    s = pr.sum(0)
+    ref = P.silu(s[:, :ff]) * s[:, ff:]
+    tol = 1e-6 if out_dtype == "float32" else 1e-2
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=tol, atol=tol * np.abs(ref).max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    ops = _ops()
+    table, tr = _rand((301, 80), DT[dtype], 10)
+    ids = torch.tensor([300, 0, 17, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty((4, 80), device=DEV)
+    ops.embed(table, ids, out)
+    np.testing.assert_array_equal(out.cpu().numpy(), tr[[300, 0, 17, 17]])
+
+
+def _paged(dense_k, dense_v, page_size, num_pages, seed):
+    """Scatter dense [L, nkv, hd] keys/values of ONE request into pages picked at random.
+    Unused slots are filled with large numbers so that a read beyond the request shows."""
+    L, nkv, hd = dense_k.shape
+    nb = (L + page_size - 1) // page_size
+    rng = np.random.default_rng(seed)
+    pages = rng.permutation(num_pages)[:nb]
+    kc = np.full((num_pages, nkv, page_size, hd), 1e4, dtype=np.float32)
+    vc = np.full((num_pages, nkv, page_size, hd), -1e4, dtype=np.float32)
+    for s in range(L):
+        kc[pages[s // page_size], :, s % page_size, :] = dense_k[s]
+        vc[pages[s // page_size], :, s % page_size, :] = dense_v[s]
+    return kc, vc, pages.astype(np.int32)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,hd,window,page", [(6, 2, 32, 0, 16), (5, 5, 48, 40, 16), (8, 1, 128, 0, 4),
+                                                   (3, 3, 80, 7, 16), (4, 2, 16, 0, 1), (2, 1, 256, 100, 32)])
+def test_attention_plain(dtype, nq, nkv, hd, window, page):
+    ops = _ops()
+    L = 150
+    rng = np.random.default_rng(nq * 100 + hd)
+    td = DT[dtype]
+
+    def r16(a):
+        return torch.from_numpy(a.astype(np.float32)).to(td).float().numpy()
+    q = r16(rng.normal(size=(L, nq, hd)))
+    k = r16(rng.normal(size=(L, nkv, hd)))
+    v = r16(rng.normal(size=(L, nkv, hd)))
+    ref = P.causal_attention(q, k, v, window)
+    kc, vc, pages = _paged(k, v, page, 64 if page >= 4 else 200, 1)
+    # queries: a portion of the request (positions 100..149) as the last step would hold
+    lo = 100
+    pos = torch.arange(lo, L, dtype=torch.int32, device=DEV)
+    seq = torch.zeros(L - lo, dtype=torch.int32, device=DEV)
+    table = torch.from_numpy(pages)[None, :].contiguous().to(DEV)
+    out = torch.empty((L - lo, nq * hd), dtype=td, device=DEV)
+    ops.attention_plain(torch.from_numpy(q[lo:].reshape(L - lo, -1)).to(td).to(DEV),
+                        torch.from_numpy(kc).to(td).to(DEV), torch.from_numpy(vc).to(td).to(DEV),
+                        pos, seq, table, page, out, nq, nkv, hd, window, 1.0 / math.sqrt(hd))
+    tol = 2e-6 if dtype == "float32" else 1e-2
+    np.testing.assert_allclose(out.float().cpu().numpy().reshape(L - lo, nq, hd), ref[lo:], rtol=0,
+                               atol=tol * np.abs(ref).max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far", [0, 15, 16, 255, 256, 299])
+def test_attention_finds_one_far_key(dtype, far):
+    """One key among 300 matches the query strongly; the output must be that key's value.
+    Random keys alone would hide a kernel that skips a page edge or the first position."""
+    ops = _ops()
+    L, nq, nkv, hd, page = 300, 4, 2, 64, 16
+    rng = np.random.default_rng(far)
+    k = rng.normal(size=(L, nkv, hd)).astype(np.float32) * 0.1
+    v = rng.normal(size=(L, nkv, hd)).astype(np.float32)
+    q = rng.normal(size=(1, nq, hd)).astype(np.float32) * 0.1
+    direction = np.ones(hd, dtype=np.float32)
+    k[far, :, :] = 4.0 * direction
+    q[0, :, :] = 4.0 * direction             # score 16*64/8 = 128 against ~0 elsewhere
+    td = DT[dtype]
+    kc, vc, pages = _paged(k, v, page, 40, 2)
+    out = torch.empty((1, nq * hd), dtype=td, device=DEV)
+    ops.attention_plain(torch.from_numpy(q.reshape(1, -1)).to(td).to(DEV), torch.from_numpy(kc).to(td).to(DEV),
+                        torch.from_numpy(vc).to(td).to(DEV), torch.tensor([L - 1], dtype=torch.int32, device=DEV),
+                        torch.zeros(1, dtype=torch.int32, device=DEV),
+                        torch.from_numpy(pages)[None, :].contiguous().to(DEV), page, out, nq, nkv, hd, 0,
+                        1.0 / math.sqrt(hd))
+    got = out.float().cpu().numpy().reshape(nq, hd)
+    want = np.stack([v[far, (h * nkv) // nq] for h in range(nq)])
+    np.testing.assert_allclose(got, torch.from_numpy(want).to(td).float().numpy(), atol=2e-2 if dtype == "bfloat16" else 1e-5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_window_edge(dtype):
+    """A strongly matching key just inside the window decides the output; the same key one
+    position further back, just outside, must have no influence at all."""
+    ops = _ops()
+    L, nq, nkv, hd, page, window = 200, 2, 2, 32, 16, 48
+    td = DT[dtype]
+    for offset, inside in ((window - 1, True), (window, False)):
+        rng = np.random.default_rng(5)
+        k = rng.normal(size=(L, nkv, hd)).astype(np.float32) * 0.1
+        v = rng.normal(size=(L, nkv, hd)).astype(np.float32)
+        q = np.full((1, nq, hd), 4.0, dtype=np.float32)
+        spot = L - 1 - offset
+        k[spot] = 4.0
+        kc, vc, pages = _paged(k, v, page, 40, 3)
+        out = torch.empty((1, nq * hd), dtype=td, device=DEV)
+        ops.attention_plain(torch.from_numpy(q.reshape(1, -1)).to(td).to(DEV), torch.from_numpy(kc).to(td).to(DEV),
+                            torch.from_numpy(vc).to(td).to(DEV), torch.tensor([L - 1], dtype=torch.int32, device=DEV),
+                            torch.zeros(1, dtype=torch.int32, device=DEV),
+                            torch.from_numpy(pages)[None, :].contiguous().to(DEV), page, out, nq, nkv, hd, window,
+                            1.0 / math.sqrt(hd))
+        got = out.float().cpu().numpy().reshape(nq, hd)
+        close = np.abs(got - v[spot]).max() < 3e-2
+        assert close == inside, f"key at distance {offset} (window {window}): inside={inside}, output follows it={close}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,hd,rot,bias,norm", [(6, 2, 32, 32, True, True), (5, 5, 48, 48, False, True),
+                                                     (3, 1, 80, 40, True, False), (8, 2, 128, 128, False, True),
+                                                     (2, 2, 16, 0, False, False)])
+def test_attn_prepare(dtype, nq, nkv, hd, rot, bias, norm):
+    ops = _ops()
+    td = DT[dtype]
+    T, S, page, num_pages = 9, 2, 4, 12
+    width = (nq + 2 * nkv) * hd
+    part, pr = _rand((S, T, width), torch.float32, 11)
+    b, br = _rand((width,), torch.float32, 12, 0.2) if bias else (None, None)
+    qw, qwr = _rand((hd,), torch.float32, 13) if norm else (None, None)
+    kw, kwr = _rand((hd,), torch.float32, 14) if norm else (None, None)
+    theta = 1e6
+    inv = (np.float32(1) / np.power(np.float32(theta), np.arange(rot // 2, dtype=np.float32) / np.float32(max(rot // 2, 1)))).astype(np.float32)
+    # two requests: tokens 0..4 are positions 7..11 of request 0, tokens 5..8 positions 0..3 of request 1
+    positions = np.array([7, 8, 9, 10, 11, 0, 1, 2, 3], dtype=np.int32)
+    seqs = np.array([0, 0, 0, 0, 0, 1, 1, 1, 1], dtype=np.int32)
+    table = np.array([[5, 9, 2, -1], [7, -1, -1, -1]], dtype=np.int32)
+    kc = torch.zeros((num_pages, nkv, page, hd), dtype=td, device=DEV)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty((T, nq * hd), dtype=td, device=DEV)
+    ops.attn_prepare(ops.Partials(part, b), qw, kw, 1e-5, torch.from_numpy(inv).to(DEV) if rot else None, rot,
+                     torch.from_numpy(positions).to(DEV), torch.from_numpy(seqs).to(DEV),
+                     torch.from_numpy(table).to(DEV), page, kc, vc, q_out, nq, nkv, hd)
+    x = pr.sum(0) + (br if bias else 0)
+    q = x[:, :nq * hd].reshape(T, nq, hd)
+    k = x[:, nq * hd:(nq + nkv) * hd].reshape(T, nkv, hd)
+    v = x[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+    if norm:
+        q, k = P.head_rms_norm(q, qwr, 1e-5), P.head_rms_norm(k, kwr, 1e-5)
+    if rot:
+        ang = positions.astype(np.float32)[:, None] * inv[None, :]
+        cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+        q = np.concatenate([P.rope(q[..., :rot], cos, sin), q[..., rot:]], -1)
+        k = np.concatenate([P.rope(k[..., :rot], cos, sin), k[..., rot:]], -1)
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    np.testing.assert_allclose(q_out.float().cpu().numpy().reshape(T, nq, hd), q, rtol=tol, atol=tol * 4)
+    kcn, vcn = kc.float().cpu().numpy(), vc.float().cpu().numpy()
+    for t in range(T):
+        pg = table[seqs[t], positions[t] // page]
+        np.testing.assert_allclose(kcn[pg, :, positions[t] % page, :], k[t], rtol=tol, atol=tol * 4)
+        np.testing.assert_allclose(vcn[pg, :, positions[t] % page, :], v[t], rtol=tol, atol=tol * 4)
+    written = {(table[seqs[t], positions[t] // page], positions[t] % page) for t in range(T)}
+    for pg in range(num_pages):
+        for sl in range(page):
+            if (pg, sl) not in written:
+                assert not kcn[pg, :, sl].any() and not vcn[pg, :, sl].any(), f"page {pg} slot {sl} was written"
+
+
+def test_attn_prepare_refuses_odd_sizes():
+    ops = _ops()
+    z = torch.zeros((1, 1, (1 + 2) * 600), device=DEV)
+    i32 = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError, match="head size"):
+        ops.attn_prepare(ops.Partials(z), None, None, 0.0, None, 0, i32, i32, i32[None], 4,
+                         torch.zeros(4, device=DEV), torch.zeros(4, device=DEV), torch.empty((1, 600), device=DEV), 1, 1, 600)
+
+
+def test_argmax_first_maximum_wins():
+    ops = _ops()
+    V = 151936 + 7
+    l = torch.randn((5, V), device=DEV)
+    l[0, 77] = 50.0; l[0, 90000] = 50.0
+    l[1, V - 1] = 60.0
+    l[2, 0] = 70.0
+    l[3, :] = -3.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax(l, out)
+    got = out.cpu().tolist()
+    assert got[:4] == [77, V - 1, 0, 0] and got[4] == int(l[4].argmax())
+
+
+@pytest.mark.parametrize("V", [509, 151936])
+def test_sample_against_plain_sampler(V):
+    ops = _ops()
+    from kestrel_llm_b200.sampling import uniform_for
+    rng = np.random.default_rng(V)
+    rows = [(0.8, 0, 0.0, 1.0), (1.0, 20, 0.0, 1.0), (0.7, 0, 0.05, 1.0), (1.3, 0, 0.0, 0.9), (0.9, 50, 0.02, 0.8),
+            (0.0, 0, 0.0, 1.0), (1.0, 0, 0.0, 0.0), (2.0, 1, 0.0, 1.0), (0.5, 0, 0.0, 0.3)] * 3
+    R = len(rows)
+    logits = (rng.normal(size=(R, V)) * 3).astype(np.float32)
+    u = np.array([uniform_for(123, i) for i in range(R)], dtype=np.float32)
+    assert ((u > 0) & (u <= 1)).all()
+    dev = lambda a, dt: torch.tensor(a, dtype=dt, device=DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample(torch.from_numpy(logits).to(DEV), dev([r[0] for r in rows], torch.float32),
+               dev([r[1] for r in rows], torch.int32), dev([r[3] for r in rows], torch.float32),
+               dev([r[2] for r in rows], torch.float32), torch.from_numpy(u).to(DEV), out)
+    got = out.cpu().tolist()
+    for r, (temp, tk, mp, tp) in enumerate(rows):
+        if temp <= 0 or tp <= 0:
+            assert got[r] == P.greedy(logits[r])
+            continue
+        p = P.sample_probs(logits[r], temp, tk, mp, tp)
+        assert p[got[r]] > 0, f"row {r}: token {got[r]} was filtered out by the plain sampler"
+        want = P.sample_from(p, float(u[r]))
+        if got[r] != want:
+            # sums run in another order on the device: accept a neighbour only if u*total lies
+            # within rounding of the boundary between the two
+            c = np.cumsum(p.astype(np.float64))
+            target = float(u[r]) * c[-1]
+            edge = c[min(got[r], want)]
+            assert abs(edge - target) <= 1e-5 * c[-1], f"row {r}: got {got[r]}, plain {want}"
+    # a draw depends on (seed, index) only
+    assert uniform_for(5, 3) == uniform_for(5, 3) and uniform_for(5, 3) != uniform_for(5, 4) != uniform_for(6, 4)
+
+
+def test_kernels_refuse_host_tensors():
+    ops = _ops()
+    with pytest.raises(ops.KernelError, match="CUDA device only"):
+        ops.gemm_plain(torch.zeros((2, 2)), torch.zeros((2, 2)), torch.zeros((2, 2)))

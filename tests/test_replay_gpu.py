@@ -14,15 +14,18 @@ import tiny_configs
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": (5, 11, 17, 40, 70), "B": (1, 33, 70, 129, 47, 90), "C": (3, 50, 97, 130, 64, 81)}
+# more requests than fit the pool at once, so that finished requests' pages are used again
+LENGTHS_MIXED = {"A": (5, 11, 17, 40, 70, 64, 33, 90, 25, 70, 48), "B": (1, 33, 70, 129, 47, 90, 16, 65, 120, 31),
+                 "C": (3, 50, 97, 130, 64, 81, 17, 111, 49, 128)}
 DTYPES = ("float32", "bfloat16")
 
 
-def _requests(name):
-    return R.random_requests(tiny_configs.CONFIGS[name][0]["vocab_size"], LENGTHS[name], seed=1 + ord(name))
+def _requests(name, lengths=None):
+    return R.random_requests(tiny_configs.CONFIGS[name][0]["vocab_size"], lengths or LENGTHS[name], seed=1 + ord(name))
 
 
-def _run(model_dirs, name, dtype, family, record_property, **kw):
-    reqs = _requests(name)
+def _run(model_dirs, name, dtype, family, record_property, lengths=None, **kw):
+    reqs = _requests(name, lengths)
     steps, max_tokens = family(reqs, **kw)
     engine = R.make_engine(model_dirs[name][dtype], dtype, max_tokens)
     got = R.run_trace(engine, steps)
@@ -55,7 +58,7 @@ def test_portions_of_changing_size(model_dirs, name, dtype, record_property):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_mixed_with_page_reuse(model_dirs, name, dtype, record_property):
-    engine = _run(model_dirs, name, dtype, R.trace_mixed, record_property)
+    engine = _run(model_dirs, name, dtype, R.trace_mixed, record_property, lengths=LENGTHS_MIXED[name])
     # the pool was so small that pages were handed out more often than there are pages
     assert engine.cache.pages_handed_out() > engine.cache.num_pages(0)
 
@@ -70,7 +73,7 @@ def test_cuttings_agree_with_each_other(model_dirs, dtype):
     for family in (R.trace_whole, R.trace_tail_decode, R.trace_portions, R.trace_mixed):
         steps, max_tokens = family(reqs)
         results.append(R.run_trace(R.make_engine(model_dirs[name][dtype], dtype, max_tokens), steps))
-    tol = {"float32": 1e-5, "bfloat16": 4e-2}[dtype]
+    tol = {"float32": 2e-6, "bfloat16": 2e-2}[dtype]
     for other in results[1:]:
         for rname, toks in reqs.items():
             scale = max(float(np.abs(results[0][rname][p]).max()) for p in range(len(toks)))
