@@ -1,0 +1,284 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens a second at batch 8 (the headline),
+at batch 1 and 64, prefill of 2,048 tokens, and the same decode through the Python entry
+point with host tokens in and out.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+Model: the sizes of Qwen3-8B (36 layers, width 4096, 32/8 heads of 128, feed-forward 12288,
+vocabulary 151936), bfloat16, random weights; prompts are uniform random token ids.  A step is
+one decode step of the whole batch at a context that ends at 4,096 tokens.  `--layers` runs
+fewer layers of the same sizes (the record names both numbers); layer sizes never shrink.
+
+Timing: CUDA events on the launching stream around exactly K steps after W warm-up steps, with
+a synchronize on both sides.  Every step streams all weights (15 GB) and the live requests'
+cache from HBM, far more than the 126 MB of L2, so nothing a step reads is still cached from
+the step before.  SM clocks and throttle reasons are sampled with nvidia-smi during the timed
+regions.  One JSON line is printed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=4096,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                attention_bias=False, max_position_embeddings=40960, hidden_act="silu")
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(p.get(k), (int, float)) and p[k] > 0:
+                    out[k] = float(p[k])
+            out["source"] = "measured"
+            return out
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while `active`."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.rows = []
+        self.active = False
+        self._stop = False
+        self._proc = None
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}",
+                                           "--format=csv,noheader,nounits", "-lms", "200"],
+                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._t = threading.Thread(target=self._read, daemon=True)
+            self._t.start()
+        except OSError:
+            self._proc = None
+
+    def _read(self):
+        for line in self._proc.stdout:
+            if self._stop:
+                break
+            if self.active:
+                self.rows.append([c.strip() for c in line.split(",")])
+
+    def close(self):
+        self._stop = True
+        if self._proc:
+            self._proc.terminate()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(int(float(r[0])))
+                mx = max(mx, int(float(r[1])))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--layers", type=int, default=0, help="run this many layers of the model's 36 (0 = all)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "not installable offline: pip finds neither setup.py nor pyproject.toml (a CMake C11 "
+                          "project), and the engine is CPU-only and loads only its own quantized VQF files, "
+                          "not bfloat16 safetensors"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported (no multi-GPU path exists)")
+        return 2
+    W, K = max(3, args.warmup), max(1, args.steps)
+
+    import numpy as np
+    import torch
+    from kestrel_llm_b200 import LLM, SamplingParams
+    from kestrel_llm_b200.config import EngineOptions, Qwen3Config
+    from kestrel_llm_b200.config.registry import resolve_architecture
+    from kestrel_llm_b200.csrc import ops
+    from kestrel_llm_b200.engine import Entry
+    from kestrel_llm_b200.weights import fill_random_
+
+    raw = dict(QWEN3_8B)
+    full_layers = raw["num_hidden_layers"]
+    if args.layers:
+        raw["num_hidden_layers"] = min(args.layers, full_layers)
+    cfg = Qwen3Config.from_dict(raw)
+    L = cfg.num_hidden_layers
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    model = resolve_architecture(cfg.architecture).build(cfg, torch.bfloat16, dev)
+    fill_random_(model, 0)
+    max_batch = 64 if not args.skip_points else max(args.batch, 1)
+    opts = EngineOptions(dtype="bfloat16", page_size=16, batch_max=max_batch, max_model_len=CONTEXT + 64,
+                         max_tokens=max_batch * (CONTEXT + 64), max_step_tokens=max(PREFILL_TOKENS, max_batch),
+                         prefill_batch=PREFILL_TOKENS)
+    llm = LLM(model, dtype="bfloat16", options=opts)
+    engine = llm.engine
+    for t in engine.cache.k + engine.cache.v:        # cache contents for the synthetic contexts
+        if t is not None:
+            t.normal_(0.0, 0.5)
+    rng = np.random.default_rng(0)
+    pk = peaks()
+    clocks = ClockSampler(0)
+
+    # bytes a decode step has to read: every weight it uses once, and the live requests' cache
+    esz = 2
+    per_layer = (cfg.q_size + 2 * cfg.kv_size) * cfg.hidden_size + cfg.hidden_size * cfg.q_size \
+        + 3 * cfg.intermediate_size * cfg.hidden_size
+    weight_bytes = esz * (L * per_layer + cfg.vocab_size * cfg.hidden_size)
+    kv_bytes_per_token = L * 2 * cfg.kv_size * esz
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        clocks.active = True
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        clocks.active = False
+        return a.elapsed_time(b) / 1000.0
+
+    def decode_point(B):
+        """K timed decode steps of B requests whose context ends at CONTEXT; device-timed, the
+        step function called directly, tokens picked on the device."""
+        ctx0 = CONTEXT - (W + K)
+        rids = list(range(1000, 1000 + B))
+        for r in rids:
+            engine.admit(r)
+            engine.cache.reserve(r, ctx0)       # a context of ctx0 tokens whose cache holds random values
+            engine.cache.commit(r, ctx0)
+        toks = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)).to(dev)
+        nxt = torch.empty(B, dtype=torch.int32, device=dev)
+        state = {"toks": toks.cpu().tolist()}
+
+        def one():
+            logits = engine.step([Entry(r, [t], (0,)) for r, t in zip(rids, state["toks"])])
+            ops.argmax(logits, nxt)
+
+        for _ in range(W):
+            one()
+        before = ops.launches + engine.graph_launches
+        secs = timed(one, K)
+        launched = ops.launches + engine.graph_launches - before
+        for r in rids:
+            engine.release(r)
+        mean_ctx = ctx0 + W + (K - 1) / 2.0 + 1
+        bytes_step = weight_bytes + B * mean_ctx * kv_bytes_per_token
+        return {"tok_s": B * K / secs, "ms": 1000.0 * secs / K, "bytes_step": bytes_step, "launches": launched}
+
+    out_points = {}
+    main_pt = decode_point(args.batch)
+    if not args.skip_points:
+        out_points["decode_b1"] = round(decode_point(1)["tok_s"], 2)
+        out_points["decode_b64"] = round(decode_point(64)["tok_s"], 2)
+
+    # prefill of one 2,048-token prompt in one step (logits of the last token)
+    def prefill_once(rid):
+        toks = rng.integers(0, cfg.vocab_size, size=PREFILL_TOKENS).tolist()
+        engine.step([Entry(rid, toks, (PREFILL_TOKENS - 1,))])
+        engine.release(rid)
+    for i in range(2):
+        prefill_once(2000 + i)
+    pre_runs = 3
+    counter = {"i": 0}
+
+    def pf():
+        counter["i"] += 1
+        prefill_once(2100 + counter["i"])
+    pre_secs = timed(pf, pre_runs) / pre_runs
+    T = PREFILL_TOKENS
+    gemm_flops = 2.0 * T * L * per_layer + 2.0 * cfg.vocab_size * cfg.hidden_size     # head: one row
+    attn_flops = L * 4.0 * cfg.num_attention_heads * cfg.head_dim * (T * (T + 1) / 2.0)
+    pre_flops = gemm_flops + attn_flops
+    prefill = {"value": round(T / pre_secs, 1), "tokens": T, "ms": round(1000 * pre_secs, 3),
+               "frac": round(pre_flops / pre_secs / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # end to end: the same decode through the Python entry point (scheduler, one H2D copy of the
+    # step's description from pinned memory, sampling on the device, token ids read back)
+    B = args.batch
+    ctx0 = CONTEXT - (W + K) - 1
+    prompts = [rng.integers(0, cfg.vocab_size, size=ctx0).tolist() for _ in range(B)]
+    sp = SamplingParams(temperature=0.0, max_tokens=W + K + 1, ignore_eos=True)
+    for p in prompts:
+        llm.add_request(p, sp)
+    while llm.stats.generated_tokens < B:        # prompts, untimed
+        llm.step()
+    for _ in range(W):
+        llm.step()
+    h0, d0 = llm.stats.h2d_bytes, llm.stats.d2h_bytes
+    torch.cuda.synchronize()
+    clocks.active = True
+    t0 = time.perf_counter()
+    for _ in range(K):
+        llm.step()                               # ends with the read-back of the sampled ids
+    torch.cuda.synchronize()
+    e2e_secs = time.perf_counter() - t0
+    clocks.active = False
+    e2e = {"value": round(B * K / e2e_secs, 2), "unit": "tokens/s", "ms_per_step": round(1000 * e2e_secs / K, 3),
+           "h2d_bytes_per_step": (llm.stats.h2d_bytes - h0) // K, "d2h_bytes_per_step": (llm.stats.d2h_bytes - d0) // K}
+    while llm.has_unfinished():
+        llm.step()
+    clocks.close()
+
+    achieved = main_pt["bytes_step"] / (main_pt["ms"] / 1000.0) / 1e9
+    rec = {
+        "metric": "decode tokens/s, Qwen3-8B bf16, batch 8, context 4096", "value": round(main_pt["tok_s"], 2),
+        "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(main_pt["ms"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights, uniform random token ids, cache of the context filled with random values",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B shape", "layers": L, "layers_of_model": full_layers, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "page_size": 16, "parallelism": "single GPU",
+                   "cache_flush": "inputs larger than L2: each step streams all weights and cache from HBM",
+                   "peaks": pk["source"]},
+        "e2e": e2e, "gpu_launches": int(main_pt["launches"]), "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": out_points, "clocks": clocks.summary(),
+    }
+    print(json.dumps(rec))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

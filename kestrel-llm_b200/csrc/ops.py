@@ -69,7 +69,12 @@ def _declare(lib) -> None:
         fn.restype = _i
 
 
+launches = 0     # kernels launched through this module since import (graph replays are counted by their runner)
+
+
 def _check(rc: int) -> None:
+    global launches
+    launches += 1
     if rc != 0:
         raise KernelError(library().kestrel_last_error().decode("utf-8", "replace"))
 

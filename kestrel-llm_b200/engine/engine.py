@@ -43,6 +43,7 @@ class Engine:
                                   options.batch_max, self.max_model_len)
         self.vocab_size = model.vocab_size
         self.steps_run = 0
+        self.graph_launches = 0      # kernels replayed from CUDA graphs (not counted by ops.launches)
 
     # ---- requests -----------------------------------------------------------------------
     def admit(self, rid: int) -> int:
@@ -68,6 +69,9 @@ class Engine:
             if e.rid in seen:
                 raise ValueError(f"request {e.rid} appears twice in one step")
             seen.add(e.rid)
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise ValueError(f"request {e.rid}: wanted place {w} outside its {len(e.tokens)} tokens of this step")
             for t in e.tokens:
                 if not 0 <= int(t) < self.vocab_size:
                     raise ValueError(f"request {e.rid}: token id {t} outside the vocabulary of {self.vocab_size}")
