@@ -1,0 +1,381 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: out[t, n] = sum_k x[t, k] w[n, k].
+//
+// The weight matrix is the MMA's M operand: a CTA owns 128 output features (TMEM lanes) by BN
+// tokens (TMEM columns), BN from 16 to 256.  So one kernel serves decode (few tokens, the
+// product is a stream of weights from HBM) and prefill (many tokens, tensor-core bound), and an
+// output element is accumulated in the same k order whatever the number of tokens.
+//
+//   warp 0   : one thread issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the
+//              weight tile [128 x 64] and the activation tile [BN x 64] into a ring of stages;
+//   warp 1   : allocates TMEM; one thread issues tcgen05.mma (M=128, N=BN, K=16, bf16 in,
+//              float32 accumulate in TMEM) and releases stages with tcgen05.commit;
+//   warps 2-5: epilogue - tcgen05.ld the accumulator (each warp its 32 lanes) and store.
+//
+// Epilogues: PARTIAL writes float32 [split, t, n] - the K range can be split over blockIdx.z
+// so that few-token products still fill 148 SMs, and the consumer kernel sums the slices in a
+// fixed order; SWIGLU runs two accumulators (gate rows n and up rows ff + n of a fused weight)
+// and writes silu(gate) * up as bfloat16, so the gate/up product never reaches memory.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host
+// reads (kestrel_gemm_tc_error) and the CTA leaves through the common exit, which frees TMEM.
+// Sizes: K and the row strides must be multiples of 8 elements and the bases 16-byte aligned
+// (TMA); N, T and K need not be multiples of the tile - TMA fills out-of-range rows and
+// columns with zeros and stores are predicated.  Anything else is refused
+// (kestrel_gemm_tc_supported) and takes the CUDA-core kernel.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_WAIT_LIMIT (1u << 22)
+
+enum { TC_PARTIAL = 0, TC_SWIGLU = 1 };
+
+__device__ int g_tc_error = 0;
+
+// ---------------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// false if the barrier did not flip within the limit
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float *v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle, 8-row groups of
+// 1024 bytes: start address >> 4, leading offset 1 (unused with swizzle), stride offset
+// 1024 >> 4, descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// ------------------------------------------------------------------------------- kernel
+template <int BN, int MODE>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               void *__restrict__ out, int T, int N, int K, int kb_per_split, long long slice_stride,
+               long long ldo, int stages, int up_row_offset) {
+    constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
+    constexpr uint32_t B_BYTES = BN * TC_BK * 2;
+    constexpr uint32_t STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = (A_TILES * BN) < 32 ? 32 : (A_TILES * BN);
+    // M = 128, N = BN, bf16 x bf16 -> f32, both operands K-major
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint32_t bars = base + (uint32_t)stages * STAGE_BYTES;          // full[stages], empty[stages], accum, tmem slot
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (stages + s); };
+    uint32_t accum_bar = bars + 16u * stages;
+    uint32_t tmem_slot = accum_bar + 8;
+    volatile uint32_t *tmem_slot_ptr = (volatile uint32_t *)(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int n0 = blockIdx.x * TC_BM, t0 = blockIdx.y * BN;
+    int total_kb = (K + TC_BK - 1) / TC_BK;
+    int kb0 = blockIdx.z * kb_per_split;
+    int num_kb = min(kb_per_split, total_kb - kb0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait(empty_bar(stage), phase ^ 1)) { atomicExch(&g_tc_error, 1); break; }
+                mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+                uint32_t sa = base + (uint32_t)stage * STAGE_BYTES;
+                int kc = (kb0 + kb) * TC_BK;
+                tma_load_2d(sa, &map_w, full_bar(stage), kc, n0);
+                if (MODE == TC_SWIGLU) tma_load_2d(sa + A_BYTES, &map_w, full_bar(stage), kc, up_row_offset + n0);
+                tma_load_2d(sa + A_TILES * A_BYTES, &map_x, full_bar(stage), kc, t0);
+                if (++stage == stages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                if (!mbar_wait(full_bar(stage), phase)) { atomicExch(&g_tc_error, 2); ok = false; break; }
+                tc_fence_after();
+                uint32_t sa = base + (uint32_t)stage * STAGE_BYTES;
+                uint64_t da = smem_desc(sa), db = smem_desc(sa + A_TILES * A_BYTES);
+#pragma unroll
+                for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
+                    uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
+                    tc_mma(tmem, da + 2 * k4, db + 2 * k4, IDESC, acc);
+                    if (MODE == TC_SWIGLU) tc_mma(tmem + BN, smem_desc(sa + A_BYTES) + 2 * k4, db + 2 * k4, IDESC, acc);
+                }
+                tc_commit(empty_bar(stage));
+                if (++stage == stages) { stage = 0; phase ^= 1; }
+            }
+            tc_commit(accum_bar);
+        }
+    } else {
+        int q = warp & 3;                       // TMEM lanes 32q .. 32q+31 belong to this warp
+        int n = n0 + 32 * q + lane;
+        bool waited = mbar_wait(accum_bar, 0);
+        if (!waited && lane == 0) atomicExch(&g_tc_error, 3);
+        tc_fence_after();
+        if (waited && num_kb > 0) {
+            int valid = min(BN, T - t0);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (c >= valid) break;
+                float g[16];
+                tc_ld16(tmem + ((uint32_t)(32 * q) << 16) + c, g);
+                if (MODE == TC_SWIGLU) {
+                    float u[16];
+                    tc_ld16(tmem + ((uint32_t)(32 * q) << 16) + BN + c, u);
+                    __nv_bfloat16 *o = (__nv_bfloat16 *)out;
+                    if (n < N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c + j < valid) {
+                                float a = g[j] / (1.0f + expf(-g[j]));
+                                o[(size_t)(t0 + c + j) * ldo + n] = __float2bfloat16_rn(a * u[j]);
+                            }
+                    }
+                } else {
+                    float *o = (float *)out + (size_t)blockIdx.z * slice_stride;
+                    if (n < N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c + j < valid) o[(size_t)(t0 + c + j) * ldo + n] = g[j];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void *ptr; long long rows, cols, ld; int box_rows;
+    bool operator==(const MapKey &o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.ld;   h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+
+// bf16 matrix [rows, cols] with row stride ld elements; box = box_rows x 64 columns, 128-byte swizzle
+static int make_map(CUtensorMap *out, const void *ptr, long long rows, long long cols, long long ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *out = it->second; return 0; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return kestrel_fail(-4, "gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return kestrel_fail(-4, "gemm_tc: cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld)", (int)r, rows, cols, ld);
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+KESTREL_API int kestrel_gemm_tc_supported(const void *x, const void *w, int T, int N, int K, long long ldx, long long ldw) {
+    if (T <= 0 || N <= 0 || K <= 0) return 0;
+    if (K % 8 || ldx % 8 || ldw % 8) return 0;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return 0;
+    return 1;
+}
+
+// Slices a product of T tokens and N output features would be split into, so that the grid
+// covers the GPU's 148 SMs about twice where the K range allows it.
+KESTREL_API int kestrel_gemm_tc_splits(int T, int N, int K) {
+    int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
+    int total_kb = (K + TC_BK - 1) / TC_BK;
+    if (tiles >= 296 || T > 256) return 1;
+    int s = (int)((296 + tiles - 1) / tiles);
+    int max_s = total_kb / 8 > 0 ? total_kb / 8 : 1;       // at least 8 k-blocks (512 columns) a slice
+    if (s > max_s) s = max_s;
+    if (s > 16) s = 16;
+    int per = (total_kb + s - 1) / s;
+    return (total_kb + per - 1) / per;                      // no empty slice
+}
+
+template <int BN, int MODE>
+static int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, void *out, int T, int N, int K, int splits,
+                     long long slice_stride, long long ldo, int up_off, cudaStream_t stream) {
+    constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
+    constexpr int STAGE_BYTES = A_TILES * TC_BM * TC_BK * 2 + BN * TC_BK * 2;
+    int total_kb = (K + TC_BK - 1) / TC_BK;
+    int per = (total_kb + splits - 1) / splits;
+    // few tokens: two CTAs share an SM, each with about 100 KB of stages; else one CTA takes it all
+    int budget = (BN <= 64 && MODE == TC_PARTIAL) ? 100 * 1024 : 200 * 1024;
+    int stages = budget / STAGE_BYTES;
+    if (stages > per) stages = per < 2 ? 2 : per;
+    if (stages > 12) stages = 12;
+    if (stages < 2) stages = 2;
+    size_t smem = (size_t)stages * STAGE_BYTES + 16 * stages + 16 + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return kestrel_fail(-3, "gemm_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    dim3 grid((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
+    if (grid.y > 65535) return kestrel_fail(-2, "gemm_tc: T=%d needs more than 65535 token tiles", T);
+    gemm_tc_kernel<BN, MODE><<<grid, TC_THREADS, smem, stream>>>(mw, mx, out, T, N, K, per, slice_stride, ldo, stages, up_off);
+    return kestrel_check_launch("gemm_tc");
+}
+
+template <int MODE>
+static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, int w_rows, int K, long long ldx, long long ldw,
+                       long long ldo, int splits, long long slice_stride, int up_off, cudaStream_t stream) {
+    int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    if (MODE == TC_SWIGLU && bn == 256) bn = 128;          // two accumulators of 256 columns would not leave room for a second CTA's TMEM
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, w, w_rows, K, ldw, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mx, x, T, K, ldx, bn);
+    if (rc) return rc;
+    switch (bn) {
+        case 16: return launch_tc<16, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
+        case 32: return launch_tc<32, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
+        case 64: return launch_tc<64, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
+        case 128: return launch_tc<128, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
+        default: return launch_tc<256, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
+    }
+}
+
+// out float32 [splits, T, N] (slice stride given), x bf16 [T, K], w bf16 [N, K]
+KESTREL_API int kestrel_gemm_tc(const void *x, const void *w, float *out, int T, int N, int K, long long ldx,
+                                long long ldw, long long ldo, int splits, long long slice_stride, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(kestrel_gemm_tc_supported(x, w, T, N, K, ldx, ldw), "gemm_tc: sizes T=%d N=%d K=%d ldx=%lld ldw=%lld do not fit the TMA rules (multiples of 8, 16-byte aligned)", T, N, K, ldx, ldw);
+    int total_kb = (K + TC_BK - 1) / TC_BK;
+    KESTREL_REQUIRE(splits >= 1 && splits <= total_kb && ((total_kb + splits - 1) / splits) * (splits - 1) < total_kb,
+                    "gemm_tc: %d slices over %d k-blocks would leave a slice empty", splits, total_kb);
+    return dispatch_tc<TC_PARTIAL>(x, w, out, T, N, N, K, ldx, ldw, ldo, splits, slice_stride, 0, stream);
+}
+
+// out bf16 [T, ff] = silu(x Wg^T) * (x Wu^T), w bf16 [2 ff, K] with the gate rows first
+KESTREL_API int kestrel_gemm_tc_swiglu(const void *x, const void *w, void *out, int T, int ff, int K, long long ldx,
+                                       long long ldw, long long ldo, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(kestrel_gemm_tc_supported(x, w, T, ff, K, ldx, ldw), "gemm_tc_swiglu: sizes T=%d ff=%d K=%d do not fit the TMA rules", T, ff, K);
+    return dispatch_tc<TC_SWIGLU>(x, w, out, T, ff, 2 * ff, K, ldx, ldw, ldo, 1, 0, ff, stream);
+}
+
+// Reads (and clears) the error word that a bounded wait sets when it runs out: 0 = none,
+// 1 = the loader waited for a free stage, 2 = the MMA thread waited for data, 3 = the epilogue
+// waited for the accumulator.  Synchronises the device.
+KESTREL_API int kestrel_gemm_tc_error(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    return v;
+}

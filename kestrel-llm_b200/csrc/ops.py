@@ -60,6 +60,11 @@ def _declare(lib) -> None:
         "kestrel_gemm_plain": [_vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
         "kestrel_attention_plain": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _i,
                                     _f, _vp],
+        "kestrel_gemm_tc_supported": [_vp, _vp, _i, _i, _i, _ll, _ll],
+        "kestrel_gemm_tc_splits": [_i, _i, _i],
+        "kestrel_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _ll, _vp],
+        "kestrel_gemm_tc_swiglu": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
+        "kestrel_gemm_tc_error": [],
         "kestrel_argmax": [_vp, _ll, _i, _i, _vp, _vp],
         "kestrel_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     }
@@ -275,6 +280,58 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                                     uniform.data_ptr(), out.data_ptr(), _stream()))
 
 
+def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 product takes these operands: bfloat16, K and both row strides
+    multiples of 8 elements, bases 16-byte aligned (the TMA rules)."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    return bool(library().kestrel_gemm_tc_supported(x.data_ptr(), w.data_ptr(), x.shape[0], w.shape[0], x.shape[1],
+                                                    x.stride(0), w.stride(0)))
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+            splits: Optional[int] = None) -> torch.Tensor:
+    """y = x w^T on the tensor cores (tcgen05, TMA, TMEM) as float32 slices [S, T, N]."""
+    _need(x, "gemm_tc.x", torch.bfloat16, 2)
+    _need(w, "gemm_tc.w", torch.bfloat16, 2)
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm_tc: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    lib = library()
+    if out is not None:
+        if out.dim() == 2:
+            out = out.unsqueeze(0)
+        _need(out, "gemm_tc.out", torch.float32, 3)
+        if out.shape[1:] != (T, N):
+            raise KernelError(f"gemm_tc: out {tuple(out.shape)} for T={T}, N={N}")
+        S = out.shape[0]
+    else:
+        S = splits if splits is not None else lib.kestrel_gemm_tc_splits(T, N, K)
+        out = torch.empty((S, T, N), dtype=torch.float32, device=x.device)
+    _check(lib.kestrel_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, x.stride(0), w.stride(0),
+                               out.stride(1), S, out.stride(0), _stream()))
+    return out
+
+
+def gemm_tc_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(x Wg^T) * (x Wu^T) in one tcgen05 kernel with two accumulators."""
+    _need(x, "gemm_tc_swiglu.x", torch.bfloat16, 2)
+    _need(w_gate_up, "gemm_tc_swiglu.w", torch.bfloat16, 2)
+    _need(out, "gemm_tc_swiglu.out", torch.bfloat16, 2)
+    T, K = x.shape
+    ff = out.shape[1]
+    if w_gate_up.shape != (2 * ff, K) or out.shape[0] != T:
+        raise KernelError("gemm_tc_swiglu: shapes differ")
+    _check(library().kestrel_gemm_tc_swiglu(x.data_ptr(), w_gate_up.data_ptr(), out.data_ptr(), T, ff, K,
+                                            x.stride(0), w_gate_up.stride(0), out.stride(0), _stream()))
+
+
+def gemm_tc_error() -> int:
+    """Error word of the tcgen05 kernels' bounded waits (0 = none); synchronises the device."""
+    return library().kestrel_gemm_tc_error()
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x w^T as float32 slices [S, T, N] (S = 1 unless a split-K kernel ran).
 
@@ -282,6 +339,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None)
     product when its tiling rules hold (see `gemm_tc_supported`) and the CUDA-core one
     otherwise."""
     T, N = x.shape[0], w.shape[0]
+    if gemm_tc_supported(x, w):
+        return gemm_tc(x, w, out)
     if out is None:
         out = torch.empty((1, T, N), dtype=torch.float32, device=x.device)
     elif out.dim() == 2:
@@ -293,7 +352,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None)
 def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) in x's dtype, Wg and Wu being the two halves of w_gate_up's rows."""
     out = torch.empty((x.shape[0], ff), dtype=x.dtype, device=x.device)
-    swiglu(Partials(linear(x, w_gate_up)), out)
+    if x.shape[0] > 256 and gemm_tc_supported(x, w_gate_up):
+        gemm_tc_swiglu(x, w_gate_up, out)          # many tokens: the activation is the product's epilogue
+    else:
+        swiglu(Partials(linear(x, w_gate_up)), out)  # few tokens: split-K slices, summed by the activation kernel
     return out
 
 

@@ -49,6 +49,61 @@ def test_gemm_plain_is_the_same_for_any_batch():
     assert torch.equal(one[0], full[41])            # bit-identical: the k order does not depend on T
 
 
+@pytest.mark.parametrize("T,N,K,splits", [(1, 509, 96, None), (8, 4096, 4096, None), (37, 200, 96, 1), (130, 96, 200, 1),
+                                          (65, 1000, 776, 3), (16, 128, 64, 1), (17, 129, 72, 1), (300, 640, 512, None),
+                                          (2048, 384, 256, 1), (64, 6144, 1024, 2), (3, 260, 4096, None)])
+def test_gemm_tcgen05(T, N, K, splits):
+    """The tensor-core product against the CUDA-core product of the same bfloat16 operands."""
+    ops = _ops()
+    x, xr = _rand((T, K), torch.bfloat16, 1)
+    w, wr = _rand((N, K), torch.bfloat16, 2, 0.05)
+    assert ops.gemm_tc_supported(x, w)
+    out = ops.gemm_tc(x, w, splits=splits)
+    assert ops.gemm_tc_error() == 0
+    if splits is not None:
+        assert out.shape[0] == splits
+    got = out.sum(0).cpu().numpy()
+    ref = xr.astype(np.float64) @ wr.astype(np.float64).T
+    np.testing.assert_allclose(got, ref, rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max() + 1e-7)
+    plain = torch.empty((T, N), device=DEV)
+    ops.gemm_plain(x, w, plain)
+    np.testing.assert_allclose(got, plain.cpu().numpy(), rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max() + 1e-7)
+
+
+def test_gemm_tcgen05_row_does_not_depend_on_the_batch():
+    ops = _ops()
+    x, _ = _rand((300, 512), torch.bfloat16, 3)
+    w, _ = _rand((384, 512), torch.bfloat16, 4, 0.05)
+    full = ops.gemm_tc(x, w, splits=1)[0]
+    one = ops.gemm_tc(x[41:42].contiguous(), w, splits=1)[0]
+    assert torch.equal(one[0], full[41])
+
+
+@pytest.mark.parametrize("T,ff,K", [(5, 200, 96), (300, 200, 96), (257, 640, 512), (1024, 384, 320)])
+def test_gemm_tcgen05_swiglu(T, ff, K):
+    ops = _ops()
+    x, xr = _rand((T, K), torch.bfloat16, 5)
+    w, wr = _rand((2 * ff, K), torch.bfloat16, 6, 0.1)
+    out = torch.empty((T, ff), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc_swiglu(x, w, out)
+    assert ops.gemm_tc_error() == 0
+    y = xr.astype(np.float64) @ wr.astype(np.float64).T
+    ref = (y[:, :ff] / (1 + np.exp(-y[:, :ff]))) * y[:, ff:]
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=1e-2, atol=1e-2 * np.abs(ref).max())
+
+
+def test_gemm_tcgen05_refuses_what_tma_cannot_address():
+    ops = _ops()
+    x, _ = _rand((4, 100), torch.bfloat16, 7)          # K = 100 is no multiple of 8
+    w, _ = _rand((16, 100), torch.bfloat16, 8)
+    assert not ops.gemm_tc_supported(x, w)
+    with pytest.raises(ops.KernelError, match="TMA rules"):
+        ops.gemm_tc(x, w)
+    out = ops.linear(x, w)                               # the dispatcher takes the CUDA-core kernel instead
+    ref = x.float() @ w.float().T
+    assert torch.allclose(out[0], ref, atol=1e-4)
+
+
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("d", [96, 1000, 5120, 13000])
 def test_add_rmsnorm(out_dtype, d):
