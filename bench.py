@@ -234,12 +234,11 @@ def main() -> int:
     # end to end: the same decode through the Python entry point (scheduler, one H2D copy of the
     # step's description from pinned memory, sampling on the device, token ids read back)
     B = args.batch
-    ctx0 = CONTEXT - (W + K) - 1
+    ctx0 = CONTEXT - (W + K) - 24
     prompts = [rng.integers(0, cfg.vocab_size, size=ctx0).tolist() for _ in range(B)]
-    sp = SamplingParams(temperature=0.0, max_tokens=W + K + 1, ignore_eos=True)
-    for p in prompts:
-        llm.add_request(p, sp)
-    while llm.stats.generated_tokens < B:        # prompts, untimed
+    sp = SamplingParams(temperature=0.0, max_tokens=CONTEXT + 32 - ctx0, ignore_eos=True)
+    rids = [llm.add_request(p, sp) for p in prompts]
+    while any(len(llm._live[r].out.token_ids) == 0 for r in rids):      # prompts, untimed
         llm.step()
     for _ in range(W):
         llm.step()
@@ -254,8 +253,8 @@ def main() -> int:
     clocks.active = False
     e2e = {"value": round(B * K / e2e_secs, 2), "unit": "tokens/s", "ms_per_step": round(1000 * e2e_secs / K, 3),
            "h2d_bytes_per_step": (llm.stats.h2d_bytes - h0) // K, "d2h_bytes_per_step": (llm.stats.d2h_bytes - d0) // K}
-    while llm.has_unfinished():
-        llm.step()
+    for r in rids:
+        llm.abort_request(r)
     clocks.close()
 
     achieved = main_pt["bytes_step"] / (main_pt["ms"] / 1000.0) / 1e9

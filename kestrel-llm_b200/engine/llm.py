@@ -94,6 +94,15 @@ class LLM:
         self._live[rid] = _Live(RequestOutput(rid, prompt), params, seed, frozenset(stop))
         return rid
 
+    def abort_request(self, rid: int) -> Optional[RequestOutput]:
+        """Ends a request now, whatever its state; its pages and slot are given back."""
+        lv = self._live.pop(rid, None)
+        if lv is None:
+            return None
+        self.scheduler.finish(rid)
+        lv.out.finish_reason = "abort"
+        return lv.out
+
     def has_unfinished(self) -> bool:
         return bool(self._live)
 
