@@ -1,0 +1,405 @@
+// Causal attention of bfloat16 queries over the paged cache on the tensor cores
+// (mma.sync.m16n8k16, float32 softmax statistics and accumulators), for prompt portions and
+// for decode tokens, with the key range optionally split over CTAs.
+//
+// Rows of work are (token, query head of one kv group) pairs of one request's tokens in this
+// step, flattened token-major: row r is token r / G, head r % G (G = query heads per kv head),
+// so the G heads that share a kv head read its keys and values once.  A CTA takes a tile of
+// rows of one (request, kv head) and a slice of the key range:
+//   * ROWS mode (tile of 64 rows): each of the 4 warps owns 16 rows and walks all keys of the
+//     slice in tiles of 64 - prompt portions;
+//   * KEYS mode (tile of 16 rows): all warps share the 16 rows, each takes 16 keys of every
+//     64-key tile, and the four running (max, sum, out) states are merged in warp order at
+//     the end - decode tokens, where rows are few and keys many.
+// K and V tiles go from the cache pages (through the block table) to shared memory with
+// cp.async, double buffered; fragments come from ldmatrix.  Key tiles are anchored at
+// multiples of 64 of the absolute position, so the order of sums for a row depends on its
+// position and on the slice length only.  With more than one slice each CTA writes its
+// unnormalised out, max and sum to scratch and attention_merge_kernel combines the slices in
+// ascending order.  Formulas as in attention_plain.cu (reference: st.c:10779-10911,
+// st.c:9762-9859); exp is taken as exp2 of the score scaled by log2(e).
+//
+// Head sizes up to 256 in any multiple of 8; the kernel is instantiated for 32, 64, 128 and 256
+// and a smaller head is padded with zero columns in shared memory.
+#include "common.cuh"
+#include <math.h>
+
+#define AM_THREADS 128
+#define AM_BN 64            // keys per tile
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
+    int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float *c, const uint32_t *a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+struct AttnParams {
+    const __nv_bfloat16 *q;         // [T, nq * hd]
+    const __nv_bfloat16 *k_cache;   // [pages, nkv, page_size, hd]
+    const __nv_bfloat16 *v_cache;
+    __nv_bfloat16 *out;             // [T, nq * hd]
+    float *part_o;                  // [T * nq, slices, hd]   (slices > 1)
+    float *part_ml;                 // [T * nq, slices, 2]
+    const int *tile_seq;            // [tiles] request index of the tile
+    const int *tile_row0;           // [tiles] first row (token-major, head-minor) among the request's rows
+    const int *cu_seqlens;          // [nseq + 1] first token of each request in this step
+    const int *kv_lens;             // [nseq] request length after this step
+    const int *block_table;         // [nseq, table_stride]
+    int table_stride, page_size, nq, nkv, hd, window, slices, slice_len;
+    float scale_log2;
+};
+
+template <int HD, bool KEYS_MODE>
+__global__ void __launch_bounds__(AM_THREADS)
+attention_mma_kernel(const AttnParams p) {
+    constexpr int BM = KEYS_MODE ? 16 : 64;
+    constexpr int LDS = HD + 8;                       // padded row, in elements: ldmatrix without bank conflicts
+    constexpr int KS = HD / 16;                       // k-steps of the QK product
+    constexpr int NT_S = KEYS_MODE ? 2 : 8;           // 8-key tiles of a warp's score block
+    constexpr int NT_O = HD / 8;                      // 8-dim tiles of the output
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(smem_raw);
+    __nv_bfloat16 *Ks = Qs + BM * LDS;                // [2][AM_BN][LDS]
+    __nv_bfloat16 *Vs = Ks + 2 * AM_BN * LDS;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, kvh = blockIdx.y, slice = blockIdx.z;
+    const int seq = p.tile_seq[tile], row0 = p.tile_row0[tile];
+    const int G = p.nq / p.nkv, hd = p.hd;
+    const int tok_begin = p.cu_seqlens[seq], n_tok = p.cu_seqlens[seq + 1] - tok_begin;
+    const int kv_len = p.kv_lens[seq];
+    const int pos_begin = kv_len - n_tok;             // position of the request's first token of this step
+    const int n_rows = n_tok * G;
+    const int rows_here = min(BM, n_rows - row0);
+    const int *table = p.block_table + (size_t)seq * p.table_stride;
+
+    // key range of this CTA: what its rows may see, cut to the slice, on 64-key tile boundaries
+    const int first_tok = row0 / G, last_tok = (row0 + rows_here - 1) / G;
+    int k_hi = pos_begin + last_tok + 1;              // exclusive
+    int k_lo = p.window > 0 ? max(0, pos_begin + first_tok - p.window + 1) : 0;
+    k_lo = max(k_lo, slice * p.slice_len);
+    k_hi = min(k_hi, (slice + 1) * p.slice_len);
+    const int k_first = k_lo;                         // keys before it are never read: their page may be gone
+    k_lo = (k_lo / AM_BN) * AM_BN;
+    const int n_tiles = k_hi > k_lo ? (k_hi - k_lo + AM_BN - 1) / AM_BN : 0;
+
+    // ---- loads -------------------------------------------------------------------------
+    constexpr int CHUNKS = HD / 8;                    // 16-byte chunks of a padded row
+    auto load_kv_tile = [&](int t, int stage) {
+        int kbase = k_lo + t * AM_BN;
+        for (int idx = tid; idx < AM_BN * CHUNKS; idx += AM_THREADS) {
+            int r = idx / CHUNKS, c = idx % CHUNKS;
+            int s = kbase + r;
+            bool valid = s >= k_first && s < k_hi && c * 8 < hd;
+            size_t off = 0;
+            if (valid) {
+                int page = table[s / p.page_size];
+                off = (((size_t)page * p.nkv + kvh) * p.page_size + (s % p.page_size)) * hd + c * 8;
+            }
+            uint32_t dk = (uint32_t)__cvta_generic_to_shared(Ks + ((size_t)stage * AM_BN + r) * LDS + c * 8);
+            uint32_t dv = (uint32_t)__cvta_generic_to_shared(Vs + ((size_t)stage * AM_BN + r) * LDS + c * 8);
+            cp_async16(dk, p.k_cache + off, valid);
+            cp_async16(dv, p.v_cache + off, valid);
+        }
+    };
+    for (int idx = tid; idx < BM * CHUNKS; idx += AM_THREADS) {
+        int r = idx / CHUNKS, c = idx % CHUNKS;
+        bool valid = r < rows_here && c * 8 < hd;
+        size_t off = 0;
+        if (valid) {
+            int row = row0 + r;
+            int tok = tok_begin + row / G, head = kvh * G + row % G;
+            off = ((size_t)tok * p.nq + head) * hd + c * 8;
+        }
+        cp_async16((uint32_t)__cvta_generic_to_shared(Qs + r * LDS + c * 8), p.q + off, valid);
+    }
+    if (n_tiles > 0) load_kv_tile(0, 0);
+    cp_async_commit();
+
+    // ---- per-thread state ----------------------------------------------------------------
+    // a warp's 16 rows: ROWS mode rows 16*warp.., KEYS mode rows 0..15 for every warp
+    const int wrow0 = KEYS_MODE ? 0 : 16 * warp;
+    const int r_lo = wrow0 + (lane >> 2), r_hi = r_lo + 8;     // the two rows this thread holds
+    int pos_r[2], lo_r[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        int r = i ? r_hi : r_lo;
+        bool ok = r < rows_here;
+        int ps = pos_begin + (row0 + r) / G;
+        pos_r[i] = ok ? ps : -1;                               // an absent row sees no key
+        lo_r[i] = p.window > 0 ? max(0, ps - p.window + 1) : 0;
+    }
+    float o[NT_O][4];
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
+    const bool warp_active = KEYS_MODE ? true : (wrow0 < rows_here);
+
+    for (int t = 0; t < n_tiles; ++t) {
+        int stage = t & 1;
+        if (t + 1 < n_tiles) load_kv_tile(t + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (warp_active) {
+            const int kbase = k_lo + t * AM_BN + (KEYS_MODE ? 16 * warp : 0);
+            const __nv_bfloat16 *Kt = Ks + ((size_t)stage * AM_BN + (KEYS_MODE ? 16 * warp : 0)) * LDS;
+            const __nv_bfloat16 *Vt = Vs + ((size_t)stage * AM_BN + (KEYS_MODE ? 16 * warp : 0)) * LDS;
+            if (kbase < k_hi) {
+                float s[NT_S][4];
+#pragma unroll
+                for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    uint32_t a[4];
+                    // A fragment of Q: rows wrow0 + (lane % 16), columns 16 ks + 8 (lane / 16)
+                    ldmatrix_x4((uint32_t)__cvta_generic_to_shared(Qs + (wrow0 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8),
+                                a[0], a[1], a[2], a[3]);
+#pragma unroll
+                    for (int np = 0; np < NT_S / 2; ++np) {
+                        uint32_t b0, b1, b2, b3;
+                        // keys 16 np + (lane % 8) + 8 (lane / 16), dims 16 ks + 8 ((lane / 8) % 2)
+                        ldmatrix_x4((uint32_t)__cvta_generic_to_shared(Kt + (np * 16 + (lane & 7) + ((lane >> 4) << 3)) * LDS + ks * 16 + ((lane >> 3) & 1) * 8),
+                                    b0, b1, b2, b3);
+                        mma_bf16(s[2 * np], a, b0, b1);
+                        mma_bf16(s[2 * np + 1], a, b2, b3);
+                    }
+                }
+                // scale, mask, running maximum
+                float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        int i = e >> 1;
+                        int key = kbase + nt * 8 + 2 * (lane & 3) + (e & 1);
+                        float v = s[nt][e] * p.scale_log2;
+                        bool ok = key <= pos_r[i] && key >= lo_r[i] && key < k_hi && key >= k_first;
+                        v = ok ? v : -INFINITY;
+                        s[nt][e] = v;
+                        mx[i] = fmaxf(mx[i], v);
+                    }
+                float alpha[2], m_use[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                    float mn = fmaxf(m_r[i], mx[i]);
+                    m_use[i] = mn == -INFINITY ? 0.f : mn;                 // a row that has seen no key yet
+                    alpha[i] = exp2f(m_r[i] - m_use[i]);                   // exp2(-inf) = 0 on the first keys
+                    m_r[i] = mn;
+                    l_r[i] *= alpha[i];
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt) {
+                    o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
+                    o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float pv = exp2f(s[nt][e] - m_use[e >> 1]);
+                        s[nt][e] = pv;
+                        l_r[e >> 1] += pv;
+                    }
+                // out += P V
+#pragma unroll
+                for (int kk = 0; kk < NT_S / 2; ++kk) {
+                    uint32_t a[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                                     pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+                    for (int dp = 0; dp < NT_O / 2; ++dp) {
+                        uint32_t b0, b1, b2, b3;
+                        // keys 16 kk + (lane % 8) + 8 ((lane / 8) % 2), dims 16 dp + 8 (lane / 16), transposed
+                        ldmatrix_x4_trans((uint32_t)__cvta_generic_to_shared(Vt + (kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * LDS + dp * 16 + (lane >> 4) * 8),
+                                          b0, b1, b2, b3);
+                        mma_bf16(o[2 * dp], a, b0, b1);
+                        mma_bf16(o[2 * dp + 1], a, b2, b3);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+    // row sums across the four threads of a row
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_r[i] += __shfl_xor_sync(0xffffffffu, l_r[i], 1);
+        l_r[i] += __shfl_xor_sync(0xffffffffu, l_r[i], 2);
+    }
+
+    if (KEYS_MODE) {
+        // merge the four warps' states in warp order through shared memory (reuses the K stages)
+        __syncthreads();
+        float *mo = reinterpret_cast<float *>(Ks);                 // [4][16][HD]
+        float *mml = mo + 4 * 16 * HD;                             // [4][16][2]
+#pragma unroll
+        for (int nt = 0; nt < NT_O; ++nt) {
+            int d = nt * 8 + 2 * (lane & 3);
+            *reinterpret_cast<float2 *>(mo + ((size_t)warp * 16 + (lane >> 2)) * HD + d) = make_float2(o[nt][0], o[nt][1]);
+            *reinterpret_cast<float2 *>(mo + ((size_t)warp * 16 + (lane >> 2) + 8) * HD + d) = make_float2(o[nt][2], o[nt][3]);
+        }
+        if ((lane & 3) == 0) {
+            mml[(warp * 16 + (lane >> 2)) * 2] = m_r[0];
+            mml[(warp * 16 + (lane >> 2)) * 2 + 1] = l_r[0];
+            mml[(warp * 16 + (lane >> 2) + 8) * 2] = m_r[1];
+            mml[(warp * 16 + (lane >> 2) + 8) * 2 + 1] = l_r[1];
+        }
+        __syncthreads();
+        // thread -> (row, 8-dim group): 16 rows x HD/8 groups
+        for (int idx = tid; idx < 16 * (HD / 8); idx += AM_THREADS) {
+            int r = idx / (HD / 8), d0 = (idx % (HD / 8)) * 8;
+            if (r >= rows_here) continue;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + r) * 2]);
+            float L = 0.f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                float mw = mml[(w * 16 + r) * 2];
+                if (mw == -INFINITY) continue;
+                float f = exp2f(mw - M);
+                L += mml[(w * 16 + r) * 2 + 1] * f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += mo[((size_t)w * 16 + r) * HD + d0 + j] * f;
+            }
+            int row = row0 + r;
+            int tok = tok_begin + row / G, head = kvh * G + row % G;
+            size_t qrow = (size_t)tok * p.nq + head;
+            if (p.slices > 1) {
+                float *po = p.part_o + (qrow * p.slices + slice) * hd;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (d0 + j < hd) po[d0 + j] = acc[j];
+                if (d0 == 0) { p.part_ml[(qrow * p.slices + slice) * 2] = M; p.part_ml[(qrow * p.slices + slice) * 2 + 1] = L; }
+            } else {
+                float inv = 1.0f / L;
+                __nv_bfloat16 *po = p.out + qrow * hd;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (d0 + j < hd) po[d0 + j] = __float2bfloat16_rn(acc[j] * inv);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            int r = i ? r_hi : r_lo;
+            if (r >= rows_here) continue;
+            int row = row0 + r;
+            int tok = tok_begin + row / G, head = kvh * G + row % G;
+            size_t qrow = (size_t)tok * p.nq + head;
+            if (p.slices > 1) {
+                float *po = p.part_o + (qrow * p.slices + slice) * hd;
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt) {
+                    int d = nt * 8 + 2 * (lane & 3);
+                    if (d < hd) { po[d] = o[nt][2 * i]; po[d + 1] = o[nt][2 * i + 1]; }
+                }
+                if ((lane & 3) == 0) { p.part_ml[(qrow * p.slices + slice) * 2] = m_r[i]; p.part_ml[(qrow * p.slices + slice) * 2 + 1] = l_r[i]; }
+            } else {
+                float inv = 1.0f / l_r[i];
+                __nv_bfloat16 *po = p.out + qrow * hd;
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt) {
+                    int d = nt * 8 + 2 * (lane & 3);
+                    if (d < hd) *reinterpret_cast<__nv_bfloat162 *>(po + d) = __floats2bfloat162_rn(o[nt][2 * i] * inv, o[nt][2 * i + 1] * inv);
+                }
+            }
+        }
+    }
+}
+
+// out[row] = sum over slices of part_o * 2^(m - M) / sum of l * 2^(m - M), slices in ascending order
+__global__ void attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
+                                       __nv_bfloat16 *__restrict__ out, int slices, int hd) {
+    size_t qrow = blockIdx.x;
+    const float *ml = part_ml + qrow * slices * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < slices; ++s) M = fmaxf(M, ml[2 * s]);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float L = 0.f, acc = 0.f;
+        for (int s = 0; s < slices; ++s) {
+            float ms = ml[2 * s];
+            if (ms == -INFINITY) continue;
+            float f = exp2f(ms - M);
+            L += ml[2 * s + 1] * f;
+            acc += part_o[(qrow * slices + s) * hd + d] * f;
+        }
+        out[qrow * hd + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
+template <int HD, bool KEYS_MODE>
+static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream) {
+    constexpr int BM = KEYS_MODE ? 16 : 64;
+    constexpr int LDS = HD + 8;
+    size_t smem = (size_t)(BM + 4 * AM_BN) * LDS * 2;
+    size_t merge = KEYS_MODE ? (size_t)(4 * 16 * HD + 4 * 16 * 2) * 4 + (size_t)BM * LDS * 2 : 0;
+    if (merge > smem) smem = merge;
+    static bool attr_set = false;
+    if (!attr_set && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, KEYS_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return kestrel_fail(-3, "attention_mma: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    dim3 grid(tiles, p.nkv, p.slices);
+    attention_mma_kernel<HD, KEYS_MODE><<<grid, AM_THREADS, smem, stream>>>(p);
+    return kestrel_check_launch("attention_mma");
+}
+
+// rows_per_tile must be 16 (KEYS mode) or 64 (ROWS mode); tile_seq / tile_row0 describe the
+// tiles.  part_o / part_ml are scratch for slices > 1: float32 [T * nq * slices * hd] and
+// [T * nq * slices * 2].
+KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const void *v_cache, void *out,
+                                      float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
+                                      int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens,
+                                      const int *block_table, int table_stride, int page_size, int T, int nq,
+                                      int nkv, int hd, int window, int slices, int slice_len, float scale,
+                                      cudaStream_t stream) {
+    if (T == 0 || tiles == 0) return 0;
+    KESTREL_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_mma: %d query heads over %d kv heads", nq, nkv);
+    KESTREL_REQUIRE(hd > 0 && hd % 8 == 0 && hd <= 256, "attention_mma: head size %d is not a multiple of 8 up to 256", hd);
+    KESTREL_REQUIRE(rows_per_tile == 16 || rows_per_tile == 64, "attention_mma: tiles of %d rows", rows_per_tile);
+    KESTREL_REQUIRE(slices >= 1 && slice_len > 0 && slice_len % AM_BN == 0, "attention_mma: slice length %d must be a positive multiple of %d", slice_len, AM_BN);
+    KESTREL_REQUIRE(slices == 1 || (part_o && part_ml), "attention_mma: %d slices without scratch", slices);
+    KESTREL_REQUIRE(nkv <= 65535 && slices <= 65535, "attention_mma: grid too large");
+    AttnParams p;
+    p.q = (const __nv_bfloat16 *)q; p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
+    p.out = (__nv_bfloat16 *)out; p.part_o = part_o; p.part_ml = part_ml; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
+    p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.block_table = block_table; p.table_stride = table_stride;
+    p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = slices; p.slice_len = slice_len;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    bool keys = rows_per_tile == 16;
+    int rc;
+    if (hd <= 32) rc = keys ? launch_attention<32, true>(p, tiles, stream) : launch_attention<32, false>(p, tiles, stream);
+    else if (hd <= 64) rc = keys ? launch_attention<64, true>(p, tiles, stream) : launch_attention<64, false>(p, tiles, stream);
+    else if (hd <= 128) rc = keys ? launch_attention<128, true>(p, tiles, stream) : launch_attention<128, false>(p, tiles, stream);
+    else rc = keys ? launch_attention<256, true>(p, tiles, stream) : launch_attention<256, false>(p, tiles, stream);
+    if (rc) return rc;
+    if (slices > 1) {
+        attention_merge_kernel<<<(unsigned)((size_t)T * nq), hd >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (__nv_bfloat16 *)out, slices, hd);
+        return kestrel_check_launch("attention_merge");
+    }
+    return 0;
+}

@@ -65,6 +65,8 @@ def _declare(lib) -> None:
         "kestrel_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _ll, _vp],
         "kestrel_gemm_tc_swiglu": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
         "kestrel_gemm_tc_error": [],
+        "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                                  _i, _i, _i, _i, _f, _vp],
         "kestrel_argmax": [_vp, _ll, _i, _i, _vp, _vp],
         "kestrel_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     }
@@ -359,9 +361,66 @@ def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int) -> torch.T
     return out
 
 
+def attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                  tile_seq: torch.Tensor, tile_row0: torch.Tensor, rows_per_tile: int, cu_seqlens: torch.Tensor,
+                  kv_lens: torch.Tensor, block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int,
+                  window: int, scale: float, slices: int = 1, slice_len: int = 1 << 30) -> None:
+    """Tensor-core attention (mma.sync) of the tiles listed in tile_seq / tile_row0; rows of
+    other requests in ``out`` are left alone.  With ``slices`` > 1 the key range is cut into
+    slices of ``slice_len`` keys (a multiple of 64) that are merged in ascending order."""
+    _need(q, "attention_mma.q", torch.bfloat16, 2)
+    _need(out, "attention_mma.out", torch.bfloat16, 2)
+    _need(k_cache, "attention_mma.k_cache", torch.bfloat16)
+    _need(v_cache, "attention_mma.v_cache", torch.bfloat16)
+    _need(block_table, "attention_mma.block_table", torch.int32, 2)
+    _need(tile_seq, "attention_mma.tile_seq", torch.int32, 1)
+    _need(tile_row0, "attention_mma.tile_row0", torch.int32, 1)
+    T = q.shape[0]
+    tiles = tile_seq.shape[0]
+    if q.shape[1] != nq * hd or out.shape != q.shape or tile_row0.shape[0] != tiles:
+        raise KernelError("attention_mma: shapes differ")
+    part_o = part_ml = None
+    if slices > 1:
+        part_o = torch.empty((T * nq, slices, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((T * nq, slices, 2), dtype=torch.float32, device=q.device)
+    slice_len = min(int(slice_len), 1 << 30)
+    _check(library().kestrel_attention_mma(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
+        tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, rows_per_tile, cu_seqlens.data_ptr(), kv_lens.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), int(page_size), T, nq, nkv, hd, int(window), int(slices),
+        slice_len, float(scale), _stream()))
+    if slices > 1:
+        global launches
+        launches += 1          # the merge kernel
+
+
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch, block_table: torch.Tensor,
               page_size: int, out: torch.Tensor, nq: int, nkv: int, hd: int, window: int, scale: float) -> None:
     """Causal attention of this step's queries over their requests' cache pages.  ``batch``
-    gives positions, seq_of_token and the per-request lengths."""
-    attention_plain(q, k_cache, v_cache, batch.positions, batch.seq_of_token, block_table, page_size,
-                    out, nq, nkv, hd, window, scale)
+    gives positions, seq_of_token, per-request lengths and the tiling of rows.
+
+    float32 takes the plain kernel (one block per token and head, order of sums fixed per
+    token).  bfloat16 takes the tensor-core kernel: requests with at most 16 (token, head) rows
+    per kv head - decode tokens - in KEYS mode with the key range cut into slices so that the
+    grid fills the GPU, the others - prompt portions - in ROWS mode."""
+    if q.dtype != torch.bfloat16 or hd % 8 or hd > 256:
+        attention_plain(q, k_cache, v_cache, batch.positions, batch.seq_of_token, block_table, page_size,
+                        out, nq, nkv, hd, window, scale)
+        return
+    plan = batch.attention_plan(nq // nkv)
+    no_split = (1 << 30) // 64 * 64
+    if plan.small is not None:
+        seq_t, row_t, n_tiles, max_kv = plan.small
+        slices, slice_len = 1, no_split
+        if window <= 0:         # a window is short; only full-length key ranges are cut into slices
+            want = -(-296 // max(1, n_tiles * nkv))                   # CTAs for two per SM
+            slices = max(1, min(want, -(-max_kv // 256)))             # at least 256 keys a slice
+            if slices > 1:
+                slice_len = -(-(-(-max_kv // slices)) // 64) * 64
+                slices = -(-max_kv // slice_len)
+        attention_mma(q, k_cache, v_cache, out, seq_t, row_t, 16, batch.cu_seqlens, batch.kv_lens, block_table,
+                      page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split)
+    if plan.large is not None:
+        seq_t, row_t, n_tiles, max_kv = plan.large
+        attention_mma(q, k_cache, v_cache, out, seq_t, row_t, 64, batch.cu_seqlens, batch.kv_lens, block_table,
+                      page_size, nq, nkv, hd, window, scale, 1, no_split)

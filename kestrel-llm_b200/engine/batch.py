@@ -23,6 +23,14 @@ class Entry:
     want: Sequence[int] = ()
 
 
+@dataclass
+class AttentionPlan:
+    """Tiles of the tensor-core attention kernel: (tile_seq, tile_row0, number of tiles, longest
+    request) for requests with few rows and for the others; None where there are none."""
+    small: Optional[tuple]
+    large: Optional[tuple]
+
+
 class StepBatch:
     def __init__(self, entries: Sequence[Entry], cache, device, table_width: Optional[int] = None):
         """``cache`` is the `CacheManager`; pages for every entry must be reserved already."""
@@ -98,6 +106,40 @@ class StepBatch:
         self.max_count = max(counts) if counts else 0
         self.max_kv_len = max(self.kv_lens_host) if counts else 0
         self.bytes_h2d = int(host.nbytes)
+        self._plans = {}
+
+    def attention_plan(self, group_size: int) -> "AttentionPlan":
+        """How the tensor-core attention kernel tiles this step's rows for mixers with
+        ``group_size`` query heads per kv head: requests with at most 16 rows (token, head) go
+        into tiles of 16 rows, the others into tiles of 64.  Built once per step and group
+        size; the tile lists are a second, small copy to the device."""
+        plan = self._plans.get(group_size)
+        if plan is None:
+            small_s, small_r, large_s, large_r = [], [], [], []
+            small_kv = large_kv = 0
+            for i, c in enumerate(self.counts):
+                rows = c * group_size
+                if rows <= 16:
+                    small_s.append(i)
+                    small_r.append(0)
+                    small_kv = max(small_kv, self.kv_lens_host[i])
+                else:
+                    for r0 in range(0, rows, 64):
+                        large_s.append(i)
+                        large_r.append(r0)
+                    large_kv = max(large_kv, self.kv_lens_host[i])
+            flat = np.asarray(small_s + small_r + large_s + large_r, dtype=np.int32)
+            dev = torch.from_numpy(flat)
+            if self.device_buffer.is_cuda:
+                dev = dev.pin_memory()
+            dev = dev.to(self.device_buffer.device, non_blocking=True)
+            ns, nl = len(small_s), len(large_s)
+            self.bytes_h2d += int(flat.nbytes)
+            plan = AttentionPlan(
+                (dev[:ns], dev[ns:2 * ns], ns, small_kv) if ns else None,
+                (dev[2 * ns:2 * ns + nl], dev[2 * ns + nl:], nl, large_kv) if nl else None)
+            self._plans[group_size] = plan
+        return plan
 
     def block_table(self, group: int) -> torch.Tensor:
         return self._tables[group]

@@ -212,6 +212,139 @@ def test_attention_plain(dtype, nq, nkv, hd, window, page):
                                atol=tol * np.abs(ref).max())
 
 
+def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slices, slice_len, seed=0):
+    """Several requests in one launch of the tensor-core kernel: request i holds lens_ctx[i]
+    earlier tokens in its pages and lens_new[i] new ones whose queries run now."""
+    ops = _ops()
+    rng = np.random.default_rng(seed)
+    G = nq // nkv
+
+    def r16(a):
+        return torch.from_numpy(a.astype(np.float32)).to(torch.bfloat16).float().numpy()
+    nseq = len(lens_new)
+    total = [c + n for c, n in zip(lens_ctx, lens_new)]
+    num_pages = sum((t + page - 1) // page for t in total) + 3
+    perm = rng.permutation(num_pages)
+    kc = np.full((num_pages, nkv, page, hd), 1e4, dtype=np.float32)
+    vc = np.full((num_pages, nkv, page, hd), -1e4, dtype=np.float32)
+    width = max((t + page - 1) // page for t in total)
+    table = np.full((nseq, width), -1, dtype=np.int32)
+    qs, refs, used = [], [], 0
+    for i in range(nseq):
+        L = total[i]
+        q = r16(rng.normal(size=(L, nq, hd)))
+        k = r16(rng.normal(size=(L, nkv, hd)))
+        v = r16(rng.normal(size=(L, nkv, hd)))
+        nb = (L + page - 1) // page
+        table[i, :nb] = perm[used:used + nb]
+        used += nb
+        for s_ in range(L):
+            kc[table[i, s_ // page], :, s_ % page] = k[s_]
+            vc[table[i, s_ // page], :, s_ % page] = v[s_]
+        refs.append(P.causal_attention(q, k, v, window)[lens_ctx[i]:])
+        qs.append(q[lens_ctx[i]:])
+    qcat = np.concatenate(qs).reshape(-1, nq * hd)
+    T = qcat.shape[0]
+    cu = np.concatenate([[0], np.cumsum(lens_new)]).astype(np.int32)
+    tile_seq, tile_row0 = [], []
+    for i in range(nseq):
+        for r0 in range(0, lens_new[i] * G, rows_per_tile):
+            tile_seq.append(i)
+            tile_row0.append(r0)
+    dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+    out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attention_mma(torch.from_numpy(qcat).to(torch.bfloat16).to(DEV), torch.from_numpy(kc).to(torch.bfloat16).to(DEV),
+                      torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out, dev(tile_seq), dev(tile_row0), rows_per_tile,
+                      dev(cu), dev(total), dev(table), page, nq, nkv, hd, window, 1.0 / math.sqrt(hd), slices, slice_len)
+    ref = np.concatenate(refs).reshape(T, nq * hd)
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    np.testing.assert_allclose(got, ref, rtol=0, atol=1e-2 * np.abs(ref).max())
+
+
+@pytest.mark.parametrize("nq,nkv,hd,window,page", [(6, 2, 32, 0, 16), (5, 5, 48, 40, 16), (8, 1, 128, 0, 4),
+                                                   (3, 3, 80, 7, 16), (4, 2, 16, 0, 1), (2, 1, 256, 100, 32),
+                                                   (32, 8, 128, 0, 16), (40, 2, 64, 0, 16)])
+def test_attention_mma_prompt_portions(nq, nkv, hd, window, page):
+    """ROWS mode: portions of three requests, one of them from position 0, one deep into its context."""
+    _mma_case(nq, nkv, hd, window, page, lens_new=(50, 3, 130), lens_ctx=(100, 0, 77), rows_per_tile=64,
+              slices=1, slice_len=(1 << 30) // 64 * 64, seed=hd)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,window,page,slices,slice_len", [
+    (6, 2, 32, 0, 16, 1, 1 << 24), (32, 8, 128, 0, 16, 4, 128), (32, 8, 128, 0, 16, 3, 192), (5, 5, 48, 40, 16, 1, 1 << 24),
+    (8, 1, 128, 0, 4, 7, 64), (3, 3, 80, 0, 16, 2, 256), (16, 1, 64, 0, 16, 5, 64), (2, 1, 256, 0, 32, 2, 192)])
+def test_attention_mma_decode_tokens(nq, nkv, hd, window, page, slices, slice_len):
+    """KEYS mode: one new token for each of five requests of very different lengths, the key
+    range cut into slices; requests shorter than a slice leave later slices empty."""
+    _mma_case(nq, nkv, hd, window, page, lens_new=(1, 1, 1, 1, 1), lens_ctx=(0, 15, 64, 200, 330), rows_per_tile=16,
+              slices=slices, slice_len=slice_len, seed=hd + 1)
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 255, 256, 299])
+@pytest.mark.parametrize("mode", ["decode", "decode-sliced", "portion"])
+def test_attention_mma_finds_one_far_key(far, mode):
+    """One key among 300 matches the query strongly; the output must be that key's value."""
+    ops = _ops()
+    L, nq, nkv, hd, page = 300, 4, 2, 64, 16
+    rng = np.random.default_rng(far)
+    k = rng.normal(size=(L, nkv, hd)).astype(np.float32) * 0.1
+    v = rng.normal(size=(L, nkv, hd)).astype(np.float32)
+    k[far] = 4.0
+    n_new = 1 if mode != "portion" else 40
+    q = np.full((n_new, nq, hd), 4.0, dtype=np.float32)
+    kc, vc, pages = _paged(k, v, page, 40, 2)
+    if far >= L - n_new + 1 and mode == "portion":
+        pytest.skip("the key lies inside the portion: earlier queries do not see it")
+    G = nq // nkv
+    rpt = 16 if mode != "portion" else 64
+    tiles = list(range(0, n_new * G, rpt))
+    dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+    out = torch.empty((n_new, nq * hd), dtype=torch.bfloat16, device=DEV)
+    slices, slice_len = (5, 64) if mode == "decode-sliced" else (1, 1 << 24)
+    ops.attention_mma(torch.from_numpy(q.reshape(n_new, -1)).to(torch.bfloat16).to(DEV),
+                      torch.from_numpy(kc).to(torch.bfloat16).to(DEV), torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out,
+                      dev([0] * len(tiles)), dev(tiles), rpt, dev([0, n_new]), dev([L]), dev(pages[None, :]), page,
+                      nq, nkv, hd, 0, 1.0 / math.sqrt(hd), slices, slice_len)
+    got = out.float().cpu().numpy().reshape(n_new, nq, hd)
+    want = np.stack([v[far, (h * nkv) // nq] for h in range(nq)])
+    want = torch.from_numpy(want).to(torch.bfloat16).float().numpy()
+    for t in range(n_new):
+        np.testing.assert_allclose(got[t], want, atol=2e-2)
+
+
+def test_attention_mma_window_edge():
+    ops = _ops()
+    L, nq, nkv, hd, page, window = 200, 2, 2, 32, 16, 48
+    for offset, inside in ((window - 1, True), (window, False)):
+        rng = np.random.default_rng(5)
+        k = rng.normal(size=(L, nkv, hd)).astype(np.float32) * 0.1
+        v = rng.normal(size=(L, nkv, hd)).astype(np.float32)
+        q = np.full((1, nq, hd), 4.0, dtype=np.float32)
+        spot = L - 1 - offset
+        k[spot] = 4.0
+        kc, vc, pages = _paged(k, v, page, 40, 3)
+        pages = pages.copy()
+        pages[: (L - window) // page] = -1            # pages behind the window were given back
+        dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+        out = torch.empty((1, nq * hd), dtype=torch.bfloat16, device=DEV)
+        ops.attention_mma(torch.from_numpy(q.reshape(1, -1)).to(torch.bfloat16).to(DEV),
+                          torch.from_numpy(kc).to(torch.bfloat16).to(DEV), torch.from_numpy(vc).to(torch.bfloat16).to(DEV),
+                          out, dev([0]), dev([0]), 16, dev([0, 1]), dev([L]), dev(pages[None, :]), page, nq, nkv, hd,
+                          window, 1.0 / math.sqrt(hd))
+        got = out.float().cpu().numpy().reshape(nq, hd)
+        close = np.abs(got - v[spot]).max() < 3e-2
+        assert close == inside, f"key at distance {offset} (window {window}): inside={inside}, output follows it={close}"
+
+
+def test_attention_mma_refuses_odd_head_sizes():
+    ops = _ops()
+    z = torch.zeros((1, 12), dtype=torch.bfloat16, device=DEV)
+    i = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.attention_mma(z, z, z, torch.empty_like(z), i[:1], i[:1], 16, i, i[:1], i[None, :1], 4, 1, 1, 12, 0, 1.0)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("far", [0, 15, 16, 255, 256, 299])
 def test_attention_finds_one_far_key(dtype, far):
