@@ -228,13 +228,16 @@ class CacheManager(PageTable):
         super().__init__(windows, [num_pages] * len(windows), page_size, max_requests, max_blocks)
         self.groups = [GroupInfo(w, num_pages, tuple(m)) for w, m in zip(windows, members)]
         self.specs = list(specs)
+        self.null_page = num_pages
         self.dtype, self.device = dtype, torch.device(device)
         self.k: List[Optional[torch.Tensor]] = []
         self.v: List[Optional[torch.Tensor]] = []
         self.state: List[Optional[torch.Tensor]] = []
         for sp in specs:
             if isinstance(sp, PagedKVSpec):
-                shape = (num_pages, sp.kv_heads, page_size, sp.head_dim)
+                # one page more than the manager hands out: the "null page", where padding tokens
+                # of a captured step write their keys and values
+                shape = (num_pages + 1, sp.kv_heads, page_size, sp.head_dim)
                 self.k.append(torch.zeros(shape, dtype=dtype, device=device))
                 self.v.append(torch.zeros(shape, dtype=dtype, device=device))
                 self.state.append(None)

@@ -65,6 +65,7 @@ struct AttnParams {
     const int *cu_seqlens;          // [nseq + 1] first token of each request in this step
     const int *kv_lens;             // [nseq] request length after this step
     const int *block_table;         // [nseq, table_stride]
+    const int *slice_len_ptr;       // if not null, the slice length is read from here (a step of a captured graph)
     int table_stride, page_size, nq, nkv, hd, window, slices, slice_len;
     float scale_log2;
 };
@@ -92,13 +93,14 @@ attention_mma_kernel(const AttnParams p) {
     const int n_rows = n_tok * G;
     const int rows_here = min(BM, n_rows - row0);
     const int *table = p.block_table + (size_t)seq * p.table_stride;
+    const int slice_len = p.slice_len_ptr ? *p.slice_len_ptr : p.slice_len;
 
     // key range of this CTA: what its rows may see, cut to the slice, on 64-key tile boundaries
     const int first_tok = row0 / G, last_tok = (row0 + rows_here - 1) / G;
     int k_hi = pos_begin + last_tok + 1;              // exclusive
     int k_lo = p.window > 0 ? max(0, pos_begin + first_tok - p.window + 1) : 0;
-    k_lo = max(k_lo, slice * p.slice_len);
-    k_hi = min(k_hi, (slice + 1) * p.slice_len);
+    k_lo = max(k_lo, slice * slice_len);
+    k_hi = min(k_hi, (slice + 1) * slice_len);
     const int k_first = k_lo;                         // keys before it are never read: their page may be gone
     k_lo = (k_lo / AM_BN) * AM_BN;
     const int n_tiles = k_hi > k_lo ? (k_hi - k_lo + AM_BN - 1) / AM_BN : 0;
@@ -370,13 +372,14 @@ static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream)
 
 // rows_per_tile must be 16 (KEYS mode) or 64 (ROWS mode); tile_seq / tile_row0 describe the
 // tiles.  part_o / part_ml are scratch for slices > 1: float32 [T * nq * slices * hd] and
-// [T * nq * slices * 2].
+// [T * nq * slices * 2].  slice_len_ptr, if given, points to the slice length on the device (a
+// multiple of 64) and overrides slice_len, so that a captured launch can follow the context.
 KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const void *v_cache, void *out,
                                       float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
                                       int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens,
                                       const int *block_table, int table_stride, int page_size, int T, int nq,
-                                      int nkv, int hd, int window, int slices, int slice_len, float scale,
-                                      cudaStream_t stream) {
+                                      int nkv, int hd, int window, int slices, int slice_len, const int *slice_len_ptr,
+                                      float scale, cudaStream_t stream) {
     if (T == 0 || tiles == 0) return 0;
     KESTREL_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_mma: %d query heads over %d kv heads", nq, nkv);
     KESTREL_REQUIRE(hd > 0 && hd % 8 == 0 && hd <= 256, "attention_mma: head size %d is not a multiple of 8 up to 256", hd);
@@ -389,6 +392,7 @@ KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const 
     p.out = (__nv_bfloat16 *)out; p.part_o = part_o; p.part_ml = part_ml; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
     p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.block_table = block_table; p.table_stride = table_stride;
     p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = slices; p.slice_len = slice_len;
+    p.slice_len_ptr = slice_len_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
     bool keys = rows_per_tile == 16;
     int rc;

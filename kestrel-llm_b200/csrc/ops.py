@@ -66,7 +66,7 @@ def _declare(lib) -> None:
         "kestrel_gemm_tc_swiglu": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
         "kestrel_gemm_tc_error": [],
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                                  _i, _i, _i, _i, _f, _vp],
+                                  _i, _i, _i, _i, _vp, _f, _vp],
         "kestrel_argmax": [_vp, _ll, _i, _i, _vp, _vp],
         "kestrel_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     }
@@ -364,10 +364,12 @@ def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int) -> torch.T
 def attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                   tile_seq: torch.Tensor, tile_row0: torch.Tensor, rows_per_tile: int, cu_seqlens: torch.Tensor,
                   kv_lens: torch.Tensor, block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int,
-                  window: int, scale: float, slices: int = 1, slice_len: int = 1 << 30) -> None:
+                  window: int, scale: float, slices: int = 1, slice_len: int = 1 << 30,
+                  slice_len_dev: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention (mma.sync) of the tiles listed in tile_seq / tile_row0; rows of
     other requests in ``out`` are left alone.  With ``slices`` > 1 the key range is cut into
-    slices of ``slice_len`` keys (a multiple of 64) that are merged in ascending order."""
+    slices of ``slice_len`` keys (a multiple of 64) that are merged in ascending order;
+    ``slices * slice_len`` must reach the longest request, keys beyond it are not seen."""
     _need(q, "attention_mma.q", torch.bfloat16, 2)
     _need(out, "attention_mma.out", torch.bfloat16, 2)
     _need(k_cache, "attention_mma.k_cache", torch.bfloat16)
@@ -388,7 +390,7 @@ def attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
         tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, rows_per_tile, cu_seqlens.data_ptr(), kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), int(page_size), T, nq, nkv, hd, int(window), int(slices),
-        slice_len, float(scale), _stream()))
+        slice_len, _p(slice_len_dev), float(scale), _stream()))
     if slices > 1:
         global launches
         launches += 1          # the merge kernel
@@ -410,17 +412,22 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
     plan = batch.attention_plan(nq // nkv)
     no_split = (1 << 30) // 64 * 64
     if plan.small is not None:
-        seq_t, row_t, n_tiles, max_kv = plan.small
-        slices, slice_len = 1, no_split
+        tl = plan.small
+        slices, slice_len, slice_dev = 1, no_split, None
         if window <= 0:         # a window is short; only full-length key ranges are cut into slices
-            want = -(-296 // max(1, n_tiles * nkv))                   # CTAs for two per SM
-            slices = max(1, min(want, -(-max_kv // 256)))             # at least 256 keys a slice
-            if slices > 1:
-                slice_len = -(-(-(-max_kv // slices)) // 64) * 64
-                slices = -(-max_kv // slice_len)
-        attention_mma(q, k_cache, v_cache, out, seq_t, row_t, 16, batch.cu_seqlens, batch.kv_lens, block_table,
-                      page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split)
+            want = min(32, -(-296 // max(1, tl.count * nkv)))         # CTAs for two per SM
+            if tl.slice_len_table is not None:
+                # a captured step: the number of slices is fixed, their length follows the context
+                slices = want
+                slice_dev = tl.slice_len_table[slices:slices + 1] if slices > 1 else None
+            else:
+                slices = max(1, min(want, -(-tl.max_kv // 256)))      # at least 256 keys a slice
+                if slices > 1:
+                    slice_len = -(-(-(-tl.max_kv // slices)) // 64) * 64
+                    slices = -(-tl.max_kv // slice_len)
+        attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, 16, batch.cu_seqlens, batch.kv_lens, block_table,
+                      page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
     if plan.large is not None:
-        seq_t, row_t, n_tiles, max_kv = plan.large
-        attention_mma(q, k_cache, v_cache, out, seq_t, row_t, 64, batch.cu_seqlens, batch.kv_lens, block_table,
+        tl = plan.large
+        attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, 64, batch.cu_seqlens, batch.kv_lens, block_table,
                       page_size, nq, nkv, hd, window, scale, 1, no_split)

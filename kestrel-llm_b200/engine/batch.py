@@ -24,11 +24,24 @@ class Entry:
 
 
 @dataclass
+class TileList:
+    """Tiles of the tensor-core attention kernel: request and first row of each tile (device
+    int32), their number and the longest request among them.  ``slice_len_table``, set only
+    for a captured decode step, is a device table whose entry s is the slice length to use
+    with s slices."""
+    seq: torch.Tensor
+    row0: torch.Tensor
+    count: int
+    max_kv: int
+    slice_len_table: Optional[torch.Tensor] = None
+
+
+@dataclass
 class AttentionPlan:
-    """Tiles of the tensor-core attention kernel: (tile_seq, tile_row0, number of tiles, longest
-    request) for requests with few rows and for the others; None where there are none."""
-    small: Optional[tuple]
-    large: Optional[tuple]
+    """Tile lists for requests with few rows (at most 16 per kv head: decode tokens) and for
+    the others (prompt portions); None where there are none."""
+    small: Optional[TileList]
+    large: Optional[TileList]
 
 
 class StepBatch:
@@ -136,8 +149,8 @@ class StepBatch:
             ns, nl = len(small_s), len(large_s)
             self.bytes_h2d += int(flat.nbytes)
             plan = AttentionPlan(
-                (dev[:ns], dev[ns:2 * ns], ns, small_kv) if ns else None,
-                (dev[2 * ns:2 * ns + nl], dev[2 * ns + nl:], nl, large_kv) if nl else None)
+                TileList(dev[:ns], dev[ns:2 * ns], ns, small_kv) if ns else None,
+                TileList(dev[2 * ns:2 * ns + nl], dev[2 * ns + nl:], nl, large_kv) if nl else None)
             self._plans[group_size] = plan
         return plan
 

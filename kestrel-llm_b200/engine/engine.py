@@ -42,6 +42,10 @@ class Engine:
         self.cache = CacheManager(model.cache_specs(), model.dtype, dev, page, num_pages,
                                   options.batch_max, self.max_model_len)
         self.vocab_size = model.vocab_size
+        self.graphs = None
+        if options.cuda_graphs and getattr(model, "graph_safe", False):
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(model, self.cache, options.batch_max)
         self.steps_run = 0
         self.graph_launches = 0      # kernels replayed from CUDA graphs (not counted by ops.launches)
 
@@ -90,8 +94,16 @@ class Engine:
             for rid in admitted:
                 self.cache.release(rid)
             raise
-        batch = StepBatch(entries, self.cache, self.model.device)
-        logits = self.model.forward(batch, self.cache)
+        if self.graphs is not None and all(len(e.tokens) == 1 for e in entries):
+            # decode tokens only: replay the captured step of this batch-size bucket
+            logits, batch, replayed = self.graphs.run(entries)
+            self.graph_launches += replayed
+            if any(len(e.want) == 0 for e in entries):
+                keep = [i for i, e in enumerate(entries) if len(e.want)]
+                logits = logits[torch.tensor(keep, dtype=torch.long, device=logits.device)] if keep else None
+        else:
+            batch = StepBatch(entries, self.cache, self.model.device)
+            logits = self.model.forward(batch, self.cache)
         for e in entries:
             self.cache.commit(e.rid, len(e.tokens))
         self.steps_run += 1

@@ -1,0 +1,160 @@
+"""Decode steps as CUDA graphs.
+
+A step in which every request brings one token launches some 330 kernels at Qwen3-8B size,
+each a few microseconds long; launched one by one from the host they take longer to launch
+than to run.  Such a step is therefore captured once per batch-size bucket (1, 2, 4 ... up to
+``batch_max``) and replayed: the host fills ONE pinned int32 buffer (token ids, positions,
+lengths, slots, slice lengths of the attention kernel, block tables), copies it to the
+buffer's fixed device twin, and replays the graph.  Buckets are padded with dummy requests of
+one token at position 0 whose keys and values go to the cache's null page.
+
+The captured kernels are the same ones an uncaptured step launches; nothing is compiled or
+traced.  A model takes part only if all its parts declare ``graph_safe``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Sequence
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+from .batch import AttentionPlan, Entry, TileList
+
+MAX_SLICES = 32
+
+
+class StaticDecodeBatch:
+    """The fixed-address twin of `StepBatch` for ``size`` requests of one token each."""
+
+    def __init__(self, size: int, cache, device):
+        B, W, G = size, cache.max_blocks, cache.num_groups
+        self.size = size
+        self.num_tokens = self.num_seqs = self.num_logit_rows = B
+        self.table_width = W
+        o_tok, o_pos, o_kv, o_slot = 0, B, 2 * B, 3 * B
+        o_misc = 4 * B
+        o_tab = o_misc + MAX_SLICES + 1
+        total = o_tab + G * B * W
+        self._o = (o_tok, o_pos, o_kv, o_slot, o_misc, o_tab)
+        # a ring of pinned buffers: a buffer is rewritten only after the copy that read it is done
+        self._ring = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(3)]
+        self._ring_np = [t.numpy() for t in self._ring]
+        self._ring_done = [None, None, None]
+        self._turn = 0
+        self.dev = torch.zeros(total, dtype=torch.int32, device=device)
+        ar = torch.arange(B + 1, dtype=torch.int32, device=device)
+        self.token_ids = self.dev[o_tok:o_tok + B]
+        self.positions = self.dev[o_pos:o_pos + B]
+        self.kv_lens = self.dev[o_kv:o_kv + B]
+        self.slots = self.dev[o_slot:o_slot + B]
+        self.slice_len_table = self.dev[o_misc:o_misc + MAX_SLICES + 1]
+        self.seq_of_token = ar[:B].contiguous()
+        self.cu_seqlens = ar
+        self.logit_rows = ar[:B].contiguous()
+        self._tile_row0 = torch.zeros(B, dtype=torch.int32, device=device)
+        self._tables = [self.dev[o_tab + g * B * W: o_tab + (g + 1) * B * W].view(B, W) for g in range(G)]
+        self.counts = [1] * B
+        self.cu_seqlens_host = list(range(B + 1))
+        self.slots_host: List[int] = [0] * B
+        self.kv_lens_host: List[int] = [1] * B
+        self.max_count = 1
+        self.null_page = cache.null_page
+        self.bytes_h2d = int(total * 4)
+        self.fill([], cache)
+
+    @property
+    def is_decode_only(self) -> bool:
+        return True
+
+    def block_table(self, group: int) -> torch.Tensor:
+        return self._tables[group]
+
+    def attention_plan(self, group_size: int) -> AttentionPlan:
+        if group_size > 16:
+            raise RuntimeError("a captured decode step needs at most 16 query heads per kv head")
+        return AttentionPlan(TileList(self.seq_of_token, self._tile_row0, self.size, 0, self.slice_len_table), None)
+
+    def fill(self, entries: Sequence[Entry], cache) -> None:
+        """Writes this step's values into the pinned buffer and starts its copy to the device."""
+        o_tok, o_pos, o_kv, o_slot, o_misc, o_tab = self._o
+        B, W, G = self.size, self.table_width, cache.num_groups
+        turn = self._turn
+        self._turn = (turn + 1) % len(self._ring)
+        if self._ring_done[turn] is not None:
+            self._ring_done[turn].synchronize()
+        h = self._ring_np[turn]
+        n = len(entries)
+        max_kv = 1
+        for i, e in enumerate(entries):
+            L = cache.length(e.rid)
+            h[o_tok + i] = int(e.tokens[0])
+            h[o_pos + i] = L
+            h[o_kv + i] = L + 1
+            h[o_slot + i] = cache.slot(e.rid)
+            max_kv = max(max_kv, L + 1)
+            for g in range(G):
+                b = o_tab + (g * B + i) * W
+                cache.block_table_into(e.rid, g, h[b:b + W])
+        if n < B:                       # dummy requests: one token at position 0 on the null page
+            h[o_tok + n:o_tok + B] = 0
+            h[o_pos + n:o_pos + B] = 0
+            h[o_kv + n:o_kv + B] = 1
+            h[o_slot + n:o_slot + B] = 0
+            for g in range(G):
+                for i in range(n, B):
+                    h[o_tab + (g * B + i) * W] = self.null_page
+        for s in range(1, MAX_SLICES + 1):
+            h[o_misc + s] = max(64, -(-(-(-max_kv // s)) // 64) * 64)
+        self.dev.copy_(self._ring[turn], non_blocking=True)
+        ev = self._ring_done[turn] or torch.cuda.Event()
+        ev.record()
+        self._ring_done[turn] = ev
+
+
+class DecodeGraphs:
+    """One captured decode step per bucket size, made at first use."""
+
+    def __init__(self, model, cache, batch_max: int):
+        self.model, self.cache = model, cache
+        self.sizes = []
+        s = 1
+        while s < batch_max:
+            self.sizes.append(s)
+            s *= 2
+        self.sizes.append(batch_max)
+        self._graphs: Dict[int, tuple] = {}
+        self.launches_per_replay: Dict[int, int] = {}
+
+    def bucket(self, n: int) -> int:
+        for s in self.sizes:
+            if n <= s:
+                return s
+        raise ValueError(f"{n} requests exceed the largest bucket {self.sizes[-1]}")
+
+    def _capture(self, size: int):
+        dev = self.model.device
+        batch = StaticDecodeBatch(size, self.cache, dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):               # one uncaptured run: loads modules, sets attributes
+            self.model.forward(batch, self.cache)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launches
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(batch, self.cache)
+        self.launches_per_replay[size] = ops.launches - before
+        self._graphs[size] = (graph, batch, logits)
+        return self._graphs[size]
+
+    def run(self, entries: Sequence[Entry]):
+        """Replays the bucket's graph for these one-token entries; returns (logits of the
+        first len(entries) rows, static batch, kernels replayed)."""
+        size = self.bucket(len(entries))
+        g = self._graphs.get(size) or self._capture(size)
+        graph, batch, logits = g
+        batch.fill(entries, self.cache)
+        graph.replay()
+        return logits[:len(entries)], batch, self.launches_per_replay[size]

@@ -60,6 +60,14 @@ class DecoderModel(Part):
         self._cache_owner = owners
 
     @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step through the whole model can be captured in a CUDA graph."""
+        pos_ok = self.position is None or (getattr(self.position, "graph_safe", False)
+                                           or type(self.position).add_to_embedding is PositionEncoding.add_to_embedding)
+        return (pos_ok and all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+                and self.embedding.graph_safe and self.lm_head.graph_safe)
+
+    @property
     def vocab_size(self) -> int:
         return self.lm_head.vocab
 

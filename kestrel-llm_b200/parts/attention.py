@@ -20,6 +20,8 @@ from .linear import Linear
 
 
 class GroupedQueryAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype,
                  device, prefix: str, position: Optional[PositionEncoding], qk_norm_eps: Optional[float],
                  bias: bool = False, window: int = 0):

@@ -51,7 +51,14 @@ CacheSpec = Union[PagedKVSpec, FixedStateSpec, None]
 
 
 class Part:
-    """Base of all parts: weights by checkpoint name."""
+    """Base of all parts: weights by checkpoint name.
+
+    ``graph_safe`` says that ``forward`` only launches kernels whose arguments are device
+    tensors of the batch (no value of the batch is read on the host), so a decode step through
+    the part can be captured in a CUDA graph and replayed with other contents.  The default is
+    False; the engine captures only if every part of the model says True."""
+
+    graph_safe = False
 
     def weight_slots(self) -> List[WeightSlot]:
         return []
@@ -112,6 +119,14 @@ class Block(Part):
 
     def cache_spec(self) -> CacheSpec:
         return self.mixer.cache_spec()
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in self.parts())
+
+    def parts(self) -> Sequence[Part]:
+        """The parts this block arranges (for checks that concern all of them)."""
+        return [self.mixer]
 
     def forward(self, residual: torch.Tensor, pending, batch, cache):
         raise NotImplementedError

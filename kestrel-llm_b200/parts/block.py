@@ -17,6 +17,9 @@ class PreNormBlock(Block):
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
         self.dtype = dtype
 
+    def parts(self):
+        return [self.norm1, self.mixer, self.norm2, self.ffn]
+
     def weight_slots(self) -> List[WeightSlot]:
         return (self.norm1.weight_slots() + self.mixer.weight_slots() + self.norm2.weight_slots()
                 + self.ffn.weight_slots())

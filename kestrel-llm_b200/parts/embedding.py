@@ -15,6 +15,8 @@ from .base import Part, WeightSlot
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab: int, width: int, dtype: torch.dtype, device, weight_name: str):
         self.vocab, self.width = vocab, width
         self.weight = torch.empty((vocab, width), dtype=dtype, device=device)
@@ -30,6 +32,8 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    graph_safe = True
+
     def __init__(self, vocab: int, width: int, dtype: torch.dtype, device, weight_name: str,
                  tied_to: Optional[TokenEmbedding] = None):
         self.vocab, self.width = vocab, width

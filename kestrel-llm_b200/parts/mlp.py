@@ -13,6 +13,8 @@ from .linear import Linear
 
 
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, width: int, intermediate: int, dtype: torch.dtype, device, prefix: str,
                  activation: str = "silu"):
         if activation != "silu":

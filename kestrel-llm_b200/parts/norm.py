@@ -14,6 +14,8 @@ from .base import Norm, WeightSlot
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, width: int, eps: float, device, weight_name: str):
         self.width = width
         self.eps = float(eps)

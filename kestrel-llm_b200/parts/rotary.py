@@ -17,6 +17,8 @@ from .base import PositionEncoding
 
 
 class RotaryHalf(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, head_dim: int, theta: float, device, rotary_dim: Optional[int] = None):
         rot = head_dim if rotary_dim is None else rotary_dim
         if rot % 2 or rot <= 0 or rot > head_dim:

@@ -24,10 +24,10 @@ def _requests(name, lengths=None):
     return R.random_requests(tiny_configs.CONFIGS[name][0]["vocab_size"], lengths or LENGTHS[name], seed=1 + ord(name))
 
 
-def _run(model_dirs, name, dtype, family, record_property, lengths=None, **kw):
+def _run(model_dirs, name, dtype, family, record_property, lengths=None, graphs=False, **kw):
     reqs = _requests(name, lengths)
     steps, max_tokens = family(reqs, **kw)
-    engine = R.make_engine(model_dirs[name][dtype], dtype, max_tokens)
+    engine = R.make_engine(model_dirs[name][dtype], dtype, max_tokens, graphs=graphs)
     got = R.run_trace(engine, steps)
     assert engine.cache.live_requests() == 0
     engine.cache.check()
@@ -47,6 +47,20 @@ def test_whole_prompts(model_dirs, name, dtype, record_property):
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_last_tokens_one_by_one(model_dirs, name, dtype, record_property):
     _run(model_dirs, name, dtype, R.trace_tail_decode, record_property)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("family", ["tail", "mixed"])
+def test_decode_steps_replayed_from_cuda_graphs(model_dirs, name, dtype, family, record_property):
+    """The same traces with decode-only steps captured once per batch-size bucket and replayed
+    (what generation does); prompt portions and mixed steps still launch kernel by kernel."""
+    if family == "tail":
+        engine = _run(model_dirs, name, dtype, R.trace_tail_decode, record_property, graphs=True)
+    else:
+        engine = _run(model_dirs, name, dtype, R.trace_mixed, record_property, lengths=LENGTHS_MIXED[name], graphs=True,
+                      tail=24)
+    assert engine.graphs is not None and engine.graph_launches > 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
