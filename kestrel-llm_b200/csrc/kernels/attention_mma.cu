@@ -332,14 +332,25 @@ attention_mma_kernel(const AttnParams p) {
     }
 }
 
-// out[row] = sum over slices of part_o * 2^(m - M) / sum of l * 2^(m - M), slices in ascending order
+// out[row] = sum over slices of part_o * 2^(m - M) / sum of l * 2^(m - M), slices in ascending
+// order, for the rows of the listed tiles (16 rows each at most); one block per (tile, kv head)
 __global__ void attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
-                                       __nv_bfloat16 *__restrict__ out, int slices, int hd) {
-    size_t qrow = blockIdx.x;
-    const float *ml = part_ml + qrow * slices * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < slices; ++s) M = fmaxf(M, ml[2 * s]);
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+                                       __nv_bfloat16 *__restrict__ out, const int *__restrict__ tile_seq,
+                                       const int *__restrict__ tile_row0, const int *__restrict__ cu_seqlens,
+                                       int slices, int hd, int nq, int nkv) {
+    int tile = blockIdx.x, kvh = blockIdx.y;
+    int seq = tile_seq[tile], row0 = tile_row0[tile];
+    int G = nq / nkv;
+    int tok_begin = cu_seqlens[seq];
+    int n_rows = (cu_seqlens[seq + 1] - tok_begin) * G;
+    int rows_here = min(16, n_rows - row0);
+    for (int idx = threadIdx.x; idx < rows_here * hd; idx += blockDim.x) {
+        int r = idx / hd, d = idx % hd;
+        int row = row0 + r;
+        size_t qrow = (size_t)(tok_begin + row / G) * nq + kvh * G + row % G;
+        const float *ml = part_ml + qrow * slices * 2;
+        float M = -INFINITY;
+        for (int s = 0; s < slices; ++s) M = fmaxf(M, ml[2 * s]);
         float L = 0.f, acc = 0.f;
         for (int s = 0; s < slices; ++s) {
             float ms = ml[2 * s];
@@ -402,7 +413,9 @@ KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const 
     else rc = keys ? launch_attention<256, true>(p, tiles, stream) : launch_attention<256, false>(p, tiles, stream);
     if (rc) return rc;
     if (slices > 1) {
-        attention_merge_kernel<<<(unsigned)((size_t)T * nq), hd >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (__nv_bfloat16 *)out, slices, hd);
+        KESTREL_REQUIRE(keys, "attention_mma: slices are merged for tiles of 16 rows only");
+        attention_merge_kernel<<<dim3(tiles, nkv), 256, 0, stream>>>(part_o, part_ml, (__nv_bfloat16 *)out, tile_seq, tile_row0,
+                                                                  cu_seqlens, slices, hd, nq, nkv);
         return kestrel_check_launch("attention_merge");
     }
     return 0;

@@ -80,6 +80,93 @@ __global__ void add_rmsnorm_kernel(float *__restrict__ residual, const float *__
     for (int i = threadIdx.x; i < d; i += NORM_THREADS) o[i] = from_f32<TOut>((xs[i] * rinv) * w[i]);
 }
 
+// The same for widths that are a multiple of 4: 1024 threads, float4 accesses, and the loads
+// of the slices issued four at a time (they are independent; the adds stay in ascending s).
+// With few rows in the batch (decode) the kernel is latency-bound, so the work of a row is
+// spread over as many threads as there are vectors.
+#define NORMV_THREADS 1024
+
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ void store4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16 *p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t *>(&lo);
+    u.y = *reinterpret_cast<uint32_t *>(&hi);
+    *reinterpret_cast<uint2 *>(p) = u;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(NORMV_THREADS)
+add_rmsnorm_vec_kernel(float *__restrict__ residual, const float *__restrict__ partial, int S, size_t slice_stride,
+                       const float *__restrict__ bias, const int *__restrict__ rows, const float *__restrict__ w,
+                       float eps, TOut *__restrict__ out, int d, int write_back) {
+    extern __shared__ float xs[];
+    __shared__ float red[NORMV_THREADS / 32];
+    int r = blockIdx.x;
+    int t = rows ? rows[r] : r;
+    int d4 = d >> 2;
+    float4 *res = reinterpret_cast<float4 *>(residual + (size_t)t * d);
+    const float4 *bias4 = reinterpret_cast<const float4 *>(bias);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d4; i += NORMV_THREADS) {
+        float4 x = res[i];
+        if (partial) {
+            const float4 *p4 = reinterpret_cast<const float4 *>(partial + (size_t)t * d) + i;
+            size_t st4 = slice_stride >> 2;
+            float4 delta = make_float4(0.f, 0.f, 0.f, 0.f);
+            int s = 0;
+            for (; s + 4 <= S; s += 4) {
+                float4 a = p4[(size_t)s * st4], b = p4[(size_t)(s + 1) * st4], c = p4[(size_t)(s + 2) * st4], e = p4[(size_t)(s + 3) * st4];
+                delta = add4(add4(add4(add4(delta, a), b), c), e);
+            }
+            for (; s < S; ++s) delta = add4(delta, p4[(size_t)s * st4]);
+            if (bias) delta = add4(delta, bias4[i]);
+            x = add4(x, delta);
+            if (write_back) res[i] = x;
+        }
+        reinterpret_cast<float4 *>(xs)[i] = x;
+        ss += x.x * x.x;
+        ss += x.y * x.y;
+        ss += x.z * x.z;
+        ss += x.w * x.w;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORMV_THREADS / 32; ++k) tot += red[k];
+    float rinv = 1.0f / sqrtf(tot / (float)d + eps);
+    TOut *o = out + (size_t)r * d;
+    const float4 *w4 = reinterpret_cast<const float4 *>(w);
+    for (int i = threadIdx.x; i < d4; i += NORMV_THREADS) {
+        float4 x = reinterpret_cast<float4 *>(xs)[i], g = w4[i];
+        store4(o + 4 * i, make_float4((x.x * rinv) * g.x, (x.y * rinv) * g.y, (x.z * rinv) * g.z, (x.w * rinv) * g.w));
+    }
+}
+
+template <typename TOut>
+static void launch_add_rmsnorm(float *residual, const float *partial, int S, long long slice_stride, const float *bias,
+                               const int *rows, const float *w, float eps, TOut *out, int R, int d, int write_back,
+                               size_t smem, cudaStream_t stream) {
+    // the vector kernel for widths of at least 2048 that are multiples of 4 (and slices and
+    // pointers that keep float4 alignment); which kernel runs depends on the width alone, so a
+    // row's result does not depend on the batch
+    bool vec = d % 4 == 0 && d >= 2048 && slice_stride % 4 == 0 &&
+               ((((uintptr_t)residual | (uintptr_t)partial | (uintptr_t)bias | (uintptr_t)w) & 15) == 0) &&
+               (((uintptr_t)out & 7) == 0);
+    if (vec) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_vec_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_vec_kernel<TOut><<<R, NORMV_THREADS, smem, stream>>>(residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, d, write_back);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<TOut><<<R, NORM_THREADS, smem, stream>>>(residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, d, write_back);
+    }
+}
+
 KESTREL_API int kestrel_add_rmsnorm(float *residual, const float *partial, int S,
                                     long long slice_stride, const float *bias, const int *rows,
                                     const float *w, float eps, void *out, int out_dtype, int R,
@@ -89,19 +176,12 @@ KESTREL_API int kestrel_add_rmsnorm(float *residual, const float *partial, int S
     KESTREL_REQUIRE(!(rows && write_back), "add_rmsnorm: write_back with gathered rows");
     size_t smem = (size_t)d * sizeof(float);
     KESTREL_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: width %d exceeds the 51200 the kernel holds in shared memory", d);
-    if (out_dtype == KESTREL_F32) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<float><<<R, NORM_THREADS, smem, stream>>>(
-            residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, (float *)out, d, write_back);
-    } else if (out_dtype == KESTREL_BF16) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<__nv_bfloat16><<<R, NORM_THREADS, smem, stream>>>(
-            residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, (__nv_bfloat16 *)out, d, write_back);
-    } else {
+    if (out_dtype == KESTREL_F32)
+        launch_add_rmsnorm<float>(residual, partial, S, slice_stride, bias, rows, w, eps, (float *)out, R, d, write_back, smem, stream);
+    else if (out_dtype == KESTREL_BF16)
+        launch_add_rmsnorm<__nv_bfloat16>(residual, partial, S, slice_stride, bias, rows, w, eps, (__nv_bfloat16 *)out, R, d, write_back, smem, stream);
+    else
         return kestrel_fail(-2, "add_rmsnorm: unknown dtype %d", out_dtype);
-    }
     return kestrel_check_launch("add_rmsnorm");
 }
 
@@ -176,15 +256,36 @@ __global__ void attn_prepare_kernel(const float *__restrict__ partial, int S, si
     float x[PREP_MAX_PER_LANE];
     float ss = 0.f;
 #pragma unroll
+    for (int c = 0; c < PREP_MAX_PER_LANE; ++c) x[c] = 0.f;
+    // the loads of a slice's elements are issued together, four slices at a time; the adds
+    // stay in ascending s
+    int s0 = 0;
+    for (; s0 + 4 <= S; s0 += 4) {
+        float v[4][PREP_MAX_PER_LANE];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
+                int i = lane + 32 * c;
+                v[u][c] = i < hd ? row[(size_t)(s0 + u) * slice_stride + i] : 0.f;
+            }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int c = 0; c < PREP_MAX_PER_LANE; ++c) x[c] += v[u][c];
+    }
+    for (; s0 < S; ++s0) {
+#pragma unroll
+        for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
+            int i = lane + 32 * c;
+            if (i < hd) x[c] += row[(size_t)s0 * slice_stride + i];
+        }
+    }
+#pragma unroll
     for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
         int i = lane + 32 * c;
-        float v = 0.f;
-        if (i < hd) {
-            for (int s = 0; s < S; ++s) v += row[(size_t)s * slice_stride + i];
-            if (b) v += b[i];
-        }
-        x[c] = v;
-        ss += v * v;
+        if (b && i < hd) x[c] += b[i];
+        ss += x[c] * x[c];
     }
     const float *nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
     if (nw) {

@@ -291,19 +291,40 @@ KESTREL_API int kestrel_gemm_tc_supported(const void *x, const void *w, int T, i
     return 1;
 }
 
-// Slices a product of T tokens and N output features would be split into, so that the grid
-// covers the GPU's 148 SMs about twice where the K range allows it.
+// Tuning of few-token products (T <= 256), which stream the weights once and are bound by HBM:
+// g_ctas_per_sm CTAs share an SM's shared memory for their stages; a CTA costs about
+// g_overhead_kb k-blocks of time beyond its own k-blocks (launch, barrier set-up, TMEM
+// allocation, first tensor-map fetch, pipeline fill, epilogue).
+static int g_overhead_kb = 6;
+static int g_ctas_per_sm = 1;
+
+KESTREL_API void kestrel_gemm_tc_set_tuning(int overhead_kb, int ctas_per_sm) {
+    if (overhead_kb >= 0) g_overhead_kb = overhead_kb;
+    if (ctas_per_sm == 1 || ctas_per_sm == 2) g_ctas_per_sm = ctas_per_sm;
+}
+
+// Slices into which a product of T tokens and N output features splits its K range: the
+// number that minimises waves x (overhead + k-blocks per slice) over the GPU's 148 SMs.
+// Many-token products are not split.
 KESTREL_API int kestrel_gemm_tc_splits(int T, int N, int K) {
+    if (T > 256) return 1;
     int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
     long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
     int total_kb = (K + TC_BK - 1) / TC_BK;
-    if (tiles >= 296 || T > 256) return 1;
-    int s = (int)((296 + tiles - 1) / tiles);
-    int max_s = total_kb / 8 > 0 ? total_kb / 8 : 1;       // at least 8 k-blocks (512 columns) a slice
-    if (s > max_s) s = max_s;
-    if (s > 16) s = 16;
-    int per = (total_kb + s - 1) / s;
-    return (total_kb + per - 1) / per;                      // no empty slice
+    int slots = 148 * g_ctas_per_sm;
+    int best = 1;
+    long long best_cost = -1;
+    int max_s = total_kb / 4 > 0 ? total_kb / 4 : 1;          // at least 4 k-blocks (256 columns) a slice
+    if (max_s > 16) max_s = 16;
+    for (int s = 1; s <= max_s; ++s) {
+        int per = (total_kb + s - 1) / s;
+        int real = (total_kb + per - 1) / per;                  // no empty slice
+        if (real != s) continue;
+        long long waves = (tiles * s + slots - 1) / slots;
+        long long cost = waves * (g_overhead_kb + per) * g_ctas_per_sm;
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+    }
+    return best;
 }
 
 template <int BN, int MODE>
@@ -313,8 +334,8 @@ static int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, void *out, in
     constexpr int STAGE_BYTES = A_TILES * TC_BM * TC_BK * 2 + BN * TC_BK * 2;
     int total_kb = (K + TC_BK - 1) / TC_BK;
     int per = (total_kb + splits - 1) / splits;
-    // few tokens: two CTAs share an SM, each with about 100 KB of stages; else one CTA takes it all
-    int budget = (BN <= 64 && MODE == TC_PARTIAL) ? 100 * 1024 : 200 * 1024;
+    // few tokens: the CTAs that share an SM divide its shared memory; else one CTA takes it all
+    int budget = (BN <= 64 && MODE == TC_PARTIAL && g_ctas_per_sm == 2) ? 100 * 1024 : 200 * 1024;
     int stages = budget / STAGE_BYTES;
     if (stages > per) stages = per < 2 ? 2 : per;
     if (stages > 12) stages = 12;
@@ -336,7 +357,6 @@ template <int MODE>
 static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, int w_rows, int K, long long ldx, long long ldw,
                        long long ldo, int splits, long long slice_stride, int up_off, cudaStream_t stream) {
     int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
-    if (MODE == TC_SWIGLU && bn == 256) bn = 128;          // two accumulators of 256 columns would not leave room for a second CTA's TMEM
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, w_rows, K, ldw, TC_BM);
     if (rc) return rc;

@@ -77,13 +77,53 @@ argmax_kernel(const float *__restrict__ logits, long long ld, int V, int *__rest
     if (threadIdx.x == 0) out[blockIdx.x] = idx;
 }
 
-KESTREL_API int kestrel_argmax(const float *logits, long long ld, int R, int V, int *out,
+// A large vocabulary in two passes, so that a row is read by many SMs: each block finds the
+// first maximum of a chunk of ARGMAX_CHUNK entries and writes (value, index) to scratch; then
+// one thread per row takes the first maximum over the chunks in ascending order.
+#define ARGMAX_CHUNK 8192
+
+__global__ void __launch_bounds__(256)
+argmax_chunks_kernel(const float *__restrict__ logits, long long ld, int V, float *__restrict__ cand_v,
+                     int *__restrict__ cand_i) {
+    __shared__ float red[8];
+    __shared__ int redi[8];
+    int row = blockIdx.x, chunk = blockIdx.y, chunks = gridDim.y;
+    int b = chunk * ARGMAX_CHUNK, n = min(ARGMAX_CHUNK, V - b);
+    int idx = block_argmax(logits + (size_t)row * ld + b, n, red, redi);
+    if (threadIdx.x == 0) {
+        cand_v[(size_t)row * chunks + chunk] = logits[(size_t)row * ld + b + idx];
+        cand_i[(size_t)row * chunks + chunk] = b + idx;
+    }
+}
+
+__global__ void argmax_final_kernel(const float *__restrict__ cand_v, const int *__restrict__ cand_i, int chunks,
+                                    int R, int *__restrict__ out) {
+    int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= R) return;
+    const float *v = cand_v + (size_t)row * chunks;
+    int best = 0;
+    for (int c = 1; c < chunks; ++c)
+        if (v[c] > v[best]) best = c;
+    out[row] = cand_i[(size_t)row * chunks + best];
+}
+
+// scratch (used for V > ARGMAX_CHUNK): float [R * chunks] and int [R * chunks], chunks = ceil(V / 8192)
+KESTREL_API int kestrel_argmax(const float *logits, long long ld, int R, int V, int *out, float *cand_v, int *cand_i,
                                cudaStream_t stream) {
     if (R == 0) return 0;
     KESTREL_REQUIRE(R > 0 && V > 0, "argmax: bad sizes R=%d V=%d", R, V);
-    argmax_kernel<<<R, SP_THREADS, 0, stream>>>(logits, ld, V, out);
+    int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+    if (chunks == 1 || !cand_v || !cand_i) {
+        argmax_kernel<<<R, SP_THREADS, 0, stream>>>(logits, ld, V, out);
+        return kestrel_check_launch("argmax");
+    }
+    KESTREL_REQUIRE(chunks <= 65535, "argmax: vocabulary %d too large", V);
+    argmax_chunks_kernel<<<dim3(R, chunks), 256, 0, stream>>>(logits, ld, V, cand_v, cand_i);
+    argmax_final_kernel<<<(R + 63) / 64, 64, 0, stream>>>(cand_v, cand_i, chunks, R, out);
     return kestrel_check_launch("argmax");
 }
+
+KESTREL_API int kestrel_argmax_chunks(int V) { return (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK; }
 
 __global__ void __launch_bounds__(SP_THREADS)
 sample_kernel(const float *__restrict__ logits, long long ld, int V, const float *__restrict__ temperature,

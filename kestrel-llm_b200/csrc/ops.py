@@ -67,7 +67,8 @@ def _declare(lib) -> None:
         "kestrel_gemm_tc_error": [],
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _vp, _f, _vp],
-        "kestrel_argmax": [_vp, _ll, _i, _i, _vp, _vp],
+        "kestrel_argmax": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp],
+        "kestrel_argmax_chunks": [_i],
         "kestrel_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     }
     for name, args in sig.items():
@@ -263,7 +264,14 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     _need(logits, "argmax.logits", torch.float32, 2)
     _need(out, "argmax.out", torch.int32, 1)
     R, V = logits.shape
-    _check(library().kestrel_argmax(logits.data_ptr(), logits.stride(0), R, V, out.data_ptr(), _stream()))
+    lib = library()
+    chunks = lib.kestrel_argmax_chunks(V)
+    cand_v = cand_i = None
+    if chunks > 1:              # a large vocabulary is scanned by many blocks; their candidates go to scratch
+        cand_v = torch.empty((R, chunks), dtype=torch.float32, device=logits.device)
+        cand_i = torch.empty((R, chunks), dtype=torch.int32, device=logits.device)
+    _check(lib.kestrel_argmax(logits.data_ptr(), logits.stride(0), R, V, out.data_ptr(), _p(cand_v), _p(cand_i),
+                              _stream()))
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
@@ -327,6 +335,13 @@ def gemm_tc_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) 
         raise KernelError("gemm_tc_swiglu: shapes differ")
     _check(library().kestrel_gemm_tc_swiglu(x.data_ptr(), w_gate_up.data_ptr(), out.data_ptr(), T, ff, K,
                                             x.stride(0), w_gate_up.stride(0), out.stride(0), _stream()))
+
+
+def gemm_tc_set_tuning(overhead_kb: int = -1, ctas_per_sm: int = 0) -> None:
+    """Tuning of the split heuristic of few-token products (see gemm_tcgen05.cu)."""
+    fn = library().kestrel_gemm_tc_set_tuning
+    fn.restype, fn.argtypes = None, [_i, _i]
+    fn(int(overhead_kb), int(ctas_per_sm))
 
 
 def gemm_tc_error() -> int:
