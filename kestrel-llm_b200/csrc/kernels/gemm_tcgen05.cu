@@ -296,7 +296,7 @@ KESTREL_API int kestrel_gemm_tc_supported(const void *x, const void *w, int T, i
 // g_overhead_kb k-blocks of time beyond its own k-blocks (launch, barrier set-up, TMEM
 // allocation, first tensor-map fetch, pipeline fill, epilogue).
 static int g_overhead_kb = 6;
-static int g_ctas_per_sm = 1;
+static int g_ctas_per_sm = 2;
 
 KESTREL_API void kestrel_gemm_tc_set_tuning(int overhead_kb, int ctas_per_sm) {
     if (overhead_kb >= 0) g_overhead_kb = overhead_kb;
