@@ -73,15 +73,18 @@ struct AttnParams {
 template <int HD, bool KEYS_MODE>
 __global__ void __launch_bounds__(AM_THREADS)
 attention_mma_kernel(const AttnParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int BM = KEYS_MODE ? 16 : 64;
     constexpr int LDS = HD + 8;                       // padded row, in elements: ldmatrix without bank conflicts
     constexpr int KS = HD / 16;                       // k-steps of the QK product
     constexpr int NT_S = KEYS_MODE ? 2 : 8;           // 8-key tiles of a warp's score block
     constexpr int NT_O = HD / 8;                      // 8-dim tiles of the output
+    constexpr int STAGES = KEYS_MODE ? 3 : 2;         // decode is bound by HBM latency: more tiles in flight
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(smem_raw);
-    __nv_bfloat16 *Ks = Qs + BM * LDS;                // [2][AM_BN][LDS]
-    __nv_bfloat16 *Vs = Ks + 2 * AM_BN * LDS;
+    __nv_bfloat16 *Ks = Qs + BM * LDS;                // [STAGES][AM_BN][LDS]
+    __nv_bfloat16 *Vs = Ks + STAGES * AM_BN * LDS;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x, kvh = blockIdx.y, slice = blockIdx.z;
@@ -107,21 +110,34 @@ attention_mma_kernel(const AttnParams p) {
 
     // ---- loads -------------------------------------------------------------------------
     constexpr int CHUNKS = HD / 8;                    // 16-byte chunks of a padded row
+    constexpr int RPT = AM_BN * CHUNKS / AM_THREADS;  // a thread copies chunk ld_c of RPT consecutive keys
+    const int ld_c = tid % CHUNKS, ld_r0 = (tid / CHUNKS) * RPT;
+    const bool one_page = p.page_size % RPT == 0;     // the RPT keys then lie in one page: one table lookup
     auto load_kv_tile = [&](int t, int stage) {
-        int kbase = k_lo + t * AM_BN;
-        for (int idx = tid; idx < AM_BN * CHUNKS; idx += AM_THREADS) {
-            int r = idx / CHUNKS, c = idx % CHUNKS;
-            int s = kbase + r;
-            bool valid = s >= k_first && s < k_hi && c * 8 < hd;
+        int s0 = k_lo + t * AM_BN + ld_r0;
+        __nv_bfloat16 *dk = Ks + ((size_t)stage * AM_BN + ld_r0) * LDS + ld_c * 8;
+        __nv_bfloat16 *dv = Vs + ((size_t)stage * AM_BN + ld_r0) * LDS + ld_c * 8;
+        bool col_ok = ld_c * 8 < hd;
+        size_t page_off = 0;
+        if (one_page && col_ok && s0 + RPT > k_first && s0 < k_hi) {
+            int page = table[s0 / p.page_size];
+            page_off = (((size_t)page * p.nkv + kvh) * p.page_size + (s0 % p.page_size)) * hd + ld_c * 8;
+        }
+#pragma unroll
+        for (int j = 0; j < RPT; ++j) {
+            int s = s0 + j;
+            bool valid = col_ok && s >= k_first && s < k_hi;
             size_t off = 0;
             if (valid) {
-                int page = table[s / p.page_size];
-                off = (((size_t)page * p.nkv + kvh) * p.page_size + (s % p.page_size)) * hd + c * 8;
+                if (one_page) {
+                    off = page_off + (size_t)j * hd;
+                } else {
+                    int page = table[s / p.page_size];
+                    off = (((size_t)page * p.nkv + kvh) * p.page_size + (s % p.page_size)) * hd + ld_c * 8;
+                }
             }
-            uint32_t dk = (uint32_t)__cvta_generic_to_shared(Ks + ((size_t)stage * AM_BN + r) * LDS + c * 8);
-            uint32_t dv = (uint32_t)__cvta_generic_to_shared(Vs + ((size_t)stage * AM_BN + r) * LDS + c * 8);
-            cp_async16(dk, p.k_cache + off, valid);
-            cp_async16(dv, p.v_cache + off, valid);
+            cp_async16((uint32_t)__cvta_generic_to_shared(dk + j * LDS), p.k_cache + off, valid);
+            cp_async16((uint32_t)__cvta_generic_to_shared(dv + j * LDS), p.v_cache + off, valid);
         }
     };
     for (int idx = tid; idx < BM * CHUNKS; idx += AM_THREADS) {
@@ -135,8 +151,10 @@ attention_mma_kernel(const AttnParams p) {
         }
         cp_async16((uint32_t)__cvta_generic_to_shared(Qs + r * LDS + c * 8), p.q + off, valid);
     }
-    if (n_tiles > 0) load_kv_tile(0, 0);
-    cp_async_commit();
+    for (int st = 0; st < STAGES - 1; ++st) {          // Q travels with the first group
+        if (st < n_tiles) load_kv_tile(st, st);
+        cp_async_commit();
+    }
 
     // ---- per-thread state ----------------------------------------------------------------
     // a warp's 16 rows: ROWS mode rows 16*warp.., KEYS mode rows 0..15 for every warp
@@ -158,11 +176,11 @@ attention_mma_kernel(const AttnParams p) {
     const bool warp_active = KEYS_MODE ? true : (wrow0 < rows_here);
 
     for (int t = 0; t < n_tiles; ++t) {
-        int stage = t & 1;
-        if (t + 1 < n_tiles) load_kv_tile(t + 1, stage ^ 1);
+        int stage = t % STAGES;
+        cp_async_wait<STAGES - 2>();                   // tile t has landed
+        __syncthreads();                               // ... for everyone, and tile t-1 is no longer read
+        if (t + STAGES - 1 < n_tiles) load_kv_tile(t + STAGES - 1, (t + STAGES - 1) % STAGES);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
         if (warp_active) {
             const int kbase = k_lo + t * AM_BN + (KEYS_MODE ? 16 * warp : 0);
             const __nv_bfloat16 *Kt = Ks + ((size_t)stage * AM_BN + (KEYS_MODE ? 16 * warp : 0)) * LDS;
@@ -242,7 +260,6 @@ attention_mma_kernel(const AttnParams p) {
                 }
             }
         }
-        __syncthreads();
     }
     cp_async_wait<0>();
 
@@ -338,6 +355,8 @@ __global__ void attention_merge_kernel(const float *__restrict__ part_o, const f
                                        __nv_bfloat16 *__restrict__ out, const int *__restrict__ tile_seq,
                                        const int *__restrict__ tile_row0, const int *__restrict__ cu_seqlens,
                                        int slices, int hd, int nq, int nkv) {
+    pdl_launch_dependents();
+    pdl_wait();
     int tile = blockIdx.x, kvh = blockIdx.y;
     int seq = tile_seq[tile], row0 = tile_row0[tile];
     int G = nq / nkv;
@@ -367,9 +386,8 @@ template <int HD, bool KEYS_MODE>
 static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream) {
     constexpr int BM = KEYS_MODE ? 16 : 64;
     constexpr int LDS = HD + 8;
-    size_t smem = (size_t)(BM + 4 * AM_BN) * LDS * 2;
-    size_t merge = KEYS_MODE ? (size_t)(4 * 16 * HD + 4 * 16 * 2) * 4 + (size_t)BM * LDS * 2 : 0;
-    if (merge > smem) smem = merge;
+    constexpr int STAGES = KEYS_MODE ? 3 : 2;
+    size_t smem = (size_t)(BM + 2 * STAGES * AM_BN) * LDS * 2;
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, KEYS_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -377,8 +395,18 @@ static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream)
         attr_set = true;
     }
     dim3 grid(tiles, p.nkv, p.slices);
-    attention_mma_kernel<HD, KEYS_MODE><<<grid, AM_THREADS, smem, stream>>>(p);
+    kestrel_launch(attention_mma_kernel<HD, KEYS_MODE>, dim3(grid), dim3(AM_THREADS), smem, stream, p);
     return kestrel_check_launch("attention_mma");
+}
+
+// CTAs of the KEYS-mode kernel that the GPU's 148 SMs hold at once, by shared memory and threads
+KESTREL_API int kestrel_attention_mma_slots(int hd) {
+    int HD = hd <= 32 ? 32 : hd <= 64 ? 64 : hd <= 128 ? 128 : 256;
+    size_t smem = (size_t)(16 + 2 * 3 * AM_BN) * (HD + 8) * 2 + 1024;
+    int per_sm = (int)((227 * 1024) / smem);
+    if (per_sm > 2048 / AM_THREADS) per_sm = 2048 / AM_THREADS;
+    if (per_sm < 1) per_sm = 1;
+    return 148 * per_sm;
 }
 
 // rows_per_tile must be 16 (KEYS mode) or 64 (ROWS mode); tile_seq / tile_row0 describe the
@@ -414,7 +442,7 @@ KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const 
     if (rc) return rc;
     if (slices > 1) {
         KESTREL_REQUIRE(keys, "attention_mma: slices are merged for tiles of 16 rows only");
-        attention_merge_kernel<<<dim3(tiles, nkv), 256, 0, stream>>>(part_o, part_ml, (__nv_bfloat16 *)out, tile_seq, tile_row0,
+        kestrel_launch(attention_merge_kernel, dim3(dim3(tiles, nkv)), dim3(256), 0, stream, part_o, part_ml, (__nv_bfloat16 *)out, tile_seq, tile_row0,
                                                                   cu_seqlens, slices, hd, nq, nkv);
         return kestrel_check_launch("attention_merge");
     }

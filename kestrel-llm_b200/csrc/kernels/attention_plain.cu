@@ -24,6 +24,8 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
                        const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                        const int *__restrict__ block_table, int table_stride, int page_size,
                        T *__restrict__ out, int nq, int nkv, int hd, int window, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     int t = blockIdx.x, h = blockIdx.y;
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int kvh = (h * nkv) / nq;
@@ -130,12 +132,10 @@ KESTREL_API int kestrel_attention_plain(const void *q, const void *k_cache, cons
     KESTREL_REQUIRE(nq <= 65535, "attention_plain: %d query heads exceed the grid", nq);
     dim3 grid(T, nq);
     if (dtype == KESTREL_F32)
-        attention_plain_kernel<float><<<grid, PA_WARPS * 32, 0, stream>>>(
-            (const float *)q, (const float *)k_cache, (const float *)v_cache, positions, seq_of_token,
+        kestrel_launch(attention_plain_kernel<float>, dim3(grid), dim3(PA_WARPS * 32), 0, stream, (const float *)q, (const float *)k_cache, (const float *)v_cache, positions, seq_of_token,
             block_table, table_stride, page_size, (float *)out, nq, nkv, hd, window, scale);
     else if (dtype == KESTREL_BF16)
-        attention_plain_kernel<__nv_bfloat16><<<grid, PA_WARPS * 32, 0, stream>>>(
-            (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, positions,
+        kestrel_launch(attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(PA_WARPS * 32), 0, stream, (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, positions,
             seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)out, nq, nkv, hd, window, scale);
     else
         return kestrel_fail(-2, "attention_plain: unknown dtype %d", dtype);

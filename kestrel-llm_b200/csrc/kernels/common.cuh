@@ -23,6 +23,35 @@ int kestrel_check_launch(const char *what);
         if (!(cond)) return kestrel_fail(-2, __VA_ARGS__); \
     } while (0)
 
+// Programmatic dependent launch.  Every kernel of the library is launched with the attribute
+// that lets it start while its predecessor on the stream is still draining, calls
+// pdl_launch_dependents() first thing (so that its own successor may be scheduled as soon as
+// all of its blocks are resident) and pdl_wait() before it touches global memory (which
+// returns once the predecessor has completed and its writes are visible).  Because every
+// kernel waits, completion is transitive along the stream.  What runs before the wait - barrier
+// set-up, TMEM allocation, descriptor prefetch, index arithmetic - overlaps the predecessor's
+// tail.  kestrel_set_pdl(0) switches the attribute off; the instructions are then no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+extern int g_kestrel_pdl;
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t kestrel_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_kestrel_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

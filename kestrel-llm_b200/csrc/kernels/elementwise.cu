@@ -16,6 +16,8 @@
 template <typename T>
 __global__ void embed_kernel(const T *__restrict__ table, const int *__restrict__ ids,
                              float *__restrict__ out, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
     int t = blockIdx.x;
     const T *row = table + (size_t)ids[t] * d;
     float *o = out + (size_t)t * d;
@@ -27,9 +29,9 @@ KESTREL_API int kestrel_embed(const void *table, int dtype, const int *ids, floa
     if (T == 0) return 0;
     KESTREL_REQUIRE(T > 0 && d > 0, "embed: bad sizes T=%d d=%d", T, d);
     if (dtype == KESTREL_F32)
-        embed_kernel<float><<<T, 256, 0, stream>>>((const float *)table, ids, out, d);
+        kestrel_launch(embed_kernel<float>, dim3(T), dim3(256), 0, stream, (const float *)table, ids, out, d);
     else if (dtype == KESTREL_BF16)
-        embed_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16 *)table, ids, out, d);
+        kestrel_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16 *)table, ids, out, d);
     else
         return kestrel_fail(-2, "embed: unknown dtype %d", dtype);
     return kestrel_check_launch("embed");
@@ -51,6 +53,8 @@ __global__ void add_rmsnorm_kernel(float *__restrict__ residual, const float *__
                                    int S, size_t slice_stride, const float *__restrict__ bias,
                                    const int *__restrict__ rows, const float *__restrict__ w,
                                    float eps, TOut *__restrict__ out, int d, int write_back) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float xs[];
     __shared__ float red[NORM_THREADS / 32];
     int r = blockIdx.x;
@@ -101,6 +105,8 @@ __global__ void __launch_bounds__(NORMV_THREADS)
 add_rmsnorm_vec_kernel(float *__restrict__ residual, const float *__restrict__ partial, int S, size_t slice_stride,
                        const float *__restrict__ bias, const int *__restrict__ rows, const float *__restrict__ w,
                        float eps, TOut *__restrict__ out, int d, int write_back) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float xs[];
     __shared__ float red[NORMV_THREADS / 32];
     int r = blockIdx.x;
@@ -159,11 +165,11 @@ static void launch_add_rmsnorm(float *residual, const float *partial, int S, lon
     if (vec) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_vec_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_vec_kernel<TOut><<<R, NORMV_THREADS, smem, stream>>>(residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, d, write_back);
+        kestrel_launch(add_rmsnorm_vec_kernel<TOut>, dim3(R), dim3(NORMV_THREADS), smem, stream, residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, d, write_back);
     } else {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<TOut><<<R, NORM_THREADS, smem, stream>>>(residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, d, write_back);
+        kestrel_launch(add_rmsnorm_kernel<TOut>, dim3(R), dim3(NORM_THREADS), smem, stream, residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, d, write_back);
     }
 }
 
@@ -191,6 +197,8 @@ KESTREL_API int kestrel_add_rmsnorm(float *residual, const float *partial, int S
 template <typename TOut>
 __global__ void swiglu_kernel(const float *__restrict__ partial, int S, size_t slice_stride,
                               TOut *__restrict__ out, int T, int ff) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)T * ff) return;
     int t = (int)(idx / ff), i = (int)(idx % ff);
@@ -211,9 +219,9 @@ KESTREL_API int kestrel_swiglu(const float *partial, int S, long long slice_stri
     size_t n = (size_t)T * ff;
     unsigned blocks = (unsigned)((n + 255) / 256);
     if (out_dtype == KESTREL_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>(partial, S, (size_t)slice_stride, (float *)out, T, ff);
+        kestrel_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, partial, S, (size_t)slice_stride, (float *)out, T, ff);
     else if (out_dtype == KESTREL_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(partial, S, (size_t)slice_stride, (__nv_bfloat16 *)out, T, ff);
+        kestrel_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, partial, S, (size_t)slice_stride, (__nv_bfloat16 *)out, T, ff);
     else
         return kestrel_fail(-2, "swiglu: unknown dtype %d", out_dtype);
     return kestrel_check_launch("swiglu");
@@ -242,6 +250,8 @@ __global__ void attn_prepare_kernel(const float *__restrict__ partial, int S, si
                                     const int *__restrict__ block_table, int table_stride, int page_size,
                                     T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out,
                                     int Tn, int nq, int nkv, int hd, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
     int warp = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
     int lane = threadIdx.x & 31;
     int heads = nq + 2 * nkv;
@@ -360,13 +370,11 @@ KESTREL_API int kestrel_attn_prepare(const float *partial, int S, long long slic
     long long warps = (long long)T * (nq + 2 * nkv);
     unsigned blocks = (unsigned)((warps + 3) / 4);
     if (dtype == KESTREL_F32)
-        attn_prepare_kernel<float><<<blocks, 128, 0, stream>>>(
-            partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, positions,
+        kestrel_launch(attn_prepare_kernel<float>, dim3(blocks), dim3(128), 0, stream, partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, positions,
             seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache,
             (float *)q_out, T, nq, nkv, hd, write_kv);
     else if (dtype == KESTREL_BF16)
-        attn_prepare_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(
-            partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, positions,
+        kestrel_launch(attn_prepare_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, positions,
             seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)k_cache,
             (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, T, nq, nkv, hd, write_kv);
     else
@@ -382,6 +390,8 @@ template <typename TOut>
 __global__ void reduce_partials_kernel(const float *__restrict__ partial, int S, size_t slice_stride,
                                        const float *__restrict__ bias, TOut *__restrict__ out,
                                        size_t n, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
     float v = 0.f;
@@ -397,9 +407,9 @@ KESTREL_API int kestrel_reduce_partials(const float *partial, int S, long long s
     size_t n = (size_t)T * width;
     unsigned blocks = (unsigned)((n + 255) / 256);
     if (out_dtype == KESTREL_F32)
-        reduce_partials_kernel<float><<<blocks, 256, 0, stream>>>(partial, S, (size_t)slice_stride, bias, (float *)out, n, width);
+        kestrel_launch(reduce_partials_kernel<float>, dim3(blocks), dim3(256), 0, stream, partial, S, (size_t)slice_stride, bias, (float *)out, n, width);
     else if (out_dtype == KESTREL_BF16)
-        reduce_partials_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(partial, S, (size_t)slice_stride, bias, (__nv_bfloat16 *)out, n, width);
+        kestrel_launch(reduce_partials_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, partial, S, (size_t)slice_stride, bias, (__nv_bfloat16 *)out, n, width);
     else
         return kestrel_fail(-2, "reduce_partials: unknown dtype %d", out_dtype);
     return kestrel_check_launch("reduce_partials");

@@ -15,6 +15,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(const T *__restrict__ x, const T *__restrict__ w, float *__restrict__ out,
                   int Tn, int N, int K, long long ldx, long long ldw, long long ldo) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float xs[PG_BK][PG_BM + 4];
     __shared__ float ws[PG_BK][PG_BN + 4];
     int tid = threadIdx.x;
@@ -76,9 +78,9 @@ KESTREL_API int kestrel_gemm_plain(const void *x, const void *w, float *out, int
     dim3 grid((N + PG_BN - 1) / PG_BN, (T + PG_BM - 1) / PG_BM);
     KESTREL_REQUIRE(grid.y <= 65535, "gemm_plain: T=%d needs more than 65535 row tiles", T);
     if (dtype == KESTREL_F32)
-        gemm_plain_kernel<float><<<grid, 256, 0, stream>>>((const float *)x, (const float *)w, out, T, N, K, ldx, ldw, ldo);
+        kestrel_launch(gemm_plain_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float *)x, (const float *)w, out, T, N, K, ldx, ldw, ldo);
     else if (dtype == KESTREL_BF16)
-        gemm_plain_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16 *)x, (const __nv_bfloat16 *)w, out, T, N, K, ldx, ldw, ldo);
+        kestrel_launch(gemm_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)w, out, T, N, K, ldx, ldw, ldo);
     else
         return kestrel_fail(-2, "gemm_plain: unknown dtype %d", dtype);
     return kestrel_check_launch("gemm_plain");

@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void *__restrict__ out, int T, int N, int K, int kb_per_split, long long slice_stride,
                long long ldo, int stages, int up_row_offset) {
+    pdl_launch_dependents();
     constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = BN * TC_BK * 2;
@@ -146,6 +147,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     uint32_t tmem = *tmem_slot_ptr;
+    pdl_wait();                                       // barriers and TMEM are ready; now wait for the operands
 
     if (warp == 0) {
         if (lane == 0) {
@@ -349,7 +351,7 @@ static int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, void *out, in
     }
     dim3 grid((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
     if (grid.y > 65535) return kestrel_fail(-2, "gemm_tc: T=%d needs more than 65535 token tiles", T);
-    gemm_tc_kernel<BN, MODE><<<grid, TC_THREADS, smem, stream>>>(mw, mx, out, T, N, K, per, slice_stride, ldo, stages, up_off);
+    kestrel_launch(gemm_tc_kernel<BN, MODE>, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, out, T, N, K, per, slice_stride, ldo, stages, up_off);
     return kestrel_check_launch("gemm_tc");
 }
 

@@ -19,6 +19,11 @@ int kestrel_check_launch(const char *what) {
     return 0;
 }
 
+int g_kestrel_pdl = 1;
+
+// 1: kernels are launched with programmatic dependent launch (the default); 0: plain stream order
+KESTREL_API void kestrel_set_pdl(int on) { g_kestrel_pdl = on ? 1 : 0; }
+
 KESTREL_API const char *kestrel_last_error(void) { return g_error; }
 
 // Compute capability of the current device as major*10+minor, or a negative code.

@@ -71,6 +71,8 @@ __device__ int block_argmax(const float *__restrict__ row, int V, float *red, in
 
 __global__ void __launch_bounds__(SP_THREADS)
 argmax_kernel(const float *__restrict__ logits, long long ld, int V, int *__restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[SP_THREADS / 32];
     __shared__ int redi[SP_THREADS / 32];
     int idx = block_argmax(logits + (size_t)blockIdx.x * ld, V, red, redi);
@@ -85,6 +87,8 @@ argmax_kernel(const float *__restrict__ logits, long long ld, int V, int *__rest
 __global__ void __launch_bounds__(256)
 argmax_chunks_kernel(const float *__restrict__ logits, long long ld, int V, float *__restrict__ cand_v,
                      int *__restrict__ cand_i) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[8];
     __shared__ int redi[8];
     int row = blockIdx.x, chunk = blockIdx.y, chunks = gridDim.y;
@@ -98,6 +102,8 @@ argmax_chunks_kernel(const float *__restrict__ logits, long long ld, int V, floa
 
 __global__ void argmax_final_kernel(const float *__restrict__ cand_v, const int *__restrict__ cand_i, int chunks,
                                     int R, int *__restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     int row = blockIdx.x * blockDim.x + threadIdx.x;
     if (row >= R) return;
     const float *v = cand_v + (size_t)row * chunks;
@@ -114,12 +120,12 @@ KESTREL_API int kestrel_argmax(const float *logits, long long ld, int R, int V, 
     KESTREL_REQUIRE(R > 0 && V > 0, "argmax: bad sizes R=%d V=%d", R, V);
     int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
     if (chunks == 1 || !cand_v || !cand_i) {
-        argmax_kernel<<<R, SP_THREADS, 0, stream>>>(logits, ld, V, out);
+        kestrel_launch(argmax_kernel, dim3(R), dim3(SP_THREADS), 0, stream, logits, ld, V, out);
         return kestrel_check_launch("argmax");
     }
     KESTREL_REQUIRE(chunks <= 65535, "argmax: vocabulary %d too large", V);
-    argmax_chunks_kernel<<<dim3(R, chunks), 256, 0, stream>>>(logits, ld, V, cand_v, cand_i);
-    argmax_final_kernel<<<(R + 63) / 64, 64, 0, stream>>>(cand_v, cand_i, chunks, R, out);
+    kestrel_launch(argmax_chunks_kernel, dim3(dim3(R, chunks)), dim3(256), 0, stream, logits, ld, V, cand_v, cand_i);
+    kestrel_launch(argmax_final_kernel, dim3((R + 63) / 64), dim3(64), 0, stream, cand_v, cand_i, chunks, R, out);
     return kestrel_check_launch("argmax");
 }
 
@@ -129,6 +135,8 @@ __global__ void __launch_bounds__(SP_THREADS)
 sample_kernel(const float *__restrict__ logits, long long ld, int V, const float *__restrict__ temperature,
               const int *__restrict__ top_k, const float *__restrict__ top_p, const float *__restrict__ min_p,
               const float *__restrict__ uniform, int *__restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[SP_THREADS / 32];
     __shared__ int redi[SP_THREADS / 32];
     __shared__ float scan[SP_THREADS];
@@ -225,6 +233,6 @@ KESTREL_API int kestrel_sample(const float *logits, long long ld, int R, int V, 
                                const float *uniform, int *out, cudaStream_t stream) {
     if (R == 0) return 0;
     KESTREL_REQUIRE(R > 0 && V > 0, "sample: bad sizes R=%d V=%d", R, V);
-    sample_kernel<<<R, SP_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, min_p, uniform, out);
+    kestrel_launch(sample_kernel, dim3(R), dim3(SP_THREADS), 0, stream, logits, ld, V, temperature, top_k, top_p, min_p, uniform, out);
     return kestrel_check_launch("sample");
 }

@@ -8,6 +8,7 @@ first call raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -37,6 +38,8 @@ def library() -> ctypes.CDLL:
         lib.kestrel_last_error.restype = ctypes.c_char_p
         _declare(lib)
         _lib = lib
+        if os.environ.get("KESTREL_PDL", "1") == "0":      # for A/B measurements only
+            set_pdl(False)
     return _lib
 
 
@@ -67,6 +70,7 @@ def _declare(lib) -> None:
         "kestrel_gemm_tc_error": [],
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _vp, _f, _vp],
+        "kestrel_attention_mma_slots": [_i],
         "kestrel_argmax": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp],
         "kestrel_argmax_chunks": [_i],
         "kestrel_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -110,6 +114,13 @@ def _code(t: torch.Tensor, name: str) -> int:
     if t.dtype not in _DT:
         raise KernelError(f"{name}: dtype {t.dtype} is neither float32 nor bfloat16")
     return _DT[t.dtype]
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for all kernels of the library (default on)."""
+    fn = library().kestrel_set_pdl
+    fn.restype, fn.argtypes = None, [_i]
+    fn(1 if on else 0)
 
 
 def device_arch() -> int:
@@ -430,16 +441,23 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
         tl = plan.small
         slices, slice_len, slice_dev = 1, no_split, None
         if window <= 0:         # a window is short; only full-length key ranges are cut into slices
-            want = min(32, -(-296 // max(1, tl.count * nkv)))         # CTAs for two per SM
+            slots = library().kestrel_attention_mma_slots(hd)
+            ctas = max(1, tl.count * nkv)
             if tl.slice_len_table is not None:
-                # a captured step: the number of slices is fixed, their length follows the context
-                slices = want
+                # a captured step: the number of slices is fixed (one wave of CTAs), their
+                # length follows the context through the table on the device
+                slices = max(1, min(32, slots // ctas))
                 slice_dev = tl.slice_len_table[slices:slices + 1] if slices > 1 else None
             else:
-                slices = max(1, min(want, -(-tl.max_kv // 256)))      # at least 256 keys a slice
-                if slices > 1:
-                    slice_len = -(-(-(-tl.max_kv // slices)) // 64) * 64
-                    slices = -(-tl.max_kv // slice_len)
+                # the number that minimises waves x (a CTA's fixed cost + its keys), at least 256 keys a slice
+                best = None
+                for cand in range(1, max(1, min(32, -(-tl.max_kv // 256))) + 1):
+                    length = -(-(-(-tl.max_kv // cand)) // 64) * 64
+                    real = -(-tl.max_kv // length)
+                    cost = -(-ctas * real // slots) * (128 + length)
+                    if best is None or cost < best[0]:
+                        best = (cost, real, length)
+                slices, slice_len = best[1], best[2]
         attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, 16, batch.cu_seqlens, batch.kv_lens, block_table,
                       page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
     if plan.large is not None:
