@@ -134,20 +134,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     int kb0 = blockIdx.z * kb_per_split;
     int num_kb = min(kb_per_split, total_kb - kb0);
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(accum_bar, 1);
+    // Prologue, before the wait on the predecessor kernel.  Warp 0 sets up the barriers and
+    // fetches the tensor maps; after the first block-wide sync its loader thread starts the
+    // copies at once.  TMEM is allocated by warp 1 meanwhile and its address published to the
+    // MMA and epilogue warps by a second barrier that the loader does not take part in.
+    if (warp == 0) {
+        if (lane < stages) { mbar_init(full_bar(lane), 1); mbar_init(empty_bar(lane), 1); }
+        if (lane == 31) mbar_init(accum_bar, 1);
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
     __syncthreads();
-    tc_fence_after();
-    uint32_t tmem = *tmem_slot_ptr;
-    pdl_wait();                                       // barriers and TMEM are ready; now wait for the operands
+    uint32_t tmem = 0;
+    if (warp != 0) {
+        if (warp == 1) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        tc_fence_before();
+        asm volatile("bar.sync 1, %0;" ::"n"(TC_THREADS - 32) : "memory");
+        tc_fence_after();
+        tmem = *tmem_slot_ptr;
+    }
+    pdl_wait();                                       // now wait for the operands of the predecessor
 
     if (warp == 0) {
         if (lane == 0) {
@@ -302,7 +314,7 @@ static int g_ctas_per_sm = 2;
 
 KESTREL_API void kestrel_gemm_tc_set_tuning(int overhead_kb, int ctas_per_sm) {
     if (overhead_kb >= 0) g_overhead_kb = overhead_kb;
-    if (ctas_per_sm == 1 || ctas_per_sm == 2) g_ctas_per_sm = ctas_per_sm;
+    if (ctas_per_sm >= 1 && ctas_per_sm <= 4) g_ctas_per_sm = ctas_per_sm;
 }
 
 // Slices into which a product of T tokens and N output features splits its K range: the
@@ -337,7 +349,7 @@ static int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, void *out, in
     int total_kb = (K + TC_BK - 1) / TC_BK;
     int per = (total_kb + splits - 1) / splits;
     // few tokens: the CTAs that share an SM divide its shared memory; else one CTA takes it all
-    int budget = (BN <= 64 && MODE == TC_PARTIAL && g_ctas_per_sm == 2) ? 100 * 1024 : 200 * 1024;
+    int budget = (BN <= 64 && MODE == TC_PARTIAL) ? (216 * 1024) / g_ctas_per_sm - 2048 : 200 * 1024;
     int stages = budget / STAGE_BYTES;
     if (stages > per) stages = per < 2 ? 2 : per;
     if (stages > 12) stages = 12;
