@@ -100,13 +100,18 @@ __device__ __forceinline__ void store4(__nv_bfloat16 *p, float4 v) {
     *reinterpret_cast<uint2 *>(p) = u;
 }
 
-template <typename TOut>
-__global__ void __launch_bounds__(NORMV_THREADS)
+// THREADS is 1024 or 256.  With 256 threads a thread plays four of the 1024 "virtual lanes"
+// (t, t + 256, ...): vector i always belongs to virtual lane i mod 1024 and the sums of
+// squares are combined in the same tree, so both variants give the same bits and the choice
+// can follow the number of rows (few rows: spread a row wide; many rows: more blocks per SM).
+template <typename TOut, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 add_rmsnorm_vec_kernel(float *__restrict__ residual, const float *__restrict__ partial, int S, size_t slice_stride,
                        const float *__restrict__ bias, const int *__restrict__ rows, const float *__restrict__ w,
                        float eps, TOut *__restrict__ out, int d, int write_back) {
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int VL = NORMV_THREADS / THREADS;
     extern __shared__ float xs[];
     __shared__ float red[NORMV_THREADS / 32];
     int r = blockIdx.x;
@@ -114,31 +119,41 @@ add_rmsnorm_vec_kernel(float *__restrict__ residual, const float *__restrict__ p
     int d4 = d >> 2;
     float4 *res = reinterpret_cast<float4 *>(residual + (size_t)t * d);
     const float4 *bias4 = reinterpret_cast<const float4 *>(bias);
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < d4; i += NORMV_THREADS) {
-        float4 x = res[i];
-        if (partial) {
-            const float4 *p4 = reinterpret_cast<const float4 *>(partial + (size_t)t * d) + i;
-            size_t st4 = slice_stride >> 2;
-            float4 delta = make_float4(0.f, 0.f, 0.f, 0.f);
-            int s = 0;
-            for (; s + 4 <= S; s += 4) {
-                float4 a = p4[(size_t)s * st4], b = p4[(size_t)(s + 1) * st4], c = p4[(size_t)(s + 2) * st4], e = p4[(size_t)(s + 3) * st4];
-                delta = add4(add4(add4(add4(delta, a), b), c), e);
+    float ss[VL];
+#pragma unroll
+    for (int k = 0; k < VL; ++k) ss[k] = 0.f;
+    for (int base = 0; base < d4; base += NORMV_THREADS) {
+#pragma unroll
+        for (int k = 0; k < VL; ++k) {
+            int i = base + threadIdx.x + k * THREADS;
+            if (i >= d4) continue;
+            float4 x = res[i];
+            if (partial) {
+                const float4 *p4 = reinterpret_cast<const float4 *>(partial + (size_t)t * d) + i;
+                size_t st4 = slice_stride >> 2;
+                float4 delta = make_float4(0.f, 0.f, 0.f, 0.f);
+                int s = 0;
+                for (; s + 4 <= S; s += 4) {
+                    float4 a = p4[(size_t)s * st4], b = p4[(size_t)(s + 1) * st4], c = p4[(size_t)(s + 2) * st4], e = p4[(size_t)(s + 3) * st4];
+                    delta = add4(add4(add4(add4(delta, a), b), c), e);
+                }
+                for (; s < S; ++s) delta = add4(delta, p4[(size_t)s * st4]);
+                if (bias) delta = add4(delta, bias4[i]);
+                x = add4(x, delta);
+                if (write_back) res[i] = x;
             }
-            for (; s < S; ++s) delta = add4(delta, p4[(size_t)s * st4]);
-            if (bias) delta = add4(delta, bias4[i]);
-            x = add4(x, delta);
-            if (write_back) res[i] = x;
+            reinterpret_cast<float4 *>(xs)[i] = x;
+            ss[k] += x.x * x.x;
+            ss[k] += x.y * x.y;
+            ss[k] += x.z * x.z;
+            ss[k] += x.w * x.w;
         }
-        reinterpret_cast<float4 *>(xs)[i] = x;
-        ss += x.x * x.x;
-        ss += x.y * x.y;
-        ss += x.z * x.z;
-        ss += x.w * x.w;
     }
-    ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+#pragma unroll
+    for (int k = 0; k < VL; ++k) {
+        float v = warp_sum(ss[k]);
+        if ((threadIdx.x & 31) == 0) red[(threadIdx.x >> 5) + k * (THREADS / 32)] = v;
+    }
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
@@ -146,7 +161,7 @@ add_rmsnorm_vec_kernel(float *__restrict__ residual, const float *__restrict__ p
     float rinv = 1.0f / sqrtf(tot / (float)d + eps);
     TOut *o = out + (size_t)r * d;
     const float4 *w4 = reinterpret_cast<const float4 *>(w);
-    for (int i = threadIdx.x; i < d4; i += NORMV_THREADS) {
+    for (int i = threadIdx.x; i < d4; i += THREADS) {
         float4 x = reinterpret_cast<float4 *>(xs)[i], g = w4[i];
         store4(o + 4 * i, make_float4((x.x * rinv) * g.x, (x.y * rinv) * g.y, (x.z * rinv) * g.z, (x.w * rinv) * g.w));
     }
@@ -162,10 +177,14 @@ static void launch_add_rmsnorm(float *residual, const float *partial, int S, lon
     bool vec = d % 4 == 0 && d >= 2048 && slice_stride % 4 == 0 &&
                ((((uintptr_t)residual | (uintptr_t)partial | (uintptr_t)bias | (uintptr_t)w) & 15) == 0) &&
                (((uintptr_t)out & 7) == 0);
-    if (vec) {
+    if (vec && R >= 296) {
         if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_rmsnorm_vec_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kestrel_launch(add_rmsnorm_vec_kernel<TOut>, dim3(R), dim3(NORMV_THREADS), smem, stream, residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, d, write_back);
+            cudaFuncSetAttribute(add_rmsnorm_vec_kernel<TOut, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kestrel_launch(add_rmsnorm_vec_kernel<TOut, 256>, dim3(R), dim3(256), smem, stream, residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, d, write_back);
+    } else if (vec) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_vec_kernel<TOut, NORMV_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kestrel_launch(add_rmsnorm_vec_kernel<TOut, NORMV_THREADS>, dim3(R), dim3(NORMV_THREADS), smem, stream, residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, d, write_back);
     } else {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -241,6 +260,20 @@ KESTREL_API int kestrel_swiglu(const float *partial, int S, long long slice_stri
 // ------------------------------------------------------------------------------------------
 #define PREP_MAX_PER_LANE 8   // head size up to 512
 
+// rotation when half the rotary size is HP * 32: the pair (j, j + half) sits in registers c and c + HP
+template <int HP>
+__device__ __forceinline__ void rotate_in_registers(float *x, int pos, const float *__restrict__ inv_freq, int lane) {
+#pragma unroll
+    for (int c = 0; c < HP; ++c) {
+        float ang = (float)pos * inv_freq[lane + 32 * c];
+        float sn, cs;
+        sincosf(ang, &sn, &cs);
+        float lo = x[c], hi = x[c + HP];
+        x[c] = lo * cs - hi * sn;
+        x[c + HP] = hi * cs + lo * sn;
+    }
+}
+
 template <typename T>
 __global__ void attn_prepare_kernel(const float *__restrict__ partial, int S, size_t slice_stride,
                                     const float *__restrict__ bias, const float *__restrict__ q_norm_w,
@@ -309,27 +342,36 @@ __global__ void attn_prepare_kernel(const float *__restrict__ partial, int S, si
     }
     int pos = positions[t];
     if ((is_q || is_k) && rot > 0) {
-        // The partner of element i lives in another lane/register; exchange through shared
-        // memory is avoided by recomputing: each lane fetches its partner with a shuffle
-        // when half is a multiple of 32, else through a per-warp shared row.
-        __shared__ float stage[4][PREP_MAX_PER_LANE * 32];
-        float *st = stage[threadIdx.x >> 5];
-#pragma unroll
-        for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
-            int i = lane + 32 * c;
-            if (i < hd) st[i] = x[c];
-        }
-        __syncwarp();
         int half = rot >> 1;
+        if ((half & 31) == 0) {
+            // element lane + 32 c pairs with lane + 32 (c + half / 32): both are in this lane
+            switch (half >> 5) {
+                case 1: rotate_in_registers<1>(x, pos, inv_freq, lane); break;
+                case 2: rotate_in_registers<2>(x, pos, inv_freq, lane); break;
+                case 3: rotate_in_registers<3>(x, pos, inv_freq, lane); break;
+                default: rotate_in_registers<4>(x, pos, inv_freq, lane); break;
+            }
+        } else {
+            // the partner lives in another lane: exchange through a per-warp row of shared memory
+            __shared__ float stage[4][PREP_MAX_PER_LANE * 32];
+            float *st = stage[threadIdx.x >> 5];
 #pragma unroll
-        for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
-            int i = lane + 32 * c;
-            if (i < rot) {
-                int j = i < half ? i : i - half;
-                float ang = (float)pos * inv_freq[j];
-                float cs = cosf(ang), sn = sinf(ang);
-                float lo = st[j], hi = st[j + half];
-                x[c] = i < half ? lo * cs - hi * sn : hi * cs + lo * sn;
+            for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
+                int i = lane + 32 * c;
+                if (i < hd) st[i] = x[c];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
+                int i = lane + 32 * c;
+                if (i < rot) {
+                    int j = i < half ? i : i - half;
+                    float ang = (float)pos * inv_freq[j];
+                    float sn, cs;
+                    sincosf(ang, &sn, &cs);
+                    float lo = st[j], hi = st[j + half];
+                    x[c] = i < half ? lo * cs - hi * sn : hi * cs + lo * sn;
+                }
             }
         }
     }

@@ -135,6 +135,24 @@ def test_add_rmsnorm(out_dtype, d):
     np.testing.assert_allclose(out3.float().cpu().numpy(), ref3, rtol=tol, atol=tol * np.abs(ref3).max())
 
 
+def test_add_rmsnorm_row_does_not_depend_on_the_batch():
+    """Few rows take the wide variant of the kernel, many rows the narrow one; a row's bits are the same."""
+    ops = _ops()
+    d, S = 4096, 5
+    res, _ = _rand((400, d), torch.float32, 21)
+    part, _ = _rand((S, 400, d), torch.float32, 22, 0.3)
+    w, _ = _rand((d,), torch.float32, 23)
+    many = torch.empty((400, d), dtype=torch.bfloat16, device=DEV)
+    r1 = res.clone()
+    ops.add_rmsnorm(r1, ops.Partials(part), w, 1e-6, many)
+    one = torch.empty((1, d), dtype=torch.float32, device=DEV)
+    many32 = torch.empty((400, d), dtype=torch.float32, device=DEV)
+    ops.add_rmsnorm(res.clone(), ops.Partials(part), w, 1e-6, many32)
+    r2 = res[123:124].clone()
+    ops.add_rmsnorm(r2, ops.Partials(part[:, 123:124].contiguous()), w, 1e-6, one)
+    assert torch.equal(one[0], many32[123]) and torch.equal(r2[0], r1[123])
+
+
 def test_add_rmsnorm_refuses_what_it_cannot_hold():
     ops = _ops()
     d = 60000
