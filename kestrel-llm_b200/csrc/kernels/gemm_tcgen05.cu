@@ -241,6 +241,167 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
+// ------------------------------------------------------------------- persistent kernel
+// Many tokens (T > 256): one CTA per SM walks over output tiles (tile = blockIdx.x + i *
+// gridDim.x) and keeps TWO accumulators in TMEM (2 x 256 columns), so that the epilogue warps
+// drain tile i while the MMA thread already accumulates tile i+1 and the loader runs ahead
+// across tile boundaries.  PARTIAL uses tiles of 128 features x 256 tokens; SWIGLU tiles of
+// (128 gate + 128 up) features x 128 tokens, which moves the same bytes per FLOP.
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                          void *__restrict__ out, int T, int N, int K, long long ldo, int stages, int up_row_offset,
+                          int tiles_n, int tiles_total) {
+    pdl_launch_dependents();
+    constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
+    constexpr uint32_t B_BYTES = BN * TC_BK * 2;
+    constexpr uint32_t STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
+    constexpr uint32_t ACC_COLS = A_TILES * BN;
+    static_assert(ACC_COLS == 256, "two accumulators of 256 columns fill the 512 columns of TMEM");
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint32_t bars = base + (uint32_t)stages * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (stages + s); };
+    auto acc_full = [&](int b) { return bars + 16u * stages + 8u * b; };
+    auto acc_empty = [&](int b) { return bars + 16u * stages + 16u + 8u * b; };
+    uint32_t tmem_slot = bars + 16u * stages + 32u;
+    volatile uint32_t *tmem_slot_ptr = (volatile uint32_t *)(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int num_kb = (K + TC_BK - 1) / TC_BK;
+
+    if (warp == 0) {
+        if (lane < stages) { mbar_init(full_bar(lane), 1); mbar_init(empty_bar(lane), 1); }
+        if (lane >= 28 && lane < 30) mbar_init(acc_full(lane - 28), 1);
+        if (lane >= 30) mbar_init(acc_empty(lane - 30), 4);              // one arrival per epilogue warp
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    uint32_t tmem = 0;
+    if (warp != 0) {
+        if (warp == 1) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        tc_fence_before();
+        asm volatile("bar.sync 1, %0;" ::"n"(TC_THREADS - 32) : "memory");
+        tc_fence_after();
+        tmem = *tmem_slot_ptr;
+    }
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
+                int n0 = (tile % tiles_n) * TC_BM, t0 = (tile / tiles_n) * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1)) { atomicExch(&g_tc_error, 1); ok = false; break; }
+                    mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+                    uint32_t sa = base + (uint32_t)stage * STAGE_BYTES;
+                    int kc = kb * TC_BK;
+                    tma_load_2d(sa, &map_w, full_bar(stage), kc, n0);
+                    if (MODE == TC_SWIGLU) tma_load_2d(sa + A_BYTES, &map_w, full_bar(stage), kc, up_row_offset + n0);
+                    tma_load_2d(sa + A_TILES * A_BYTES, &map_x, full_bar(stage), kc, t0);
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int j = 0;
+            for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x, ++j) {
+                int b = j & 1;
+                uint32_t acc_phase = (uint32_t)(j >> 1) & 1u;
+                if (!mbar_wait(acc_empty(b), acc_phase ^ 1)) { atomicExch(&g_tc_error, 4); ok = false; break; }
+                tc_fence_after();
+                uint32_t d = tmem + (uint32_t)b * ACC_COLS;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase)) { atomicExch(&g_tc_error, 2); ok = false; break; }
+                    tc_fence_after();
+                    uint32_t sa = base + (uint32_t)stage * STAGE_BYTES;
+                    uint64_t da = smem_desc(sa), db = smem_desc(sa + A_TILES * A_BYTES);
+#pragma unroll
+                    for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
+                        uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
+                        tc_mma(d, da + 2 * k4, db + 2 * k4, IDESC, acc);
+                        if (MODE == TC_SWIGLU) tc_mma(d + BN, smem_desc(sa + A_BYTES) + 2 * k4, db + 2 * k4, IDESC, acc);
+                    }
+                    tc_commit(empty_bar(stage));
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+                tc_commit(acc_full(b));
+            }
+        }
+    } else {
+        int q = warp & 3;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++j) {
+            int b = j & 1;
+            uint32_t acc_phase = (uint32_t)(j >> 1) & 1u;
+            int n0 = (tile % tiles_n) * TC_BM, t0 = (tile / tiles_n) * BN;
+            int n = n0 + 32 * q + lane;
+            if (!mbar_wait(acc_full(b), acc_phase)) { if (lane == 0) atomicExch(&g_tc_error, 3); break; }
+            tc_fence_after();
+            uint32_t d = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)b * ACC_COLS;
+            int valid = min(BN, T - t0);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (c >= valid) break;
+                float g[16];
+                tc_ld16(d + c, g);
+                if (MODE == TC_SWIGLU) {
+                    float u[16];
+                    tc_ld16(d + BN + c, u);
+                    __nv_bfloat16 *o = (__nv_bfloat16 *)out;
+                    if (n < N) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj)
+                            if (c + jj < valid) {
+                                float a = g[jj] / (1.0f + expf(-g[jj]));
+                                o[(size_t)(t0 + c + jj) * ldo + n] = __float2bfloat16_rn(a * u[jj]);
+                            }
+                    }
+                } else {
+                    float *o = (float *)out;
+                    if (n < N) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj)
+                            if (c + jj < valid) o[(size_t)(t0 + c + jj) * ldo + n] = g[jj];
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(b));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -309,8 +470,11 @@ KESTREL_API int kestrel_gemm_tc_supported(const void *x, const void *w, int T, i
 // g_ctas_per_sm CTAs share an SM's shared memory for their stages; a CTA costs about
 // g_overhead_kb k-blocks of time beyond its own k-blocks (launch, barrier set-up, TMEM
 // allocation, first tensor-map fetch, pipeline fill, epilogue).
+static int g_persistent = 1;       // many-token products on the persistent kernel (0: one tile per CTA)
 static int g_overhead_kb = 6;
 static int g_ctas_per_sm = 2;
+
+KESTREL_API void kestrel_gemm_tc_set_persistent(int on) { g_persistent = on ? 1 : 0; }
 
 KESTREL_API void kestrel_gemm_tc_set_tuning(int overhead_kb, int ctas_per_sm) {
     if (overhead_kb >= 0) g_overhead_kb = overhead_kb;
@@ -367,15 +531,44 @@ static int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, void *out, in
     return kestrel_check_launch("gemm_tc");
 }
 
+template <int BN, int MODE>
+static int launch_tc_persistent(const CUtensorMap &mw, const CUtensorMap &mx, void *out, int T, int N, int K,
+                                long long ldo, int up_off, cudaStream_t stream) {
+    constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
+    constexpr int STAGE_BYTES = A_TILES * TC_BM * TC_BK * 2 + BN * TC_BK * 2;
+    int stages = (200 * 1024) / STAGE_BYTES;
+    if (stages > 8) stages = 8;
+    size_t smem = (size_t)stages * STAGE_BYTES + 16 * stages + 48 + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return kestrel_fail(-3, "gemm_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    int tiles_n = (N + TC_BM - 1) / TC_BM, tiles_t = (T + BN - 1) / BN;
+    long long total = (long long)tiles_n * tiles_t;
+    if (total > 0x7fffffff) return kestrel_fail(-2, "gemm_tc: too many tiles");
+    int grid = total < 148 ? (int)total : 148;
+    kestrel_launch(gemm_tc_persistent_kernel<BN, MODE>, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, out, T, N, K, ldo,
+                   stages, up_off, tiles_n, (int)total);
+    return kestrel_check_launch("gemm_tc_persistent");
+}
+
 template <int MODE>
 static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, int w_rows, int K, long long ldx, long long ldw,
                        long long ldo, int splits, long long slice_stride, int up_off, cudaStream_t stream) {
     int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    bool persistent = T > 256 && splits == 1 && g_persistent;
+    if (persistent && MODE == TC_SWIGLU) bn = 128;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, w_rows, K, ldw, TC_BM);
     if (rc) return rc;
     rc = make_map(&mx, x, T, K, ldx, bn);
     if (rc) return rc;
+    if (persistent) {
+        if (MODE == TC_SWIGLU) return launch_tc_persistent<128, TC_SWIGLU>(mw, mx, out, T, N, K, ldo, up_off, stream);
+        return launch_tc_persistent<256, TC_PARTIAL>(mw, mx, out, T, N, K, ldo, up_off, stream);
+    }
     switch (bn) {
         case 16: return launch_tc<16, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
         case 32: return launch_tc<32, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
@@ -406,7 +599,7 @@ KESTREL_API int kestrel_gemm_tc_swiglu(const void *x, const void *w, void *out, 
 
 // Reads (and clears) the error word that a bounded wait sets when it runs out: 0 = none,
 // 1 = the loader waited for a free stage, 2 = the MMA thread waited for data, 3 = the epilogue
-// waited for the accumulator.  Synchronises the device.
+// waited for the accumulator, 4 = the MMA thread waited for a drained accumulator.  Synchronises the device.
 KESTREL_API int kestrel_gemm_tc_error(void) {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;

@@ -51,7 +51,7 @@ def test_gemm_plain_is_the_same_for_any_batch():
 
 @pytest.mark.parametrize("T,N,K,splits", [(1, 509, 96, None), (8, 4096, 4096, None), (37, 200, 96, 1), (130, 96, 200, 1),
                                           (65, 1000, 776, 3), (16, 128, 64, 1), (17, 129, 72, 1), (300, 640, 512, None),
-                                          (2048, 384, 256, 1), (64, 6144, 1024, 2), (3, 260, 4096, None)])
+                                          (2048, 384, 256, 1), (64, 6144, 1024, 2), (3, 260, 4096, None), (600, 40000, 512, 1), (257, 129, 8, 1)])
 def test_gemm_tcgen05(T, N, K, splits):
     """The tensor-core product against the CUDA-core product of the same bfloat16 operands."""
     ops = _ops()
@@ -79,7 +79,7 @@ def test_gemm_tcgen05_row_does_not_depend_on_the_batch():
     assert torch.equal(one[0], full[41])
 
 
-@pytest.mark.parametrize("T,ff,K", [(5, 200, 96), (300, 200, 96), (257, 640, 512), (1024, 384, 320)])
+@pytest.mark.parametrize("T,ff,K", [(5, 200, 96), (300, 200, 96), (257, 640, 512), (1024, 384, 320), (700, 20000, 256)])
 def test_gemm_tcgen05_swiglu(T, ff, K):
     ops = _ops()
     x, xr = _rand((T, K), torch.bfloat16, 5)
