@@ -6,8 +6,8 @@
 // step, flattened token-major: row r is token r / G, head r % G (G = query heads per kv head),
 // so the G heads that share a kv head read its keys and values once.  A CTA takes a tile of
 // rows of one (request, kv head) and a slice of the key range:
-//   * ROWS mode (tile of 64 rows): each of the 4 warps owns 16 rows and walks all keys of the
-//     slice in tiles of 64 - prompt portions;
+//   * ROWS mode (tile of 128 rows, 64 for head sizes above 128): each of the 4 warps owns 32
+//     (16) rows and walks all keys of the slice in tiles of 64 - prompt portions;
 //   * KEYS mode (tile of 16 rows): all warps share the 16 rows, each takes 16 keys of every
 //     64-key tile, and the four running (max, sum, out) states are merged in warp order at
 //     the end - decode tokens, where rows are few and keys many.
@@ -26,6 +26,7 @@
 
 #define AM_THREADS 128
 #define AM_BN 64            // keys per tile
+#define AM_ROWS_MT 2        // 16-row tiles per warp in ROWS mode (head sizes up to 128): a tile of 128 rows per CTA
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
     int sz = valid ? 16 : 0;
@@ -47,6 +48,11 @@ __device__ __forceinline__ void mma_bf16(float *c, const uint32_t *a, uint32_t b
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {          // 2^x, 2 ulp; 2^(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -70,12 +76,13 @@ struct AttnParams {
     float scale_log2;
 };
 
-template <int HD, bool KEYS_MODE>
+template <int HD, bool KEYS_MODE, int MT>
 __global__ void __launch_bounds__(AM_THREADS)
 attention_mma_kernel(const AttnParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int BM = KEYS_MODE ? 16 : 64;
+    static_assert(!KEYS_MODE || MT == 1, "KEYS mode has one 16-row tile");
+    constexpr int BM = KEYS_MODE ? 16 : 64 * MT;       // ROWS mode: each warp owns MT tiles of 16 rows
     constexpr int LDS = HD + 8;                       // padded row, in elements: ldmatrix without bank conflicts
     constexpr int KS = HD / 16;                       // k-steps of the QK product
     constexpr int NT_S = KEYS_MODE ? 2 : 8;           // 8-key tiles of a warp's score block
@@ -157,22 +164,36 @@ attention_mma_kernel(const AttnParams p) {
     }
 
     // ---- per-thread state ----------------------------------------------------------------
-    // a warp's 16 rows: ROWS mode rows 16*warp.., KEYS mode rows 0..15 for every warp
-    const int wrow0 = KEYS_MODE ? 0 : 16 * warp;
-    const int r_lo = wrow0 + (lane >> 2), r_hi = r_lo + 8;     // the two rows this thread holds
-    int pos_r[2], lo_r[2];
+    // a warp's rows: ROWS mode rows 16*MT*warp.. (MT tiles of 16), KEYS mode rows 0..15 for every warp
+    const int wrow0 = KEYS_MODE ? 0 : 16 * MT * warp;
+    int pos_r[MT][2], lo_r[MT][2];
+    int min_pos = 0x7fffffff, max_lo = 0;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        int r = i ? r_hi : r_lo;
-        bool ok = r < rows_here;
-        int ps = pos_begin + (row0 + r) / G;
-        pos_r[i] = ok ? ps : -1;                               // an absent row sees no key
-        lo_r[i] = p.window > 0 ? max(0, ps - p.window + 1) : 0;
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            int r = wrow0 + 16 * mt + (lane >> 2) + 8 * i;     // the rows this thread holds
+            bool ok = r < rows_here;
+            int ps = pos_begin + (row0 + r) / G;
+            pos_r[mt][i] = ok ? ps : -1;                       // an absent row sees no key
+            lo_r[mt][i] = p.window > 0 ? max(0, ps - p.window + 1) : 0;
+            min_pos = min(min_pos, pos_r[mt][i]);
+            max_lo = max(max_lo, lo_r[mt][i]);
+        }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {                   // over the warp: tiles every row sees whole need no mask
+        min_pos = min(min_pos, __shfl_xor_sync(0xffffffffu, min_pos, off));
+        max_lo = max(max_lo, __shfl_xor_sync(0xffffffffu, max_lo, off));
     }
-    float o[NT_O][4];
+    float o[MT][NT_O][4];
+    float m_r[MT][2], l_r[MT][2];
 #pragma unroll
-    for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.f;
+        m_r[mt][0] = m_r[mt][1] = -INFINITY;
+        l_r[mt][0] = l_r[mt][1] = 0.f;
+    }
     const bool warp_active = KEYS_MODE ? true : (wrow0 < rows_here);
 
     for (int t = 0; t < n_tiles; ++t) {
@@ -185,77 +206,108 @@ attention_mma_kernel(const AttnParams p) {
             const int kbase = k_lo + t * AM_BN + (KEYS_MODE ? 16 * warp : 0);
             const __nv_bfloat16 *Kt = Ks + ((size_t)stage * AM_BN + (KEYS_MODE ? 16 * warp : 0)) * LDS;
             const __nv_bfloat16 *Vt = Vs + ((size_t)stage * AM_BN + (KEYS_MODE ? 16 * warp : 0)) * LDS;
-            if (kbase < k_hi) {
-                float s[NT_S][4];
+            if (kbase < k_hi && kbase <= pos_begin + last_tok) {
+                float s[MT][NT_S][4];
 #pragma unroll
-                for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int i = 0; i < NT_S; ++i) s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.f;
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
-                    uint32_t a[4];
-                    // A fragment of Q: rows wrow0 + (lane % 16), columns 16 ks + 8 (lane / 16)
-                    ldmatrix_x4((uint32_t)__cvta_generic_to_shared(Qs + (wrow0 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8),
-                                a[0], a[1], a[2], a[3]);
+                    uint32_t a[MT][4];
+                    // A fragments of Q: rows wrow0 + 16 mt + (lane % 16), columns 16 ks + 8 (lane / 16)
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+                        ldmatrix_x4((uint32_t)__cvta_generic_to_shared(Qs + (wrow0 + 16 * mt + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8),
+                                    a[mt][0], a[mt][1], a[mt][2], a[mt][3]);
 #pragma unroll
                     for (int np = 0; np < NT_S / 2; ++np) {
                         uint32_t b0, b1, b2, b3;
                         // keys 16 np + (lane % 8) + 8 (lane / 16), dims 16 ks + 8 ((lane / 8) % 2)
                         ldmatrix_x4((uint32_t)__cvta_generic_to_shared(Kt + (np * 16 + (lane & 7) + ((lane >> 4) << 3)) * LDS + ks * 16 + ((lane >> 3) & 1) * 8),
                                     b0, b1, b2, b3);
-                        mma_bf16(s[2 * np], a, b0, b1);
-                        mma_bf16(s[2 * np + 1], a, b2, b3);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            mma_bf16(s[mt][2 * np], a[mt], b0, b1);
+                            mma_bf16(s[mt][2 * np + 1], a[mt], b2, b3);
+                        }
                     }
                 }
-                // scale, mask, running maximum
-                float mx[2] = {-INFINITY, -INFINITY};
+                // scale, mask (only on tiles that some row of the warp does not see whole), running maximum
+                const bool whole = kbase >= k_first && kbase + 8 * NT_S <= k_hi && kbase + 8 * NT_S - 1 <= min_pos && kbase >= max_lo;
 #pragma unroll
-                for (int nt = 0; nt < NT_S; ++nt)
+                for (int mt = 0; mt < MT; ++mt) {
+                    float mx[2] = {-INFINITY, -INFINITY};
+                    if (whole) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        int i = e >> 1;
-                        int key = kbase + nt * 8 + 2 * (lane & 3) + (e & 1);
-                        float v = s[nt][e] * p.scale_log2;
-                        bool ok = key <= pos_r[i] && key >= lo_r[i] && key < k_hi && key >= k_first;
-                        v = ok ? v : -INFINITY;
-                        s[nt][e] = v;
-                        mx[i] = fmaxf(mx[i], v);
+                        for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                float v = s[mt][nt][e] * p.scale_log2;
+                                s[mt][nt][e] = v;
+                                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                            }
+                    } else {
+#pragma unroll
+                        for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                int i = e >> 1;
+                                int key = kbase + nt * 8 + 2 * (lane & 3) + (e & 1);
+                                float v = s[mt][nt][e] * p.scale_log2;
+                                bool ok = key <= pos_r[mt][i] && key >= lo_r[mt][i] && key < k_hi && key >= k_first;
+                                v = ok ? v : -INFINITY;
+                                s[mt][nt][e] = v;
+                                mx[i] = fmaxf(mx[i], v);
+                            }
                     }
-                float alpha[2], m_use[2];
+                    float alpha[2], m_use[2];
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
-                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-                    float mn = fmaxf(m_r[i], mx[i]);
-                    m_use[i] = mn == -INFINITY ? 0.f : mn;                 // a row that has seen no key yet
-                    alpha[i] = exp2f(m_r[i] - m_use[i]);                   // exp2(-inf) = 0 on the first keys
-                    m_r[i] = mn;
-                    l_r[i] *= alpha[i];
-                }
-#pragma unroll
-                for (int nt = 0; nt < NT_O; ++nt) {
-                    o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0];
-                    o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
-                }
-#pragma unroll
-                for (int nt = 0; nt < NT_S; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float pv = exp2f(s[nt][e] - m_use[e >> 1]);
-                        s[nt][e] = pv;
-                        l_r[e >> 1] += pv;
+                    for (int i = 0; i < 2; ++i) {
+                        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                        float mn = fmaxf(m_r[mt][i], mx[i]);
+                        m_use[i] = mn == -INFINITY ? 0.f : mn;             // a row that has seen no key yet
+                        alpha[i] = fast_exp2(m_r[mt][i] - m_use[i]);       // exp2(-inf) = 0 on the first keys
+                        m_r[mt][i] = mn;
+                        l_r[mt][i] *= alpha[i];
                     }
+#pragma unroll
+                    for (int nt = 0; nt < NT_O; ++nt) {
+                        o[mt][nt][0] *= alpha[0]; o[mt][nt][1] *= alpha[0];
+                        o[mt][nt][2] *= alpha[1]; o[mt][nt][3] *= alpha[1];
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float pv = fast_exp2(s[mt][nt][e] - m_use[e >> 1]);
+                            s[mt][nt][e] = pv;
+                            l_r[mt][e >> 1] += pv;
+                        }
+                }
                 // out += P V
 #pragma unroll
                 for (int kk = 0; kk < NT_S / 2; ++kk) {
-                    uint32_t a[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
-                                     pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+                    uint32_t a[MT][4];
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        a[mt][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+                        a[mt][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+                        a[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+                        a[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+                    }
 #pragma unroll
                     for (int dp = 0; dp < NT_O / 2; ++dp) {
                         uint32_t b0, b1, b2, b3;
                         // keys 16 kk + (lane % 8) + 8 ((lane / 8) % 2), dims 16 dp + 8 (lane / 16), transposed
                         ldmatrix_x4_trans((uint32_t)__cvta_generic_to_shared(Vt + (kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * LDS + dp * 16 + (lane >> 4) * 8),
                                           b0, b1, b2, b3);
-                        mma_bf16(o[2 * dp], a, b0, b1);
-                        mma_bf16(o[2 * dp + 1], a, b2, b3);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            mma_bf16(o[mt][2 * dp], a[mt], b0, b1);
+                            mma_bf16(o[mt][2 * dp + 1], a[mt], b2, b3);
+                        }
                     }
                 }
             }
@@ -265,10 +317,12 @@ attention_mma_kernel(const AttnParams p) {
 
     // row sums across the four threads of a row
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        l_r[i] += __shfl_xor_sync(0xffffffffu, l_r[i], 1);
-        l_r[i] += __shfl_xor_sync(0xffffffffu, l_r[i], 2);
-    }
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            l_r[mt][i] += __shfl_xor_sync(0xffffffffu, l_r[mt][i], 1);
+            l_r[mt][i] += __shfl_xor_sync(0xffffffffu, l_r[mt][i], 2);
+        }
 
     if (KEYS_MODE) {
         // merge the four warps' states in warp order through shared memory (reuses the K stages)
@@ -278,14 +332,14 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
         for (int nt = 0; nt < NT_O; ++nt) {
             int d = nt * 8 + 2 * (lane & 3);
-            *reinterpret_cast<float2 *>(mo + ((size_t)warp * 16 + (lane >> 2)) * HD + d) = make_float2(o[nt][0], o[nt][1]);
-            *reinterpret_cast<float2 *>(mo + ((size_t)warp * 16 + (lane >> 2) + 8) * HD + d) = make_float2(o[nt][2], o[nt][3]);
+            *reinterpret_cast<float2 *>(mo + ((size_t)warp * 16 + (lane >> 2)) * HD + d) = make_float2(o[0][nt][0], o[0][nt][1]);
+            *reinterpret_cast<float2 *>(mo + ((size_t)warp * 16 + (lane >> 2) + 8) * HD + d) = make_float2(o[0][nt][2], o[0][nt][3]);
         }
         if ((lane & 3) == 0) {
-            mml[(warp * 16 + (lane >> 2)) * 2] = m_r[0];
-            mml[(warp * 16 + (lane >> 2)) * 2 + 1] = l_r[0];
-            mml[(warp * 16 + (lane >> 2) + 8) * 2] = m_r[1];
-            mml[(warp * 16 + (lane >> 2) + 8) * 2 + 1] = l_r[1];
+            mml[(warp * 16 + (lane >> 2)) * 2] = m_r[0][0];
+            mml[(warp * 16 + (lane >> 2)) * 2 + 1] = l_r[0][0];
+            mml[(warp * 16 + (lane >> 2) + 8) * 2] = m_r[0][1];
+            mml[(warp * 16 + (lane >> 2) + 8) * 2 + 1] = l_r[0][1];
         }
         __syncthreads();
         // thread -> (row, 8-dim group): 16 rows x HD/8 groups
@@ -322,30 +376,32 @@ attention_mma_kernel(const AttnParams p) {
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            int r = i ? r_hi : r_lo;
-            if (r >= rows_here) continue;
-            int row = row0 + r;
-            int tok = tok_begin + row / G, head = kvh * G + row % G;
-            size_t qrow = (size_t)tok * p.nq + head;
-            if (p.slices > 1) {
-                float *po = p.part_o + (qrow * p.slices + slice) * hd;
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int nt = 0; nt < NT_O; ++nt) {
-                    int d = nt * 8 + 2 * (lane & 3);
-                    if (d < hd) { po[d] = o[nt][2 * i]; po[d + 1] = o[nt][2 * i + 1]; }
-                }
-                if ((lane & 3) == 0) { p.part_ml[(qrow * p.slices + slice) * 2] = m_r[i]; p.part_ml[(qrow * p.slices + slice) * 2 + 1] = l_r[i]; }
-            } else {
-                float inv = 1.0f / l_r[i];
-                __nv_bfloat16 *po = p.out + qrow * hd;
+            for (int i = 0; i < 2; ++i) {
+                int r = wrow0 + 16 * mt + (lane >> 2) + 8 * i;
+                if (r >= rows_here) continue;
+                int row = row0 + r;
+                int tok = tok_begin + row / G, head = kvh * G + row % G;
+                size_t qrow = (size_t)tok * p.nq + head;
+                if (p.slices > 1) {
+                    float *po = p.part_o + (qrow * p.slices + slice) * hd;
 #pragma unroll
-                for (int nt = 0; nt < NT_O; ++nt) {
-                    int d = nt * 8 + 2 * (lane & 3);
-                    if (d < hd) *reinterpret_cast<__nv_bfloat162 *>(po + d) = __floats2bfloat162_rn(o[nt][2 * i] * inv, o[nt][2 * i + 1] * inv);
+                    for (int nt = 0; nt < NT_O; ++nt) {
+                        int d = nt * 8 + 2 * (lane & 3);
+                        if (d < hd) { po[d] = o[mt][nt][2 * i]; po[d + 1] = o[mt][nt][2 * i + 1]; }
+                    }
+                    if ((lane & 3) == 0) { p.part_ml[(qrow * p.slices + slice) * 2] = m_r[mt][i]; p.part_ml[(qrow * p.slices + slice) * 2 + 1] = l_r[mt][i]; }
+                } else {
+                    float inv = 1.0f / l_r[mt][i];
+                    __nv_bfloat16 *po = p.out + qrow * hd;
+#pragma unroll
+                    for (int nt = 0; nt < NT_O; ++nt) {
+                        int d = nt * 8 + 2 * (lane & 3);
+                        if (d < hd) *reinterpret_cast<__nv_bfloat162 *>(po + d) = __floats2bfloat162_rn(o[mt][nt][2 * i] * inv, o[mt][nt][2 * i + 1] * inv);
+                    }
                 }
             }
-        }
     }
 }
 
@@ -382,22 +438,25 @@ __global__ void attention_merge_kernel(const float *__restrict__ part_o, const f
     }
 }
 
-template <int HD, bool KEYS_MODE>
+template <int HD, bool KEYS_MODE, int MT>
 static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream) {
-    constexpr int BM = KEYS_MODE ? 16 : 64;
+    constexpr int BM = KEYS_MODE ? 16 : 64 * MT;
     constexpr int LDS = HD + 8;
     constexpr int STAGES = KEYS_MODE ? 3 : 2;
     size_t smem = (size_t)(BM + 2 * STAGES * AM_BN) * LDS * 2;
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, KEYS_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, KEYS_MODE, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return kestrel_fail(-3, "attention_mma: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
         attr_set = true;
     }
     dim3 grid(tiles, p.nkv, p.slices);
-    kestrel_launch(attention_mma_kernel<HD, KEYS_MODE>, dim3(grid), dim3(AM_THREADS), smem, stream, p);
+    kestrel_launch(attention_mma_kernel<HD, KEYS_MODE, MT>, dim3(grid), dim3(AM_THREADS), smem, stream, p);
     return kestrel_check_launch("attention_mma");
 }
+
+// rows (token, head) of a ROWS-mode tile for this head size
+KESTREL_API int kestrel_attention_mma_rows_per_tile(int hd) { return hd <= 128 ? 64 * AM_ROWS_MT : 64; }
 
 // CTAs of the KEYS-mode kernel that the GPU's 148 SMs hold at once, by shared memory and threads
 KESTREL_API int kestrel_attention_mma_slots(int hd) {
@@ -422,7 +481,9 @@ KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const 
     if (T == 0 || tiles == 0) return 0;
     KESTREL_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_mma: %d query heads over %d kv heads", nq, nkv);
     KESTREL_REQUIRE(hd > 0 && hd % 8 == 0 && hd <= 256, "attention_mma: head size %d is not a multiple of 8 up to 256", hd);
-    KESTREL_REQUIRE(rows_per_tile == 16 || rows_per_tile == 64, "attention_mma: tiles of %d rows", rows_per_tile);
+    int rows_mode_tile = hd <= 128 ? 64 * AM_ROWS_MT : 64;
+    KESTREL_REQUIRE(rows_per_tile == 16 || rows_per_tile == rows_mode_tile,
+                    "attention_mma: tiles of %d rows; head size %d takes 16 or %d", rows_per_tile, hd, rows_mode_tile);
     KESTREL_REQUIRE(slices >= 1 && slice_len > 0 && slice_len % AM_BN == 0, "attention_mma: slice length %d must be a positive multiple of %d", slice_len, AM_BN);
     KESTREL_REQUIRE(slices == 1 || (part_o && part_ml), "attention_mma: %d slices without scratch", slices);
     KESTREL_REQUIRE(nkv <= 65535 && slices <= 65535, "attention_mma: grid too large");
@@ -435,10 +496,10 @@ KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const 
     p.scale_log2 = scale * 1.4426950408889634f;
     bool keys = rows_per_tile == 16;
     int rc;
-    if (hd <= 32) rc = keys ? launch_attention<32, true>(p, tiles, stream) : launch_attention<32, false>(p, tiles, stream);
-    else if (hd <= 64) rc = keys ? launch_attention<64, true>(p, tiles, stream) : launch_attention<64, false>(p, tiles, stream);
-    else if (hd <= 128) rc = keys ? launch_attention<128, true>(p, tiles, stream) : launch_attention<128, false>(p, tiles, stream);
-    else rc = keys ? launch_attention<256, true>(p, tiles, stream) : launch_attention<256, false>(p, tiles, stream);
+    if (hd <= 32) rc = keys ? launch_attention<32, true, 1>(p, tiles, stream) : launch_attention<32, false, AM_ROWS_MT>(p, tiles, stream);
+    else if (hd <= 64) rc = keys ? launch_attention<64, true, 1>(p, tiles, stream) : launch_attention<64, false, AM_ROWS_MT>(p, tiles, stream);
+    else if (hd <= 128) rc = keys ? launch_attention<128, true, 1>(p, tiles, stream) : launch_attention<128, false, AM_ROWS_MT>(p, tiles, stream);
+    else rc = keys ? launch_attention<256, true, 1>(p, tiles, stream) : launch_attention<256, false, 1>(p, tiles, stream);
     if (rc) return rc;
     if (slices > 1) {
         KESTREL_REQUIRE(keys, "attention_mma: slices are merged for tiles of 16 rows only");

@@ -71,6 +71,7 @@ def _declare(lib) -> None:
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _vp, _f, _vp],
         "kestrel_attention_mma_slots": [_i],
+        "kestrel_attention_mma_rows_per_tile": [_i],
         "kestrel_argmax": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp],
         "kestrel_argmax_chunks": [_i],
         "kestrel_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -435,7 +436,8 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
         attention_plain(q, k_cache, v_cache, batch.positions, batch.seq_of_token, block_table, page_size,
                         out, nq, nkv, hd, window, scale)
         return
-    plan = batch.attention_plan(nq // nkv)
+    rows_large = library().kestrel_attention_mma_rows_per_tile(hd)
+    plan = batch.attention_plan(nq // nkv, rows_large)
     no_split = (1 << 30) // 64 * 64
     if plan.small is not None:
         tl = plan.small
@@ -462,5 +464,5 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
                       page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
     if plan.large is not None:
         tl = plan.large
-        attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, 64, batch.cu_seqlens, batch.kv_lens, block_table,
-                      page_size, nq, nkv, hd, window, scale, 1, no_split)
+        attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, rows_large, batch.cu_seqlens, batch.kv_lens,
+                      block_table, page_size, nq, nkv, hd, window, scale, 1, no_split)

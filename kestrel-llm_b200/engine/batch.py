@@ -121,12 +121,12 @@ class StepBatch:
         self.bytes_h2d = int(host.nbytes)
         self._plans = {}
 
-    def attention_plan(self, group_size: int) -> "AttentionPlan":
+    def attention_plan(self, group_size: int, rows_large: int = 64) -> "AttentionPlan":
         """How the tensor-core attention kernel tiles this step's rows for mixers with
         ``group_size`` query heads per kv head: requests with at most 16 rows (token, head) go
-        into tiles of 16 rows, the others into tiles of 64.  Built once per step and group
-        size; the tile lists are a second, small copy to the device."""
-        plan = self._plans.get(group_size)
+        into tiles of 16 rows, the others into tiles of ``rows_large``.  Built once per step and
+        (group size, tile size); the tile lists are a second, small copy to the device."""
+        plan = self._plans.get((group_size, rows_large))
         if plan is None:
             small_s, small_r, large_s, large_r = [], [], [], []
             small_kv = large_kv = 0
@@ -137,7 +137,7 @@ class StepBatch:
                     small_r.append(0)
                     small_kv = max(small_kv, self.kv_lens_host[i])
                 else:
-                    for r0 in range(0, rows, 64):
+                    for r0 in range(0, rows, rows_large):
                         large_s.append(i)
                         large_r.append(r0)
                     large_kv = max(large_kv, self.kv_lens_host[i])
@@ -151,7 +151,7 @@ class StepBatch:
             plan = AttentionPlan(
                 TileList(dev[:ns], dev[ns:2 * ns], ns, small_kv) if ns else None,
                 TileList(dev[2 * ns:2 * ns + nl], dev[2 * ns + nl:], nl, large_kv) if nl else None)
-            self._plans[group_size] = plan
+            self._plans[(group_size, rows_large)] = plan
         return plan
 
     def block_table(self, group: int) -> torch.Tensor:

@@ -70,7 +70,7 @@ class StaticDecodeBatch:
     def block_table(self, group: int) -> torch.Tensor:
         return self._tables[group]
 
-    def attention_plan(self, group_size: int) -> AttentionPlan:
+    def attention_plan(self, group_size: int, rows_large: int = 64) -> AttentionPlan:
         if group_size > 16:
             raise RuntimeError("a captured decode step needs at most 16 query heads per kv head")
         return AttentionPlan(TileList(self.seq_of_token, self._tile_row0, self.size, 0, self.slice_len_table), None)

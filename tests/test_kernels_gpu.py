@@ -285,7 +285,8 @@ def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slic
                                                    (32, 8, 128, 0, 16), (40, 2, 64, 0, 16)])
 def test_attention_mma_prompt_portions(nq, nkv, hd, window, page):
     """ROWS mode: portions of three requests, one of them from position 0, one deep into its context."""
-    _mma_case(nq, nkv, hd, window, page, lens_new=(50, 3, 130), lens_ctx=(100, 0, 77), rows_per_tile=64,
+    _mma_case(nq, nkv, hd, window, page, lens_new=(50, 3, 130), lens_ctx=(100, 0, 77),
+              rows_per_tile=_ops().library().kestrel_attention_mma_rows_per_tile(hd),
               slices=1, slice_len=(1 << 30) // 64 * 64, seed=hd)
 
 
@@ -315,7 +316,7 @@ def test_attention_mma_finds_one_far_key(far, mode):
     if far >= L - n_new + 1 and mode == "portion":
         pytest.skip("the key lies inside the portion: earlier queries do not see it")
     G = nq // nkv
-    rpt = 16 if mode != "portion" else 64
+    rpt = 16 if mode != "portion" else ops.library().kestrel_attention_mma_rows_per_tile(hd)
     tiles = list(range(0, n_new * G, rpt))
     dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
     out = torch.empty((n_new, nq * hd), dtype=torch.bfloat16, device=DEV)
