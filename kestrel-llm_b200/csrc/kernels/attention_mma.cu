@@ -59,22 +59,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
-struct AttnParams {
-    const __nv_bfloat16 *q;         // [T, nq * hd]
-    const __nv_bfloat16 *k_cache;   // [pages, nkv, page_size, hd]
-    const __nv_bfloat16 *v_cache;
-    __nv_bfloat16 *out;             // [T, nq * hd]
-    float *part_o;                  // [T * nq, slices, hd]   (slices > 1)
-    float *part_ml;                 // [T * nq, slices, 2]
-    const int *tile_seq;            // [tiles] request index of the tile
-    const int *tile_row0;           // [tiles] first row (token-major, head-minor) among the request's rows
-    const int *cu_seqlens;          // [nseq + 1] first token of each request in this step
-    const int *kv_lens;             // [nseq] request length after this step
-    const int *block_table;         // [nseq, table_stride]
-    const int *slice_len_ptr;       // if not null, the slice length is read from here (a step of a captured graph)
-    int table_stride, page_size, nq, nkv, hd, window, slices, slice_len;
-    float scale_log2;
-};
+#include "attention_params.cuh"
 
 template <int HD, bool KEYS_MODE, int MT>
 __global__ void __launch_bounds__(AM_THREADS)

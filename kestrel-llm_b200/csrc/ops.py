@@ -70,6 +70,8 @@ def _declare(lib) -> None:
         "kestrel_gemm_tc_error": [],
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _vp, _f, _vp],
+        "kestrel_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "kestrel_attention_tc_error": [],
         "kestrel_attention_mma_slots": [_i],
         "kestrel_attention_mma_rows_per_tile": [_i],
         "kestrel_argmax": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp],
@@ -423,6 +425,31 @@ def attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         launches += 1          # the merge kernel
 
 
+def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                 tile_seq: torch.Tensor, tile_row0: torch.Tensor, cu_seqlens: torch.Tensor, kv_lens: torch.Tensor,
+                 block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int, window: int, scale: float) -> None:
+    """tcgen05 attention of the listed tiles of 128 rows (prompt portions), head size 128."""
+    _need(q, "attention_tc.q", torch.bfloat16, 2)
+    _need(out, "attention_tc.out", torch.bfloat16, 2)
+    _need(k_cache, "attention_tc.k_cache", torch.bfloat16)
+    _need(v_cache, "attention_tc.v_cache", torch.bfloat16)
+    _need(block_table, "attention_tc.block_table", torch.int32, 2)
+    _need(tile_seq, "attention_tc.tile_seq", torch.int32, 1)
+    _need(tile_row0, "attention_tc.tile_row0", torch.int32, 1)
+    T, tiles = q.shape[0], tile_seq.shape[0]
+    if q.shape[1] != nq * hd or out.shape != q.shape or tile_row0.shape[0] != tiles:
+        raise KernelError("attention_tc: shapes differ")
+    _check(library().kestrel_attention_tc(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(),
+        tiles, cu_seqlens.data_ptr(), kv_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size),
+        T, nq, nkv, hd, int(window), float(scale), _stream()))
+
+
+def attention_tc_error() -> int:
+    """Error word of the tcgen05 attention kernel's bounded waits (0 = none); synchronises the device."""
+    return library().kestrel_attention_tc_error()
+
+
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch, block_table: torch.Tensor,
               page_size: int, out: torch.Tensor, nq: int, nkv: int, hd: int, window: int, scale: float) -> None:
     """Causal attention of this step's queries over their requests' cache pages.  ``batch``
@@ -431,7 +458,8 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
     float32 takes the plain kernel (one block per token and head, order of sums fixed per
     token).  bfloat16 takes the tensor-core kernel: requests with at most 16 (token, head) rows
     per kv head - decode tokens - in KEYS mode with the key range cut into slices so that the
-    grid fills the GPU, the others - prompt portions - in ROWS mode."""
+    grid fills the GPU, the others - prompt portions - on the tcgen05 kernel when the head size
+    is 128 and in ROWS mode of the mma.sync kernel otherwise."""
     if q.dtype != torch.bfloat16 or hd % 8 or hd > 256:
         attention_plain(q, k_cache, v_cache, batch.positions, batch.seq_of_token, block_table, page_size,
                         out, nq, nkv, hd, window, scale)
@@ -464,5 +492,9 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
                       page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
     if plan.large is not None:
         tl = plan.large
-        attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, rows_large, batch.cu_seqlens, batch.kv_lens,
-                      block_table, page_size, nq, nkv, hd, window, scale, 1, no_split)
+        if hd == 128 and rows_large == 128:
+            attention_tc(q, k_cache, v_cache, out, tl.seq, tl.row0, batch.cu_seqlens, batch.kv_lens, block_table,
+                         page_size, nq, nkv, hd, window, scale)
+        else:
+            attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, rows_large, batch.cu_seqlens, batch.kv_lens,
+                          block_table, page_size, nq, nkv, hd, window, scale, 1, no_split)

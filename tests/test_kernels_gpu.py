@@ -230,7 +230,7 @@ def test_attention_plain(dtype, nq, nkv, hd, window, page):
                                atol=tol * np.abs(ref).max())
 
 
-def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slices, slice_len, seed=0):
+def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slices, slice_len, seed=0, tc=False):
     """Several requests in one launch of the tensor-core kernel: request i holds lens_ctx[i]
     earlier tokens in its pages and lens_new[i] new ones whose queries run now."""
     ops = _ops()
@@ -271,9 +271,15 @@ def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slic
             tile_row0.append(r0)
     dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
     out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.attention_mma(torch.from_numpy(qcat).to(torch.bfloat16).to(DEV), torch.from_numpy(kc).to(torch.bfloat16).to(DEV),
-                      torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out, dev(tile_seq), dev(tile_row0), rows_per_tile,
-                      dev(cu), dev(total), dev(table), page, nq, nkv, hd, window, 1.0 / math.sqrt(hd), slices, slice_len)
+    if tc:
+        ops.attention_tc(torch.from_numpy(qcat).to(torch.bfloat16).to(DEV), torch.from_numpy(kc).to(torch.bfloat16).to(DEV),
+                         torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out, dev(tile_seq), dev(tile_row0), dev(cu),
+                         dev(total), dev(table), page, nq, nkv, hd, window, 1.0 / math.sqrt(hd))
+        assert ops.attention_tc_error() == 0
+    else:
+        ops.attention_mma(torch.from_numpy(qcat).to(torch.bfloat16).to(DEV), torch.from_numpy(kc).to(torch.bfloat16).to(DEV),
+                          torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out, dev(tile_seq), dev(tile_row0), rows_per_tile,
+                          dev(cu), dev(total), dev(table), page, nq, nkv, hd, window, 1.0 / math.sqrt(hd), slices, slice_len)
     ref = np.concatenate(refs).reshape(T, nq * hd)
     got = out.float().cpu().numpy()
     assert np.isfinite(got).all()
@@ -288,6 +294,40 @@ def test_attention_mma_prompt_portions(nq, nkv, hd, window, page):
     _mma_case(nq, nkv, hd, window, page, lens_new=(50, 3, 130), lens_ctx=(100, 0, 77),
               rows_per_tile=_ops().library().kestrel_attention_mma_rows_per_tile(hd),
               slices=1, slice_len=(1 << 30) // 64 * 64, seed=hd)
+
+
+@pytest.mark.parametrize("nq,nkv,window,page", [(32, 8, 0, 16), (8, 1, 0, 4), (4, 4, 100, 16), (6, 2, 0, 1), (5, 1, 33, 32)])
+def test_attention_tcgen05_prompt_portions(nq, nkv, window, page):
+    """The tcgen05 kernel (head size 128): portions of three requests, one from position 0, one
+    deep into its context, key tiles of 128 with the last one cut."""
+    _mma_case(nq, nkv, 128, window, page, lens_new=(50, 3, 300), lens_ctx=(100, 0, 77), rows_per_tile=128,
+              slices=1, slice_len=0, seed=nq, tc=True)
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 127, 128, 255, 256])
+def test_attention_tcgen05_finds_one_far_key(far):
+    ops = _ops()
+    L, nq, nkv, hd, page, n_new = 300, 4, 2, 128, 16, 40
+    rng = np.random.default_rng(far)
+    k = rng.normal(size=(L, nkv, hd)).astype(np.float32) * 0.1
+    v = rng.normal(size=(L, nkv, hd)).astype(np.float32)
+    k[far] = 4.0
+    q = np.full((n_new, nq, hd), 4.0, dtype=np.float32)
+    kc, vc, pages = _paged(k, v, page, 40, 2)
+    G = nq // nkv
+    tiles = list(range(0, n_new * G, 128))
+    dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+    out = torch.empty((n_new, nq * hd), dtype=torch.bfloat16, device=DEV)
+    ops.attention_tc(torch.from_numpy(q.reshape(n_new, -1)).to(torch.bfloat16).to(DEV),
+                     torch.from_numpy(kc).to(torch.bfloat16).to(DEV), torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out,
+                     dev([0] * len(tiles)), dev(tiles), dev([0, n_new]), dev([L]), dev(pages[None, :]), page,
+                     nq, nkv, hd, 0, 1.0 / math.sqrt(hd))
+    assert ops.attention_tc_error() == 0
+    got = out.float().cpu().numpy().reshape(n_new, nq, hd)
+    want = np.stack([v[far, (h * nkv) // nq] for h in range(nq)])
+    want = torch.from_numpy(want).to(torch.bfloat16).float().numpy()
+    for t in range(n_new):
+        np.testing.assert_allclose(got[t], want, atol=2e-2)
 
 
 @pytest.mark.parametrize("nq,nkv,hd,window,page,slices,slice_len", [
