@@ -6,23 +6,24 @@
 //   S = Q K^T    tcgen05.mma M=128 N=128, 8 steps of K=16 over the head size; Q and the K tile
 //                sit in shared memory as K-major operands (two panels of 64 dims, rows of 128
 //                bytes, 128-byte swizzle); S goes to TMEM columns 0..127;
-//   softmax      thread r owns row r: two passes of tcgen05.ld over S (row maximum, then
-//                exp2 and sum in float32), P written as bfloat16 into the K tile's shared
-//                memory (K is no longer needed), again as a K-major operand;
+//   softmax      two threads own a row, 64 keys each: one tcgen05.ld of S, row maximum (the
+//                halves exchange it), exp2 and sum in float32, P written as bfloat16 into the
+//                K tile's shared memory (K is no longer needed), again as a K-major operand;
 //   PV           tcgen05.mma with P as A and the V tile as an MN-major B operand (V rows are
 //                keys, 128 bytes of 64 dims each, which is MN-major for a [dim, key] product);
 //                the tile's product goes to TMEM columns 128..255 and is added to the row's
 //                float32 output registers after rescaling by 2^(m_old - m_new).
 // The tiles come from the paged cache through the block table with cp.async, written at the
-// swizzled addresses the operand descriptors expect.  Shared memory per CTA is 96 KB (Q, K/P,
-// V), so two CTAs share an SM and one computes while the other loads.  Every mbarrier wait is
+// swizzled addresses the operand descriptors expect: V(t) lands while S(t) is computed and
+// softmaxed, K(t+1) while the output is updated.  Shared memory per CTA is 97 KB (Q, K/P, V),
+// so two CTAs share an SM.  Every mbarrier wait is
 // bounded; the error word is read by kestrel_attention_tc_error.  Formulas as in
 // attention_plain.cu (reference: st.c:10779-10911, st.c:9762-9859).
 #include "attention_params.cuh"
 #include "tcgen05.cuh"
 #include <math.h>
 
-#define AT_THREADS 128
+#define AT_THREADS 256
 #define AT_BM 128
 #define AT_BN 128
 #define AT_HD 128
@@ -39,11 +40,26 @@ __device__ __forceinline__ float at_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float *v) {
-    tc_ld16(taddr, v);
-    tc_ld16(taddr + 16, v + 16);
+// 64 consecutive TMEM columns of this thread's lane: four loads in flight, one wait
+__device__ __forceinline__ void tc_ld64(uint32_t taddr, float *v) {
+    uint32_t r[64];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(r[16 * q + 0]), "=r"(r[16 * q + 1]), "=r"(r[16 * q + 2]), "=r"(r[16 * q + 3]), "=r"(r[16 * q + 4]),
+              "=r"(r[16 * q + 5]), "=r"(r[16 * q + 6]), "=r"(r[16 * q + 7]), "=r"(r[16 * q + 8]), "=r"(r[16 * q + 9]),
+              "=r"(r[16 * q + 10]), "=r"(r[16 * q + 11]), "=r"(r[16 * q + 12]), "=r"(r[16 * q + 13]), "=r"(r[16 * q + 14]),
+              "=r"(r[16 * q + 15])
+            : "r"(taddr + 16 * q));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 256 threads: thread (r, h) = (tid % 128, tid / 128) owns row r and half h of it: 64 of the
+// tile's 128 keys in the softmax, 64 of the 128 output dims.  Warps w and w + 4 share TMEM
+// lanes 32 (w % 4)...; the two halves of a row exchange their maxima through shared memory.
 __global__ void __launch_bounds__(AT_THREADS)
 attention_tc_kernel(const AttnParams p) {
     pdl_launch_dependents();
@@ -54,10 +70,13 @@ attention_tc_kernel(const AttnParams p) {
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_s = base, kp_s = base + 2 * AT_PANEL, v_s = base + 4 * AT_PANEL;
     const uint32_t bar = base + 6 * AT_PANEL, tmem_slot = bar + 8;
-    volatile uint32_t *tmem_slot_ptr = (volatile uint32_t *)(smem_raw + (tmem_slot - smem_u32(smem_raw)));
-    uint8_t *kp_ptr = smem_raw + (kp_s - smem_u32(smem_raw));
+    uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot_ptr = (volatile uint32_t *)(aligned + 6 * AT_PANEL + 8);
+    float *xchg = (float *)(aligned + 6 * AT_PANEL + 16);           // [2][128] row maxima of the halves
+    uint8_t *kp_ptr = aligned + 2 * AT_PANEL;
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    const int r = tid & 127, h = tid >> 7;
     if (tid == 0) {
         mbar_init(bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -86,37 +105,37 @@ attention_tc_kernel(const AttnParams p) {
     const int k_lo = (k_first / AT_BN) * AT_BN;
     const int n_tiles = (k_hi - k_lo + AT_BN - 1) / AT_BN;
 
-    // this thread's row
-    const bool row_ok = tid < rows_here;
-    const int my_pos = row_ok ? pos_begin + (row0 + tid) / G : -1;
+    const bool row_ok = r < rows_here;
+    const int my_pos = row_ok ? pos_begin + (row0 + r) / G : -1;
     const int my_lo = p.window > 0 ? max(0, my_pos - p.window + 1) : 0;
 
-    // Q: row r of the tile, 16 chunks of 8 dims; thread t copies chunk t % 16 of rows t / 16 + 8 j
+    // copies: thread t moves 16-byte chunk t % 16 of rows (t / 16) * 8 .. + 7
+    const int ld_c = tid & 15, ld_r0 = (tid >> 4) * 8;
+    const uint32_t ld_panel = (uint32_t)(ld_c >> 3) * AT_PANEL;
     {
-        int c = tid & 15;
-        for (int r = tid >> 4; r < AT_BM; r += 8) {
-            bool valid = r < rows_here;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int rr = ld_r0 + j;
+            bool valid = rr < rows_here;
             size_t off = 0;
             if (valid) {
-                int row = row0 + r;
-                off = ((size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G) * AT_HD + c * 8;
+                int row = row0 + rr;
+                off = ((size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G) * AT_HD + ld_c * 8;
             }
-            at_cp_async16(q_s + (c >> 3) * AT_PANEL + swizzle128(r, c & 7), p.q + off, valid);
+            at_cp_async16(q_s + ld_panel + swizzle128(rr, ld_c & 7), p.q + off, valid);
         }
     }
-    // K and V tile: thread t copies chunk t % 16 of keys (t / 16) * 16 .. + 15
-    auto load_kv = [&](int t) {
-        int c = tid & 15, r0 = (tid >> 4) * 16;
-        int s0 = k_lo + t * AT_BN + r0;
-        bool one_page = p.page_size % 16 == 0;
+    const bool one_page = p.page_size % 8 == 0;
+    auto load_tile = [&](int t, uint32_t dst, const __nv_bfloat16 *cache) {
+        int s0 = k_lo + t * AT_BN + ld_r0;
         size_t page_off = 0;
-        if (one_page && s0 + 16 > k_first && s0 < k_hi) {
+        if (one_page && s0 + 8 > k_first && s0 < k_hi) {
             int page = table[s0 / p.page_size];
-            page_off = (((size_t)page * p.nkv + kvh) * p.page_size + (s0 % p.page_size)) * AT_HD + c * 8;
+            page_off = (((size_t)page * p.nkv + kvh) * p.page_size + (s0 % p.page_size)) * AT_HD + ld_c * 8;
         }
-#pragma unroll 4
-        for (int j = 0; j < 16; ++j) {
-            int s = s0 + j, r = r0 + j;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int s = s0 + j;
             bool valid = s >= k_first && s < k_hi;
             size_t off = 0;
             if (valid) {
@@ -124,29 +143,30 @@ attention_tc_kernel(const AttnParams p) {
                     off = page_off + (size_t)j * AT_HD;
                 } else {
                     int page = table[s / p.page_size];
-                    off = (((size_t)page * p.nkv + kvh) * p.page_size + (s % p.page_size)) * AT_HD + c * 8;
+                    off = (((size_t)page * p.nkv + kvh) * p.page_size + (s % p.page_size)) * AT_HD + ld_c * 8;
                 }
             }
-            uint32_t sw = (c >> 3) * AT_PANEL + swizzle128(r, c & 7);
-            at_cp_async16(kp_s + sw, p.k_cache + off, valid);
-            at_cp_async16(v_s + sw, p.v_cache + off, valid);
+            at_cp_async16(dst + ld_panel + swizzle128(ld_r0 + j, ld_c & 7), cache + off, valid);
         }
     };
+    if (n_tiles > 0) load_tile(0, kp_s, p.k_cache);
+    asm volatile("cp.async.commit_group;" ::: "memory");             // group: Q and K(0)
 
-    float o[AT_HD];
+    float o[64];
 #pragma unroll
-    for (int i = 0; i < AT_HD; ++i) o[i] = 0.f;
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
     uint32_t phase = 0;
     bool ok = true;
-    const uint32_t lane_base = ((uint32_t)(32 * warp)) << 16;
+    const uint32_t lane_base = ((uint32_t)(32 * (warp & 3))) << 16;
+    const int col0 = 64 * h;
 
     for (int t = 0; t < n_tiles && ok; ++t) {
         const int kbase = k_lo + t * AT_BN;
-        load_kv(t);
+        load_tile(t, v_s, p.v_cache);                                 // V(t) lands while S is computed and softmaxed
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // cp.async writes -> tensor-core reads
+        asm volatile("cp.async.wait_group 1;" ::: "memory");          // K(t) (and Q) have landed
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor-core reads
         __syncthreads();
         if (tid == 0) {
             tc_fence_after();
@@ -161,55 +181,53 @@ attention_tc_kernel(const AttnParams p) {
         phase ^= 1;
         tc_fence_after();
 
-        // softmax of this thread's row: pass 1, the maximum
+        // softmax of this thread's half row
+        float s[64];
+        tc_ld64(tmem + lane_base + col0, s);
         const bool whole = kbase >= k_first && kbase + AT_BN <= k_hi && kbase + AT_BN - 1 <= my_pos && kbase >= my_lo;
         float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < AT_BN; c += 32) {
-            float s[32];
-            tc_ld32(tmem + lane_base + c, s);
+        if (whole) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                int key = kbase + c + j;
-                bool vis = whole || (key <= my_pos && key >= my_lo && key < k_hi && key >= k_first);
-                mx = fmaxf(mx, vis ? s[j] * p.scale_log2 : -INFINITY);
+            for (int j = 0; j < 64; ++j) { s[j] *= p.scale_log2; mx = fmaxf(mx, s[j]); }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+                int key = kbase + col0 + j;
+                bool vis = key <= my_pos && key >= my_lo && key < k_hi && key >= k_first;
+                s[j] = vis ? s[j] * p.scale_log2 : -INFINITY;
+                mx = fmaxf(mx, s[j]);
             }
         }
+        xchg[h * 128 + r] = mx;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");       // the two warps that share these rows
+        mx = fmaxf(mx, xchg[(h ^ 1) * 128 + r]);
         float m_new = fmaxf(m_run, mx);
         float m_use = m_new == -INFINITY ? 0.f : m_new;
         float alpha = at_exp2(m_run - m_use);
         m_run = m_new;
-        // pass 2: p = 2^(s - m), row sum, P as bfloat16 into the K tile's memory
         float l_add = 0.f;
-#pragma unroll 1
-        for (int c = 0; c < AT_BN; c += 32) {
-            float s[32];
-            tc_ld32(tmem + lane_base + c, s);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                int key = kbase + c + j;
-                bool vis = whole || (key <= my_pos && key >= my_lo && key < k_hi && key >= k_first);
-                float pv = vis ? at_exp2(s[j] * p.scale_log2 - m_use) : 0.f;
-                s[j] = pv;
-                l_add += pv;
-            }
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {        // four chunks of 8 keys
-                int chunk = (c >> 3) + g;        // 0..15 over the 128 keys
-                uint4 u;
-                __nv_bfloat162 b0 = __floats2bfloat162_rn(s[8 * g + 0], s[8 * g + 1]);
-                __nv_bfloat162 b1 = __floats2bfloat162_rn(s[8 * g + 2], s[8 * g + 3]);
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(s[8 * g + 4], s[8 * g + 5]);
-                __nv_bfloat162 b3 = __floats2bfloat162_rn(s[8 * g + 6], s[8 * g + 7]);
-                u.x = *reinterpret_cast<uint32_t *>(&b0);
-                u.y = *reinterpret_cast<uint32_t *>(&b1);
-                u.z = *reinterpret_cast<uint32_t *>(&b2);
-                u.w = *reinterpret_cast<uint32_t *>(&b3);
-                *reinterpret_cast<uint4 *>(kp_ptr + (chunk >> 3) * AT_PANEL + swizzle128(tid, chunk & 7)) = u;
-            }
+        for (int j = 0; j < 64; ++j) {
+            s[j] = at_exp2(s[j] - m_use);
+            l_add += s[j];
         }
         l_run = l_run * alpha + l_add;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P written by threads -> tensor-core reads
+        // P as bfloat16 into the K tile's memory: keys 64 h .. + 63 are panel h of row r
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            uint4 u;
+            __nv_bfloat162 b0 = __floats2bfloat162_rn(s[8 * g + 0], s[8 * g + 1]);
+            __nv_bfloat162 b1 = __floats2bfloat162_rn(s[8 * g + 2], s[8 * g + 3]);
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(s[8 * g + 4], s[8 * g + 5]);
+            __nv_bfloat162 b3 = __floats2bfloat162_rn(s[8 * g + 6], s[8 * g + 7]);
+            u.x = *reinterpret_cast<uint32_t *>(&b0);
+            u.y = *reinterpret_cast<uint32_t *>(&b1);
+            u.z = *reinterpret_cast<uint32_t *>(&b2);
+            u.w = *reinterpret_cast<uint32_t *>(&b3);
+            *reinterpret_cast<uint4 *>(kp_ptr + h * AT_PANEL + swizzle128(r, g)) = u;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");          // V(t) has landed
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P and V -> tensor-core reads
         tc_fence_before();
         __syncthreads();
         if (tid == 0) {
@@ -226,24 +244,31 @@ attention_tc_kernel(const AttnParams p) {
         if (!mbar_wait(bar, phase)) { atomicExch(&g_at_error, 2); ok = false; }
         phase ^= 1;
         tc_fence_after();
+        if (t + 1 < n_tiles) load_tile(t + 1, kp_s, p.k_cache);       // P is consumed: K(t+1) may overwrite it
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        {
+            float pvv[64];
+            tc_ld64(tmem + lane_base + 128 + col0, pvv);
 #pragma unroll
-        for (int c = 0; c < AT_HD; c += 32) {
-            float pvv[32];
-            tc_ld32(tmem + lane_base + 128 + c, pvv);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) o[c + j] = o[c + j] * alpha + pvv[j];
+            for (int j = 0; j < 64; ++j) o[j] = o[j] * alpha + pvv[j];
         }
         tc_fence_before();
-        __syncthreads();          // K/P and V may be overwritten, S and PV columns rewritten
+        __syncthreads();          // S and PV columns may be rewritten, V overwritten
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
+    // the row's sum is the sum of its halves
+    __syncthreads();
+    xchg[h * 128 + r] = l_run;
+    __syncthreads();
+    float l_tot = l_run + xchg[(h ^ 1) * 128 + r];
     if (row_ok && ok) {
-        int row = row0 + tid;
+        int row = row0 + r;
         size_t qrow = (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G;
-        float inv = 1.0f / l_run;
-        __nv_bfloat16 *po = p.out + qrow * AT_HD;
+        float inv = 1.0f / l_tot;
+        __nv_bfloat16 *po = p.out + qrow * AT_HD + col0;
 #pragma unroll
-        for (int c = 0; c < AT_HD; c += 8) {
+        for (int c = 0; c < 64; c += 8) {
             uint4 u;
             __nv_bfloat162 b0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
             __nv_bfloat162 b1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
@@ -279,7 +304,7 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
     p.kv_lens = kv_lens; p.block_table = block_table; p.table_stride = table_stride; p.page_size = page_size;
     p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = 1; p.slice_len = 1 << 30;
     p.scale_log2 = scale * 1.4426950408889634f;
-    size_t smem = 6 * AT_PANEL + 64 + 1024;
+    size_t smem = 6 * AT_PANEL + 16 + 2 * 128 * 4 + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
