@@ -148,7 +148,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             if (c + j < valid) {
-                                float a = g[j] / (1.0f + expf(-g[j]));
+                                float a = __fdividef(g[j], 1.0f + __expf(-g[j]));     // bfloat16 output: 2-ulp float32 intrinsics
                                 o[(size_t)(t0 + c + j) * ldo + n] = __float2bfloat16_rn(a * u[j]);
                             }
                     }
@@ -175,8 +175,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // Many tokens (T > 256): one CTA per SM walks over output tiles (tile = blockIdx.x + i *
 // gridDim.x) and keeps TWO accumulators in TMEM (2 x 256 columns), so that the epilogue warps
 // drain tile i while the MMA thread already accumulates tile i+1 and the loader runs ahead
-// across tile boundaries.  PARTIAL uses tiles of 128 features x 256 tokens; SWIGLU tiles of
-// (128 gate + 128 up) features x 128 tokens, which moves the same bytes per FLOP.
+// across tile boundaries.  PARTIAL uses tiles of 128 features x 256 tokens.  SWIGLU uses tiles
+// of (128 gate + 128 up) features x 256 tokens, whose two accumulators fill TMEM (the epilogue
+// then does not overlap, but operand traffic per FLOP, which bounds the kernel, is a third
+// lower than with 128-token tiles and two accumulator pairs).
 template <int BN, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -188,8 +190,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     constexpr uint32_t B_BYTES = BN * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
     constexpr uint32_t ACC_COLS = A_TILES * BN;
-    static_assert(ACC_COLS == 256, "two accumulators of 256 columns fill the 512 columns of TMEM");
+    static_assert(ACC_COLS == 256 || ACC_COLS == 512, "accumulators of 256 or 512 columns");
     constexpr uint32_t TMEM_COLS = 512;
+    constexpr int NBUF = TMEM_COLS / ACC_COLS;          // 2: the epilogue overlaps the next tile; 1: it does not
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
 
     extern __shared__ uint8_t smem_raw[];
@@ -255,8 +258,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             bool ok = true;
             int j = 0;
             for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x, ++j) {
-                int b = j & 1;
-                uint32_t acc_phase = (uint32_t)(j >> 1) & 1u;
+                int b = j % NBUF;
+                uint32_t acc_phase = (uint32_t)(j / NBUF) & 1u;
                 if (!mbar_wait(acc_empty(b), acc_phase ^ 1)) { atomicExch(&g_tc_error, 4); ok = false; break; }
                 tc_fence_after();
                 uint32_t d = tmem + (uint32_t)b * ACC_COLS;
@@ -281,8 +284,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         int q = warp & 3;
         int j = 0;
         for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++j) {
-            int b = j & 1;
-            uint32_t acc_phase = (uint32_t)(j >> 1) & 1u;
+            int b = j % NBUF;
+            uint32_t acc_phase = (uint32_t)(j / NBUF) & 1u;
             int n0 = (tile % tiles_n) * TC_BM, t0 = (tile / tiles_n) * BN;
             int n = n0 + 32 * q + lane;
             if (!mbar_wait(acc_full(b), acc_phase)) { if (lane == 0) atomicExch(&g_tc_error, 3); break; }
@@ -302,7 +305,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 #pragma unroll
                         for (int jj = 0; jj < 16; ++jj)
                             if (c + jj < valid) {
-                                float a = g[jj] / (1.0f + expf(-g[jj]));
+                                float a = __fdividef(g[jj], 1.0f + __expf(-g[jj]));   // bfloat16 output: 2-ulp float32 intrinsics
                                 o[(size_t)(t0 + c + jj) * ldo + n] = __float2bfloat16_rn(a * u[jj]);
                             }
                     }
@@ -396,11 +399,13 @@ KESTREL_API int kestrel_gemm_tc_supported(const void *x, const void *w, int T, i
 // g_ctas_per_sm CTAs share an SM's shared memory for their stages; a CTA costs about
 // g_overhead_kb k-blocks of time beyond its own k-blocks (launch, barrier set-up, TMEM
 // allocation, first tensor-map fetch, pipeline fill, epilogue).
+static int g_swiglu_bn = 256;      // token tile of the persistent SwiGLU product: 256 (one accumulator pair) or 128 (two)
 static int g_persistent = 1;       // many-token products on the persistent kernel (0: one tile per CTA)
 static int g_overhead_kb = 6;
 static int g_ctas_per_sm = 2;
 
 KESTREL_API void kestrel_gemm_tc_set_persistent(int on) { g_persistent = on ? 1 : 0; }
+KESTREL_API void kestrel_gemm_tc_set_swiglu_tile(int bn) { if (bn == 128 || bn == 256) g_swiglu_bn = bn; }
 
 KESTREL_API void kestrel_gemm_tc_set_tuning(int overhead_kb, int ctas_per_sm) {
     if (overhead_kb >= 0) g_overhead_kb = overhead_kb;
@@ -485,14 +490,15 @@ static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, in
                        long long ldo, int splits, long long slice_stride, int up_off, cudaStream_t stream) {
     int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
     bool persistent = T > 256 && splits == 1 && g_persistent;
-    if (persistent && MODE == TC_SWIGLU) bn = 128;
+    if (persistent && MODE == TC_SWIGLU) bn = g_swiglu_bn;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, w_rows, K, ldw, TC_BM);
     if (rc) return rc;
     rc = make_map(&mx, x, T, K, ldx, bn);
     if (rc) return rc;
     if (persistent) {
-        if (MODE == TC_SWIGLU) return launch_tc_persistent<128, TC_SWIGLU>(mw, mx, out, T, N, K, ldo, up_off, stream);
+        if (MODE == TC_SWIGLU && bn == 128) return launch_tc_persistent<128, TC_SWIGLU>(mw, mx, out, T, N, K, ldo, up_off, stream);
+        if (MODE == TC_SWIGLU) return launch_tc_persistent<256, TC_SWIGLU>(mw, mx, out, T, N, K, ldo, up_off, stream);
         return launch_tc_persistent<256, TC_PARTIAL>(mw, mx, out, T, N, K, ldo, up_off, stream);
     }
     switch (bn) {
