@@ -397,6 +397,81 @@ __global__ void attn_prepare_kernel(const float *__restrict__ partial, int S, si
     }
 }
 
+// The same for head size 128 with all 128 dims rotated (the common case): a block of 8 warps
+// takes 8 heads of one token; cos and sin of the token's 64 angles are computed once per block
+// into shared memory; a lane owns 4 consecutive dims (float4 loads, 8- or 16-byte stores) and
+// gets its rotation partner (dim +-64) from lane ^ 16 by shuffle.
+template <typename T>
+__global__ void __launch_bounds__(256)
+attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice_stride,
+                          const float *__restrict__ bias, const float *__restrict__ q_norm_w,
+                          const float *__restrict__ k_norm_w, float norm_eps, const float *__restrict__ inv_freq,
+                          const int *__restrict__ positions, const int *__restrict__ seq_of_token,
+                          const int *__restrict__ block_table, int table_stride, int page_size,
+                          T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out,
+                          int nq, int nkv, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int hd = 128;
+    __shared__ float cs_s[64], sn_s[64];
+    int t = blockIdx.x;
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int pos = positions[t];
+    if (threadIdx.x < 64) {
+        float ang = (float)pos * inv_freq[threadIdx.x];
+        float sn, cs;
+        sincosf(ang, &sn, &cs);
+        cs_s[threadIdx.x] = cs;
+        sn_s[threadIdx.x] = sn;
+    }
+    __syncthreads();
+    int heads = nq + 2 * nkv;
+    int h = blockIdx.y * 8 + warp;
+    if (h >= heads) return;
+    bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    if (!is_q && !write_kv) return;
+    const float4 *row = reinterpret_cast<const float4 *>(partial + (size_t)t * heads * hd + (size_t)h * hd) + lane;
+    size_t st4 = slice_stride >> 2;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    int s = 0;
+    for (; s + 4 <= S; s += 4) {
+        float4 a = row[(size_t)s * st4], b = row[(size_t)(s + 1) * st4], c = row[(size_t)(s + 2) * st4], e = row[(size_t)(s + 3) * st4];
+        x = add4(add4(add4(add4(x, a), b), c), e);
+    }
+    for (; s < S; ++s) x = add4(x, row[(size_t)s * st4]);
+    if (bias) x = add4(x, reinterpret_cast<const float4 *>(bias + (size_t)h * hd)[lane]);
+    const float *nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    if (nw) {
+        float ss = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+        ss = warp_sum(ss);
+        float rinv = 1.0f / sqrtf(ss / (float)hd + norm_eps);
+        float4 g = reinterpret_cast<const float4 *>(nw)[lane];
+        x = make_float4((x.x * rinv) * g.x, (x.y * rinv) * g.y, (x.z * rinv) * g.z, (x.w * rinv) * g.w);
+    }
+    if (is_q || is_k) {
+        float4 o;
+        o.x = __shfl_xor_sync(0xffffffffu, x.x, 16);
+        o.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
+        o.z = __shfl_xor_sync(0xffffffffu, x.z, 16);
+        o.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
+        int j = (4 * lane) & 63;
+        float4 cs = *reinterpret_cast<const float4 *>(cs_s + j), sn = *reinterpret_cast<const float4 *>(sn_s + j);
+        if (lane < 16)      // this lane holds the low half of the pairs: lo * c - hi * s
+            x = make_float4(x.x * cs.x - o.x * sn.x, x.y * cs.y - o.y * sn.y, x.z * cs.z - o.z * sn.z, x.w * cs.w - o.w * sn.w);
+        else                // the high half: hi * c + lo * s
+            x = make_float4(x.x * cs.x + o.x * sn.x, x.y * cs.y + o.y * sn.y, x.z * cs.z + o.z * sn.z, x.w * cs.w + o.w * sn.w);
+    }
+    if (is_q) {
+        store4(q_out + ((size_t)t * nq + h) * hd + 4 * lane, x);
+    } else {
+        int kvh = is_k ? h - nq : h - nq - nkv;
+        int seq = seq_of_token[t];
+        int page = block_table[(size_t)seq * table_stride + pos / page_size];
+        T *plane = is_k ? k_cache : v_cache;
+        store4(plane + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd + 4 * lane, x);
+    }
+}
+
 KESTREL_API int kestrel_attn_prepare(const float *partial, int S, long long slice_stride,
                                      const float *bias, const float *q_norm_w, const float *k_norm_w,
                                      float norm_eps, const float *inv_freq, int rot,
@@ -411,6 +486,23 @@ KESTREL_API int kestrel_attn_prepare(const float *partial, int S, long long slic
     KESTREL_REQUIRE(page_size > 0, "attn_prepare: page size %d", page_size);
     long long warps = (long long)T * (nq + 2 * nkv);
     unsigned blocks = (unsigned)((warps + 3) / 4);
+    bool fast = hd == 128 && rot == 128 && slice_stride % 4 == 0 && (nq + 2 * nkv + 7) / 8 <= 65535 &&
+                ((((uintptr_t)partial | (uintptr_t)bias | (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)q_out |
+                   (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0);
+    if (fast) {
+        dim3 grid(T, (nq + 2 * nkv + 7) / 8);
+        if (dtype == KESTREL_F32)
+            kestrel_launch(attn_prepare_hd128_kernel<float>, grid, dim3(256), 0, stream, partial, S, (size_t)slice_stride, bias, q_norm_w,
+                           k_norm_w, norm_eps, inv_freq, positions, seq_of_token, block_table, table_stride, page_size,
+                           (float *)k_cache, (float *)v_cache, (float *)q_out, nq, nkv, write_kv);
+        else if (dtype == KESTREL_BF16)
+            kestrel_launch(attn_prepare_hd128_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, partial, S, (size_t)slice_stride, bias,
+                           q_norm_w, k_norm_w, norm_eps, inv_freq, positions, seq_of_token, block_table, table_stride, page_size,
+                           (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, nq, nkv, write_kv);
+        else
+            return kestrel_fail(-2, "attn_prepare: unknown dtype %d", dtype);
+        return kestrel_check_launch("attn_prepare");
+    }
     if (dtype == KESTREL_F32)
         kestrel_launch(attn_prepare_kernel<float>, dim3(blocks), dim3(128), 0, stream, partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, positions,
             seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache,

@@ -459,7 +459,7 @@ def test_attention_window_edge(dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nq,nkv,hd,rot,bias,norm", [(6, 2, 32, 32, True, True), (5, 5, 48, 48, False, True),
-                                                     (3, 1, 80, 40, True, False), (8, 2, 128, 128, False, True),
+                                                     (3, 1, 80, 40, True, False), (8, 2, 128, 128, False, True), (6, 3, 128, 128, True, True), (9, 1, 128, 128, True, False), (4, 4, 128, 64, False, True),
                                                      (2, 2, 16, 0, False, False)])
 def test_attn_prepare(dtype, nq, nkv, hd, rot, bias, norm):
     ops = _ops()
