@@ -331,6 +331,186 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     }
 }
 
+// ------------------------------------------------------------------------ CTA-pair kernel
+// Many tokens, PARTIAL epilogue: two CTAs of a cluster share one tcgen05.mma (cta_group::2,
+// M = 256, N = 256).  Each CTA loads its own 128 weight rows and HALF of the 256 token rows of
+// a k-block (32 KB a stage instead of 48), the tensor cores of both SMs read the token rows
+// from both CTAs' shared memory, and each CTA ends up with its 128 features x 256 tokens in its
+// own TMEM.  Operand traffic per SM - which bounds the one-CTA kernel - drops by a third.
+//   * rank 0 ("leader") issues the MMAs; both ranks load; TMA completions of both ranks count
+//     on the leader's full barrier (cp.async.bulk.tensor ... cta_group::2);
+//   * the leader frees a stage in both CTAs, and publishes an accumulator to both, with
+//     tcgen05.commit ... multicast::cluster (a commit, not a load: no operand is multicast);
+//   * the epilogue warps of both ranks arrive on the leader's accumulator-empty barrier.
+// No TMA load uses cluster multicast.  Persistent over tiles as the one-CTA kernel, two
+// accumulators in TMEM.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t leader_bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {       // arrives on `bar` of both CTAs
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+#define TCP_BN 256          // tokens of a pair's tile (128 loaded by each rank)
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    float *__restrict__ out, int T, int N, int K, long long ldo, int stages, int tiles_n, int tiles_total) {
+    pdl_launch_dependents();
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
+    constexpr uint32_t B_BYTES = (TCP_BN / 2) * TC_BK * 2;
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;               // per CTA; a stage of the pair is twice that
+    constexpr uint32_t ACC_COLS = TCP_BN, TMEM_COLS = 512;
+    // M = 256 (two CTAs), N = 256, bf16 x bf16 -> f32, both operands K-major
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TCP_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint32_t bars = base + (uint32_t)stages * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (stages + s); };
+    auto acc_full = [&](int b) { return bars + 16u * stages + 8u * b; };
+    auto acc_empty = [&](int b) { return bars + 16u * stages + 16u + 8u * b; };
+    uint32_t tmem_slot = bars + 16u * stages + 32u;
+    volatile uint32_t *tmem_slot_ptr = (volatile uint32_t *)(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+    if (warp == 0) {
+        if (lane < stages) { mbar_init(full_bar(lane), 1); mbar_init(empty_bar(lane), 1); }
+        if (lane >= 28 && lane < 30) mbar_init(acc_full(lane - 28), 1);
+        if (lane >= 30) mbar_init(acc_empty(lane - 30), 8);              // four epilogue warps of each rank
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {                                                     // the same warp of both ranks
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync();                   // both ranks' barriers exist before anything arrives on them from afar
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot_ptr;
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < tiles_total && ok; tile += n_pairs) {
+                int n0 = (tile % tiles_n) * 256 + (int)rank * TC_BM;
+                int t0 = (tile / tiles_n) * TCP_BN + (int)rank * (TCP_BN / 2);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1)) { atomicExch(&g_tc_error, 1); ok = false; break; }
+                    uint32_t leader_full = map_to_rank(full_bar(stage), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+                    uint32_t sa = base + (uint32_t)stage * STAGE_BYTES;
+                    int kc = kb * TC_BK;
+                    tma_load_2d_pair(sa, &map_w, leader_full, kc, n0);
+                    tma_load_2d_pair(sa + A_BYTES, &map_x, leader_full, kc, t0);
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int j = 0;
+            for (int tile = pair; tile < tiles_total && ok; tile += n_pairs, ++j) {
+                int b = j & 1;
+                uint32_t acc_phase = (uint32_t)(j >> 1) & 1u;
+                if (!mbar_wait(acc_empty(b), acc_phase ^ 1)) { atomicExch(&g_tc_error, 4); ok = false; break; }
+                tc_fence_after();
+                uint32_t d = tmem + (uint32_t)b * ACC_COLS;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase)) { atomicExch(&g_tc_error, 2); ok = false; break; }
+                    tc_fence_after();
+                    uint32_t sa = base + (uint32_t)stage * STAGE_BYTES;
+                    uint64_t da = smem_desc(sa), db = smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+                        tc_mma_pair(d, da + 2 * k4, db + 2 * k4, IDESC, (kb > 0 || k4 > 0) ? 1u : 0u);
+                    tc_commit_pair(empty_bar(stage));
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+                tc_commit_pair(acc_full(b));
+            }
+        }
+    } else {
+        int q = warp & 3;
+        int j = 0;
+        for (int tile = pair; tile < tiles_total; tile += n_pairs, ++j) {
+            int b = j & 1;
+            uint32_t acc_phase = (uint32_t)(j >> 1) & 1u;
+            int n = (tile % tiles_n) * 256 + (int)rank * TC_BM + 32 * q + lane;
+            int t0 = (tile / tiles_n) * TCP_BN;
+            if (!mbar_wait(acc_full(b), acc_phase)) { if (lane == 0) atomicExch(&g_tc_error, 3); break; }
+            tc_fence_after();
+            uint32_t d = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)b * ACC_COLS;
+            int valid = min(TCP_BN, T - t0);
+#pragma unroll 1
+            for (int c = 0; c < TCP_BN; c += 16) {
+                if (c >= valid) break;
+                float g[16];
+                tc_ld16(d + c, g);
+                if (n < N) {
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj)
+                        if (c + jj < valid) out[(size_t)(t0 + c + jj) * ldo + n] = g[jj];
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(acc_empty(b), 0));
+        }
+    }
+    tc_fence_before();
+    cluster_sync();                   // nobody leaves while the other rank may still signal or read it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -400,11 +580,13 @@ KESTREL_API int kestrel_gemm_tc_supported(const void *x, const void *w, int T, i
 // g_overhead_kb k-blocks of time beyond its own k-blocks (launch, barrier set-up, TMEM
 // allocation, first tensor-map fetch, pipeline fill, epilogue).
 static int g_swiglu_bn = 256;      // token tile of the persistent SwiGLU product: 256 (one accumulator pair) or 128 (two)
+static int g_pairs = 1;            // many-token PARTIAL products on CTA pairs (cta_group::2)
 static int g_persistent = 1;       // many-token products on the persistent kernel (0: one tile per CTA)
 static int g_overhead_kb = 6;
 static int g_ctas_per_sm = 2;
 
 KESTREL_API void kestrel_gemm_tc_set_persistent(int on) { g_persistent = on ? 1 : 0; }
+KESTREL_API void kestrel_gemm_tc_set_pairs(int on) { g_pairs = on ? 1 : 0; }
 KESTREL_API void kestrel_gemm_tc_set_swiglu_tile(int bn) { if (bn == 128 || bn == 256) g_swiglu_bn = bn; }
 
 KESTREL_API void kestrel_gemm_tc_set_tuning(int overhead_kb, int ctas_per_sm) {
@@ -485,6 +667,48 @@ static int launch_tc_persistent(const CUtensorMap &mw, const CUtensorMap &mx, vo
     return kestrel_check_launch("gemm_tc_persistent");
 }
 
+static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, float *out, int T, int N, int K, long long ldo,
+                          cudaStream_t stream) {
+    const int STAGE_BYTES = TC_BM * TC_BK * 2 + (TCP_BN / 2) * TC_BK * 2;
+    int stages = (200 * 1024) / STAGE_BYTES;
+    if (stages > 8) stages = 8;
+    size_t smem = (size_t)stages * STAGE_BYTES + 16 * stages + 48 + 1024;
+    static int max_clusters = -1;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (max_clusters < 0) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return kestrel_fail(-3, "gemm_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+        cfg.gridDim = dim3(148);
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel, &cfg);
+        if (e != cudaSuccess || n < 1) {
+            cudaGetLastError();
+            max_clusters = 0;              // pairs cannot be scheduled here: the one-CTA kernel is used
+        } else {
+            max_clusters = n;
+        }
+    }
+    if (max_clusters == 0) return 1;       // not an error: tells the caller to fall back
+    int tiles_n = (N + 255) / 256, tiles_t = (T + TCP_BN - 1) / TCP_BN;
+    long long total = (long long)tiles_n * tiles_t;
+    if (total > 0x7fffffff) return kestrel_fail(-2, "gemm_tc: too many tiles");
+    int pairs = total < max_clusters ? (int)total : max_clusters;
+    cfg.gridDim = dim3(2 * pairs);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, out, T, N, K, ldo, stages, tiles_n, (int)total);
+    if (e != cudaSuccess) return kestrel_fail(-3, "gemm_tc_pair: %s", cudaGetErrorString(e));
+    return kestrel_check_launch("gemm_tc_pair");
+}
+
 template <int MODE>
 static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, int w_rows, int K, long long ldx, long long ldw,
                        long long ldo, int splits, long long slice_stride, int up_off, cudaStream_t stream) {
@@ -494,6 +718,12 @@ static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, in
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, w_rows, K, ldw, TC_BM);
     if (rc) return rc;
+    if (persistent && MODE == TC_PARTIAL && g_pairs) {
+        rc = make_map(&mx, x, T, K, ldx, TCP_BN / 2);
+        if (rc) return rc;
+        rc = launch_tc_pair(mw, mx, (float *)out, T, N, K, ldo, stream);
+        if (rc <= 0) return rc;            // 1 = pairs cannot be scheduled: go on with one CTA per tile
+    }
     rc = make_map(&mx, x, T, K, ldx, bn);
     if (rc) return rc;
     if (persistent) {
