@@ -234,9 +234,13 @@ def main() -> int:
     # end to end: the same decode through the Python entry point (scheduler, one H2D copy of the
     # step's description from pinned memory, sampling on the device, token ids read back)
     B = args.batch
-    ctx0 = CONTEXT - (W + K) - 24
+    # while the prompts are still being prefilled (2,048 tokens a step) the first requests
+    # already decode; every request must still be live when the timed steps end
+    prefill_steps = -(-B * CONTEXT // opts.max_step_tokens)
+    spare = prefill_steps + W + K + 8
+    ctx0 = max(256, CONTEXT - spare)
     prompts = [rng.integers(0, cfg.vocab_size, size=ctx0).tolist() for _ in range(B)]
-    sp = SamplingParams(temperature=0.0, max_tokens=CONTEXT + 32 - ctx0, ignore_eos=True)
+    sp = SamplingParams(temperature=0.0, max_tokens=spare + 32, ignore_eos=True)
     rids = [llm.add_request(p, sp) for p in prompts]
     while any(len(llm._live[r].out.token_ids) == 0 for r in rids):      # prompts, untimed
         llm.step()

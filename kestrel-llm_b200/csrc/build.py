@@ -94,7 +94,8 @@ def build_cuda(verbose: bool = True) -> str:
     out = build_dir()
     srcs = _sources(KERNEL_DIR, (".cu",))
     deps = srcs + _sources(KERNEL_DIR, (".cuh", ".h"))
-    digest = _digest(deps, NVCC_FLAGS)
+    flags = NVCC_FLAGS + os.environ.get("KESTREL_NVCC_EXTRA", "").split()      # e.g. -DAM_KEYS_STAGES=2 for experiments
+    digest = _digest(deps, flags)
     lib = os.path.join(out, "libkestrel_cuda.so")
     stamp = lib + ".stamp"
     if _fresh(lib, stamp, digest):
@@ -107,7 +108,7 @@ def build_cuda(verbose: bool = True) -> str:
 
     def one(src: str) -> str:
         obj = os.path.join(out, os.path.basename(src)[:-3] + f".{digest}.o")
-        _run([nvcc] + NVCC_FLAGS + ["-c", src, "-o", obj], f"nvcc {os.path.basename(src)}")
+        _run([nvcc] + flags + ["-c", src, "-o", obj], f"nvcc {os.path.basename(src)}")
         if verbose:
             _say(f"  {os.path.basename(src)} done ({time.time() - t0:.0f} s)")
         return obj

@@ -26,6 +26,9 @@
 
 #define AM_THREADS 128
 #define AM_BN 64            // keys per tile
+#ifndef AM_KEYS_STAGES
+#define AM_KEYS_STAGES 3     // cp.async stages of the KEYS (decode) mode
+#endif
 #define AM_ROWS_MT 2        // 16-row tiles per warp in ROWS mode (head sizes up to 128): a tile of 128 rows per CTA
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
@@ -72,7 +75,7 @@ attention_mma_kernel(const AttnParams p) {
     constexpr int KS = HD / 16;                       // k-steps of the QK product
     constexpr int NT_S = KEYS_MODE ? 2 : 8;           // 8-key tiles of a warp's score block
     constexpr int NT_O = HD / 8;                      // 8-dim tiles of the output
-    constexpr int STAGES = KEYS_MODE ? 3 : 2;         // decode is bound by HBM latency: more tiles in flight
+    constexpr int STAGES = KEYS_MODE ? AM_KEYS_STAGES : 2;   // decode is bound by HBM latency: more tiles in flight
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(smem_raw);
     __nv_bfloat16 *Ks = Qs + BM * LDS;                // [STAGES][AM_BN][LDS]
@@ -105,16 +108,19 @@ attention_mma_kernel(const AttnParams p) {
     constexpr int RPT = AM_BN * CHUNKS / AM_THREADS;  // a thread copies chunk ld_c of RPT consecutive keys
     const int ld_c = tid % CHUNKS, ld_r0 = (tid / CHUNKS) * RPT;
     const bool one_page = p.page_size % RPT == 0;     // the RPT keys then lie in one page: one table lookup
-    auto load_kv_tile = [&](int t, int stage) {
+    // The page of a tile's keys is looked up one iteration before the copies that need it are
+    // issued, so that the latency of that (dependent) load is not on the loop's critical path.
+    auto lookup_page = [&](int t) -> int {
+        int s0 = k_lo + t * AM_BN + ld_r0;
+        if (one_page && t < n_tiles && s0 + RPT > k_first && s0 < k_hi) return table[s0 / p.page_size];
+        return 0;
+    };
+    auto load_kv_tile = [&](int t, int stage, int page) {
         int s0 = k_lo + t * AM_BN + ld_r0;
         __nv_bfloat16 *dk = Ks + ((size_t)stage * AM_BN + ld_r0) * LDS + ld_c * 8;
         __nv_bfloat16 *dv = Vs + ((size_t)stage * AM_BN + ld_r0) * LDS + ld_c * 8;
         bool col_ok = ld_c * 8 < hd;
-        size_t page_off = 0;
-        if (one_page && col_ok && s0 + RPT > k_first && s0 < k_hi) {
-            int page = table[s0 / p.page_size];
-            page_off = (((size_t)page * p.nkv + kvh) * p.page_size + (s0 % p.page_size)) * hd + ld_c * 8;
-        }
+        size_t page_off = (((size_t)page * p.nkv + kvh) * p.page_size + (s0 % p.page_size)) * hd + ld_c * 8;
 #pragma unroll
         for (int j = 0; j < RPT; ++j) {
             int s = s0 + j;
@@ -144,9 +150,10 @@ attention_mma_kernel(const AttnParams p) {
         cp_async16((uint32_t)__cvta_generic_to_shared(Qs + r * LDS + c * 8), p.q + off, valid);
     }
     for (int st = 0; st < STAGES - 1; ++st) {          // Q travels with the first group
-        if (st < n_tiles) load_kv_tile(st, st);
+        if (st < n_tiles) load_kv_tile(st, st, lookup_page(st));
         cp_async_commit();
     }
+    int next_page = lookup_page(STAGES - 1);
 
     // ---- per-thread state ----------------------------------------------------------------
     // a warp's rows: ROWS mode rows 16*MT*warp.. (MT tiles of 16), KEYS mode rows 0..15 for every warp
@@ -185,8 +192,9 @@ attention_mma_kernel(const AttnParams p) {
         int stage = t % STAGES;
         cp_async_wait<STAGES - 2>();                   // tile t has landed
         __syncthreads();                               // ... for everyone, and tile t-1 is no longer read
-        if (t + STAGES - 1 < n_tiles) load_kv_tile(t + STAGES - 1, (t + STAGES - 1) % STAGES);
+        if (t + STAGES - 1 < n_tiles) load_kv_tile(t + STAGES - 1, (t + STAGES - 1) % STAGES, next_page);
         cp_async_commit();
+        next_page = lookup_page(t + STAGES);
         if (warp_active) {
             const int kbase = k_lo + t * AM_BN + (KEYS_MODE ? 16 * warp : 0);
             const __nv_bfloat16 *Kt = Ks + ((size_t)stage * AM_BN + (KEYS_MODE ? 16 * warp : 0)) * LDS;
@@ -427,7 +435,7 @@ template <int HD, bool KEYS_MODE, int MT>
 static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream) {
     constexpr int BM = KEYS_MODE ? 16 : 64 * MT;
     constexpr int LDS = HD + 8;
-    constexpr int STAGES = KEYS_MODE ? 3 : 2;
+    constexpr int STAGES = KEYS_MODE ? AM_KEYS_STAGES : 2;
     size_t smem = (size_t)(BM + 2 * STAGES * AM_BN) * LDS * 2;
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {
@@ -446,7 +454,7 @@ KESTREL_API int kestrel_attention_mma_rows_per_tile(int hd) { return hd <= 128 ?
 // CTAs of the KEYS-mode kernel that the GPU's 148 SMs hold at once, by shared memory and threads
 KESTREL_API int kestrel_attention_mma_slots(int hd) {
     int HD = hd <= 32 ? 32 : hd <= 64 ? 64 : hd <= 128 ? 128 : 256;
-    size_t smem = (size_t)(16 + 2 * 3 * AM_BN) * (HD + 8) * 2 + 1024;
+    size_t smem = (size_t)(16 + 2 * AM_KEYS_STAGES * AM_BN) * (HD + 8) * 2 + 1024;
     int per_sm = (int)((227 * 1024) / smem);
     if (per_sm > 2048 / AM_THREADS) per_sm = 2048 / AM_THREADS;
     if (per_sm < 1) per_sm = 1;

@@ -473,21 +473,19 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
         if window <= 0:         # a window is short; only full-length key ranges are cut into slices
             slots = library().kestrel_attention_mma_slots(hd)
             ctas = max(1, tl.count * nkv)
+            # the number of slices that minimises waves x (a CTA's fixed cost + its keys), at least
+            # 256 keys a slice; a captured step fixes the number for a nominal context and lets the
+            # slice length follow the real one through the table on the device
+            best = None
+            for cand in range(1, max(1, min(32, -(-tl.max_kv // 256))) + 1):
+                length = -(-(-(-tl.max_kv // cand)) // 64) * 64
+                real = -(-tl.max_kv // length)
+                cost = -(-ctas * real // slots) * (128 + length)
+                if best is None or cost < best[0]:
+                    best = (cost, real, length)
+            slices, slice_len = best[1], best[2]
             if tl.slice_len_table is not None:
-                # a captured step: the number of slices is fixed (one wave of CTAs), their
-                # length follows the context through the table on the device
-                slices = max(1, min(32, slots // ctas))
                 slice_dev = tl.slice_len_table[slices:slices + 1] if slices > 1 else None
-            else:
-                # the number that minimises waves x (a CTA's fixed cost + its keys), at least 256 keys a slice
-                best = None
-                for cand in range(1, max(1, min(32, -(-tl.max_kv // 256))) + 1):
-                    length = -(-(-(-tl.max_kv // cand)) // 64) * 64
-                    real = -(-tl.max_kv // length)
-                    cost = -(-ctas * real // slots) * (128 + length)
-                    if best is None or cost < best[0]:
-                        best = (cost, real, length)
-                slices, slice_len = best[1], best[2]
         attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, 16, batch.cu_seqlens, batch.kv_lens, block_table,
                       page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
     if plan.large is not None:

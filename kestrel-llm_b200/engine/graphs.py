@@ -60,6 +60,8 @@ class StaticDecodeBatch:
         self.kv_lens_host: List[int] = [1] * B
         self.max_count = 1
         self.null_page = cache.null_page
+        # context for which the captured attention launch picks its number of slices
+        self.nominal_kv = max(256, min(cache.max_blocks * cache.page_size, 4096))
         self.bytes_h2d = int(total * 4)
         self.fill([], cache)
 
@@ -73,7 +75,7 @@ class StaticDecodeBatch:
     def attention_plan(self, group_size: int, rows_large: int = 64) -> AttentionPlan:
         if group_size > 16:
             raise RuntimeError("a captured decode step needs at most 16 query heads per kv head")
-        return AttentionPlan(TileList(self.seq_of_token, self._tile_row0, self.size, 0, self.slice_len_table), None)
+        return AttentionPlan(TileList(self.seq_of_token, self._tile_row0, self.size, self.nominal_kv, self.slice_len_table), None)
 
     def fill(self, entries: Sequence[Entry], cache) -> None:
         """Writes this step's values into the pinned buffer and starts its copy to the device."""
