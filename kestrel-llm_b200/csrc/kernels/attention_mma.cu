@@ -448,6 +448,15 @@ static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream)
     return kestrel_check_launch("attention_mma");
 }
 
+// merges the slices of the listed tiles (at most 16 rows each) into out; also used by attention_tc.cu
+KESTREL_API int kestrel_attention_merge(const float *part_o, const float *part_ml, void *out, const int *tile_seq,
+                                        const int *tile_row0, int tiles, const int *cu_seqlens, int slices, int hd,
+                                        int nq, int nkv, cudaStream_t stream) {
+    kestrel_launch(attention_merge_kernel, dim3(tiles, nkv), dim3(256), 0, stream, part_o, part_ml, (__nv_bfloat16 *)out,
+                   tile_seq, tile_row0, cu_seqlens, slices, hd, nq, nkv);
+    return kestrel_check_launch("attention_merge");
+}
+
 // rows (token, head) of a ROWS-mode tile for this head size
 KESTREL_API int kestrel_attention_mma_rows_per_tile(int hd) { return hd <= 128 ? 64 * AM_ROWS_MT : 64; }
 

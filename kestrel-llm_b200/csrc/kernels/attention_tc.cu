@@ -91,7 +91,8 @@ attention_tc_kernel(const AttnParams p) {
     const uint32_t tmem = *tmem_slot_ptr;
     pdl_wait();
 
-    const int tile = blockIdx.x, kvh = blockIdx.y;
+    const int tile = blockIdx.x, kvh = blockIdx.y, slice = blockIdx.z;
+    const int slice_len = p.slice_len_ptr ? *p.slice_len_ptr : p.slice_len;
     const int seq = p.tile_seq[tile], row0 = p.tile_row0[tile];
     const int G = p.nq / p.nkv;
     const int tok_begin = p.cu_seqlens[seq], n_tok = p.cu_seqlens[seq + 1] - tok_begin;
@@ -100,10 +101,13 @@ attention_tc_kernel(const AttnParams p) {
     const int rows_here = min(AT_BM, n_tok * G - row0);
     const int *table = p.block_table + (size_t)seq * p.table_stride;
     const int first_tok = row0 / G, last_tok = (row0 + rows_here - 1) / G;
-    const int k_hi = pos_begin + last_tok + 1;
-    const int k_first = p.window > 0 ? max(0, pos_begin + first_tok - p.window + 1) : 0;
+    // keys this CTA's rows may see, cut to its slice of the key range (slices are multiples of 128)
+    const int k_hi = min(pos_begin + last_tok + 1, (slice + 1) * slice_len);
+    const int k_first = max(p.window > 0 ? max(0, pos_begin + first_tok - p.window + 1) : 0, slice * slice_len);
     const int k_lo = (k_first / AT_BN) * AT_BN;
-    const int n_tiles = (k_hi - k_lo + AT_BN - 1) / AT_BN;
+    const int n_tiles = k_hi > k_lo ? (k_hi - k_lo + AT_BN - 1) / AT_BN : 0;
+    // warps none of whose 32 rows exist (decode: a few rows per request) skip the softmax arithmetic
+    const bool warp_has_rows = 32 * (warp & 3) < rows_here;
 
     const bool row_ok = r < rows_here;
     const int my_pos = row_ok ? pos_begin + (row0 + r) / G : -1;
@@ -182,49 +186,52 @@ attention_tc_kernel(const AttnParams p) {
         tc_fence_after();
 
         // softmax of this thread's half row
-        float s[64];
-        tc_ld64(tmem + lane_base + col0, s);
-        const bool whole = kbase >= k_first && kbase + AT_BN <= k_hi && kbase + AT_BN - 1 <= my_pos && kbase >= my_lo;
-        float mx = -INFINITY;
-        if (whole) {
+        float alpha = 1.f;
+        if (warp_has_rows) {
+            float s[64];
+            tc_ld64(tmem + lane_base + col0, s);
+            const bool whole = kbase >= k_first && kbase + AT_BN <= k_hi && kbase + AT_BN - 1 <= my_pos && kbase >= my_lo;
+            float mx = -INFINITY;
+            if (whole) {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) { s[j] *= p.scale_log2; mx = fmaxf(mx, s[j]); }
-        } else {
+                for (int j = 0; j < 64; ++j) { s[j] *= p.scale_log2; mx = fmaxf(mx, s[j]); }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    int key = kbase + col0 + j;
+                    bool vis = key <= my_pos && key >= my_lo && key < k_hi && key >= k_first;
+                    s[j] = vis ? s[j] * p.scale_log2 : -INFINITY;
+                    mx = fmaxf(mx, s[j]);
+                }
+            }
+            xchg[h * 128 + r] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");   // the two warps that share these rows
+            mx = fmaxf(mx, xchg[(h ^ 1) * 128 + r]);
+            float m_new = fmaxf(m_run, mx);
+            float m_use = m_new == -INFINITY ? 0.f : m_new;
+            alpha = at_exp2(m_run - m_use);
+            m_run = m_new;
+            float l_add = 0.f;
 #pragma unroll
             for (int j = 0; j < 64; ++j) {
-                int key = kbase + col0 + j;
-                bool vis = key <= my_pos && key >= my_lo && key < k_hi && key >= k_first;
-                s[j] = vis ? s[j] * p.scale_log2 : -INFINITY;
-                mx = fmaxf(mx, s[j]);
+                s[j] = at_exp2(s[j] - m_use);
+                l_add += s[j];
             }
-        }
-        xchg[h * 128 + r] = mx;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");       // the two warps that share these rows
-        mx = fmaxf(mx, xchg[(h ^ 1) * 128 + r]);
-        float m_new = fmaxf(m_run, mx);
-        float m_use = m_new == -INFINITY ? 0.f : m_new;
-        float alpha = at_exp2(m_run - m_use);
-        m_run = m_new;
-        float l_add = 0.f;
+            l_run = l_run * alpha + l_add;
+            // P as bfloat16 into the K tile's memory: keys 64 h .. + 63 are panel h of row r
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-            s[j] = at_exp2(s[j] - m_use);
-            l_add += s[j];
-        }
-        l_run = l_run * alpha + l_add;
-        // P as bfloat16 into the K tile's memory: keys 64 h .. + 63 are panel h of row r
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            uint4 u;
-            __nv_bfloat162 b0 = __floats2bfloat162_rn(s[8 * g + 0], s[8 * g + 1]);
-            __nv_bfloat162 b1 = __floats2bfloat162_rn(s[8 * g + 2], s[8 * g + 3]);
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(s[8 * g + 4], s[8 * g + 5]);
-            __nv_bfloat162 b3 = __floats2bfloat162_rn(s[8 * g + 6], s[8 * g + 7]);
-            u.x = *reinterpret_cast<uint32_t *>(&b0);
-            u.y = *reinterpret_cast<uint32_t *>(&b1);
-            u.z = *reinterpret_cast<uint32_t *>(&b2);
-            u.w = *reinterpret_cast<uint32_t *>(&b3);
-            *reinterpret_cast<uint4 *>(kp_ptr + h * AT_PANEL + swizzle128(r, g)) = u;
+            for (int g = 0; g < 8; ++g) {
+                uint4 u;
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(s[8 * g + 0], s[8 * g + 1]);
+                __nv_bfloat162 b1 = __floats2bfloat162_rn(s[8 * g + 2], s[8 * g + 3]);
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(s[8 * g + 4], s[8 * g + 5]);
+                __nv_bfloat162 b3 = __floats2bfloat162_rn(s[8 * g + 6], s[8 * g + 7]);
+                u.x = *reinterpret_cast<uint32_t *>(&b0);
+                u.y = *reinterpret_cast<uint32_t *>(&b1);
+                u.z = *reinterpret_cast<uint32_t *>(&b2);
+                u.w = *reinterpret_cast<uint32_t *>(&b3);
+                *reinterpret_cast<uint4 *>(kp_ptr + h * AT_PANEL + swizzle128(r, g)) = u;
+            }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");          // V(t) has landed
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P and V -> tensor-core reads
@@ -246,7 +253,7 @@ attention_tc_kernel(const AttnParams p) {
         tc_fence_after();
         if (t + 1 < n_tiles) load_tile(t + 1, kp_s, p.k_cache);       // P is consumed: K(t+1) may overwrite it
         asm volatile("cp.async.commit_group;" ::: "memory");
-        {
+        if (warp_has_rows) {
             float pvv[64];
             tc_ld64(tmem + lane_base + 128 + col0, pvv);
 #pragma unroll
@@ -265,20 +272,31 @@ attention_tc_kernel(const AttnParams p) {
     if (row_ok && ok) {
         int row = row0 + r;
         size_t qrow = (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G;
-        float inv = 1.0f / l_tot;
-        __nv_bfloat16 *po = p.out + qrow * AT_HD + col0;
+        if (p.slices > 1) {
+            // this slice's unnormalised out, maximum and sum; attention_merge_kernel combines the slices
+            float *po = p.part_o + (qrow * p.slices + slice) * AT_HD + col0;
 #pragma unroll
-        for (int c = 0; c < 64; c += 8) {
-            uint4 u;
-            __nv_bfloat162 b0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
-            __nv_bfloat162 b1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
-            __nv_bfloat162 b3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
-            u.x = *reinterpret_cast<uint32_t *>(&b0);
-            u.y = *reinterpret_cast<uint32_t *>(&b1);
-            u.z = *reinterpret_cast<uint32_t *>(&b2);
-            u.w = *reinterpret_cast<uint32_t *>(&b3);
-            *reinterpret_cast<uint4 *>(po + c) = u;
+            for (int c = 0; c < 64; c += 4) *reinterpret_cast<float4 *>(po + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+            if (h == 0) {
+                p.part_ml[(qrow * p.slices + slice) * 2] = m_run;
+                p.part_ml[(qrow * p.slices + slice) * 2 + 1] = l_tot;
+            }
+        } else {
+            float inv = 1.0f / l_tot;
+            __nv_bfloat16 *po = p.out + qrow * AT_HD + col0;
+#pragma unroll
+            for (int c = 0; c < 64; c += 8) {
+                uint4 u;
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
+                __nv_bfloat162 b1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
+                __nv_bfloat162 b3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
+                u.x = *reinterpret_cast<uint32_t *>(&b0);
+                u.y = *reinterpret_cast<uint32_t *>(&b1);
+                u.z = *reinterpret_cast<uint32_t *>(&b2);
+                u.w = *reinterpret_cast<uint32_t *>(&b3);
+                *reinterpret_cast<uint4 *>(po + c) = u;
+            }
         }
     }
     tc_fence_before();
@@ -289,20 +307,32 @@ attention_tc_kernel(const AttnParams p) {
     }
 }
 
-// Tiles of 128 rows (tile_seq / tile_row0), head size 128, no slices.
+extern "C" int kestrel_attention_merge(const float *part_o, const float *part_ml, void *out, const int *tile_seq,
+                                       const int *tile_row0, int tiles, const int *cu_seqlens, int slices, int hd,
+                                       int nq, int nkv, cudaStream_t stream);
+
+// Tiles of up to 128 rows (tile_seq / tile_row0), head size 128.  With slices > 1 (tiles of at
+// most 16 rows: decode tokens) every CTA takes a slice of slice_len keys, a multiple of 128 -
+// or the value at slice_len_ptr on the device - and the slices are merged in ascending order;
+// part_o / part_ml are scratch of T * nq * slices * 128 and T * nq * slices * 2 floats.
 KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const void *v_cache, void *out,
-                                     const int *tile_seq, const int *tile_row0, int tiles, const int *cu_seqlens,
-                                     const int *kv_lens, const int *block_table, int table_stride, int page_size,
-                                     int T, int nq, int nkv, int hd, int window, float scale, cudaStream_t stream) {
+                                     float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
+                                     int tiles, const int *cu_seqlens, const int *kv_lens, const int *block_table,
+                                     int table_stride, int page_size, int T, int nq, int nkv, int hd, int window,
+                                     int slices, int slice_len, const int *slice_len_ptr, float scale,
+                                     cudaStream_t stream) {
     if (T == 0 || tiles == 0) return 0;
     KESTREL_REQUIRE(hd == AT_HD, "attention_tc: head size %d; this kernel is built for %d", hd, AT_HD);
     KESTREL_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tc: %d query heads over %d kv heads", nq, nkv);
-    KESTREL_REQUIRE(nkv <= 65535, "attention_tc: grid too large");
+    KESTREL_REQUIRE(slices >= 1 && slice_len > 0 && slice_len % AT_BN == 0, "attention_tc: slice length %d must be a positive multiple of %d", slice_len, AT_BN);
+    KESTREL_REQUIRE(slices == 1 || (part_o && part_ml), "attention_tc: %d slices without scratch", slices);
+    KESTREL_REQUIRE(nkv <= 65535 && slices <= 65535, "attention_tc: grid too large");
     AttnParams p = {};
     p.q = (const __nv_bfloat16 *)q; p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
-    p.out = (__nv_bfloat16 *)out; p.tile_seq = tile_seq; p.tile_row0 = tile_row0; p.cu_seqlens = cu_seqlens;
-    p.kv_lens = kv_lens; p.block_table = block_table; p.table_stride = table_stride; p.page_size = page_size;
-    p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = 1; p.slice_len = 1 << 30;
+    p.out = (__nv_bfloat16 *)out; p.part_o = part_o; p.part_ml = part_ml; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
+    p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.block_table = block_table; p.table_stride = table_stride;
+    p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = slices; p.slice_len = slice_len;
+    p.slice_len_ptr = slice_len_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
     size_t smem = 6 * AT_PANEL + 16 + 2 * 128 * 4 + 1024;
     static bool attr_set = false;
@@ -311,8 +341,10 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
         if (e != cudaSuccess) return kestrel_fail(-3, "attention_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
         attr_set = true;
     }
-    kestrel_launch(attention_tc_kernel, dim3(tiles, nkv), dim3(AT_THREADS), smem, stream, p);
-    return kestrel_check_launch("attention_tc");
+    kestrel_launch(attention_tc_kernel, dim3(tiles, nkv, slices), dim3(AT_THREADS), smem, stream, p);
+    int rc = kestrel_check_launch("attention_tc");
+    if (rc || slices == 1) return rc;
+    return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, cu_seqlens, slices, hd, nq, nkv, stream);
 }
 
 // Error word of the kernel's bounded waits: 0 = none, 1 = waited for S, 2 = waited for PV.

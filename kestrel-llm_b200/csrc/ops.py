@@ -70,7 +70,8 @@ def _declare(lib) -> None:
         "kestrel_gemm_tc_error": [],
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _vp, _f, _vp],
-        "kestrel_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "kestrel_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
+                                 _i, _i, _vp, _f, _vp],
         "kestrel_attention_tc_error": [],
         "kestrel_attention_mma_slots": [_i],
         "kestrel_attention_mma_rows_per_tile": [_i],
@@ -427,8 +428,12 @@ def attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
 
 def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                  tile_seq: torch.Tensor, tile_row0: torch.Tensor, cu_seqlens: torch.Tensor, kv_lens: torch.Tensor,
-                 block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int, window: int, scale: float) -> None:
-    """tcgen05 attention of the listed tiles of 128 rows (prompt portions), head size 128."""
+                 block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int, window: int, scale: float,
+                 slices: int = 1, slice_len: int = 1 << 30, slice_len_dev: Optional[torch.Tensor] = None) -> None:
+    """tcgen05 attention of the listed tiles, head size 128: tiles of up to 128 rows (prompt
+    portions), or tiles of at most 16 rows (decode tokens) with the key range cut into
+    ``slices`` slices of ``slice_len`` keys (a multiple of 128) that are merged in ascending
+    order; ``slices * slice_len`` must reach the longest request."""
     _need(q, "attention_tc.q", torch.bfloat16, 2)
     _need(out, "attention_tc.out", torch.bfloat16, 2)
     _need(k_cache, "attention_tc.k_cache", torch.bfloat16)
@@ -439,10 +444,19 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     T, tiles = q.shape[0], tile_seq.shape[0]
     if q.shape[1] != nq * hd or out.shape != q.shape or tile_row0.shape[0] != tiles:
         raise KernelError("attention_tc: shapes differ")
+    part_o = part_ml = None
+    if slices > 1:
+        part_o = torch.empty((T * nq, slices, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((T * nq, slices, 2), dtype=torch.float32, device=q.device)
+    slice_len = min(int(slice_len), (1 << 30) // 128 * 128)
     _check(library().kestrel_attention_tc(
-        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(),
-        tiles, cu_seqlens.data_ptr(), kv_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size),
-        T, nq, nkv, hd, int(window), float(scale), _stream()))
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
+        tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, cu_seqlens.data_ptr(), kv_lens.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), int(page_size), T, nq, nkv, hd, int(window), int(slices),
+        slice_len, _p(slice_len_dev), float(scale), _stream()))
+    if slices > 1:
+        global launches
+        launches += 1          # the merge kernel
 
 
 def attention_tc_error() -> int:
@@ -466,19 +480,24 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
         return
     rows_large = library().kestrel_attention_mma_rows_per_tile(hd)
     plan = batch.attention_plan(nq // nkv, rows_large)
-    no_split = (1 << 30) // 64 * 64
+    no_split = (1 << 30) // 128 * 128
+    # Decode tokens stay on the mma.sync kernel: its three-stage cp.async ring keeps more bytes in
+    # flight per SM than the tcgen05 kernel's serial load -> S -> softmax -> PV chain, which is
+    # built for tiles full of rows (measured at batch 8 / 64, context 4096: 28 / 200 us a layer
+    # against 85 / 600 us).  The tcgen05 kernel can run them (slices included) and is tested so.
+    use_tc = False
     if plan.small is not None:
         tl = plan.small
         slices, slice_len, slice_dev = 1, no_split, None
         if window <= 0:         # a window is short; only full-length key ranges are cut into slices
-            slots = library().kestrel_attention_mma_slots(hd)
+            slots = 2 * 148 if use_tc else library().kestrel_attention_mma_slots(hd)
             ctas = max(1, tl.count * nkv)
             # the number of slices that minimises waves x (a CTA's fixed cost + its keys), at least
             # 256 keys a slice; a captured step fixes the number for a nominal context and lets the
-            # slice length follow the real one through the table on the device
+            # slice length (a multiple of 128) follow the real one through the table on the device
             best = None
             for cand in range(1, max(1, min(32, -(-tl.max_kv // 256))) + 1):
-                length = -(-(-(-tl.max_kv // cand)) // 64) * 64
+                length = -(-(-(-tl.max_kv // cand)) // 128) * 128
                 real = -(-tl.max_kv // length)
                 cost = -(-ctas * real // slots) * (128 + length)
                 if best is None or cost < best[0]:
@@ -486,8 +505,12 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
             slices, slice_len = best[1], best[2]
             if tl.slice_len_table is not None:
                 slice_dev = tl.slice_len_table[slices:slices + 1] if slices > 1 else None
-        attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, 16, batch.cu_seqlens, batch.kv_lens, block_table,
-                      page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
+        if use_tc:
+            attention_tc(q, k_cache, v_cache, out, tl.seq, tl.row0, batch.cu_seqlens, batch.kv_lens, block_table,
+                         page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
+        else:
+            attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, 16, batch.cu_seqlens, batch.kv_lens, block_table,
+                          page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
     if plan.large is not None:
         tl = plan.large
         if hd == 128 and rows_large == 128:

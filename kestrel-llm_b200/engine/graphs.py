@@ -107,7 +107,7 @@ class StaticDecodeBatch:
                 for i in range(n, B):
                     h[o_tab + (g * B + i) * W] = self.null_page
         for s in range(1, MAX_SLICES + 1):
-            h[o_misc + s] = max(64, -(-(-(-max_kv // s)) // 64) * 64)
+            h[o_misc + s] = max(128, -(-(-(-max_kv // s)) // 128) * 128)
         self.dev.copy_(self._ring[turn], non_blocking=True)
         ev = self._ring_done[turn] or torch.cuda.Event()
         ev.record()

@@ -274,7 +274,8 @@ def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slic
     if tc:
         ops.attention_tc(torch.from_numpy(qcat).to(torch.bfloat16).to(DEV), torch.from_numpy(kc).to(torch.bfloat16).to(DEV),
                          torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out, dev(tile_seq), dev(tile_row0), dev(cu),
-                         dev(total), dev(table), page, nq, nkv, hd, window, 1.0 / math.sqrt(hd))
+                         dev(total), dev(table), page, nq, nkv, hd, window, 1.0 / math.sqrt(hd),
+                         slices if slices > 1 else 1, slice_len if slices > 1 else 1 << 30)
         assert ops.attention_tc_error() == 0
     else:
         ops.attention_mma(torch.from_numpy(qcat).to(torch.bfloat16).to(DEV), torch.from_numpy(kc).to(torch.bfloat16).to(DEV),
@@ -302,6 +303,15 @@ def test_attention_tcgen05_prompt_portions(nq, nkv, window, page):
     deep into its context, key tiles of 128 with the last one cut."""
     _mma_case(nq, nkv, 128, window, page, lens_new=(50, 3, 300), lens_ctx=(100, 0, 77), rows_per_tile=128,
               slices=1, slice_len=0, seed=nq, tc=True)
+
+
+@pytest.mark.parametrize("nq,nkv,window,page,slices,slice_len", [(32, 8, 0, 16, 1, 1 << 24), (32, 8, 0, 16, 3, 128), (8, 1, 0, 4, 2, 256),
+                                                                 (4, 4, 100, 16, 1, 1 << 24), (16, 1, 0, 16, 4, 128)])
+def test_attention_tcgen05_decode_tokens(nq, nkv, window, page, slices, slice_len):
+    """The tcgen05 kernel on decode tokens: one new token for each of five requests of very
+    different lengths, few rows per tile, the key range cut into slices that are merged."""
+    _mma_case(nq, nkv, 128, window, page, lens_new=(1, 1, 1, 1, 1), lens_ctx=(0, 15, 64, 200, 330), rows_per_tile=16,
+              slices=slices, slice_len=slice_len, seed=nq + 3, tc=True)
 
 
 @pytest.mark.parametrize("far", [0, 15, 16, 127, 128, 255, 256])
