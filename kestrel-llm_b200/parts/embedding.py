@@ -46,5 +46,7 @@ class LMHead(Part):
         return [] if self.tied else [WeightSlot(self.weight_name, self.weight)]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x [R, width] -> float32 logits [R, vocab]."""
-        return ops.linear(x, self.weight)[0]
+        """x [R, width] -> float32 logits [R, vocab].  The product is not split over K (a split
+        product returns slices that a consumer kernel sums; the logits have no such consumer)."""
+        logits = torch.empty((1, x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
+        return ops.linear(x, self.weight, logits)[0]

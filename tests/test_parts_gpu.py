@@ -171,14 +171,14 @@ def _toy_parts():
             return s
 
         def forward(self, x, batch):
-            score = ops.linear(x, self.router)[0]
+            score = ops.linear(x, self.router).sum(0)
             pick = score.argmax(1)
             out = torch.zeros((x.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
             for e in range(2):
                 idx = (pick == e).nonzero().flatten()
                 if idx.numel():
-                    h = torch.relu(ops.linear(x[idx].contiguous(), self.up[e])[0]).to(self.dtype)
-                    out[idx] = ops.linear(h, self.down[e])[0]
+                    h = torch.relu(ops.linear(x[idx].contiguous(), self.up[e]).sum(0)).to(self.dtype)
+                    out[idx] = ops.linear(h, self.down[e]).sum(0)
             return ops.Partials(out)
 
     return RunningMeanMixer, LearnedPositions, RoutedFeedForward
