@@ -13,6 +13,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, OutOfPages
@@ -76,9 +77,10 @@ class Engine:
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"request {e.rid}: wanted place {w} outside its {len(e.tokens)} tokens of this step")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise ValueError(f"request {e.rid}: token id {t} outside the vocabulary of {self.vocab_size}")
+            ids = np.asarray(e.tokens, dtype=np.int64)
+            if ids.min() < 0 or ids.max() >= self.vocab_size:
+                bad = int(ids[(ids < 0) | (ids >= self.vocab_size)][0])
+                raise ValueError(f"request {e.rid}: token id {bad} outside the vocabulary of {self.vocab_size}")
         admitted: List[int] = []
         try:
             for e in entries:

@@ -7,12 +7,12 @@ product when the sizes fit its tiling rules and the CUDA-core product otherwise.
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Optional
 
 import torch
 
 from ..csrc import ops
-from .base import Part, WeightSlot
+from .base import Part
 
 
 class Linear(Part):

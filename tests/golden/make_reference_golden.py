@@ -1,7 +1,7 @@
 """Makes tests/golden/reference_logits.npy: logits of the REFERENCE's own compiled float32
 forward pass on the tiny random model in tests/golden/tiny_model.
 
-    python tests/golden/make_reference_golden.py [/path/to/kestrel-llm]
+    python tests/golden/make_reference_golden.py /path/to/kestrel-llm
 
 It compiles six of the reference's C files with gcc on the CPU (the float32 fallback of
 src/model/vllm_safetensors.c needs no ARM board), links them with reference_harness.c and
@@ -87,7 +87,9 @@ def write_safetensors_bf16(path, W):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_reference_golden.py /path/to/kestrel-llm (a checkout of the reference)")
+    ref = sys.argv[1]
     W = make_weights()
     mdir = os.path.join(HERE, "tiny_model")
     os.makedirs(mdir, exist_ok=True)
