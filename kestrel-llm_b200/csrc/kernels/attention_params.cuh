@@ -15,6 +15,7 @@ struct AttnParams {
     const int *kv_lens;             // [nseq] request length after this step
     const int *block_table;         // [nseq, table_stride]
     const int *slice_len_ptr;       // if not null, the slice length is read from here (a step of a captured graph)
+    int table_width;                // entries of a request's row that may be read (attention_tc.cu)
     int table_stride, page_size, nq, nkv, hd, window, slices, slice_len;
     float scale_log2;
 };

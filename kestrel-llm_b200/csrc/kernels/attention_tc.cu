@@ -2,28 +2,30 @@
 //
 // A CTA owns 128 rows - (token, query head of one kv group) pairs, token-major, as in
 // attention_mma.cu - and walks the keys its rows may see in tiles of 128, anchored at
-// multiples of 128 of the absolute position:
-//   S = Q K^T    tcgen05.mma M=128 N=128, 8 steps of K=16 over the head size; Q and the K tile
-//                sit in shared memory as K-major operands (two panels of 64 dims, rows of 128
-//                bytes, 128-byte swizzle); S goes to TMEM columns 0..127;
-//   softmax      two threads own a row, 64 keys each: one tcgen05.ld of S, row maximum (the
-//                halves exchange it), exp2 and sum in float32, P written as bfloat16 into the
-//                K tile's shared memory (K is no longer needed), again as a K-major operand;
-//   PV           tcgen05.mma with P as A and the V tile as an MN-major B operand (V rows are
-//                keys, 128 bytes of 64 dims each, which is MN-major for a [dim, key] product);
-//                the tile's product goes to TMEM columns 128..255 and is added to the row's
-//                float32 output registers after rescaling by 2^(m_old - m_new).
-// The tiles come from the paged cache through the block table with cp.async, written at the
-// swizzled addresses the operand descriptors expect: V(t) lands while S(t) is computed and
-// softmaxed, K(t+1) while the output is updated.  Shared memory per CTA is 97 KB (Q, K/P, V),
-// so two CTAs share an SM.  Every mbarrier wait is
-// bounded; the error word is read by kestrel_attention_tc_error.  Formulas as in
-// attention_plain.cu (reference: st.c:10779-10911, st.c:9762-9859).
+// multiples of 128 of the absolute position.  Eleven warps in three roles, coupled by mbarriers:
+//   loaders  (warp 8 for K, warp 10 for V)  look the tile's pages up in the block table and
+//            fetch K(t) or V(t) with TMA (boxes of one page, or of 128 keys of a larger page, by
+//            64 dims; 128-byte swizzle) into two-stage rings, each as far ahead as its ring allows;
+//   issuer   (warp 9, one thread)  S(t+1) = Q K(t+1)^T as soon as K(t+1) has landed and the S
+//            buffer is free, then O(t) = P(t) V(t) when P(t) is written: tcgen05.mma M=128 N=128,
+//            8 steps of K=16; Q, K and P are K-major operands (two panels of 64 elements, rows of
+//            128 bytes), V is an MN-major B operand (its rows are keys).  S and the tile's PV
+//            product are double-buffered in TMEM (4 x 128 columns), so the tensor cores work on
+//            tile t+1 while tile t is softmaxed;
+//   softmax  (warps 0-7)  two threads own a row, 64 keys each: row maximum (the halves exchange
+//            it), exp2 and sum in float32, P as bfloat16 into shared memory; the tile's PV product
+//            is added to the row's float32 output registers after rescaling by 2^(m_old - m_new).
+// Keys outside [first key, last key] of the CTA's rows are masked in S; V rows outside that range
+// are zeroed in shared memory (a page may hold another request's stale values there, and
+// 0 x NaN would not be 0).  Shared memory per CTA is 194 KB: one CTA per SM; CTAs with the most
+// keys are launched first.  Every mbarrier wait is bounded; the error word is read by
+// kestrel_attention_tc_error.  Formulas as in attention_plain.cu (reference: st.c:10779-10911,
+// st.c:9762-9859).
 #include "attention_params.cuh"
 #include "tcgen05.cuh"
 #include <math.h>
 
-#define AT_THREADS 256
+#define AT_THREADS 352
 #define AT_BM 128
 #define AT_BN 128
 #define AT_HD 128
@@ -40,11 +42,11 @@ __device__ __forceinline__ float at_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// 64 consecutive TMEM columns of this thread's lane: four loads in flight, one wait
-__device__ __forceinline__ void tc_ld64(uint32_t taddr, float *v) {
-    uint32_t r[64];
+// 32 consecutive TMEM columns of this thread's lane: two loads in flight, one wait
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float *v) {
+    uint32_t r[32];
 #pragma unroll
-    for (int q = 0; q < 4; ++q)
+    for (int q = 0; q < 2; ++q)
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
             : "=r"(r[16 * q + 0]), "=r"(r[16 * q + 1]), "=r"(r[16 * q + 2]), "=r"(r[16 * q + 3]), "=r"(r[16 * q + 4]),
@@ -54,35 +56,46 @@ __device__ __forceinline__ void tc_ld64(uint32_t taddr, float *v) {
             : "r"(taddr + 16 * q));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// 256 threads: thread (r, h) = (tid % 128, tid / 128) owns row r and half h of it: 64 of the
-// tile's 128 keys in the softmax, 64 of the 128 output dims.  Warps w and w + 4 share TMEM
-// lanes 32 (w % 4)...; the two halves of a row exchange their maxima through shared memory.
-__global__ void __launch_bounds__(AT_THREADS)
-attention_tc_kernel(const AttnParams p) {
+enum {
+    B_Q_FULL = 0, B_K_FULL = 1, B_K_EMPTY = 3, B_V_FULL = 5, B_V_EMPTY = 7, B_S_FULL = 9, B_S_EMPTY = 11,
+    B_PV_FULL = 13, B_PV_EMPTY = 15, B_P_FULL = 17, B_COUNT = 18
+};
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                    const AttnParams p, int cache_pages) {
     pdl_launch_dependents();
     // M = 128, N = 128, bf16 x bf16 -> f32; both operands K-major for S, B MN-major for PV
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BN >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
     constexpr uint32_t IDESC_PV = IDESC_S | (1u << 16);
+    constexpr uint32_t TILE_BYTES = 2 * AT_PANEL;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_s = base, kp_s = base + 2 * AT_PANEL, v_s = base + 4 * AT_PANEL;
-    const uint32_t bar = base + 6 * AT_PANEL, tmem_slot = bar + 8;
     uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
-    volatile uint32_t *tmem_slot_ptr = (volatile uint32_t *)(aligned + 6 * AT_PANEL + 8);
-    float *xchg = (float *)(aligned + 6 * AT_PANEL + 16);           // [2][128] row maxima of the halves
-    uint8_t *kp_ptr = aligned + 2 * AT_PANEL;
+    const uint32_t q_s = base, k_s = base + TILE_BYTES, v_s = base + 3 * TILE_BYTES, p_s = base + 5 * TILE_BYTES;
+    const uint32_t bars = base + 6 * TILE_BYTES, tmem_slot = bars + 8 * B_COUNT;
+    volatile uint32_t *tmem_slot_ptr = (volatile uint32_t *)(aligned + 6 * TILE_BYTES + 8 * B_COUNT);
+    float *xchg = (float *)(aligned + 6 * TILE_BYTES + 8 * B_COUNT + 16);          // [3][2][128]: row maxima of the halves by tile parity, row sums
+    uint8_t *p_ptr = aligned + 5 * TILE_BYTES, *v_ptr = aligned + 3 * TILE_BYTES;
+    auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int r = tid & 127, h = tid >> 7;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        mbar_init(bar, 1);
+        mbar_init(bar(B_Q_FULL), 8);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(B_K_FULL + b), 1);  mbar_init(bar(B_K_EMPTY + b), 1);
+            mbar_init(bar(B_V_FULL + b), 1);  mbar_init(bar(B_V_EMPTY + b), 1);
+            mbar_init(bar(B_S_FULL + b), 1);  mbar_init(bar(B_S_EMPTY + b), 8);
+            mbar_init(bar(B_PV_FULL + b), 1); mbar_init(bar(B_PV_EMPTY + b), 8);
+        }
+        mbar_init(bar(B_P_FULL), 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256) : "memory");
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -91,7 +104,7 @@ attention_tc_kernel(const AttnParams p) {
     const uint32_t tmem = *tmem_slot_ptr;
     pdl_wait();
 
-    const int tile = blockIdx.x, kvh = blockIdx.y, slice = blockIdx.z;
+    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, slice = blockIdx.z;   // late tiles see the most keys
     const int slice_len = p.slice_len_ptr ? *p.slice_len_ptr : p.slice_len;
     const int seq = p.tile_seq[tile], row0 = p.tile_row0[tile];
     const int G = p.nq / p.nkv;
@@ -106,204 +119,291 @@ attention_tc_kernel(const AttnParams p) {
     const int k_first = max(p.window > 0 ? max(0, pos_begin + first_tok - p.window + 1) : 0, slice * slice_len);
     const int k_lo = (k_first / AT_BN) * AT_BN;
     const int n_tiles = k_hi > k_lo ? (k_hi - k_lo + AT_BN - 1) / AT_BN : 0;
-    // warps none of whose 32 rows exist (decode: a few rows per request) skip the softmax arithmetic
-    const bool warp_has_rows = 32 * (warp & 3) < rows_here;
 
-    const bool row_ok = r < rows_here;
-    const int my_pos = row_ok ? pos_begin + (row0 + r) / G : -1;
-    const int my_lo = p.window > 0 ? max(0, my_pos - p.window + 1) : 0;
-
-    // copies: thread t moves 16-byte chunk t % 16 of rows (t / 16) * 8 .. + 7
-    const int ld_c = tid & 15, ld_r0 = (tid >> 4) * 8;
-    const uint32_t ld_panel = (uint32_t)(ld_c >> 3) * AT_PANEL;
-    {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            int rr = ld_r0 + j;
-            bool valid = rr < rows_here;
-            size_t off = 0;
-            if (valid) {
-                int row = row0 + rr;
-                off = ((size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G) * AT_HD + ld_c * 8;
+    if (warp == 8 || warp == 10) {
+        // ------------------------------------------------------------------ loaders
+        // warp 8 fetches the K tiles, warp 10 the V tiles, each as far ahead as its ring allows;
+        // lane l fetches the l-th page of a tile (both panels)
+        const bool is_v = warp == 10;
+        const CUtensorMap *map = is_v ? &map_v : &map_k;
+        const int full0 = is_v ? B_V_FULL : B_K_FULL, empty0 = is_v ? B_V_EMPTY : B_K_EMPTY;
+        const uint32_t ring = is_v ? v_s : k_s;
+        const int box_rows = min(p.page_size, AT_BN);
+        const int boxes = AT_BN / box_rows;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int b = t & 1;
+            const uint32_t par = (uint32_t)(t >> 1) & 1u;
+            int row = 0;
+            if (lane < boxes) {
+                int s0 = k_lo + t * AT_BN + lane * box_rows;
+                int idx = s0 / p.page_size;
+                int page = idx < p.table_width ? table[idx] : 0;
+                if (page < 0 || page >= cache_pages) page = 0;      // a released or absent page: its keys are masked, its values zeroed
+                row = (page * p.nkv + kvh) * p.page_size + s0 % p.page_size;
             }
-            at_cp_async16(q_s + ld_panel + swizzle128(rr, ld_c & 7), p.q + off, valid);
+            if (!mbar_wait(bar(empty0 + b), par ^ 1u)) { atomicExch(&g_at_error, is_v ? 4 : 3); break; }
+            if (lane == 0) mbar_expect_tx(bar(full0 + b), TILE_BYTES);
+            __syncwarp();
+            if (lane < boxes) {
+                uint32_t dst = ring + b * TILE_BYTES + lane * box_rows * 128;
+                tma_load_2d(dst, map, bar(full0 + b), 0, row);
+                tma_load_2d(dst + AT_PANEL, map, bar(full0 + b), 64, row);
+            }
         }
-    }
-    const bool one_page = p.page_size % 8 == 0;
-    auto load_tile = [&](int t, uint32_t dst, const __nv_bfloat16 *cache) {
-        int s0 = k_lo + t * AT_BN + ld_r0;
-        size_t page_off = 0;
-        if (one_page && s0 + 8 > k_first && s0 < k_hi) {
-            int page = table[s0 / p.page_size];
-            page_off = (((size_t)page * p.nkv + kvh) * p.page_size + (s0 % p.page_size)) * AT_HD + ld_c * 8;
-        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ issuer
+        if (lane == 0 && n_tiles > 0) {
+            bool ok = mbar_wait(bar(B_Q_FULL), 0);
+            if (!ok) atomicExch(&g_at_error, 5);
+            auto issue_s = [&](int t) {
+                const int b = t & 1;
+                const uint32_t par = (uint32_t)(t >> 1) & 1u;
+                if (!mbar_wait(bar(B_K_FULL + b), par) || !mbar_wait(bar(B_S_EMPTY + b), par ^ 1u)) {
+                    atomicExch(&g_at_error, 1);
+                    return false;
+                }
+                tc_fence_after();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            int s = s0 + j;
-            bool valid = s >= k_first && s < k_hi;
-            size_t off = 0;
-            if (valid) {
-                if (one_page) {
-                    off = page_off + (size_t)j * AT_HD;
-                } else {
-                    int page = table[s / p.page_size];
-                    off = (((size_t)page * p.nkv + kvh) * p.page_size + (s % p.page_size)) * AT_HD + ld_c * 8;
+                for (int ks = 0; ks < AT_HD / 16; ++ks) {
+                    uint32_t off = (ks >> 2) * AT_PANEL + (ks & 3) * 32;
+                    tc_mma(tmem + b * 128, smem_desc(q_s + off), smem_desc(k_s + b * TILE_BYTES + off), IDESC_S, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bar(B_S_FULL + b));
+                tc_commit(bar(B_K_EMPTY + b));
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                if (t + 1 < n_tiles) {
+                    ok = issue_s(t + 1);
+                    if (!ok) break;
+                }
+                const int b = t & 1;
+                const uint32_t par = (uint32_t)(t >> 1) & 1u;
+                if (!mbar_wait(bar(B_P_FULL), (uint32_t)t & 1u) || !mbar_wait(bar(B_V_FULL + b), par) ||
+                    !mbar_wait(bar(B_PV_EMPTY + b), par ^ 1u)) {
+                    atomicExch(&g_at_error, 2);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < AT_BN / 16; ++ks) {
+                    // A = P: keys 16 ks.. in panel ks / 4; B = V: 16 keys down = 2 groups of 8 rows
+                    uint64_t da = smem_desc(p_s + (ks >> 2) * AT_PANEL + (ks & 3) * 32);
+                    uint64_t db = smem_desc_mn_major(v_s + b * TILE_BYTES + ks * 2048, AT_PANEL);
+                    tc_mma(tmem + 256 + b * 128, da, db, IDESC_PV, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bar(B_PV_FULL + b));
+                tc_commit(bar(B_V_EMPTY + b));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax
+        // thread (r, h) = (tid % 128, tid / 128) owns row r and half h of it: 64 of the tile's 128
+        // keys in the softmax, 64 of the 128 output dims.  Warps w and w + 4 share TMEM lanes
+        // 32 (w % 4)...
+        const int r = tid & 127, h = tid >> 7;
+        // warps none of whose 32 rows exist (decode: a few rows per request) skip the arithmetic
+        const bool warp_has_rows = 32 * (warp & 3) < rows_here;
+        const bool row_ok = r < rows_here;
+        const int my_pos = row_ok ? pos_begin + (row0 + r) / G : -1;
+        const int my_lo = p.window > 0 ? max(0, my_pos - p.window + 1) : 0;
+        {
+            // Q: thread t moves 16-byte chunk t % 16 of rows (t / 16) * 8 .. + 7
+            const int ld_c = tid & 15, ld_r0 = (tid >> 4) * 8;
+            const uint32_t ld_panel = (uint32_t)(ld_c >> 3) * AT_PANEL;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                int rr = ld_r0 + j;
+                bool valid = rr < rows_here;
+                size_t off = 0;
+                if (valid) {
+                    int row = row0 + rr;
+                    off = ((size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G) * AT_HD + ld_c * 8;
+                }
+                at_cp_async16(q_s + ld_panel + swizzle128(rr, ld_c & 7), p.q + off, valid);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor-core reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_Q_FULL));
+        }
+
+        float o[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) o[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, alpha_pending = 1.f;
+        bool ok = true;             // after a wait gave up the loop runs on without waiting: the warps' named barriers stay paired
+        const uint32_t lane_base = ((uint32_t)(32 * (warp & 3))) << 16;
+        const int col0 = 64 * h;
+
+        // adds the PV product of tile t to the output registers and frees its TMEM buffer
+        auto take_pv = [&](int t) {
+            const int b = t & 1;
+            if (ok && !mbar_wait(bar(B_PV_FULL + b), (uint32_t)(t >> 1) & 1u)) { atomicExch(&g_at_error, 6); ok = false; }
+            tc_fence_after();
+            if (warp_has_rows) {
+#pragma unroll
+                for (int c = 0; c < 64; c += 32) {
+                    float pvv[32];
+                    tc_ld32(tmem + lane_base + 256 + b * 128 + col0 + c, pvv);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[c + j] = fmaf(o[c + j], alpha_pending, pvv[j]);
                 }
             }
-            at_cp_async16(dst + ld_panel + swizzle128(ld_r0 + j, ld_c & 7), cache + off, valid);
-        }
-    };
-    if (n_tiles > 0) load_tile(0, kp_s, p.k_cache);
-    asm volatile("cp.async.commit_group;" ::: "memory");             // group: Q and K(0)
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_PV_EMPTY + b));
+        };
 
-    float o[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    uint32_t phase = 0;
-    bool ok = true;
-    const uint32_t lane_base = ((uint32_t)(32 * (warp & 3))) << 16;
-    const int col0 = 64 * h;
-
-    for (int t = 0; t < n_tiles && ok; ++t) {
-        const int kbase = k_lo + t * AT_BN;
-        load_tile(t, v_s, p.v_cache);                                 // V(t) lands while S is computed and softmaxed
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 1;" ::: "memory");          // K(t) (and Q) have landed
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor-core reads
-        __syncthreads();
-        if (tid == 0) {
+        for (int t = 0; t < n_tiles; ++t) {
+            const int b = t & 1;
+            const uint32_t par = (uint32_t)(t >> 1) & 1u;
+            const int kbase = k_lo + t * AT_BN;
+            if (ok && !mbar_wait(bar(B_S_FULL + b), par)) { atomicExch(&g_at_error, 7); ok = false; }
             tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < AT_HD / 16; ++ks) {
-                uint32_t off = (ks >> 2) * AT_PANEL + (ks & 3) * 32;
-                tc_mma(tmem, smem_desc(q_s + off), smem_desc(kp_s + off), IDESC_S, ks > 0 ? 1u : 0u);
-            }
-            tc_commit(bar);
-        }
-        if (!mbar_wait(bar, phase)) { atomicExch(&g_at_error, 1); ok = false; }
-        phase ^= 1;
-        tc_fence_after();
-
-        // softmax of this thread's half row
-        float alpha = 1.f;
-        if (warp_has_rows) {
-            float s[64];
-            tc_ld64(tmem + lane_base + col0, s);
+            const uint32_t s_addr = tmem + lane_base + b * 128 + col0;
             const bool whole = kbase >= k_first && kbase + AT_BN <= k_hi && kbase + AT_BN - 1 <= my_pos && kbase >= my_lo;
-            float mx = -INFINITY;
-            if (whole) {
+            float alpha = 1.f, m_use = 0.f;
+            if (warp_has_rows) {
+                // Two passes over the half row in chunks of 32 columns (maximum, then exponentials):
+                // reading S twice from TMEM is cheap and keeps the live registers few.
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                const bool warp_whole1 = __all_sync(0xffffffffu, whole);
 #pragma unroll
-                for (int j = 0; j < 64; ++j) { s[j] *= p.scale_log2; mx = fmaxf(mx, s[j]); }
-            } else {
+                for (int c = 0; c < 64; c += 32) {
+                    float s[32];
+                    tc_ld32(s_addr + c, s);
+                    if (warp_whole1) {
 #pragma unroll
-                for (int j = 0; j < 64; ++j) {
-                    int key = kbase + col0 + j;
-                    bool vis = key <= my_pos && key >= my_lo && key < k_hi && key >= k_first;
-                    s[j] = vis ? s[j] * p.scale_log2 : -INFINITY;
-                    mx = fmaxf(mx, s[j]);
+                        for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], s[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            int key = kbase + col0 + c + j;
+                            bool vis = key <= my_pos && key >= my_lo && key < k_hi && key >= k_first;
+                            m4[j & 3] = fmaxf(m4[j & 3], vis ? s[j] : -INFINITY);
+                        }
+                    }
+                }
+                float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                mx *= p.scale_log2;                                  // the scale is positive: max commutes with it
+                float *xm = xchg + b * 256;                          // by tile parity: the other warp may still read the tile before
+                xm[h * 128 + r] = mx;
+                asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");   // the two warps that share these rows
+                mx = fmaxf(mx, xm[(h ^ 1) * 128 + r]);
+                float m_new = fmaxf(m_run, mx);
+                m_use = m_new == -INFINITY ? 0.f : m_new;
+                alpha = at_exp2(m_run - m_use);
+                m_run = m_new;
+            }
+            // the product of the tile before: its P is consumed, so P(t) may be written after it
+            if (t > 0) take_pv(t - 1);
+            alpha_pending = alpha;
+            if (warp_has_rows) {
+                // a warp all of whose rows see the whole tile (every tile but the diagonal ones)
+                // spends no instructions on the mask
+                const bool warp_whole = __all_sync(0xffffffffu, whole);
+                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < 64; c += 32) {
+                    float s[32];
+                    tc_ld32(s_addr + c, s);
+                    if (warp_whole) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            s[j] = at_exp2(fmaf(s[j], p.scale_log2, -m_use));
+                            l4[j & 3] += s[j];
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            int key = kbase + col0 + c + j;
+                            bool vis = key <= my_pos && key >= my_lo && key < k_hi && key >= k_first;
+                            s[j] = vis ? at_exp2(fmaf(s[j], p.scale_log2, -m_use)) : 0.f;
+                            l4[j & 3] += s[j];
+                        }
+                    }
+                    // P as bfloat16: keys 64 h .. + 63 are panel h of row r
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 u;
+                        __nv_bfloat162 b0 = __floats2bfloat162_rn(s[8 * g + 0], s[8 * g + 1]);
+                        __nv_bfloat162 b1 = __floats2bfloat162_rn(s[8 * g + 2], s[8 * g + 3]);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(s[8 * g + 4], s[8 * g + 5]);
+                        __nv_bfloat162 b3 = __floats2bfloat162_rn(s[8 * g + 6], s[8 * g + 7]);
+                        u.x = *reinterpret_cast<uint32_t *>(&b0);
+                        u.y = *reinterpret_cast<uint32_t *>(&b1);
+                        u.z = *reinterpret_cast<uint32_t *>(&b2);
+                        u.w = *reinterpret_cast<uint32_t *>(&b3);
+                        *reinterpret_cast<uint4 *>(p_ptr + h * AT_PANEL + swizzle128(r, (c >> 3) + g)) = u;
+                    }
+                }
+                const float l_add = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                l_run = l_run * alpha + l_add;
+            }
+            if (kbase < k_first || kbase + AT_BN > k_hi) {
+                // V rows of keys outside the range become zero before the product reads them
+                if (ok && !mbar_wait(bar(B_V_FULL + b), par)) { atomicExch(&g_at_error, 8); ok = false; }
+                const int lo_rows = max(0, k_first - kbase), hi_row = min(AT_BN, k_hi - kbase);
+                for (int idx = tid; idx < AT_BN * 16; idx += 256) {
+                    int row = idx >> 4, c = idx & 15;
+                    if (row < lo_rows || row >= hi_row)
+                        *reinterpret_cast<uint4 *>(v_ptr + b * TILE_BYTES + (c >> 3) * AT_PANEL + row * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
             }
-            xchg[h * 128 + r] = mx;
-            asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");   // the two warps that share these rows
-            mx = fmaxf(mx, xchg[(h ^ 1) * 128 + r]);
-            float m_new = fmaxf(m_run, mx);
-            float m_use = m_new == -INFINITY ? 0.f : m_new;
-            alpha = at_exp2(m_run - m_use);
-            m_run = m_new;
-            float l_add = 0.f;
-#pragma unroll
-            for (int j = 0; j < 64; ++j) {
-                s[j] = at_exp2(s[j] - m_use);
-                l_add += s[j];
-            }
-            l_run = l_run * alpha + l_add;
-            // P as bfloat16 into the K tile's memory: keys 64 h .. + 63 are panel h of row r
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                uint4 u;
-                __nv_bfloat162 b0 = __floats2bfloat162_rn(s[8 * g + 0], s[8 * g + 1]);
-                __nv_bfloat162 b1 = __floats2bfloat162_rn(s[8 * g + 2], s[8 * g + 3]);
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(s[8 * g + 4], s[8 * g + 5]);
-                __nv_bfloat162 b3 = __floats2bfloat162_rn(s[8 * g + 6], s[8 * g + 7]);
-                u.x = *reinterpret_cast<uint32_t *>(&b0);
-                u.y = *reinterpret_cast<uint32_t *>(&b1);
-                u.z = *reinterpret_cast<uint32_t *>(&b2);
-                u.w = *reinterpret_cast<uint32_t *>(&b3);
-                *reinterpret_cast<uint4 *>(kp_ptr + h * AT_PANEL + swizzle128(r, g)) = u;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and zeroed V rows) -> tensor-core reads
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar(B_S_EMPTY + b));
+                mbar_arrive(bar(B_P_FULL));
             }
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");          // V(t) has landed
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P and V -> tensor-core reads
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < AT_BN / 16; ++ks) {
-                // A = P: keys 16 ks.. in panel ks / 4; B = V: 16 keys down = 2 groups of 8 rows
-                uint64_t da = smem_desc(kp_s + (ks >> 2) * AT_PANEL + (ks & 3) * 32);
-                uint64_t db = smem_desc_mn_major(v_s + ks * 2048, AT_PANEL);
-                tc_mma(tmem + 128, da, db, IDESC_PV, ks > 0 ? 1u : 0u);
-            }
-            tc_commit(bar);
-        }
-        if (!mbar_wait(bar, phase)) { atomicExch(&g_at_error, 2); ok = false; }
-        phase ^= 1;
-        tc_fence_after();
-        if (t + 1 < n_tiles) load_tile(t + 1, kp_s, p.k_cache);       // P is consumed: K(t+1) may overwrite it
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (warp_has_rows) {
-            float pvv[64];
-            tc_ld64(tmem + lane_base + 128 + col0, pvv);
-#pragma unroll
-            for (int j = 0; j < 64; ++j) o[j] = o[j] * alpha + pvv[j];
-        }
-        tc_fence_before();
-        __syncthreads();          // S and PV columns may be rewritten, V overwritten
-    }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (n_tiles > 0) take_pv(n_tiles - 1);
 
-    // the row's sum is the sum of its halves
-    __syncthreads();
-    xchg[h * 128 + r] = l_run;
-    __syncthreads();
-    float l_tot = l_run + xchg[(h ^ 1) * 128 + r];
-    if (row_ok && ok) {
-        int row = row0 + r;
-        size_t qrow = (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G;
-        if (p.slices > 1) {
-            // this slice's unnormalised out, maximum and sum; attention_merge_kernel combines the slices
-            float *po = p.part_o + (qrow * p.slices + slice) * AT_HD + col0;
+        // the row's sum is the sum of its halves
+        xchg[512 + h * 128 + r] = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
+        float l_tot = l_run + xchg[512 + (h ^ 1) * 128 + r];
+        if (row_ok && ok) {
+            int row = row0 + r;
+            size_t qrow = (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G;
+            if (p.slices > 1) {
+                // this slice's unnormalised out, maximum and sum; attention_merge_kernel combines the slices
+                float *po = p.part_o + (qrow * p.slices + slice) * AT_HD + col0;
 #pragma unroll
-            for (int c = 0; c < 64; c += 4) *reinterpret_cast<float4 *>(po + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
-            if (h == 0) {
-                p.part_ml[(qrow * p.slices + slice) * 2] = m_run;
-                p.part_ml[(qrow * p.slices + slice) * 2 + 1] = l_tot;
-            }
-        } else {
-            float inv = 1.0f / l_tot;
-            __nv_bfloat16 *po = p.out + qrow * AT_HD + col0;
+                for (int c = 0; c < 64; c += 4) *reinterpret_cast<float4 *>(po + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+                if (h == 0) {
+                    p.part_ml[(qrow * p.slices + slice) * 2] = m_run;
+                    p.part_ml[(qrow * p.slices + slice) * 2 + 1] = l_tot;
+                }
+            } else {
+                float inv = 1.0f / l_tot;
+                __nv_bfloat16 *po = p.out + qrow * AT_HD + col0;
 #pragma unroll
-            for (int c = 0; c < 64; c += 8) {
-                uint4 u;
-                __nv_bfloat162 b0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
-                __nv_bfloat162 b1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
-                __nv_bfloat162 b3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
-                u.x = *reinterpret_cast<uint32_t *>(&b0);
-                u.y = *reinterpret_cast<uint32_t *>(&b1);
-                u.z = *reinterpret_cast<uint32_t *>(&b2);
-                u.w = *reinterpret_cast<uint32_t *>(&b3);
-                *reinterpret_cast<uint4 *>(po + c) = u;
+                for (int c = 0; c < 64; c += 8) {
+                    uint4 u;
+                    __nv_bfloat162 b0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
+                    __nv_bfloat162 b1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
+                    __nv_bfloat162 b3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
+                    u.x = *reinterpret_cast<uint32_t *>(&b0);
+                    u.y = *reinterpret_cast<uint32_t *>(&b1);
+                    u.z = *reinterpret_cast<uint32_t *>(&b2);
+                    u.w = *reinterpret_cast<uint32_t *>(&b3);
+                    *reinterpret_cast<uint4 *>(po + c) = u;
+                }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 9) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
 }
 
@@ -311,15 +411,21 @@ extern "C" int kestrel_attention_merge(const float *part_o, const float *part_ml
                                        const int *tile_row0, int tiles, const int *cu_seqlens, int slices, int hd,
                                        int nq, int nkv, cudaStream_t stream);
 
-// Tiles of up to 128 rows (tile_seq / tile_row0), head size 128.  With slices > 1 (tiles of at
+// Whether the kernel takes this head size and page size.
+KESTREL_API int kestrel_attention_tc_supported(int hd, int page_size) {
+    return hd == AT_HD && page_size > 0 && page_size % 8 == 0 && (AT_BN % page_size == 0 || page_size % AT_BN == 0);
+}
+
+// Tiles of up to 128 rows (tile_seq / tile_row0), head size 128; cache_pages is the number of
+// pages the cache tensors hold.  With slices > 1 (tiles of at
 // most 16 rows: decode tokens) every CTA takes a slice of slice_len keys, a multiple of 128 -
 // or the value at slice_len_ptr on the device - and the slices are merged in ascending order;
 // part_o / part_ml are scratch of T * nq * slices * 128 and T * nq * slices * 2 floats.
 KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const void *v_cache, void *out,
                                      float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
                                      int tiles, const int *cu_seqlens, const int *kv_lens, const int *block_table,
-                                     int table_stride, int page_size, int T, int nq, int nkv, int hd, int window,
-                                     int slices, int slice_len, const int *slice_len_ptr, float scale,
+                                     int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd,
+                                     int window, int slices, int slice_len, const int *slice_len_ptr, float scale,
                                      cudaStream_t stream) {
     if (T == 0 || tiles == 0) return 0;
     KESTREL_REQUIRE(hd == AT_HD, "attention_tc: head size %d; this kernel is built for %d", hd, AT_HD);
@@ -327,27 +433,36 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
     KESTREL_REQUIRE(slices >= 1 && slice_len > 0 && slice_len % AT_BN == 0, "attention_tc: slice length %d must be a positive multiple of %d", slice_len, AT_BN);
     KESTREL_REQUIRE(slices == 1 || (part_o && part_ml), "attention_tc: %d slices without scratch", slices);
     KESTREL_REQUIRE(nkv <= 65535 && slices <= 65535, "attention_tc: grid too large");
+    KESTREL_REQUIRE(kestrel_attention_tc_supported(hd, page_size), "attention_tc: pages of %d keys; the page size must be a multiple of 8 that divides 128 or is a multiple of it", page_size);
+    KESTREL_REQUIRE(cache_pages > 0 && (long long)cache_pages * nkv * page_size < (1ll << 31), "attention_tc: a cache of %d pages is beyond the 32-bit row coordinate", cache_pages);
+    CUtensorMap map_k, map_v;
+    const long long cache_rows = (long long)cache_pages * nkv * page_size;
+    int rc = kestrel_tensor_map_bf16(&map_k, k_cache, cache_rows, AT_HD, AT_HD, page_size < AT_BN ? page_size : AT_BN);
+    if (rc) return rc;
+    rc = kestrel_tensor_map_bf16(&map_v, v_cache, cache_rows, AT_HD, AT_HD, page_size < AT_BN ? page_size : AT_BN);
+    if (rc) return rc;
     AttnParams p = {};
     p.q = (const __nv_bfloat16 *)q; p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
     p.out = (__nv_bfloat16 *)out; p.part_o = part_o; p.part_ml = part_ml; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
-    p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.block_table = block_table; p.table_stride = table_stride;
+    p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.block_table = block_table; p.table_width = table_width; p.table_stride = table_stride;
     p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = slices; p.slice_len = slice_len;
     p.slice_len_ptr = slice_len_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
-    size_t smem = 6 * AT_PANEL + 16 + 2 * 128 * 4 + 1024;
+    size_t smem = 12 * AT_PANEL + 8 * B_COUNT + 16 + 3 * 256 * 4 + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return kestrel_fail(-3, "attention_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
         attr_set = true;
     }
-    kestrel_launch(attention_tc_kernel, dim3(tiles, nkv, slices), dim3(AT_THREADS), smem, stream, p);
-    int rc = kestrel_check_launch("attention_tc");
+    kestrel_launch(attention_tc_kernel, dim3(tiles, nkv, slices), dim3(AT_THREADS), smem, stream, map_k, map_v, p, cache_pages);
+    rc = kestrel_check_launch("attention_tc");
     if (rc || slices == 1) return rc;
     return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, cu_seqlens, slices, hd, nq, nkv, stream);
 }
 
-// Error word of the kernel's bounded waits: 0 = none, 1 = waited for S, 2 = waited for PV.
+// Error word of the kernel's bounded waits: 0 = none, else the number of the wait that gave up
+// (1, 2, 5: issuer; 3, 4: loader; 6, 7, 8: softmax).
 // Synchronises the device and clears the word.
 KESTREL_API int kestrel_attention_tc_error(void) {
     int v = 0, zero = 0;

@@ -567,7 +567,7 @@ struct MapKeyHash {
 };
 
 // bf16 matrix [rows, cols] with row stride ld elements; box = box_rows x 64 columns, 128-byte swizzle
-static int make_map(CUtensorMap *out, const void *ptr, long long rows, long long cols, long long ld, int box_rows) {
+int kestrel_tensor_map_bf16(CUtensorMap *out, const void *ptr, long long rows, long long cols, long long ld, int box_rows) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     static std::mutex mu;
     MapKey key{ptr, rows, cols, ld, box_rows};
@@ -577,7 +577,7 @@ static int make_map(CUtensorMap *out, const void *ptr, long long rows, long long
         if (it != cache.end()) { *out = it->second; return 0; }
     }
     EncodeTiledFn fn = encode_fn();
-    if (!fn) return kestrel_fail(-4, "gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+    if (!fn) return kestrel_fail(-4, "tensor map: the driver does not offer cuTensorMapEncodeTiled");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
@@ -585,7 +585,7 @@ static int make_map(CUtensorMap *out, const void *ptr, long long rows, long long
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return kestrel_fail(-4, "gemm_tc: cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld)", (int)r, rows, cols, ld);
+    if (r != CUDA_SUCCESS) return kestrel_fail(-4, "tensor map: cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld)", (int)r, rows, cols, ld);
     std::lock_guard<std::mutex> g(mu);
     if (cache.size() > 4096) cache.clear();
     cache.emplace(key, *out);
@@ -741,15 +741,15 @@ static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, in
     bool persistent = T > 256 && splits == 1 && g_persistent;
     if (persistent && MODE == TC_SWIGLU) bn = g_swiglu_bn;
     CUtensorMap mw, mx;
-    int rc = make_map(&mw, w, w_rows, K, ldw, TC_BM);
+    int rc = kestrel_tensor_map_bf16(&mw, w, w_rows, K, ldw, TC_BM);
     if (rc) return rc;
     if (persistent && g_pairs) {
-        rc = make_map(&mx, x, T, K, ldx, TCP_BN / 2);
+        rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, TCP_BN / 2);
         if (rc) return rc;
         rc = launch_tc_pair<MODE>(mw, mx, out, T, N, K, ldo, up_off, stream);
         if (rc <= 0) return rc;            // 1 = pairs cannot be scheduled: go on with one CTA per tile
     }
-    rc = make_map(&mx, x, T, K, ldx, bn);
+    rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, bn);
     if (rc) return rc;
     if (persistent) {
         if (MODE == TC_SWIGLU && bn == 128) return launch_tc_persistent<128, TC_SWIGLU>(mw, mx, out, T, N, K, ldo, up_off, stream);

@@ -6,6 +6,10 @@
 
 #define TC_WAIT_LIMIT (1u << 22)
 
+// Host: tensor map of a bf16 matrix [rows, cols] with row stride ld elements, boxes of box_rows
+// rows by 64 columns, 128-byte swizzle (cached by its arguments; defined in gemm_tcgen05.cu).
+int kestrel_tensor_map_bf16(CUtensorMap *out, const void *ptr, long long rows, long long cols, long long ld, int box_rows);
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

@@ -71,7 +71,8 @@ def _declare(lib) -> None:
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _vp, _f, _vp],
         "kestrel_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
-                                 _i, _i, _vp, _f, _vp],
+                                 _i, _i, _i, _i, _vp, _f, _vp],
+        "kestrel_attention_tc_supported": [_i, _i],
         "kestrel_attention_tc_error": [],
         "kestrel_attention_mma_slots": [_i],
         "kestrel_attention_mma_rows_per_tile": [_i],
@@ -433,7 +434,9 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     """tcgen05 attention of the listed tiles, head size 128: tiles of up to 128 rows (prompt
     portions), or tiles of at most 16 rows (decode tokens) with the key range cut into
     ``slices`` slices of ``slice_len`` keys (a multiple of 128) that are merged in ascending
-    order; ``slices * slice_len`` must reach the longest request."""
+    order; ``slices * slice_len`` must reach the longest request.  The cache tensors are
+    [pages, kv heads, page size, 128], contiguous, with a page size the kernel's page-wise TMA
+    boxes fit (``attention_tc_supported``)."""
     _need(q, "attention_tc.q", torch.bfloat16, 2)
     _need(out, "attention_tc.out", torch.bfloat16, 2)
     _need(k_cache, "attention_tc.k_cache", torch.bfloat16)
@@ -444,6 +447,8 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     T, tiles = q.shape[0], tile_seq.shape[0]
     if q.shape[1] != nq * hd or out.shape != q.shape or tile_row0.shape[0] != tiles:
         raise KernelError("attention_tc: shapes differ")
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or v_cache.shape != k_cache.shape:
+        raise KernelError(f"attention_tc: cache of shape {tuple(k_cache.shape)}, expected [pages, {nkv}, {page_size}, {hd}]")
     part_o = part_ml = None
     if slices > 1:
         part_o = torch.empty((T * nq, slices, hd), dtype=torch.float32, device=q.device)
@@ -452,11 +457,16 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     _check(library().kestrel_attention_tc(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
         tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, cu_seqlens.data_ptr(), kv_lens.data_ptr(),
-        block_table.data_ptr(), block_table.stride(0), int(page_size), T, nq, nkv, hd, int(window), int(slices),
-        slice_len, _p(slice_len_dev), float(scale), _stream()))
+        block_table.data_ptr(), block_table.shape[1], block_table.stride(0), int(page_size), int(k_cache.shape[0]), T, nq, nkv, hd,
+        int(window), int(slices), slice_len, _p(slice_len_dev), float(scale), _stream()))
     if slices > 1:
         global launches
         launches += 1          # the merge kernel
+
+
+def attention_tc_supported(hd: int, page_size: int) -> bool:
+    """Whether the tcgen05 attention kernel takes this head size and page size."""
+    return bool(library().kestrel_attention_tc_supported(int(hd), int(page_size)))
 
 
 def attention_tc_error() -> int:
@@ -473,7 +483,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
     token).  bfloat16 takes the tensor-core kernel: requests with at most 16 (token, head) rows
     per kv head - decode tokens - in KEYS mode with the key range cut into slices so that the
     grid fills the GPU, the others - prompt portions - on the tcgen05 kernel when the head size
-    is 128 and in ROWS mode of the mma.sync kernel otherwise."""
+    is 128 (and the page size fits its TMA boxes) and in ROWS mode of the mma.sync kernel otherwise."""
     if q.dtype != torch.bfloat16 or hd % 8 or hd > 256:
         attention_plain(q, k_cache, v_cache, batch.positions, batch.seq_of_token, block_table, page_size,
                         out, nq, nkv, hd, window, scale)
@@ -481,10 +491,9 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
     rows_large = library().kestrel_attention_mma_rows_per_tile(hd)
     plan = batch.attention_plan(nq // nkv, rows_large)
     no_split = (1 << 30) // 128 * 128
-    # Decode tokens stay on the mma.sync kernel: its three-stage cp.async ring keeps more bytes in
-    # flight per SM than the tcgen05 kernel's serial load -> S -> softmax -> PV chain, which is
-    # built for tiles full of rows (measured at batch 8 / 64, context 4096: 28 / 200 us a layer
-    # against 85 / 600 us).  The tcgen05 kernel can run them (slices included) and is tested so.
+    # Decode tokens stay on the mma.sync kernel, which runs three CTAs of few rows per SM; the
+    # tcgen05 kernel is built for tiles full of rows, one CTA per SM.  It can run decode tokens
+    # (slices included) and is tested so.
     use_tc = False
     if plan.small is not None:
         tl = plan.small
@@ -513,7 +522,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
                           page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
     if plan.large is not None:
         tl = plan.large
-        if hd == 128 and rows_large == 128:
+        if rows_large == 128 and attention_tc_supported(hd, page_size):
             attention_tc(q, k_cache, v_cache, out, tl.seq, tl.row0, batch.cu_seqlens, batch.kv_lens, block_table,
                          page_size, nq, nkv, hd, window, scale)
         else:

@@ -243,8 +243,10 @@ def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slic
     total = [c + n for c, n in zip(lens_ctx, lens_new)]
     num_pages = sum((t + page - 1) // page for t in total) + 3
     perm = rng.permutation(num_pages)
-    kc = np.full((num_pages, nkv, page, hd), 1e4, dtype=np.float32)
-    vc = np.full((num_pages, nkv, page, hd), -1e4, dtype=np.float32)
+    # slots no request owns: large values for the mma.sync kernel, NaN for the tcgen05 kernel,
+    # which fetches whole pages and has to keep what lies beyond a request's end out of the sums
+    kc = np.full((num_pages, nkv, page, hd), np.nan if tc else 1e4, dtype=np.float32)
+    vc = np.full((num_pages, nkv, page, hd), np.nan if tc else -1e4, dtype=np.float32)
     width = max((t + page - 1) // page for t in total)
     table = np.full((nseq, width), -1, dtype=np.int32)
     qs, refs, used = [], [], 0
@@ -297,7 +299,8 @@ def test_attention_mma_prompt_portions(nq, nkv, hd, window, page):
               slices=1, slice_len=(1 << 30) // 64 * 64, seed=hd)
 
 
-@pytest.mark.parametrize("nq,nkv,window,page", [(32, 8, 0, 16), (8, 1, 0, 4), (4, 4, 100, 16), (6, 2, 0, 1), (5, 1, 33, 32)])
+@pytest.mark.parametrize("nq,nkv,window,page", [(32, 8, 0, 16), (8, 1, 0, 8), (4, 4, 100, 16), (6, 2, 0, 128), (5, 1, 33, 32),
+                                                (4, 2, 0, 256), (2, 2, 150, 64)])
 def test_attention_tcgen05_prompt_portions(nq, nkv, window, page):
     """The tcgen05 kernel (head size 128): portions of three requests, one from position 0, one
     deep into its context, key tiles of 128 with the last one cut."""
@@ -305,8 +308,8 @@ def test_attention_tcgen05_prompt_portions(nq, nkv, window, page):
               slices=1, slice_len=0, seed=nq, tc=True)
 
 
-@pytest.mark.parametrize("nq,nkv,window,page,slices,slice_len", [(32, 8, 0, 16, 1, 1 << 24), (32, 8, 0, 16, 3, 128), (8, 1, 0, 4, 2, 256),
-                                                                 (4, 4, 100, 16, 1, 1 << 24), (16, 1, 0, 16, 4, 128)])
+@pytest.mark.parametrize("nq,nkv,window,page,slices,slice_len", [(32, 8, 0, 16, 1, 1 << 24), (32, 8, 0, 16, 3, 128), (8, 1, 0, 8, 2, 256),
+                                                                 (4, 4, 100, 16, 1, 1 << 24), (16, 1, 0, 128, 4, 128)])
 def test_attention_tcgen05_decode_tokens(nq, nkv, window, page, slices, slice_len):
     """The tcgen05 kernel on decode tokens: one new token for each of five requests of very
     different lengths, few rows per tile, the key range cut into slices that are merged."""
@@ -412,6 +415,20 @@ def test_attention_mma_refuses_odd_head_sizes():
     i = torch.zeros(2, dtype=torch.int32, device=DEV)
     with pytest.raises(ops.KernelError, match="multiple of 8"):
         ops.attention_mma(z, z, z, torch.empty_like(z), i[:1], i[:1], 16, i, i[:1], i[None, :1], 4, 1, 1, 12, 0, 1.0)
+
+
+def test_attention_tcgen05_refuses_pages_its_boxes_do_not_fit():
+    """Pages of 4 or 48 keys do not tile the kernel's 128-key TMA boxes; the dispatcher sends such
+    caches to the mma.sync kernel and the kernel itself says no."""
+    ops = _ops()
+    assert ops.attention_tc_supported(128, 16) and ops.attention_tc_supported(128, 256)
+    assert not ops.attention_tc_supported(128, 4) and not ops.attention_tc_supported(128, 48)
+    assert not ops.attention_tc_supported(64, 16)
+    q = torch.zeros((1, 128), dtype=torch.bfloat16, device=DEV)
+    cache = torch.zeros((2, 1, 4, 128), dtype=torch.bfloat16, device=DEV)
+    i = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError, match="page size"):
+        ops.attention_tc(q, cache, cache, torch.empty_like(q), i[:1], i[:1], i, i[:1], i[None, :1], 4, 1, 1, 128, 0, 1.0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
