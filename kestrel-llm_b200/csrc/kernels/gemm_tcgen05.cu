@@ -39,7 +39,7 @@ template <int BN, int MODE>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void *__restrict__ out, int T, int N, int K, int kb_per_split, long long slice_stride,
-               long long ldo, int stages, int up_row_offset) {
+               long long ldo, int stages, int up_row_offset, int early_w) {
     pdl_launch_dependents();
     constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
@@ -89,13 +89,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         tc_fence_after();
         tmem = *tmem_slot_ptr;
     }
-    pdl_wait();                                       // now wait for the operands of the predecessor
-
     if (warp == 0) {
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int kb = 0; kb < num_kb; ++kb) {
+            // Weights that were complete before the predecessor kernel began do not depend on it:
+            // the weight tiles of the first ring of stages are on their way while it still runs,
+            // and only the activation tiles wait for it.
+            const int pre = early_w ? min(stages, num_kb) : 0;
+            for (int kb = 0; kb < pre; ++kb) {
+                mbar_expect_tx(full_bar(kb), STAGE_BYTES);
+                uint32_t sa = base + (uint32_t)kb * STAGE_BYTES;
+                int kc = (kb0 + kb) * TC_BK;
+                tma_load_2d(sa, &map_w, full_bar(kb), kc, n0);
+                if (MODE == TC_SWIGLU) tma_load_2d(sa + A_BYTES, &map_w, full_bar(kb), kc, up_row_offset + n0);
+            }
+            pdl_wait();                               // the activations are the predecessor's output
+            for (int kb = 0; kb < pre; ++kb)
+                tma_load_2d(base + (uint32_t)kb * STAGE_BYTES + A_TILES * A_BYTES, &map_x, full_bar(kb), (kb0 + kb) * TC_BK, t0);
+            int stage = pre == stages ? 0 : pre;
+            uint32_t phase = pre == stages ? 1 : 0;
+            for (int kb = pre; kb < num_kb; ++kb) {
                 if (!mbar_wait(empty_bar(stage), phase ^ 1)) { atomicExch(&g_tc_error, 1); break; }
                 mbar_expect_tx(full_bar(stage), STAGE_BYTES);
                 uint32_t sa = base + (uint32_t)stage * STAGE_BYTES;
@@ -107,6 +119,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
     } else if (warp == 1) {
+        pdl_wait();
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
@@ -128,6 +141,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tc_commit(accum_bar);
         }
     } else {
+        pdl_wait();
         int q = warp & 3;                       // TMEM lanes 32q .. 32q+31 belong to this warp
         int n = n0 + 32 * q + lane;
         bool waited = mbar_wait(accum_bar, 0);
@@ -644,7 +658,7 @@ KESTREL_API int kestrel_gemm_tc_splits(int T, int N, int K) {
 
 template <int BN, int MODE>
 static int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, void *out, int T, int N, int K, int splits,
-                     long long slice_stride, long long ldo, int up_off, cudaStream_t stream) {
+                     long long slice_stride, long long ldo, int up_off, int early_w, cudaStream_t stream) {
     constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
     constexpr int STAGE_BYTES = A_TILES * TC_BM * TC_BK * 2 + BN * TC_BK * 2;
     int total_kb = (K + TC_BK - 1) / TC_BK;
@@ -664,7 +678,7 @@ static int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, void *out, in
     }
     dim3 grid((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
     if (grid.y > 65535) return kestrel_fail(-2, "gemm_tc: T=%d needs more than 65535 token tiles", T);
-    kestrel_launch(gemm_tc_kernel<BN, MODE>, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, out, T, N, K, per, slice_stride, ldo, stages, up_off);
+    kestrel_launch(gemm_tc_kernel<BN, MODE>, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, out, T, N, K, per, slice_stride, ldo, stages, up_off, early_w);
     return kestrel_check_launch("gemm_tc");
 }
 
@@ -736,7 +750,7 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
 
 template <int MODE>
 static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, int w_rows, int K, long long ldx, long long ldw,
-                       long long ldo, int splits, long long slice_stride, int up_off, cudaStream_t stream) {
+                       long long ldo, int splits, long long slice_stride, int up_off, int early_w, cudaStream_t stream) {
     int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
     bool persistent = T > 256 && splits == 1 && g_persistent;
     if (persistent && MODE == TC_SWIGLU) bn = g_swiglu_bn;
@@ -757,23 +771,33 @@ static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, in
         return launch_tc_persistent<256, TC_PARTIAL>(mw, mx, out, T, N, K, ldo, up_off, stream);
     }
     switch (bn) {
-        case 16: return launch_tc<16, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
-        case 32: return launch_tc<32, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
-        case 64: return launch_tc<64, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
-        case 128: return launch_tc<128, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
-        default: return launch_tc<256, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, stream);
+        case 16: return launch_tc<16, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, early_w, stream);
+        case 32: return launch_tc<32, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, early_w, stream);
+        case 64: return launch_tc<64, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, early_w, stream);
+        case 128: return launch_tc<128, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, early_w, stream);
+        default: return launch_tc<256, MODE>(mw, mx, out, T, N, K, splits, slice_stride, ldo, up_off, early_w, stream);
     }
 }
 
-// out float32 [splits, T, N] (slice stride given), x bf16 [T, K], w bf16 [N, K]
-KESTREL_API int kestrel_gemm_tc(const void *x, const void *w, float *out, int T, int N, int K, long long ldx,
-                                long long ldw, long long ldo, int splits, long long slice_stride, cudaStream_t stream) {
+// out float32 [splits, T, N] (slice stride given), x bf16 [T, K], w bf16 [N, K].  weights_static
+// says that w was complete before the kernel that precedes this one in the stream began (a
+// model's weights): few-token products then fetch their first weight tiles while that kernel
+// still runs, and wait for it only before they read x.
+KESTREL_API int kestrel_gemm_tc_w(const void *x, const void *w, float *out, int T, int N, int K, long long ldx,
+                                  long long ldw, long long ldo, int splits, long long slice_stride, int weights_static,
+                                  cudaStream_t stream) {
     if (T == 0) return 0;
     KESTREL_REQUIRE(kestrel_gemm_tc_supported(x, w, T, N, K, ldx, ldw), "gemm_tc: sizes T=%d N=%d K=%d ldx=%lld ldw=%lld do not fit the TMA rules (multiples of 8, 16-byte aligned)", T, N, K, ldx, ldw);
     int total_kb = (K + TC_BK - 1) / TC_BK;
     KESTREL_REQUIRE(splits >= 1 && splits <= total_kb && ((total_kb + splits - 1) / splits) * (splits - 1) < total_kb,
                     "gemm_tc: %d slices over %d k-blocks would leave a slice empty", splits, total_kb);
-    return dispatch_tc<TC_PARTIAL>(x, w, out, T, N, N, K, ldx, ldw, ldo, splits, slice_stride, 0, stream);
+    return dispatch_tc<TC_PARTIAL>(x, w, out, T, N, N, K, ldx, ldw, ldo, splits, slice_stride, 0, weights_static ? 1 : 0, stream);
+}
+
+// The same for a w that the preceding kernel may have written.
+KESTREL_API int kestrel_gemm_tc(const void *x, const void *w, float *out, int T, int N, int K, long long ldx,
+                                long long ldw, long long ldo, int splits, long long slice_stride, cudaStream_t stream) {
+    return kestrel_gemm_tc_w(x, w, out, T, N, K, ldx, ldw, ldo, splits, slice_stride, 0, stream);
 }
 
 // out bf16 [T, ff] = silu(x Wg^T) * (x Wu^T), w bf16 [2 ff, K] with the gate rows first
@@ -781,7 +805,7 @@ KESTREL_API int kestrel_gemm_tc_swiglu(const void *x, const void *w, void *out, 
                                        long long ldw, long long ldo, cudaStream_t stream) {
     if (T == 0) return 0;
     KESTREL_REQUIRE(kestrel_gemm_tc_supported(x, w, T, ff, K, ldx, ldw), "gemm_tc_swiglu: sizes T=%d ff=%d K=%d do not fit the TMA rules", T, ff, K);
-    return dispatch_tc<TC_SWIGLU>(x, w, out, T, ff, 2 * ff, K, ldx, ldw, ldo, 1, 0, ff, stream);
+    return dispatch_tc<TC_SWIGLU>(x, w, out, T, ff, 2 * ff, K, ldx, ldw, ldo, 1, 0, ff, 0, stream);
 }
 
 // Reads (and clears) the error word that a bounded wait sets when it runs out: 0 = none,

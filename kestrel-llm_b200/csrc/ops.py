@@ -66,6 +66,7 @@ def _declare(lib) -> None:
         "kestrel_gemm_tc_supported": [_vp, _vp, _i, _i, _i, _ll, _ll],
         "kestrel_gemm_tc_splits": [_i, _i, _i],
         "kestrel_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _ll, _vp],
+        "kestrel_gemm_tc_w": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _ll, _i, _vp],
         "kestrel_gemm_tc_swiglu": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
         "kestrel_gemm_tc_error": [],
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
@@ -316,8 +317,11 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
-            splits: Optional[int] = None) -> torch.Tensor:
-    """y = x w^T on the tensor cores (tcgen05, TMA, TMEM) as float32 slices [S, T, N]."""
+            splits: Optional[int] = None, weights_static: bool = False) -> torch.Tensor:
+    """y = x w^T on the tensor cores (tcgen05, TMA, TMEM) as float32 slices [S, T, N].
+    ``weights_static``: w was complete before the kernel that precedes this call in the stream
+    began (a model's weights, never something the step itself computes); few-token products then
+    fetch their first weight tiles while that kernel still runs."""
     _need(x, "gemm_tc.x", torch.bfloat16, 2)
     _need(w, "gemm_tc.w", torch.bfloat16, 2)
     T, K = x.shape
@@ -335,8 +339,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     else:
         S = splits if splits is not None else lib.kestrel_gemm_tc_splits(T, N, K)
         out = torch.empty((S, T, N), dtype=torch.float32, device=x.device)
-    _check(lib.kestrel_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, x.stride(0), w.stride(0),
-                               out.stride(1), S, out.stride(0), _stream()))
+    _check(lib.kestrel_gemm_tc_w(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, x.stride(0), w.stride(0),
+                                 out.stride(1), S, out.stride(0), 1 if weights_static else 0, _stream()))
     return out
 
 
@@ -365,15 +369,17 @@ def gemm_tc_error() -> int:
     return library().kestrel_gemm_tc_error()
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+           weights_static: bool = False) -> torch.Tensor:
     """y = x w^T as float32 slices [S, T, N] (S = 1 unless a split-K kernel ran).
+    ``weights_static`` as in `gemm_tc`.
 
     float32 operands always take the CUDA-core product; bfloat16 operands take the tcgen05
     product when its tiling rules hold (see `gemm_tc_supported`) and the CUDA-core one
     otherwise."""
     T, N = x.shape[0], w.shape[0]
     if gemm_tc_supported(x, w):
-        return gemm_tc(x, w, out)
+        return gemm_tc(x, w, out, weights_static=weights_static)
     if out is None:
         out = torch.empty((1, T, N), dtype=torch.float32, device=x.device)
     elif out.dim() == 2:
@@ -382,13 +388,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None)
     return out
 
 
-def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) in x's dtype, Wg and Wu being the two halves of w_gate_up's rows."""
+def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, weights_static: bool = False) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) in x's dtype, Wg and Wu being the two halves of w_gate_up's rows.
+    ``weights_static`` as in `gemm_tc`."""
     out = torch.empty((x.shape[0], ff), dtype=x.dtype, device=x.device)
     if x.shape[0] > 256 and gemm_tc_supported(x, w_gate_up):
         gemm_tc_swiglu(x, w_gate_up, out)          # many tokens: the activation is the product's epilogue
     else:
-        swiglu(Partials(linear(x, w_gate_up)), out)  # few tokens: split-K slices, summed by the activation kernel
+        swiglu(Partials(linear(x, w_gate_up, weights_static=weights_static)), out)  # few tokens: split-K slices, summed by the activation kernel
     return out
 
 

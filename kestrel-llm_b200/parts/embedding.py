@@ -49,4 +49,4 @@ class LMHead(Part):
         """x [R, width] -> float32 logits [R, vocab].  The product is not split over K (a split
         product returns slices that a consumer kernel sums; the logits have no such consumer)."""
         logits = torch.empty((1, x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
-        return ops.linear(x, self.weight, logits)[0]
+        return ops.linear(x, self.weight, logits, weights_static=True)[0]

@@ -3,7 +3,9 @@ reference: weights are used in checkpoint layout, without transposing).
 
 The kernel is chosen by dtype and size: float32 always runs the CUDA-core product with
 ascending-k FMA accumulation (the true 32-bit path); bfloat16 runs the tcgen05 tensor-core
-product when the sizes fit its tiling rules and the CUDA-core product otherwise.
+product when the sizes fit its tiling rules and the CUDA-core product otherwise.  A part's
+weights are loaded once, before any step runs, and the product is told so (``weights_static``):
+it may fetch weight tiles while the kernel in front of it still runs.
 """
 from __future__ import annotations
 
@@ -25,4 +27,4 @@ class Linear(Part):
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> ops.Partials:
         """x [T, in] in the weight's dtype -> Partials [S, T, out]."""
-        return ops.Partials(ops.linear(x, self.weight, out), self.bias)
+        return ops.Partials(ops.linear(x, self.weight, out, weights_static=True), self.bias)

@@ -33,5 +33,5 @@ class GatedMLP(FeedForward):
 
     def forward(self, x: torch.Tensor, batch) -> ops.Partials:
         T = x.shape[0]
-        act = ops.gate_up_swiglu(x, self.gate_up.weight, self.intermediate)
+        act = ops.gate_up_swiglu(x, self.gate_up.weight, self.intermediate, weights_static=True)
         return self.down.forward(act)

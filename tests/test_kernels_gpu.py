@@ -70,6 +70,29 @@ def test_gemm_tcgen05(T, N, K, splits):
     np.testing.assert_allclose(got, plain.cpu().numpy(), rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max() + 1e-7)
 
 
+def test_gemm_tcgen05_static_weights_wait_for_the_activations():
+    """With weights_static the product fetches weight tiles before the kernel in front of it has
+    ended; the activations, which that kernel writes, must still be the new ones.  A chain of
+    norm -> product, run several times over with a changing residual: every result follows its
+    own input."""
+    ops = _ops()
+    T, d, N = 8, 1024, 640
+    w, wr = _rand((N, d), torch.bfloat16, 11, 0.05)
+    gain = torch.ones(d, device=DEV)
+    xs = torch.empty((T, d), dtype=torch.bfloat16, device=DEV)
+    outs, refs = [], []
+    for it in range(6):
+        res, rr = _rand((T, d), torch.float32, 20 + it, 1.0 + it)
+        ops.add_rmsnorm(res, None, gain, 1e-6, xs, write_back=False)
+        outs.append(ops.gemm_tc(xs, w, weights_static=True).sum(0))
+        xn = rr / np.sqrt((rr.astype(np.float64) ** 2).mean(-1, keepdims=True) + 1e-6)
+        xn = torch.from_numpy(xn.astype(np.float32)).to(torch.bfloat16).float().numpy()
+        refs.append(xn.astype(np.float64) @ wr.astype(np.float64).T)
+    assert ops.gemm_tc_error() == 0
+    for got, ref in zip(outs, refs):
+        np.testing.assert_allclose(got.cpu().numpy(), ref, rtol=0, atol=1e-2 * np.abs(ref).max())
+
+
 def test_gemm_tcgen05_row_does_not_depend_on_the_batch():
     ops = _ops()
     x, _ = _rand((300, 512), torch.bfloat16, 3)
