@@ -650,7 +650,9 @@ KESTREL_API int kestrel_gemm_tc_splits(int T, int N, int K) {
         int real = (total_kb + per - 1) / per;                  // no empty slice
         if (real != s) continue;
         long long waves = (tiles * s + slots - 1) / slots;
-        long long cost = waves * (g_overhead_kb + per) * g_ctas_per_sm;
+        // a CTA also writes its float32 slice [bn, 128] and the consumer reads it back: bn / 16
+        // k-blocks' worth of bytes (a k-block of weights is 16 KB)
+        long long cost = waves * (g_overhead_kb + bn / 16 + per) * g_ctas_per_sm;
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
     }
     return best;
@@ -800,12 +802,18 @@ KESTREL_API int kestrel_gemm_tc(const void *x, const void *w, float *out, int T,
     return kestrel_gemm_tc_w(x, w, out, T, N, K, ldx, ldw, ldo, splits, slice_stride, 0, stream);
 }
 
-// out bf16 [T, ff] = silu(x Wg^T) * (x Wu^T), w bf16 [2 ff, K] with the gate rows first
-KESTREL_API int kestrel_gemm_tc_swiglu(const void *x, const void *w, void *out, int T, int ff, int K, long long ldx,
-                                       long long ldw, long long ldo, cudaStream_t stream) {
+// out bf16 [T, ff] = silu(x Wg^T) * (x Wu^T), w bf16 [2 ff, K] with the gate rows first;
+// weights_static as in kestrel_gemm_tc_w
+KESTREL_API int kestrel_gemm_tc_swiglu_w(const void *x, const void *w, void *out, int T, int ff, int K, long long ldx,
+                                         long long ldw, long long ldo, int weights_static, cudaStream_t stream) {
     if (T == 0) return 0;
     KESTREL_REQUIRE(kestrel_gemm_tc_supported(x, w, T, ff, K, ldx, ldw), "gemm_tc_swiglu: sizes T=%d ff=%d K=%d do not fit the TMA rules", T, ff, K);
-    return dispatch_tc<TC_SWIGLU>(x, w, out, T, ff, 2 * ff, K, ldx, ldw, ldo, 1, 0, ff, 0, stream);
+    return dispatch_tc<TC_SWIGLU>(x, w, out, T, ff, 2 * ff, K, ldx, ldw, ldo, 1, 0, ff, weights_static ? 1 : 0, stream);
+}
+
+KESTREL_API int kestrel_gemm_tc_swiglu(const void *x, const void *w, void *out, int T, int ff, int K, long long ldx,
+                                       long long ldw, long long ldo, cudaStream_t stream) {
+    return kestrel_gemm_tc_swiglu_w(x, w, out, T, ff, K, ldx, ldw, ldo, 0, stream);
 }
 
 // Reads (and clears) the error word that a bounded wait sets when it runs out: 0 = none,

@@ -68,6 +68,7 @@ def _declare(lib) -> None:
         "kestrel_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _ll, _vp],
         "kestrel_gemm_tc_w": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _ll, _i, _vp],
         "kestrel_gemm_tc_swiglu": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
+        "kestrel_gemm_tc_swiglu_w": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp],
         "kestrel_gemm_tc_error": [],
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _vp, _f, _vp],
@@ -344,7 +345,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     return out
 
 
-def gemm_tc_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+def gemm_tc_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, weights_static: bool = False) -> None:
     """out = silu(x Wg^T) * (x Wu^T) in one tcgen05 kernel with two accumulators."""
     _need(x, "gemm_tc_swiglu.x", torch.bfloat16, 2)
     _need(w_gate_up, "gemm_tc_swiglu.w", torch.bfloat16, 2)
@@ -353,8 +354,9 @@ def gemm_tc_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) 
     ff = out.shape[1]
     if w_gate_up.shape != (2 * ff, K) or out.shape[0] != T:
         raise KernelError("gemm_tc_swiglu: shapes differ")
-    _check(library().kestrel_gemm_tc_swiglu(x.data_ptr(), w_gate_up.data_ptr(), out.data_ptr(), T, ff, K,
-                                            x.stride(0), w_gate_up.stride(0), out.stride(0), _stream()))
+    _check(library().kestrel_gemm_tc_swiglu_w(x.data_ptr(), w_gate_up.data_ptr(), out.data_ptr(), T, ff, K,
+                                              x.stride(0), w_gate_up.stride(0), out.stride(0),
+                                              1 if weights_static else 0, _stream()))
 
 
 def gemm_tc_set_tuning(overhead_kb: int = -1, ctas_per_sm: int = 0) -> None:
@@ -392,10 +394,12 @@ def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, weights_st
     """silu(x Wg^T) * (x Wu^T) in x's dtype, Wg and Wu being the two halves of w_gate_up's rows.
     ``weights_static`` as in `gemm_tc`."""
     out = torch.empty((x.shape[0], ff), dtype=x.dtype, device=x.device)
-    if x.shape[0] > 256 and gemm_tc_supported(x, w_gate_up):
-        gemm_tc_swiglu(x, w_gate_up, out)          # many tokens: the activation is the product's epilogue
+    if gemm_tc_supported(x, w_gate_up):
+        # the activation is the product's epilogue: the K range is not split, whatever the number of
+        # tokens, and the gate/up product never reaches memory
+        gemm_tc_swiglu(x, w_gate_up, out, weights_static=weights_static)
     else:
-        swiglu(Partials(linear(x, w_gate_up, weights_static=weights_static)), out)  # few tokens: split-K slices, summed by the activation kernel
+        swiglu(Partials(linear(x, w_gate_up, weights_static=weights_static)), out)
     return out
 
 
