@@ -22,6 +22,7 @@ from ..csrc import ops
 from .batch import AttentionPlan, Entry, TileList
 
 MAX_SLICES = 32
+HEAD_GRAPH_CALLS = 3          # layer calls in the first of a step's two graphs
 
 
 class StaticDecodeBatch:
@@ -143,12 +144,21 @@ class DecodeGraphs:
             self.model.forward(batch, self.cache)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
-        graph = torch.cuda.CUDAGraph()
+        # Two graphs: the first few layer calls, then the rest.  Submitting a graph of several
+        # hundred kernels takes the host longer than a layer takes the GPU; the short first graph
+        # is running while the long one is still being submitted.
+        n_calls = len(self.model.order)
+        head_calls = min(HEAD_GRAPH_CALLS, n_calls // 2)
+        first, rest = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
         before = ops.launches
-        with torch.cuda.graph(graph):
-            logits = self.model.forward(batch, self.cache)
+        with torch.cuda.graph(first):
+            x, pending = self.model.forward_embed(batch)
+            x, pending = self.model.forward_calls(x, pending, batch, self.cache, 0, head_calls)
+        with torch.cuda.graph(rest, pool=first.pool()):
+            x, pending = self.model.forward_calls(x, pending, batch, self.cache, head_calls, n_calls)
+            logits = self.model.forward_head(x, pending, batch)
         self.launches_per_replay[size] = ops.launches - before
-        self._graphs[size] = (graph, batch, logits)
+        self._graphs[size] = ((first, rest), batch, logits)
         return self._graphs[size]
 
     def run(self, entries: Sequence[Entry]):
@@ -156,7 +166,8 @@ class DecodeGraphs:
         first len(entries) rows, static batch, kernels replayed)."""
         size = self.bucket(len(entries))
         g = self._graphs.get(size) or self._capture(size)
-        graph, batch, logits = g
+        graphs, batch, logits = g
         batch.fill(entries, self.cache)
-        graph.replay()
+        for graph in graphs:
+            graph.replay()
         return logits[:len(entries)], batch, self.launches_per_replay[size]

@@ -117,8 +117,13 @@ class LLM:
         entries, sampling = [], []
         for s in plan:
             lv = self._live[s.rid]
-            toks = lv.out.prompt_token_ids + lv.out.token_ids
-            piece = toks[s.start:s.start + s.count]
+            prompt, n_prompt = lv.out.prompt_token_ids, len(lv.out.prompt_token_ids)
+            if s.start >= n_prompt:                   # a decode token (or recomputed output): no copy of the prompt
+                piece = lv.out.token_ids[s.start - n_prompt:s.start - n_prompt + s.count]
+            else:
+                piece = prompt[s.start:s.start + s.count]
+                if s.start + s.count > n_prompt:
+                    piece = piece + lv.out.token_ids[:s.start + s.count - n_prompt]
             entries.append(Entry(s.rid, piece, (s.count - 1,) if s.wants_token else ()))
             if s.wants_token:
                 sampling.append(lv)

@@ -87,13 +87,26 @@ class DecoderModel(Part):
     def forward(self, batch, cache) -> Optional[torch.Tensor]:
         """Runs this step's tokens through every layer call; returns float32 logits
         [len(batch.logit_rows), vocab], or None if no logits are wanted."""
+        x, pending = self.forward_embed(batch)
+        x, pending = self.forward_calls(x, pending, batch, cache, 0, len(self.order))
+        return self.forward_head(x, pending, batch)
+
+    # The three stages of `forward`, for callers that run a step in pieces (a captured decode
+    # step is two graphs, so that the second is submitted while the first already runs).
+    def forward_embed(self, batch):
         x = self.embedding.forward(batch.token_ids)
         if self.position is not None:
             self.position.add_to_embedding(x, batch)
-        pending = None
-        for call in self.order:
+        return x, None
+
+    def forward_calls(self, x, pending, batch, cache, lo: int, hi: int):
+        """Layer calls order[lo:hi] on the residual stream ``x`` and the not yet added ``pending``."""
+        for call in self.order[lo:hi]:
             lc = cache.layer(call.cache, call.writes_cache) if call.cache >= 0 else None
             x, pending = self.blocks[call.block].forward(x, pending, batch, lc)
+        return x, pending
+
+    def forward_head(self, x, pending, batch) -> Optional[torch.Tensor]:
         if batch.num_logit_rows == 0:
             return None
         n = self.final_norm.add_forward(x, pending, self.dtype, rows=batch.logit_rows)
