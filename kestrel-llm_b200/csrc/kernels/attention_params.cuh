@@ -19,3 +19,8 @@ struct AttnParams {
     int table_stride, page_size, nq, nkv, hd, window, slices, slice_len;
     float scale_log2;
 };
+
+// attention_mma.cu: merges the key-range slices of the listed tiles (at most 16 rows each) into out
+extern "C" int kestrel_attention_merge(const float *part_o, const float *part_ml, void *out, const int *tile_seq,
+                                       const int *tile_row0, int tiles, const int *cu_seqlens, int slices, int hd,
+                                       int nq, int nkv, cudaStream_t stream);

@@ -407,9 +407,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     }
 }
 
-extern "C" int kestrel_attention_merge(const float *part_o, const float *part_ml, void *out, const int *tile_seq,
-                                       const int *tile_row0, int tiles, const int *cu_seqlens, int slices, int hd,
-                                       int nq, int nkv, cudaStream_t stream);
 
 // Whether the kernel takes this head size and page size.
 KESTREL_API int kestrel_attention_tc_supported(int hd, int page_size) {

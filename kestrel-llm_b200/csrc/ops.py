@@ -75,6 +75,11 @@ def _declare(lib) -> None:
         "kestrel_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
                                  _i, _i, _i, _i, _vp, _f, _vp],
         "kestrel_attention_tc_supported": [_i, _i],
+        "kestrel_attention_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                     _i, _i, _i, _i, _i, _vp, _f, _vp],
+        "kestrel_attention_decode_supported": [_i, _i],
+        "kestrel_attention_decode_slots": [_i],
+        "kestrel_attention_decode_error": [],
         "kestrel_attention_tc_error": [],
         "kestrel_attention_mma_slots": [_i],
         "kestrel_attention_mma_rows_per_tile": [_i],
@@ -475,6 +480,54 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
         launches += 1          # the merge kernel
 
 
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                     tile_seq: torch.Tensor, tile_row0: torch.Tensor, cu_seqlens: torch.Tensor, kv_lens: torch.Tensor,
+                     block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int, window: int, scale: float,
+                     slices: int = 1, slice_len: int = 1 << 30, slice_len_dev: Optional[torch.Tensor] = None) -> None:
+    """Attention of decode tokens (tiles of at most 16 rows) with a TMA loader warp in front of
+    four mma.sync warps, head size 64 or 128; the key range is cut into ``slices`` slices of
+    ``slice_len`` keys (a multiple of 64) that are merged in ascending order, and
+    ``slices * slice_len`` must reach the longest request.  The cache tensors are
+    [pages, kv heads, page size, head size], contiguous (``attention_decode_supported``).  Keys
+    and values of positions before a request's first token of this step must have been written
+    by earlier steps, not by the kernel in front of this one: they are fetched before it ends."""
+    _need(q, "attention_decode.q", torch.bfloat16, 2)
+    _need(out, "attention_decode.out", torch.bfloat16, 2)
+    _need(k_cache, "attention_decode.k_cache", torch.bfloat16)
+    _need(v_cache, "attention_decode.v_cache", torch.bfloat16)
+    _need(block_table, "attention_decode.block_table", torch.int32, 2)
+    _need(tile_seq, "attention_decode.tile_seq", torch.int32, 1)
+    _need(tile_row0, "attention_decode.tile_row0", torch.int32, 1)
+    T, tiles = q.shape[0], tile_seq.shape[0]
+    if q.shape[1] != nq * hd or out.shape != q.shape or tile_row0.shape[0] != tiles:
+        raise KernelError("attention_decode: shapes differ")
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or v_cache.shape != k_cache.shape:
+        raise KernelError(f"attention_decode: cache of shape {tuple(k_cache.shape)}, expected [pages, {nkv}, {page_size}, {hd}]")
+    part_o = part_ml = None
+    if slices > 1:
+        part_o = torch.empty((T * nq, slices, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((T * nq, slices, 2), dtype=torch.float32, device=q.device)
+    slice_len = min(int(slice_len), (1 << 30) // 128 * 128)
+    _check(library().kestrel_attention_decode(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
+        tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, cu_seqlens.data_ptr(), kv_lens.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], block_table.stride(0), int(page_size), int(k_cache.shape[0]), T,
+        nq, nkv, hd, int(window), int(slices), slice_len, _p(slice_len_dev), float(scale), _stream()))
+    if slices > 1:
+        global launches
+        launches += 1          # the merge kernel
+
+
+def attention_decode_supported(hd: int, page_size: int) -> bool:
+    """Whether the decode attention kernel takes this head size and page size."""
+    return bool(library().kestrel_attention_decode_supported(int(hd), int(page_size)))
+
+
+def attention_decode_error() -> int:
+    """Error word of the decode attention kernel's bounded waits (0 = none); synchronises the device."""
+    return library().kestrel_attention_decode_error()
+
+
 def attention_tc_supported(hd: int, page_size: int) -> bool:
     """Whether the tcgen05 attention kernel takes this head size and page size."""
     return bool(library().kestrel_attention_tc_supported(int(hd), int(page_size)))
@@ -502,15 +555,15 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
     rows_large = library().kestrel_attention_mma_rows_per_tile(hd)
     plan = batch.attention_plan(nq // nkv, rows_large)
     no_split = (1 << 30) // 128 * 128
-    # Decode tokens stay on the mma.sync kernel, which runs three CTAs of few rows per SM; the
-    # tcgen05 kernel is built for tiles full of rows, one CTA per SM.  It can run decode tokens
-    # (slices included) and is tested so.
-    use_tc = False
+    # Decode tokens: the kernel with the TMA loader warp where the head size and the page size
+    # fit it, else the KEYS mode of the mma.sync kernel.  (The tcgen05 kernel is built for tiles
+    # full of rows, one CTA per SM; it can run decode tokens, slices included, and is tested so.)
     if plan.small is not None:
         tl = plan.small
+        use_decode = attention_decode_supported(hd, page_size) and nq // nkv <= 16
         slices, slice_len, slice_dev = 1, no_split, None
         if window <= 0:         # a window is short; only full-length key ranges are cut into slices
-            slots = 2 * 148 if use_tc else library().kestrel_attention_mma_slots(hd)
+            slots = library().kestrel_attention_decode_slots(hd) if use_decode else library().kestrel_attention_mma_slots(hd)
             ctas = max(1, tl.count * nkv)
             # the number of slices that minimises waves x (a CTA's fixed cost + its keys), at least
             # 256 keys a slice; a captured step fixes the number for a nominal context and lets the
@@ -525,9 +578,9 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
             slices, slice_len = best[1], best[2]
             if tl.slice_len_table is not None:
                 slice_dev = tl.slice_len_table[slices:slices + 1] if slices > 1 else None
-        if use_tc:
-            attention_tc(q, k_cache, v_cache, out, tl.seq, tl.row0, batch.cu_seqlens, batch.kv_lens, block_table,
-                         page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
+        if use_decode:
+            attention_decode(q, k_cache, v_cache, out, tl.seq, tl.row0, batch.cu_seqlens, batch.kv_lens, block_table,
+                             page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
         else:
             attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, 16, batch.cu_seqlens, batch.kv_lens, block_table,
                           page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)

@@ -60,12 +60,14 @@ class Engine:
         self.cache.release(rid)
 
     # ---- the step -----------------------------------------------------------------------
-    def step(self, entries: Sequence[Entry], reserved: bool = False) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[Entry], reserved: bool = False, checked: bool = False) -> Optional[torch.Tensor]:
         """Runs one batch.  Unknown requests are admitted.  Returns float32 logits
         [number of wanted places, vocab] on the device, in the order of entries and of each
         entry's ``want``; None if nothing was wanted.  If pages run out, `OutOfPages` is raised
         before anything runs; no request's length changes (pages that earlier entries of
-        the same call had reserved stay with those requests for their next step)."""
+        the same call had reserved stay with those requests for their next step).
+        ``reserved``: the caller has reserved the pages already; ``checked``: it has checked that
+        every token id lies inside the vocabulary."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None
@@ -77,6 +79,8 @@ class Engine:
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"request {e.rid}: wanted place {w} outside its {len(e.tokens)} tokens of this step")
+            if checked:             # the caller vouches for the ids (prompts checked on arrival, ids it sampled itself)
+                continue
             ids = np.asarray(e.tokens, dtype=np.int64)
             if ids.min() < 0 or ids.max() >= self.vocab_size:
                 bad = int(ids[(ids < 0) | (ids >= self.vocab_size)][0])

@@ -64,6 +64,7 @@ class StaticDecodeBatch:
         # context for which the captured attention launch picks its number of slices
         self.nominal_kv = max(256, min(cache.max_blocks * cache.page_size, 4096))
         self.bytes_h2d = int(total * 4)
+        self._slice_counts = np.arange(1, MAX_SLICES + 1, dtype=np.int64)
         self.fill([], cache)
 
     @property
@@ -107,8 +108,8 @@ class StaticDecodeBatch:
             for g in range(G):
                 for i in range(n, B):
                     h[o_tab + (g * B + i) * W] = self.null_page
-        for s in range(1, MAX_SLICES + 1):
-            h[o_misc + s] = max(128, -(-(-(-max_kv // s)) // 128) * 128)
+        # slice length for every number of slices: max_kv / s rounded up to a multiple of 128
+        h[o_misc + 1:o_misc + MAX_SLICES + 1] = np.maximum(128, -(-(-(-max_kv // self._slice_counts)) // 128) * 128)
         self.dev.copy_(self._ring[turn], non_blocking=True)
         ev = self._ring_done[turn] or torch.cuda.Event()
         ev.record()

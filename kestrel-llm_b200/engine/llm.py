@@ -129,7 +129,7 @@ class LLM:
                 sampling.append(lv)
             if s.start < len(lv.out.prompt_token_ids):
                 self.stats.prompt_tokens += min(s.start + s.count, len(lv.out.prompt_token_ids)) - s.start
-        logits = self.engine.step(entries, reserved=True)
+        logits = self.engine.step(entries, reserved=True, checked=True)    # prompts were checked on arrival
         self.scheduler.step_done()
         self.stats.steps += 1
         self.stats.h2d_bytes += self.engine.last_batch.bytes_h2d

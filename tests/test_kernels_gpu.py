@@ -102,7 +102,8 @@ def test_gemm_tcgen05_row_does_not_depend_on_the_batch():
     assert torch.equal(one[0], full[41])
 
 
-@pytest.mark.parametrize("T,ff,K", [(5, 200, 96), (300, 200, 96), (257, 640, 512), (1024, 384, 320), (700, 20000, 256)])
+@pytest.mark.parametrize("T,ff,K", [(5, 200, 96), (300, 200, 96), (257, 640, 512), (1024, 384, 320), (700, 20000, 256),
+                                    (1, 64, 64), (8, 1000, 512), (40, 72, 136), (100, 333 * 8, 264), (256, 520, 1024)])
 def test_gemm_tcgen05_swiglu(T, ff, K):
     ops = _ops()
     x, xr = _rand((T, K), torch.bfloat16, 5)
@@ -253,7 +254,7 @@ def test_attention_plain(dtype, nq, nkv, hd, window, page):
                                atol=tol * np.abs(ref).max())
 
 
-def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slices, slice_len, seed=0, tc=False):
+def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slices, slice_len, seed=0, tc=False, decode=False):
     """Several requests in one launch of the tensor-core kernel: request i holds lens_ctx[i]
     earlier tokens in its pages and lens_new[i] new ones whose queries run now."""
     ops = _ops()
@@ -266,10 +267,10 @@ def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slic
     total = [c + n for c, n in zip(lens_ctx, lens_new)]
     num_pages = sum((t + page - 1) // page for t in total) + 3
     perm = rng.permutation(num_pages)
-    # slots no request owns: large values for the mma.sync kernel, NaN for the tcgen05 kernel,
-    # which fetches whole pages and has to keep what lies beyond a request's end out of the sums
-    kc = np.full((num_pages, nkv, page, hd), np.nan if tc else 1e4, dtype=np.float32)
-    vc = np.full((num_pages, nkv, page, hd), np.nan if tc else -1e4, dtype=np.float32)
+    # slots no request owns: large values for the mma.sync kernel, NaN for the kernels that fetch
+    # whole pages with TMA and have to keep what lies beyond a request's end out of the sums
+    kc = np.full((num_pages, nkv, page, hd), np.nan if (tc or decode) else 1e4, dtype=np.float32)
+    vc = np.full((num_pages, nkv, page, hd), np.nan if (tc or decode) else -1e4, dtype=np.float32)
     width = max((t + page - 1) // page for t in total)
     table = np.full((nseq, width), -1, dtype=np.int32)
     qs, refs, used = [], [], 0
@@ -302,6 +303,12 @@ def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slic
                          dev(total), dev(table), page, nq, nkv, hd, window, 1.0 / math.sqrt(hd),
                          slices if slices > 1 else 1, slice_len if slices > 1 else 1 << 30)
         assert ops.attention_tc_error() == 0
+    elif decode:
+        ops.attention_decode(torch.from_numpy(qcat).to(torch.bfloat16).to(DEV), torch.from_numpy(kc).to(torch.bfloat16).to(DEV),
+                             torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out, dev(tile_seq), dev(tile_row0), dev(cu),
+                             dev(total), dev(table), page, nq, nkv, hd, window, 1.0 / math.sqrt(hd),
+                             slices if slices > 1 else 1, slice_len if slices > 1 else 1 << 30)
+        assert ops.attention_decode_error() == 0
     else:
         ops.attention_mma(torch.from_numpy(qcat).to(torch.bfloat16).to(DEV), torch.from_numpy(kc).to(torch.bfloat16).to(DEV),
                           torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out, dev(tile_seq), dev(tile_row0), rows_per_tile,
@@ -406,6 +413,87 @@ def test_attention_mma_finds_one_far_key(far, mode):
     want = torch.from_numpy(want).to(torch.bfloat16).float().numpy()
     for t in range(n_new):
         np.testing.assert_allclose(got[t], want, atol=2e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,window,page,slices,slice_len", [
+    (32, 8, 128, 0, 16, 1, 1 << 24), (32, 8, 128, 0, 16, 4, 128), (32, 8, 128, 0, 16, 3, 192), (8, 1, 128, 0, 8, 7, 64),
+    (4, 4, 128, 100, 16, 1, 1 << 24), (16, 1, 64, 0, 16, 6, 64), (6, 2, 64, 0, 64, 2, 256), (5, 5, 64, 40, 32, 1, 1 << 24),
+    (12, 3, 128, 0, 128, 3, 128), (2, 1, 128, 33, 256, 1, 1 << 24)])
+def test_attention_decode_tokens(nq, nkv, hd, window, page, slices, slice_len):
+    """The decode kernel (TMA loader warp): one new token for each of five requests of very
+    different lengths, the key range cut into slices; unused cache slots hold NaN."""
+    _mma_case(nq, nkv, hd, window, page, lens_new=(1, 1, 1, 1, 1), lens_ctx=(0, 15, 64, 200, 330), rows_per_tile=16,
+              slices=slices, slice_len=slice_len, seed=hd + 7, decode=True)
+
+
+def test_attention_decode_takes_short_portions_too():
+    """Tiles of up to 16 rows need not be single tokens: portions of two to four tokens."""
+    _mma_case(8, 2, 128, 0, 16, lens_new=(4, 2, 3), lens_ctx=(100, 0, 130), rows_per_tile=16, slices=1, slice_len=1 << 24,
+              seed=3, decode=True)
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 255, 256, 299])
+@pytest.mark.parametrize("sliced", [False, True])
+def test_attention_decode_finds_one_far_key(far, sliced):
+    """One key among 300 matches the query strongly; the output must be that key's value."""
+    ops = _ops()
+    L, nq, nkv, hd, page = 300, 4, 2, 64, 16
+    rng = np.random.default_rng(far)
+    k = rng.normal(size=(L, nkv, hd)).astype(np.float32) * 0.1
+    v = rng.normal(size=(L, nkv, hd)).astype(np.float32)
+    k[far] = 4.0
+    q = np.full((1, nq, hd), 4.0, dtype=np.float32)
+    kc, vc, pages = _paged(k, v, page, 40, 2)
+    dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+    out = torch.empty((1, nq * hd), dtype=torch.bfloat16, device=DEV)
+    slices, slice_len = (5, 64) if sliced else (1, 1 << 24)
+    ops.attention_decode(torch.from_numpy(q.reshape(1, -1)).to(torch.bfloat16).to(DEV),
+                         torch.from_numpy(kc).to(torch.bfloat16).to(DEV), torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out,
+                         dev([0]), dev([0]), dev([0, 1]), dev([L]), dev(pages[None, :]), page,
+                         nq, nkv, hd, 0, 1.0 / math.sqrt(hd), slices, slice_len)
+    assert ops.attention_decode_error() == 0
+    got = out.float().cpu().numpy().reshape(nq, hd)
+    want = np.stack([v[far, (h * nkv) // nq] for h in range(nq)])
+    want = torch.from_numpy(want).to(torch.bfloat16).float().numpy()
+    np.testing.assert_allclose(got, want, atol=2e-2)
+
+
+def test_attention_decode_window_edge():
+    """The key at distance window - 1 is the last one seen; pages behind the window are gone (-1)."""
+    ops = _ops()
+    L, nq, nkv, hd, page, window = 200, 2, 2, 64, 16, 48
+    for offset, inside in ((window - 1, True), (window, False)):
+        rng = np.random.default_rng(5)
+        k = rng.normal(size=(L, nkv, hd)).astype(np.float32) * 0.1
+        v = rng.normal(size=(L, nkv, hd)).astype(np.float32)
+        q = np.full((1, nq, hd), 4.0, dtype=np.float32)
+        spot = L - 1 - offset
+        k[spot] = 4.0
+        kc, vc, pages = _paged(k, v, page, 40, 3)
+        pages = pages.copy()
+        pages[: (L - window) // page] = -1            # pages behind the window were given back
+        dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+        out = torch.empty((1, nq * hd), dtype=torch.bfloat16, device=DEV)
+        ops.attention_decode(torch.from_numpy(q.reshape(1, -1)).to(torch.bfloat16).to(DEV),
+                             torch.from_numpy(kc).to(torch.bfloat16).to(DEV), torch.from_numpy(vc).to(torch.bfloat16).to(DEV),
+                             out, dev([0]), dev([0]), dev([0, 1]), dev([L]), dev(pages[None, :]), page, nq, nkv, hd,
+                             window, 1.0 / math.sqrt(hd))
+        assert ops.attention_decode_error() == 0
+        got = out.float().cpu().numpy().reshape(nq, hd)
+        close = np.abs(got - v[spot]).max() < 3e-2
+        assert close == inside, f"key at distance {offset} (window {window}): inside={inside}, output follows it={close}"
+
+
+def test_attention_decode_refuses_what_its_boxes_do_not_fit():
+    ops = _ops()
+    assert ops.attention_decode_supported(128, 16) and ops.attention_decode_supported(64, 128)
+    assert not ops.attention_decode_supported(128, 4) and not ops.attention_decode_supported(128, 48)
+    assert not ops.attention_decode_supported(80, 16) and not ops.attention_decode_supported(256, 16)
+    q = torch.zeros((1, 80), dtype=torch.bfloat16, device=DEV)
+    cache = torch.zeros((2, 1, 16, 80), dtype=torch.bfloat16, device=DEV)
+    i = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError, match="head size"):
+        ops.attention_decode(q, cache, cache, torch.empty_like(q), i[:1], i[:1], i, i[:1], i[None, :1], 16, 1, 1, 80, 0, 1.0)
 
 
 def test_attention_mma_window_edge():
