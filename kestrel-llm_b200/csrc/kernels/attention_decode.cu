@@ -27,7 +27,9 @@
 
 #define AD_THREADS 160          // 4 consumer warps + the loader
 #define AD_BN 64                // keys per tile
-#define AD_STAGES 3
+#ifndef AD_STAGES
+#define AD_STAGES 3               // stages of the ring: 3 x 32 KB at head size 128, two CTAs per SM
+#endif
 #define AD_PANEL (AD_BN * 128)  // bytes of a panel: 64 keys x 64 dims
 
 __device__ int g_ad_error = 0;

@@ -565,17 +565,13 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
         if window <= 0:         # a window is short; only full-length key ranges are cut into slices
             slots = library().kestrel_attention_decode_slots(hd) if use_decode else library().kestrel_attention_mma_slots(hd)
             ctas = max(1, tl.count * nkv)
-            # the number of slices that minimises waves x (a CTA's fixed cost + its keys), at least
-            # 256 keys a slice; a captured step fixes the number for a nominal context and lets the
-            # slice length (a multiple of 128) follow the real one through the table on the device
-            best = None
-            for cand in range(1, max(1, min(32, -(-tl.max_kv // 256))) + 1):
-                length = -(-(-(-tl.max_kv // cand)) // 128) * 128
-                real = -(-tl.max_kv // length)
-                cost = -(-ctas * real // slots) * (128 + length)
-                if best is None or cost < best[0]:
-                    best = (cost, real, length)
-            slices, slice_len = best[1], best[2]
+            # As many slices as still let every CTA be resident at once (measured at batch 1 to 64,
+            # context 4,096: a second wave of CTAs costs more than longer slices), at least 256 keys
+            # a slice.  A captured step fixes the number for a nominal context and lets the slice
+            # length (a multiple of 128) follow the real one through the table on the device.
+            cand = max(1, min(slots // ctas, -(-tl.max_kv // 256), 32))
+            slice_len = -(-(-(-tl.max_kv // cand)) // 128) * 128
+            slices = -(-tl.max_kv // slice_len)
             if tl.slice_len_table is not None:
                 slice_dev = tl.slice_len_table[slices:slices + 1] if slices > 1 else None
         if use_decode:
