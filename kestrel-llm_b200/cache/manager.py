@@ -45,6 +45,7 @@ def host_library() -> ctypes.CDLL:
             "kcache_reserve": (i, [vp, ll, i]), "kcache_commit": (i, [vp, ll, i]),
             "kcache_release": (i, [vp, ll]), "kcache_length": (i, [vp, ll]), "kcache_slot": (i, [vp, ll]),
             "kcache_num_blocks": (i, [vp, ll, i]), "kcache_block_table": (i, [vp, ll, i, vp, i]),
+            "kcache_describe_decode": (i, [vp, vp, i, i, i, vp, vp, vp, vp, vp]),
             "kcache_free_pages": (i, [vp, i]), "kcache_num_pages": (i, [vp, i]),
             "kcache_num_groups": (i, [vp]), "kcache_page_size": (i, [vp]),
             "kcache_live_requests": (i, [vp]), "kcache_free_slots": (i, [vp]),
@@ -166,6 +167,19 @@ class PageTable:
     def block_table_into(self, rid: int, group: int, row: np.ndarray) -> int:
         """Fill ``row`` (int32, contiguous) with the request's pages, -1 beyond them."""
         return self._lib.kcache_block_table(self._h, rid, group, row.ctypes.data, row.shape[0])
+
+    def describe_decode(self, rids: np.ndarray, batch: int, width: int, pos: np.ndarray, kv: np.ndarray,
+                        slot: np.ndarray, tables: np.ndarray) -> int:
+        """For a step in which each request of ``rids`` (int64) brings one token: fills positions,
+        lengths after the step, slots (int32 views of at least len(rids) entries) and the block
+        tables of every group (int32 [groups, batch, width]) in one native call; returns the
+        longest length after the step."""
+        bad = ctypes.c_int(0)
+        rc = self._lib.kcache_describe_decode(self._h, rids.ctypes.data, rids.shape[0], batch, width, pos.ctypes.data,
+                                              kv.ctypes.data, slot.ctypes.data, tables.ctypes.data, ctypes.byref(bad))
+        if rc < 0:
+            raise CacheError(self._explain(rc, int(rids[bad.value])))
+        return rc
 
     def block_table(self, rid: int, group: int) -> List[int]:
         n = self.num_blocks(rid, group)

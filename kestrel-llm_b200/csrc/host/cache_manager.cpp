@@ -237,6 +237,34 @@ KAPI int kcache_block_table(void *h, long long id, int group, int *out, int n) {
     return (int)t.size();
 }
 
+// Describes a step in which each of n requests brings one token, for a batch padded to B rows:
+// positions (the length so far), lengths after the step, state slots, and every group's block
+// table rows [G][B][W] (-1 beyond a request's pages).  Rows n..B-1 are left untouched.  Returns
+// the longest length after the step, or a negative error (then *bad is the request's index).
+KAPI int kcache_describe_decode(void *h, const long long *ids, int n, int B, int W, int *pos, int *kv, int *slot,
+                                int *tables, int *bad) {
+    Cache &c = *(Cache *)h;
+    const int G = (int)c.groups.size();
+    int longest = 1;
+    for (int i = 0; i < n; ++i) {
+        auto it = c.live.find(ids[i]);
+        if (it == c.live.end()) { if (bad) *bad = i; return -3; }
+        const auto &r = it->second;
+        pos[i] = r.length;
+        kv[i] = r.length + 1;
+        slot[i] = r.slot;
+        longest = std::max(longest, r.length + 1);
+        for (int g = 0; g < G; ++g) {
+            const std::vector<int> &t = r.table[g];
+            int *row = tables + ((size_t)g * B + i) * W;
+            int m = std::min(W, (int)t.size());
+            if (m > 0) memcpy(row, t.data(), sizeof(int) * m);
+            for (int j = m; j < W; ++j) row[j] = -1;
+        }
+    }
+    return longest;
+}
+
 KAPI int kcache_free_pages(void *h, int group) {
     Cache &c = *(Cache *)h;
     if (group < 0 || group >= (int)c.groups.size()) return -6;

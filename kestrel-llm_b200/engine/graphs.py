@@ -90,16 +90,11 @@ class StaticDecodeBatch:
         h = self._ring_np[turn]
         n = len(entries)
         max_kv = 1
-        for i, e in enumerate(entries):
-            L = cache.length(e.rid)
-            h[o_tok + i] = int(e.tokens[0])
-            h[o_pos + i] = L
-            h[o_kv + i] = L + 1
-            h[o_slot + i] = cache.slot(e.rid)
-            max_kv = max(max_kv, L + 1)
-            for g in range(G):
-                b = o_tab + (g * B + i) * W
-                cache.block_table_into(e.rid, g, h[b:b + W])
+        if n:
+            h[o_tok:o_tok + n] = [e.tokens[0] for e in entries]
+            rids = np.fromiter((e.rid for e in entries), dtype=np.int64, count=n)
+            max_kv = cache.describe_decode(rids, B, W, h[o_pos:o_pos + B], h[o_kv:o_kv + B], h[o_slot:o_slot + B],
+                                           h[o_tab:o_tab + G * B * W])
         if n < B:                       # dummy requests: one token at position 0 on the null page
             h[o_tok + n:o_tok + B] = 0
             h[o_pos + n:o_pos + B] = 0

@@ -2,6 +2,7 @@
 twice, under random orders of requests; windows give pages back; exhaustion changes nothing."""
 import random
 
+import numpy as np
 import pytest
 
 from kestrel_llm_b200.cache import CacheError, OutOfPages, PageTable
@@ -22,6 +23,28 @@ def test_pages_follow_length():
     pt.release(10)
     assert pt.free_pages(0) == 8 and pt.live_requests() == 0
     pt.check()
+
+
+def test_describe_decode_matches_the_single_queries():
+    """The one-call description of a decode step (positions, lengths, slots, block tables of
+    every group) agrees with the per-request queries; an unknown request is named."""
+    pt = PageTable([0, 6], [12, 12], page_size=4, max_requests=4, max_blocks_per_request=5)
+    for rid, n in ((7, 9), (3, 1), (11, 14)):
+        pt.admit(rid); pt.reserve(rid, n); pt.commit(rid, n); pt.reserve(rid, 1)
+    rids = np.array([11, 7, 3], dtype=np.int64)
+    B, W = 4, 5
+    pos, kv, slot = (np.full(B, -7, dtype=np.int32) for _ in range(3))
+    tables = np.full((2, B, W), -7, dtype=np.int32)
+    longest = pt.describe_decode(rids, B, W, pos, kv, slot, tables)
+    assert longest == 15
+    for i, rid in enumerate(rids.tolist()):
+        assert pos[i] == pt.length(rid) and kv[i] == pt.length(rid) + 1 and slot[i] == pt.slot(rid)
+        for g in range(2):
+            want = pt.block_table(rid, g)
+            assert tables[g, i, :len(want)].tolist() == want and (tables[g, i, len(want):] == -1).all()
+    assert pos[3] == -7 and (tables[:, 3] == -7).all()          # rows beyond the requests are left alone
+    with pytest.raises(CacheError):
+        pt.describe_decode(np.array([7, 99], dtype=np.int64), B, W, pos, kv, slot, tables)
 
 
 def test_freed_pages_are_used_again_first():
