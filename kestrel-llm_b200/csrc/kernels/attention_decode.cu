@@ -5,7 +5,8 @@
 // (request, kv head) - at most 16 - and one slice of the key range; its four consumer warps
 // share the rows, each takes 16 keys of every 64-key tile (mma.sync.m16n8k16, float32 softmax
 // statistics and accumulators in registers) and the four running (max, sum, out) states are
-// merged in warp order at the end.  What differs is how the tiles arrive: a fifth warp fetches
+// merged in warp order at the end; the slices of a key range (up to 8) are the CTAs of a cluster
+// and merge their results over distributed shared memory.  What differs further is how the tiles arrive: a fifth warp fetches
 // them with TMA (boxes of one page - or 64 keys of a larger page - by 64 dims, 128-byte swizzle)
 // into a ring of stages and runs ahead of the consumers as far as the ring allows; full/empty
 // mbarriers couple the two sides, so no warp issues copies between its products and the CTA
@@ -31,10 +32,20 @@
 #define AD_STAGES 3               // stages of the ring: 3 x 32 KB at head size 128, two CTAs per SM
 #endif
 #define AD_PANEL (AD_BN * 128)  // bytes of a panel: 64 keys x 64 dims
+#define AD_MAX_CLUSTER 8        // slices merged by one cluster (the portable cluster size)
 
 __device__ int g_ad_error = 0;
 
-template <int HD>
+// a float of CTA `rank` of this cluster, at the shared-memory address `addr` of this CTA's window
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, int rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const AttnParams p, int cache_pages) {
@@ -45,6 +56,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     constexpr int LDQ = HD + 8;                                 // padded Q row, in elements
     constexpr int KS = HD / 16;                                 // k-steps of the QK product
     constexpr int NT_O = HD / 8;                                // 8-dim tiles of the output
+    constexpr uint32_t FIN_OFFSET = 4 * 16 * HD * 4 + 1024;     // behind the four warps' states in the ring's memory
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring = smem_raw + (base - smem_u32(smem_raw));     // [AD_STAGES][K tile | V tile]
@@ -111,9 +123,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 }
             }
         }
-        return;
-    }
-
+    } else {
     // ---------------------------------------------------------------------- consumers
     pdl_wait();                                       // the queries are the predecessor's output
     for (int idx = tid; idx < 16 * (HD / 8); idx += 128) {
@@ -258,6 +268,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     asm volatile("bar.sync 1, 128;" ::: "memory");
     float *mo = reinterpret_cast<float *>(ring);                // [4][16][HD]
     float *mml = mo + 4 * 16 * HD;                              // [4][16][2]
+    float *fin = reinterpret_cast<float *>(ring + FIN_OFFSET);  // [16][HD], then [16][2]: this CTA's merged slice (clusters)
+    float *finml = fin + 16 * HD;
 #pragma unroll
     for (int nt = 0; nt < NT_O; ++nt) {
         int d = nt * 8 + 2 * (lane & 3);
@@ -271,7 +283,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         mml[(warp * 16 + (lane >> 2) + 8) * 2 + 1] = l_r[1];
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (!ok) return;
     // thread -> (row, 8-dim group): 16 rows x HD/8 groups
     for (int idx = tid; idx < 16 * (HD / 8); idx += 128) {
         int r = idx / (HD / 8), d0 = (idx % (HD / 8)) * 8;
@@ -291,7 +302,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         int row = row0 + r;
         size_t qrow = (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G;
-        if (p.slices > 1) {
+        if (CLUSTER) {
+            // this slice's unnormalised out, maximum and sum stay in shared memory for the cluster's merge
+            *reinterpret_cast<float4 *>(fin + r * HD + d0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            *reinterpret_cast<float4 *>(fin + r * HD + d0 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            if (d0 == 0) { finml[2 * r] = M; finml[2 * r + 1] = L; }
+        } else if (!ok) {
+            // a wait gave up: nothing is written
+        } else if (p.slices > 1) {
             float *po = p.part_o + (qrow * p.slices + slice) * HD + d0;
             *reinterpret_cast<float4 *>(po) = make_float4(acc[0], acc[1], acc[2], acc[3]);
             *reinterpret_cast<float4 *>(po + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
@@ -306,22 +324,77 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             *reinterpret_cast<uint4 *>(p.out + qrow * HD + d0) = u;
         }
     }
+    }   // consumers
+
+    if (CLUSTER) {
+        // The slices of one (request, kv head) are the CTAs of one cluster (1, 1, slices): their
+        // results are merged over distributed shared memory, in ascending order of the slices, and
+        // the rows are shared out among the CTAs.  Every thread of every CTA takes part in the
+        // cluster barriers; no CTA leaves while its shared memory may still be read.
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const uint32_t fin_s = base + FIN_OFFSET, finml_s = fin_s + 16 * HD * 4;
+        if (warp < 4) {
+            for (int idx = tid; idx < 16 * (HD / 8); idx += 128) {
+                int r = idx / (HD / 8), d0 = (idx % (HD / 8)) * 8;
+                if (r >= rows_here || r % p.slices != slice) continue;
+                float M = -INFINITY;
+                for (int s = 0; s < p.slices; ++s) M = fmaxf(M, ld_cluster_f32(finml_s + 8 * r, s));
+                float L = 0.f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                for (int s = 0; s < p.slices; ++s) {
+                    float ms = ld_cluster_f32(finml_s + 8 * r, s);
+                    if (ms == -INFINITY) continue;
+                    float f = exp2f(ms - M);
+                    L += ld_cluster_f32(finml_s + 8 * r + 4, s) * f;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += ld_cluster_f32(fin_s + (r * HD + d0 + j) * 4, s) * f;
+                }
+                int row = row0 + r;
+                size_t qrow = (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G;
+                uint4 u;
+                u.x = pack_bf16(acc[0] / L, acc[1] / L);
+                u.y = pack_bf16(acc[2] / L, acc[3] / L);
+                u.z = pack_bf16(acc[4] / L, acc[5] / L);
+                u.w = pack_bf16(acc[6] / L, acc[7] / L);
+                *reinterpret_cast<uint4 *>(p.out + qrow * HD + d0) = u;
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
 }
 
 template <int HD>
 static size_t decode_smem() { return (size_t)AD_STAGES * 2 * (HD / 64) * AD_PANEL + 16 * (HD + 8) * 2 + 16 * AD_STAGES + 1024; }
 
-template <int HD>
+template <int HD, bool CLUSTER>
 static int launch_decode(const CUtensorMap &mk, const CUtensorMap &mv, const AttnParams &p, int tiles, int cache_pages,
                          cudaStream_t stream) {
     size_t smem = decode_smem<HD>();
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return kestrel_fail(-3, "attention_decode: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
         attr_set = true;
     }
-    kestrel_launch(attention_decode_kernel<HD>, dim3(tiles, p.nkv, p.slices), dim3(AD_THREADS), smem, stream, mk, mv, p, cache_pages);
+    if (CLUSTER) {
+        // the slices of a (request, kv head) form a cluster; programmatic dependent launch as everywhere
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(tiles, p.nkv, p.slices);
+        cfg.blockDim = dim3(AD_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = p.slices;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_kestrel_pdl ? 2 : 1;
+        cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, CLUSTER>, mk, mv, p, cache_pages);
+    } else {
+        kestrel_launch(attention_decode_kernel<HD, CLUSTER>, dim3(tiles, p.nkv, p.slices), dim3(AD_THREADS), smem, stream, mk, mv, p, cache_pages);
+    }
     return kestrel_check_launch("attention_decode");
 }
 
@@ -352,7 +425,7 @@ KESTREL_API int kestrel_attention_decode(const void *q, const void *k_cache, con
                     "attention_decode: head size %d with pages of %d keys; the head size must be 64 or 128 and the page size a multiple of 8 that divides 64 or is a multiple of it", hd, page_size);
     KESTREL_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq / nkv <= 16, "attention_decode: %d query heads over %d kv heads", nq, nkv);
     KESTREL_REQUIRE(slices >= 1 && slice_len > 0 && slice_len % AD_BN == 0, "attention_decode: slice length %d must be a positive multiple of %d", slice_len, AD_BN);
-    KESTREL_REQUIRE(slices == 1 || (part_o && part_ml), "attention_decode: %d slices without scratch", slices);
+    KESTREL_REQUIRE(slices <= AD_MAX_CLUSTER || (part_o && part_ml), "attention_decode: %d slices without scratch", slices);
     KESTREL_REQUIRE(nkv <= 65535 && slices <= 65535, "attention_decode: grid too large");
     KESTREL_REQUIRE(cache_pages > 0 && (long long)cache_pages * nkv * page_size < (1ll << 31), "attention_decode: a cache of %d pages is beyond the 32-bit row coordinate", cache_pages);
     CUtensorMap mk, mv;
@@ -369,13 +442,19 @@ KESTREL_API int kestrel_attention_decode(const void *q, const void *k_cache, con
     p.table_stride = table_stride; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window;
     p.slices = slices; p.slice_len = slice_len; p.slice_len_ptr = slice_len_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
-    rc = hd == 64 ? launch_decode<64>(mk, mv, p, tiles, cache_pages, stream) : launch_decode<128>(mk, mv, p, tiles, cache_pages, stream);
-    if (rc || slices == 1) return rc;
+    // up to AD_MAX_CLUSTER slices are merged inside the kernel by a cluster; more go through scratch
+    const bool cluster = slices > 1 && slices <= AD_MAX_CLUSTER;
+    if (cluster) rc = hd == 64 ? launch_decode<64, true>(mk, mv, p, tiles, cache_pages, stream) : launch_decode<128, true>(mk, mv, p, tiles, cache_pages, stream);
+    else rc = hd == 64 ? launch_decode<64, false>(mk, mv, p, tiles, cache_pages, stream) : launch_decode<128, false>(mk, mv, p, tiles, cache_pages, stream);
+    if (rc || slices == 1 || cluster) return rc;
     return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, cu_seqlens, slices, hd, nq, nkv, stream);
 }
 
 // Error word of the kernel's bounded waits: 0 = none, 1 = the loader waited for a free stage,
 // 2 = a consumer waited for a tile.  Synchronises the device and clears the word.
+// Slices that are merged without scratch and without a second kernel.
+KESTREL_API int kestrel_attention_decode_cluster_slices(void) { return AD_MAX_CLUSTER; }
+
 KESTREL_API int kestrel_attention_decode_error(void) {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_ad_error, sizeof(int)) != cudaSuccess) return -1;

@@ -79,6 +79,7 @@ def _declare(lib) -> None:
                                      _i, _i, _i, _i, _i, _vp, _f, _vp],
         "kestrel_attention_decode_supported": [_i, _i],
         "kestrel_attention_decode_slots": [_i],
+        "kestrel_attention_decode_cluster_slices": [],
         "kestrel_attention_decode_error": [],
         "kestrel_attention_tc_error": [],
         "kestrel_attention_mma_slots": [_i],
@@ -486,7 +487,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      slices: int = 1, slice_len: int = 1 << 30, slice_len_dev: Optional[torch.Tensor] = None) -> None:
     """Attention of decode tokens (tiles of at most 16 rows) with a TMA loader warp in front of
     four mma.sync warps, head size 64 or 128; the key range is cut into ``slices`` slices of
-    ``slice_len`` keys (a multiple of 64) that are merged in ascending order, and
+    ``slice_len`` keys (a multiple of 64) that are merged in ascending order (up to 8 inside the
+    kernel, by the CTAs of a cluster; more through scratch and a second kernel), and
     ``slices * slice_len`` must reach the longest request.  The cache tensors are
     [pages, kv heads, page size, head size], contiguous (``attention_decode_supported``).  Keys
     and values of positions before a request's first token of this step must have been written
@@ -504,7 +506,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or v_cache.shape != k_cache.shape:
         raise KernelError(f"attention_decode: cache of shape {tuple(k_cache.shape)}, expected [pages, {nkv}, {page_size}, {hd}]")
     part_o = part_ml = None
-    if slices > 1:
+    scratch = slices > library().kestrel_attention_decode_cluster_slices()    # fewer are merged inside the kernel
+    if scratch:
         part_o = torch.empty((T * nq, slices, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((T * nq, slices, 2), dtype=torch.float32, device=q.device)
     slice_len = min(int(slice_len), (1 << 30) // 128 * 128)
@@ -513,7 +516,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, cu_seqlens.data_ptr(), kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], block_table.stride(0), int(page_size), int(k_cache.shape[0]), T,
         nq, nkv, hd, int(window), int(slices), slice_len, _p(slice_len_dev), float(scale), _stream()))
-    if slices > 1:
+    if scratch:
         global launches
         launches += 1          # the merge kernel
 
@@ -569,7 +572,8 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
             # context 4,096: a second wave of CTAs costs more than longer slices), at least 256 keys
             # a slice.  A captured step fixes the number for a nominal context and lets the slice
             # length (a multiple of 128) follow the real one through the table on the device.
-            cand = max(1, min(slots // ctas, -(-tl.max_kv // 256), 32))
+            most = library().kestrel_attention_decode_cluster_slices() if use_decode else 32     # a cluster merges up to 8
+            cand = max(1, min(slots // ctas, -(-tl.max_kv // 256), most))
             slice_len = -(-(-(-tl.max_kv // cand)) // 128) * 128
             slices = -(-tl.max_kv // slice_len)
             if tl.slice_len_table is not None:

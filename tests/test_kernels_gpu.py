@@ -418,7 +418,8 @@ def test_attention_mma_finds_one_far_key(far, mode):
 @pytest.mark.parametrize("nq,nkv,hd,window,page,slices,slice_len", [
     (32, 8, 128, 0, 16, 1, 1 << 24), (32, 8, 128, 0, 16, 4, 128), (32, 8, 128, 0, 16, 3, 192), (8, 1, 128, 0, 8, 7, 64),
     (4, 4, 128, 100, 16, 1, 1 << 24), (16, 1, 64, 0, 16, 6, 64), (6, 2, 64, 0, 64, 2, 256), (5, 5, 64, 40, 32, 1, 1 << 24),
-    (12, 3, 128, 0, 128, 3, 128), (2, 1, 128, 33, 256, 1, 1 << 24)])
+    (12, 3, 128, 0, 128, 3, 128), (2, 1, 128, 33, 256, 1, 1 << 24), (8, 2, 128, 0, 16, 8, 64), (8, 2, 128, 0, 16, 11, 64),
+    (4, 1, 64, 0, 8, 9, 64)])
 def test_attention_decode_tokens(nq, nkv, hd, window, page, slices, slice_len):
     """The decode kernel (TMA loader warp): one new token for each of five requests of very
     different lengths, the key range cut into slices; unused cache slots hold NaN."""
