@@ -1,23 +1,29 @@
 // Causal attention of prompt portions on the 5th-generation tensor cores, head size 128.
 //
-// A CTA owns 128 rows - (token, query head of one kv group) pairs, token-major, as in
-// attention_mma.cu - and walks the keys its rows may see in tiles of 128, anchored at
-// multiples of 128 of the absolute position.  Eleven warps in three roles, coupled by mbarriers:
-//   loaders  (warp 8 for K, warp 10 for V)  look the tile's pages up in the block table and
+// A CTA owns up to 256 rows - (token, query head of one kv group) pairs, token-major, as in
+// attention_mma.cu - as two row tiles A and B of 128, and walks the keys its rows may see in
+// tiles of 128, anchored at multiples of 128 of the absolute position.  Both row tiles use the
+// same K and V tiles, so a key tile is fetched once per 256 rows.  Nineteen warps in three roles,
+// coupled by mbarriers:
+//   loaders  (warp 16 for K, warp 18 for V)  look the tile's pages up in the block table and
 //            fetch K(t) or V(t) with TMA (boxes of one page, or of 128 keys of a larger page, by
 //            64 dims; 128-byte swizzle) into two-stage rings, each as far ahead as its ring allows;
-//   issuer   (warp 9, one thread)  S(t+1) = Q K(t+1)^T as soon as K(t+1) has landed and the S
-//            buffer is free, then O(t) = P(t) V(t) when P(t) is written: tcgen05.mma M=128 N=128,
-//            8 steps of K=16; Q, K and P are K-major operands (two panels of 64 elements, rows of
-//            128 bytes), V is an MN-major B operand (its rows are keys).  S and the tile's PV
-//            product are double-buffered in TMEM (4 x 128 columns), so the tensor cores work on
-//            tile t+1 while tile t is softmaxed;
-//   softmax  (warps 0-7)  two threads own a row, 64 keys each: row maximum (the halves exchange
-//            it), exp2 and sum in float32, P as bfloat16 into shared memory; the tile's PV product
-//            is added to the row's float32 output registers after rescaling by 2^(m_old - m_new).
-// Keys outside [first key, last key] of the CTA's rows are masked in S; V rows outside that range
-// are zeroed in shared memory (a page may hold another request's stale values there, and
-// 0 x NaN would not be 0).  Shared memory per CTA is 194 KB: one CTA per SM; CTAs with the most
+//   issuer   (warp 17, one thread)  S_X(t) = Q_X K(t)^T and O_X += P_X(t) V(t) for X = A, B in the
+//            order S_A S_B | PV_A S_A' PV_B S_B' | ..., so that the tensor cores work on one row
+//            tile while the other is softmaxed: tcgen05.mma M=128 N=128, 8 steps of K=16.  Q and K
+//            are K-major operands in shared memory (two panels of 64 elements, rows of 128
+//            bytes), V an MN-major one (its rows are keys); P is read from TMEM;
+//   softmax  (warps 0-7 for A, 8-15 for B)  two threads own a row, 64 keys each: row maximum (the
+//            halves exchange it), exp2 and sum in float32, P written as packed bfloat16 over the
+//            first 64 columns of S in TMEM.  Four softmax warps per scheduler hide each other's
+//            TMEM and MUFU latencies.
+// TMEM (512 columns): S_A, S_B, O_A, O_B.  The output accumulates in TMEM; it is rescaled by
+// 2^(m_old - m_new) only when a row's maximum has grown by more than 8 (in log2 units) since the
+// reference it was accumulated against - P then stays below 2^8, which costs bfloat16 and the
+// float32 sum no precision - and the normalisation at the end uses the same reference.
+// Keys outside [first key, last key] of a row tile are masked in S; V rows outside the CTA's
+// range are zeroed in shared memory (a page may hold another request's stale values there, and
+// 0 x NaN would not be 0).  Shared memory per CTA is 193 KB: one CTA per SM; CTAs with the most
 // keys are launched first.  Every mbarrier wait is bounded; the error word is read by
 // kestrel_attention_tc_error.  Formulas as in attention_plain.cu (reference: st.c:10779-10911,
 // st.c:9762-9859).
@@ -25,7 +31,7 @@
 #include "tcgen05.cuh"
 #include <math.h>
 
-#define AT_THREADS 352
+#define AT_THREADS 608           // 16 softmax warps, two loaders, the issuer
 #define AT_BM 128
 #define AT_BN 128
 #define AT_HD 128
@@ -59,14 +65,34 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float *v) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 16 packed words into 16 consecutive TMEM columns of this thread's lane
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t *r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D (TMEM) = or += A (TMEM, M x 16 bfloat16 packed two to a column) x B (shared memory)
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 enum {
-    B_Q_FULL = 0, B_K_FULL = 1, B_K_EMPTY = 3, B_V_FULL = 5, B_V_EMPTY = 7, B_S_FULL = 9, B_S_EMPTY = 11,
-    B_PV_FULL = 13, B_PV_EMPTY = 15, B_P_FULL = 17, B_COUNT = 18
+    B_Q_FULL = 0, B_K_FULL = 1, B_K_EMPTY = 3, B_V_FULL = 5, B_V_EMPTY = 7, B_S_FULL = 9, B_P_FULL = 11, B_PV_DONE = 13,
+    B_COUNT = 15
 };
+#define AT_RESCALE_STEP 8.0f            // log2 units by which a row's maximum may outgrow its reference
 
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                    const AttnParams p, int cache_pages) {
+                    const AttnParams p, int cache_pages, int rows_per_tile) {
     pdl_launch_dependents();
     // M = 128, N = 128, bf16 x bf16 -> f32; both operands K-major for S, B MN-major for PV
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BN >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
@@ -75,26 +101,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t q_s = base, k_s = base + TILE_BYTES, v_s = base + 3 * TILE_BYTES, p_s = base + 5 * TILE_BYTES;
+    const uint32_t q_s = base, k_s = base + 2 * TILE_BYTES, v_s = base + 4 * TILE_BYTES;       // Q_A Q_B | K ring | V ring
     const uint32_t bars = base + 6 * TILE_BYTES, tmem_slot = bars + 8 * B_COUNT;
     volatile uint32_t *tmem_slot_ptr = (volatile uint32_t *)(aligned + 6 * TILE_BYTES + 8 * B_COUNT);
-    float *xchg = (float *)(aligned + 6 * TILE_BYTES + 8 * B_COUNT + 16);          // [3][2][128]: row maxima of the halves by tile parity, row sums
-    uint8_t *p_ptr = aligned + 5 * TILE_BYTES, *v_ptr = aligned + 3 * TILE_BYTES;
+    uint8_t *v_ptr = aligned + 4 * TILE_BYTES;
+    float *xchg = (float *)(aligned + 6 * TILE_BYTES + 8 * B_COUNT + 16);       // [2 row tiles][768]
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        mbar_init(bar(B_Q_FULL), 8);
+        mbar_init(bar(B_Q_FULL), 16);
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(B_K_FULL + b), 1);  mbar_init(bar(B_K_EMPTY + b), 1);
             mbar_init(bar(B_V_FULL + b), 1);  mbar_init(bar(B_V_EMPTY + b), 1);
-            mbar_init(bar(B_S_FULL + b), 1);  mbar_init(bar(B_S_EMPTY + b), 8);
-            mbar_init(bar(B_PV_FULL + b), 1); mbar_init(bar(B_PV_EMPTY + b), 8);
+            mbar_init(bar(B_S_FULL + b), 1);  mbar_init(bar(B_P_FULL + b), 8);
+            mbar_init(bar(B_PV_DONE + b), 1);
         }
-        mbar_init(bar(B_P_FULL), 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {
+    if (warp == 17) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -111,7 +136,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int tok_begin = p.cu_seqlens[seq], n_tok = p.cu_seqlens[seq + 1] - tok_begin;
     const int kv_len = p.kv_lens[seq];
     const int pos_begin = kv_len - n_tok;
-    const int rows_here = min(AT_BM, n_tok * G - row0);
+    const int rows_here = min(rows_per_tile, n_tok * G - row0);         // up to 256: row tile A, then B
     const int *table = p.block_table + (size_t)seq * p.table_stride;
     const int first_tok = row0 / G, last_tok = (row0 + rows_here - 1) / G;
     // keys this CTA's rows may see, cut to its slice of the key range (slices are multiples of 128)
@@ -119,12 +144,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int k_first = max(p.window > 0 ? max(0, pos_begin + first_tok - p.window + 1) : 0, slice * slice_len);
     const int k_lo = (k_first / AT_BN) * AT_BN;
     const int n_tiles = k_hi > k_lo ? (k_hi - k_lo + AT_BN - 1) / AT_BN : 0;
+    // row tile A ends earlier: it skips the key tiles beyond its last row
+    const int rows_a = min(rows_here, AT_BM);
+    const bool has_b = rows_here > AT_BM;
+    const int k_hi_a = min(pos_begin + (row0 + rows_a - 1) / G + 1, (slice + 1) * slice_len);
+    const int n_tiles_a = has_b ? (k_hi_a > k_lo ? (k_hi_a - k_lo + AT_BN - 1) / AT_BN : 0) : n_tiles;
 
-    if (warp == 8 || warp == 10) {
+    if (warp == 16 || warp == 18) {
         // ------------------------------------------------------------------ loaders
-        // warp 8 fetches the K tiles, warp 10 the V tiles, each as far ahead as its ring allows;
+        // warp 16 fetches the K tiles, warp 18 the V tiles, each as far ahead as its ring allows;
         // lane l fetches the l-th page of a tile (both panels)
-        const bool is_v = warp == 10;
+        const bool is_v = warp == 18;
         const CUtensorMap *map = is_v ? &map_v : &map_k;
         const int full0 = is_v ? B_V_FULL : B_K_FULL, empty0 = is_v ? B_V_EMPTY : B_K_EMPTY;
         const uint32_t ring = is_v ? v_s : k_s;
@@ -150,79 +180,82 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 tma_load_2d(dst + AT_PANEL, map, bar(full0 + b), 64, row);
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == 17) {
         // ------------------------------------------------------------------ issuer
         if (lane == 0 && n_tiles > 0) {
             bool ok = mbar_wait(bar(B_Q_FULL), 0);
             if (!ok) atomicExch(&g_at_error, 5);
-            auto issue_s = [&](int t) {
+            // S_X(t) = Q_X K(t)^T into S_X; the K stage is free once the last S product of the tile is done
+            auto issue_s = [&](int x, int t) {
                 const int b = t & 1;
-                const uint32_t par = (uint32_t)(t >> 1) & 1u;
-                if (!mbar_wait(bar(B_K_FULL + b), par) || !mbar_wait(bar(B_S_EMPTY + b), par ^ 1u)) {
-                    atomicExch(&g_at_error, 1);
-                    return false;
-                }
-                tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < AT_HD / 16; ++ks) {
                     uint32_t off = (ks >> 2) * AT_PANEL + (ks & 3) * 32;
-                    tc_mma(tmem + b * 128, smem_desc(q_s + off), smem_desc(k_s + b * TILE_BYTES + off), IDESC_S, ks > 0 ? 1u : 0u);
+                    tc_mma(tmem + x * 128, smem_desc(q_s + x * TILE_BYTES + off), smem_desc(k_s + b * TILE_BYTES + off), IDESC_S, ks > 0 ? 1u : 0u);
                 }
-                tc_commit(bar(B_S_FULL + b));
-                tc_commit(bar(B_K_EMPTY + b));
-                return true;
+                tc_commit(bar(B_S_FULL + x));
             };
-            if (ok) ok = issue_s(0);
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                if (t + 1 < n_tiles) {
-                    ok = issue_s(t + 1);
-                    if (!ok) break;
-                }
+            // O_X (+)= P_X(t) V(t): P is read from the first 64 columns of S_X
+            auto issue_pv = [&](int x, int t) {
                 const int b = t & 1;
-                const uint32_t par = (uint32_t)(t >> 1) & 1u;
-                if (!mbar_wait(bar(B_P_FULL), (uint32_t)t & 1u) || !mbar_wait(bar(B_V_FULL + b), par) ||
-                    !mbar_wait(bar(B_PV_EMPTY + b), par ^ 1u)) {
-                    atomicExch(&g_at_error, 2);
-                    ok = false;
-                    break;
-                }
+                if (!mbar_wait(bar(B_P_FULL + x), (uint32_t)t & 1u)) { atomicExch(&g_at_error, 2); return false; }
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < AT_BN / 16; ++ks) {
-                    // A = P: keys 16 ks.. in panel ks / 4; B = V: 16 keys down = 2 groups of 8 rows
-                    uint64_t da = smem_desc(p_s + (ks >> 2) * AT_PANEL + (ks & 3) * 32);
+                    // A = P: keys 16 ks.. are columns 8 ks..; B = V: 16 keys down = 2 groups of 8 rows
                     uint64_t db = smem_desc_mn_major(v_s + b * TILE_BYTES + ks * 2048, AT_PANEL);
-                    tc_mma(tmem + 256 + b * 128, da, db, IDESC_PV, ks > 0 ? 1u : 0u);
+                    tc_mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8, db, IDESC_PV, (t > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(bar(B_PV_FULL + b));
+                tc_commit(bar(B_PV_DONE + x));
+                return true;
+            };
+            auto wait_k = [&](int t) {
+                if (mbar_wait(bar(B_K_FULL + (t & 1)), (uint32_t)(t >> 1) & 1u)) { tc_fence_after(); return true; }
+                atomicExch(&g_at_error, 1);
+                return false;
+            };
+            if (ok) ok = wait_k(0);
+            if (ok) {
+                if (n_tiles_a > 0) issue_s(0, 0);
+                if (has_b) issue_s(1, 0);
+                tc_commit(bar(B_K_EMPTY + 0));
+            }
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                const int b = t & 1;
+                const bool next = t + 1 < n_tiles;
+                if (!mbar_wait(bar(B_V_FULL + b), (uint32_t)(t >> 1) & 1u)) { atomicExch(&g_at_error, 6); ok = false; break; }
+                if (next && !(ok = wait_k(t + 1))) break;
+                // PV_A(t), S_A(t+1), PV_B(t), S_B(t+1): the products of one row tile fill the time the other's softmax takes
+                if (t < n_tiles_a && !(ok = issue_pv(0, t))) break;
+                if (next && t + 1 < n_tiles_a) issue_s(0, t + 1);
+                if (has_b && !(ok = issue_pv(1, t))) break;
+                if (next && has_b) issue_s(1, t + 1);
+                if (next) tc_commit(bar(B_K_EMPTY + ((t + 1) & 1)));
                 tc_commit(bar(B_V_EMPTY + b));
             }
         }
     } else {
         // ------------------------------------------------------------------ softmax
-        // thread (r, h) = (tid % 128, tid / 128) owns row r and half h of it: 64 of the tile's 128
-        // keys in the softmax, 64 of the 128 output dims.  Warps w and w + 4 share TMEM lanes
-        // 32 (w % 4)...
-        const int r = tid & 127, h = tid >> 7;
-        // warps none of whose 32 rows exist (decode: a few rows per request) skip the arithmetic
-        const bool warp_has_rows = 32 * (warp & 3) < rows_here;
-        const bool row_ok = r < rows_here;
-        const int my_pos = row_ok ? pos_begin + (row0 + r) / G : -1;
-        const int my_lo = p.window > 0 ? max(0, my_pos - p.window + 1) : 0;
+        // warps 0-7: row tile A, warps 8-15: row tile B.  Two threads own a row: thread (r, h) of a
+        // tile takes 64 h .. + 63 of the tile's 128 keys in the softmax and the same 64 of the 128
+        // output dims.  Warps w and w + 4 of a tile share TMEM lanes 32 (w % 4)...; the halves
+        // exchange their maxima (and at the end their sums) through shared memory.
+        const int x = warp >> 3, h = (warp >> 2) & 1, r = tid & 127;
         {
-            // Q: thread t moves 16-byte chunk t % 16 of rows (t / 16) * 8 .. + 7
-            const int ld_c = tid & 15, ld_r0 = (tid >> 4) * 8;
+            // Q: thread t moves 16-byte chunk t % 16 of rows (t / 16) * 8 .. + 7 of row tile t / 256
+            const int xt = tid >> 8, lt = tid & 255;
+            const int ld_c = lt & 15, ld_r0 = (lt >> 4) * 8;
             const uint32_t ld_panel = (uint32_t)(ld_c >> 3) * AT_PANEL;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 int rr = ld_r0 + j;
-                bool valid = rr < rows_here;
+                bool valid = xt * AT_BM + rr < rows_here;
                 size_t off = 0;
                 if (valid) {
-                    int row = row0 + rr;
+                    int row = row0 + xt * AT_BM + rr;
                     off = ((size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G) * AT_HD + ld_c * 8;
                 }
-                at_cp_async16(q_s + ld_panel + swizzle128(rr, ld_c & 7), p.q + off, valid);
+                at_cp_async16(q_s + xt * TILE_BYTES + ld_panel + swizzle128(rr, ld_c & 7), p.q + off, valid);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -230,83 +263,79 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_Q_FULL));
         }
-
-        float o[64];
-#pragma unroll
-        for (int i = 0; i < 64; ++i) o[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, alpha_pending = 1.f;
-        bool ok = true;             // after a wait gave up the loop runs on without waiting: the warps' named barriers stay paired
+        const int rows_x = x == 0 ? rows_a : rows_here - AT_BM;          // rows of this row tile (<= 0: none)
+        const int n_tiles_x = x == 0 ? n_tiles_a : (has_b ? n_tiles : 0);
+        const int k_hi_x = x == 0 ? k_hi_a : k_hi;
+        const bool row_ok = r < rows_x;
+        const int my_pos = row_ok ? pos_begin + (row0 + x * AT_BM + r) / G : -1;
+        const int my_lo = p.window > 0 ? max(0, my_pos - p.window + 1) : 0;
+        // warps none of whose 32 rows exist (decode: a few rows per request) skip the arithmetic
+        const bool warp_has_rows = 32 * (warp & 3) < rows_x;
         const uint32_t lane_base = ((uint32_t)(32 * (warp & 3))) << 16;
         const int col0 = 64 * h;
+        const uint32_t s_addr = tmem + lane_base + x * 128 + col0, o_addr = tmem + lane_base + 256 + x * 128 + col0;
+        const uint32_t p_addr = tmem + lane_base + x * 128 + 32 * h;     // P: two keys to a column
+        float *xch = xchg + x * 768;                                     // [2 tile parities + sums][2 halves][128 rows]
+        const int pair_bar = 1 + 4 * x + (warp & 3);                     // the two warps that share these rows
+        float m_ref = -INFINITY, l_run = 0.f;       // the reference the output is accumulated against, and this half's sum
+        bool ok = true;             // after a wait gave up the loop runs on without waiting, so that the warps still meet
 
-        // adds the PV product of tile t to the output registers and frees its TMEM buffer
-        auto take_pv = [&](int t) {
+        for (int t = 0; t < n_tiles_x; ++t) {
             const int b = t & 1;
-            if (ok && !mbar_wait(bar(B_PV_FULL + b), (uint32_t)(t >> 1) & 1u)) { atomicExch(&g_at_error, 6); ok = false; }
-            tc_fence_after();
-            if (warp_has_rows) {
-#pragma unroll
-                for (int c = 0; c < 64; c += 32) {
-                    float pvv[32];
-                    tc_ld32(tmem + lane_base + 256 + b * 128 + col0 + c, pvv);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) o[c + j] = fmaf(o[c + j], alpha_pending, pvv[j]);
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(B_PV_EMPTY + b));
-        };
-
-        for (int t = 0; t < n_tiles; ++t) {
-            const int b = t & 1;
-            const uint32_t par = (uint32_t)(t >> 1) & 1u;
             const int kbase = k_lo + t * AT_BN;
-            if (ok && !mbar_wait(bar(B_S_FULL + b), par)) { atomicExch(&g_at_error, 7); ok = false; }
+            // S_X(t) is done - and with it, in the issuer's order, O_X += P_X(t-1) V(t-1)
+            if (ok && !mbar_wait(bar(B_S_FULL + x), (uint32_t)t & 1u)) { atomicExch(&g_at_error, 7); ok = false; }
             tc_fence_after();
-            const uint32_t s_addr = tmem + lane_base + b * 128 + col0;
-            const bool whole = kbase >= k_first && kbase + AT_BN <= k_hi && kbase + AT_BN - 1 <= my_pos && kbase >= my_lo;
-            float alpha = 1.f, m_use = 0.f;
             if (warp_has_rows) {
-                // Two passes over the half row in chunks of 32 columns (maximum, then exponentials):
-                // reading S twice from TMEM is cheap and keeps the live registers few.
+                const bool whole = kbase >= k_first && kbase + AT_BN <= k_hi_x && kbase + AT_BN - 1 <= my_pos && kbase >= my_lo;
+                const bool warp_whole = __all_sync(0xffffffffu, whole);
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                const bool warp_whole1 = __all_sync(0xffffffffu, whole);
 #pragma unroll
                 for (int c = 0; c < 64; c += 32) {
                     float s[32];
                     tc_ld32(s_addr + c, s);
-                    if (warp_whole1) {
+                    if (warp_whole) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], s[j]);
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             int key = kbase + col0 + c + j;
-                            bool vis = key <= my_pos && key >= my_lo && key < k_hi && key >= k_first;
+                            bool vis = key <= my_pos && key >= my_lo && key < k_hi_x && key >= k_first;
                             m4[j & 3] = fmaxf(m4[j & 3], vis ? s[j] : -INFINITY);
                         }
                     }
                 }
-                float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-                mx *= p.scale_log2;                                  // the scale is positive: max commutes with it
-                float *xm = xchg + b * 256;                          // by tile parity: the other warp may still read the tile before
+                float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;   // the scale is positive
+                float *xm = xch + b * 256;              // by tile parity: the other warp may still read the tile before
                 xm[h * 128 + r] = mx;
-                asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");   // the two warps that share these rows
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
                 mx = fmaxf(mx, xm[(h ^ 1) * 128 + r]);
-                float m_new = fmaxf(m_run, mx);
-                m_use = m_new == -INFINITY ? 0.f : m_new;
-                alpha = at_exp2(m_run - m_use);
-                m_run = m_new;
-            }
-            // the product of the tile before: its P is consumed, so P(t) may be written after it
-            if (t > 0) take_pv(t - 1);
-            alpha_pending = alpha;
-            if (warp_has_rows) {
-                // a warp all of whose rows see the whole tile (every tile but the diagonal ones)
-                // spends no instructions on the mask
-                const bool warp_whole = __all_sync(0xffffffffu, whole);
+                // the reference moves only when the maximum has outgrown it by more than the step;
+                // both halves of a row see the same maximum and decide alike
+                const bool grow = mx > m_ref + AT_RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
+                if (__any_sync(0xffffffffu, grow && m_ref != -INFINITY && t > 0)) {
+                    // the whole warp walks its rows' outputs (tcgen05.ld / st are warp-wide); rows
+                    // whose reference stays are multiplied by one
+                    const float alpha = (grow && m_ref != -INFINITY) ? at_exp2(m_ref - mx) : 1.f;
+                    l_run *= alpha;
+#pragma unroll
+                    for (int c = 0; c < 64; c += 32) {
+                        float o[32];
+                        tc_ld32(o_addr + c, o);
+                        uint32_t w[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(o[j] * alpha);
+                        tc_st16(o_addr + c, w);
+                        tc_st16(o_addr + c + 16, w + 16);
+                    }
+                }
+                if (grow) m_ref = mx;
+                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
                 float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                // P may overwrite S only when BOTH halves have read their scores: half 1's P (columns
+                // 32..63) lies over scores of half 0
+                uint32_t w[32];
 #pragma unroll
                 for (int c = 0; c < 64; c += 32) {
                     float s[32];
@@ -321,111 +350,117 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             int key = kbase + col0 + c + j;
-                            bool vis = key <= my_pos && key >= my_lo && key < k_hi && key >= k_first;
+                            bool vis = key <= my_pos && key >= my_lo && key < k_hi_x && key >= k_first;
                             s[j] = vis ? at_exp2(fmaf(s[j], p.scale_log2, -m_use)) : 0.f;
                             l4[j & 3] += s[j];
                         }
                     }
-                    // P as bfloat16: keys 64 h .. + 63 are panel h of row r
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint4 u;
-                        __nv_bfloat162 b0 = __floats2bfloat162_rn(s[8 * g + 0], s[8 * g + 1]);
-                        __nv_bfloat162 b1 = __floats2bfloat162_rn(s[8 * g + 2], s[8 * g + 3]);
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(s[8 * g + 4], s[8 * g + 5]);
-                        __nv_bfloat162 b3 = __floats2bfloat162_rn(s[8 * g + 6], s[8 * g + 7]);
-                        u.x = *reinterpret_cast<uint32_t *>(&b0);
-                        u.y = *reinterpret_cast<uint32_t *>(&b1);
-                        u.z = *reinterpret_cast<uint32_t *>(&b2);
-                        u.w = *reinterpret_cast<uint32_t *>(&b3);
-                        *reinterpret_cast<uint4 *>(p_ptr + h * AT_PANEL + swizzle128(r, (c >> 3) + g)) = u;
+                    for (int j = 0; j < 16; ++j) {
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(s[2 * j], s[2 * j + 1]);
+                        w[(c >> 1) + j] = *reinterpret_cast<uint32_t *>(&b2);
                     }
                 }
-                const float l_add = (l4[0] + l4[1]) + (l4[2] + l4[3]);
-                l_run = l_run * alpha + l_add;
+                l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");     // both halves hold their scores in registers now
+                tc_st16(p_addr, w);
+                tc_st16(p_addr + 16, w + 16);
+                tc_wait_st();
             }
             if (kbase < k_first || kbase + AT_BN > k_hi) {
-                // V rows of keys outside the range become zero before the product reads them
-                if (ok && !mbar_wait(bar(B_V_FULL + b), par)) { atomicExch(&g_at_error, 8); ok = false; }
+                // V rows of keys outside the CTA's range become zero before this row tile's product
+                // reads them (both row tiles write the same zeros: either may be the only one at a tile)
+                if (ok && !mbar_wait(bar(B_V_FULL + b), (uint32_t)(t >> 1) & 1u)) { atomicExch(&g_at_error, 8); ok = false; }
                 const int lo_rows = max(0, k_first - kbase), hi_row = min(AT_BN, k_hi - kbase);
-                for (int idx = tid; idx < AT_BN * 16; idx += 256) {
+                for (int idx = (tid & 255); idx < AT_BN * 16; idx += 256) {
                     int row = idx >> 4, c = idx & 15;
                     if (row < lo_rows || row >= hi_row)
                         *reinterpret_cast<uint4 *>(v_ptr + b * TILE_BYTES + (c >> 3) * AT_PANEL + row * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // zeroed V rows -> tensor-core reads
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and zeroed V rows) -> tensor-core reads
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar(B_S_EMPTY + b));
-                mbar_arrive(bar(B_P_FULL));
-            }
+            if (lane == 0) mbar_arrive(bar(B_P_FULL + x));
         }
-        if (n_tiles > 0) take_pv(n_tiles - 1);
 
-        // the row's sum is the sum of its halves
-        xchg[512 + h * 128 + r] = l_run;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
-        float l_tot = l_run + xchg[512 + (h ^ 1) * 128 + r];
-        if (row_ok && ok) {
-            int row = row0 + r;
-            size_t qrow = (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G;
-            if (p.slices > 1) {
-                // this slice's unnormalised out, maximum and sum; attention_merge_kernel combines the slices
-                float *po = p.part_o + (qrow * p.slices + slice) * AT_HD + col0;
+        // the last product of this row tile
+        if (n_tiles_x > 0 && ok && !mbar_wait(bar(B_PV_DONE + x), (uint32_t)(n_tiles_x - 1) & 1u)) { atomicExch(&g_at_error, 9); ok = false; }
+        tc_fence_after();
+        if (warp_has_rows) {
+            // the row's sum is the sum of its halves
+            xch[512 + h * 128 + r] = l_run;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            const float l_tot = l_run + xch[512 + (h ^ 1) * 128 + r];
+            const bool write = row_ok && ok;
+            int row = row0 + x * AT_BM + r;
+            size_t qrow = write ? (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G : 0;
+            const float inv = p.slices > 1 ? 1.f : 1.0f / l_tot;
 #pragma unroll
-                for (int c = 0; c < 64; c += 4) *reinterpret_cast<float4 *>(po + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
-                if (h == 0) {
-                    p.part_ml[(qrow * p.slices + slice) * 2] = m_run;
-                    p.part_ml[(qrow * p.slices + slice) * 2 + 1] = l_tot;
-                }
-            } else {
-                float inv = 1.0f / l_tot;
-                __nv_bfloat16 *po = p.out + qrow * AT_HD + col0;
+            for (int c = 0; c < 64; c += 32) {
+                float o[32];
+                if (n_tiles_x > 0) {
+                    tc_ld32(o_addr + c, o);             // warp-wide, whatever rows exist
+                } else {
 #pragma unroll
-                for (int c = 0; c < 64; c += 8) {
-                    uint4 u;
-                    __nv_bfloat162 b0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
-                    __nv_bfloat162 b1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
-                    __nv_bfloat162 b2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
-                    __nv_bfloat162 b3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
-                    u.x = *reinterpret_cast<uint32_t *>(&b0);
-                    u.y = *reinterpret_cast<uint32_t *>(&b1);
-                    u.z = *reinterpret_cast<uint32_t *>(&b2);
-                    u.w = *reinterpret_cast<uint32_t *>(&b3);
-                    *reinterpret_cast<uint4 *>(po + c) = u;
+                    for (int j = 0; j < 32; ++j) o[j] = 0.f;
                 }
+                if (!write) continue;
+                if (p.slices > 1) {
+                    // this slice's unnormalised out; attention_merge_kernel combines the slices
+                    float *po = p.part_o + (qrow * p.slices + slice) * AT_HD + col0 + c;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(po + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+                } else {
+                    __nv_bfloat16 *po = p.out + qrow * AT_HD + col0 + c;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 u;
+                        __nv_bfloat162 b0 = __floats2bfloat162_rn(o[j] * inv, o[j + 1] * inv);
+                        __nv_bfloat162 b1 = __floats2bfloat162_rn(o[j + 2] * inv, o[j + 3] * inv);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(o[j + 4] * inv, o[j + 5] * inv);
+                        __nv_bfloat162 b3 = __floats2bfloat162_rn(o[j + 6] * inv, o[j + 7] * inv);
+                        u.x = *reinterpret_cast<uint32_t *>(&b0);
+                        u.y = *reinterpret_cast<uint32_t *>(&b1);
+                        u.z = *reinterpret_cast<uint32_t *>(&b2);
+                        u.w = *reinterpret_cast<uint32_t *>(&b3);
+                        *reinterpret_cast<uint4 *>(po + j) = u;
+                    }
+                }
+            }
+            if (write && p.slices > 1 && h == 0) {
+                p.part_ml[(qrow * p.slices + slice) * 2] = m_ref;
+                p.part_ml[(qrow * p.slices + slice) * 2 + 1] = l_tot;
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 17) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
 }
-
 
 // Whether the kernel takes this head size and page size.
 KESTREL_API int kestrel_attention_tc_supported(int hd, int page_size) {
     return hd == AT_HD && page_size > 0 && page_size % 8 == 0 && (AT_BN % page_size == 0 || page_size % AT_BN == 0);
 }
 
-// Tiles of up to 128 rows (tile_seq / tile_row0), head size 128; cache_pages is the number of
-// pages the cache tensors hold.  With slices > 1 (tiles of at
+// Tiles of rows_per_tile rows, up to 256 (tile_seq / tile_row0 list them), head size 128;
+// cache_pages is the number of pages the cache tensors hold.  With slices > 1 (tiles of at
 // most 16 rows: decode tokens) every CTA takes a slice of slice_len keys, a multiple of 128 -
 // or the value at slice_len_ptr on the device - and the slices are merged in ascending order;
 // part_o / part_ml are scratch of T * nq * slices * 128 and T * nq * slices * 2 floats.
 KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const void *v_cache, void *out,
                                      float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
-                                     int tiles, const int *cu_seqlens, const int *kv_lens, const int *block_table,
+                                     int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table,
                                      int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd,
                                      int window, int slices, int slice_len, const int *slice_len_ptr, float scale,
                                      cudaStream_t stream) {
     if (T == 0 || tiles == 0) return 0;
     KESTREL_REQUIRE(hd == AT_HD, "attention_tc: head size %d; this kernel is built for %d", hd, AT_HD);
+    KESTREL_REQUIRE(rows_per_tile >= 1 && rows_per_tile <= 2 * AT_BM, "attention_tc: tiles of %d rows; a CTA takes up to %d", rows_per_tile, 2 * AT_BM);
     KESTREL_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tc: %d query heads over %d kv heads", nq, nkv);
     KESTREL_REQUIRE(slices >= 1 && slice_len > 0 && slice_len % AT_BN == 0, "attention_tc: slice length %d must be a positive multiple of %d", slice_len, AT_BN);
     KESTREL_REQUIRE(slices == 1 || (part_o && part_ml), "attention_tc: %d slices without scratch", slices);
@@ -445,21 +480,21 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
     p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = slices; p.slice_len = slice_len;
     p.slice_len_ptr = slice_len_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
-    size_t smem = 12 * AT_PANEL + 8 * B_COUNT + 16 + 3 * 256 * 4 + 1024;
+    size_t smem = 12 * AT_PANEL + 8 * B_COUNT + 16 + 2 * 768 * 4 + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return kestrel_fail(-3, "attention_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
         attr_set = true;
     }
-    kestrel_launch(attention_tc_kernel, dim3(tiles, nkv, slices), dim3(AT_THREADS), smem, stream, map_k, map_v, p, cache_pages);
+    kestrel_launch(attention_tc_kernel, dim3(tiles, nkv, slices), dim3(AT_THREADS), smem, stream, map_k, map_v, p, cache_pages, rows_per_tile);
     rc = kestrel_check_launch("attention_tc");
     if (rc || slices == 1) return rc;
     return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, cu_seqlens, slices, hd, nq, nkv, stream);
 }
 
 // Error word of the kernel's bounded waits: 0 = none, else the number of the wait that gave up
-// (1, 2, 5: issuer; 3, 4: loader; 6, 7, 8: softmax).
+// (1, 2, 5, 6: issuer; 3, 4: loaders; 7, 8, 9: softmax).
 // Synchronises the device and clears the word.
 KESTREL_API int kestrel_attention_tc_error(void) {
     int v = 0, zero = 0;

@@ -18,16 +18,20 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// false if the barrier did not flip within the limit
+// false if the barrier did not flip within the limit.  Each poll may sleep for at most the given
+// hint (in nanoseconds), so the limit is also a limit in time: about a second.
+#ifndef TC_WAIT_HINT_NS
+#define TC_WAIT_HINT_NS 250u
+#endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(bar), "r"(parity)
+            : "r"(bar), "r"(parity), "r"(TC_WAIT_HINT_NS)
             : "memory");
         if (ok) return true;
     }

@@ -72,7 +72,7 @@ def _declare(lib) -> None:
         "kestrel_gemm_tc_error": [],
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _vp, _f, _vp],
-        "kestrel_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
+        "kestrel_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
                                  _i, _i, _i, _i, _vp, _f, _vp],
         "kestrel_attention_tc_supported": [_i, _i],
         "kestrel_attention_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
@@ -447,9 +447,10 @@ def attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
 def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                  tile_seq: torch.Tensor, tile_row0: torch.Tensor, cu_seqlens: torch.Tensor, kv_lens: torch.Tensor,
                  block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int, window: int, scale: float,
-                 slices: int = 1, slice_len: int = 1 << 30, slice_len_dev: Optional[torch.Tensor] = None) -> None:
-    """tcgen05 attention of the listed tiles, head size 128: tiles of up to 128 rows (prompt
-    portions), or tiles of at most 16 rows (decode tokens) with the key range cut into
+                 slices: int = 1, slice_len: int = 1 << 30, slice_len_dev: Optional[torch.Tensor] = None,
+                 rows_per_tile: int = 128) -> None:
+    """tcgen05 attention of the listed tiles, head size 128: tiles of ``rows_per_tile`` rows, up
+    to 256 (prompt portions), or tiles of at most 16 rows (decode tokens) with the key range cut into
     ``slices`` slices of ``slice_len`` keys (a multiple of 128) that are merged in ascending
     order; ``slices * slice_len`` must reach the longest request.  The cache tensors are
     [pages, kv heads, page size, 128], contiguous, with a page size the kernel's page-wise TMA
@@ -473,7 +474,7 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     slice_len = min(int(slice_len), (1 << 30) // 128 * 128)
     _check(library().kestrel_attention_tc(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
-        tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, cu_seqlens.data_ptr(), kv_lens.data_ptr(),
+        tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, int(rows_per_tile), cu_seqlens.data_ptr(), kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], block_table.stride(0), int(page_size), int(k_cache.shape[0]), T, nq, nkv, hd,
         int(window), int(slices), slice_len, _p(slice_len_dev), float(scale), _stream()))
     if slices > 1:
@@ -555,7 +556,8 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
         attention_plain(q, k_cache, v_cache, batch.positions, batch.seq_of_token, block_table, page_size,
                         out, nq, nkv, hd, window, scale)
         return
-    rows_large = library().kestrel_attention_mma_rows_per_tile(hd)
+    use_tc = attention_tc_supported(hd, page_size)
+    rows_large = 256 if use_tc else library().kestrel_attention_mma_rows_per_tile(hd)
     plan = batch.attention_plan(nq // nkv, rows_large)
     no_split = (1 << 30) // 128 * 128
     # Decode tokens: the kernel with the TMA loader warp where the head size and the page size
@@ -586,9 +588,9 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
                           page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
     if plan.large is not None:
         tl = plan.large
-        if rows_large == 128 and attention_tc_supported(hd, page_size):
+        if use_tc:
             attention_tc(q, k_cache, v_cache, out, tl.seq, tl.row0, batch.cu_seqlens, batch.kv_lens, block_table,
-                         page_size, nq, nkv, hd, window, scale)
+                         page_size, nq, nkv, hd, window, scale, rows_per_tile=rows_large)
         else:
             attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, rows_large, batch.cu_seqlens, batch.kv_lens,
                           block_table, page_size, nq, nkv, hd, window, scale, 1, no_split)

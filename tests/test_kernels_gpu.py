@@ -301,7 +301,7 @@ def _mma_case(nq, nkv, hd, window, page, lens_new, lens_ctx, rows_per_tile, slic
         ops.attention_tc(torch.from_numpy(qcat).to(torch.bfloat16).to(DEV), torch.from_numpy(kc).to(torch.bfloat16).to(DEV),
                          torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out, dev(tile_seq), dev(tile_row0), dev(cu),
                          dev(total), dev(table), page, nq, nkv, hd, window, 1.0 / math.sqrt(hd),
-                         slices if slices > 1 else 1, slice_len if slices > 1 else 1 << 30)
+                         slices if slices > 1 else 1, slice_len if slices > 1 else 1 << 30, rows_per_tile=rows_per_tile)
         assert ops.attention_tc_error() == 0
     elif decode:
         ops.attention_decode(torch.from_numpy(qcat).to(torch.bfloat16).to(DEV), torch.from_numpy(kc).to(torch.bfloat16).to(DEV),
@@ -331,11 +331,41 @@ def test_attention_mma_prompt_portions(nq, nkv, hd, window, page):
 
 @pytest.mark.parametrize("nq,nkv,window,page", [(32, 8, 0, 16), (8, 1, 0, 8), (4, 4, 100, 16), (6, 2, 0, 128), (5, 1, 33, 32),
                                                 (4, 2, 0, 256), (2, 2, 150, 64)])
-def test_attention_tcgen05_prompt_portions(nq, nkv, window, page):
+@pytest.mark.parametrize("rows", [256, 128])
+def test_attention_tcgen05_prompt_portions(nq, nkv, window, page, rows):
     """The tcgen05 kernel (head size 128): portions of three requests, one from position 0, one
-    deep into its context, key tiles of 128 with the last one cut."""
-    _mma_case(nq, nkv, 128, window, page, lens_new=(50, 3, 300), lens_ctx=(100, 0, 77), rows_per_tile=128,
+    deep into its context, key tiles of 128 with the last one cut; two row tiles a CTA, or one."""
+    _mma_case(nq, nkv, 128, window, page, lens_new=(50, 3, 300), lens_ctx=(100, 0, 77), rows_per_tile=rows,
               slices=1, slice_len=0, seed=nq, tc=True)
+
+
+def test_attention_tcgen05_rescales_when_the_maximum_grows():
+    """Scores that grow steeply along the keys: the running reference has to move (and the output
+    accumulated so far be rescaled) at almost every key tile."""
+    ops = _ops()
+    L, nq, nkv, hd, page = 700, 4, 1, 128, 16
+    rng = np.random.default_rng(1)
+    k = rng.normal(size=(L, nkv, hd)).astype(np.float32) * 0.05
+    k[:, :, 0] += np.linspace(0.0, 60.0, L)[:, None]            # q[0] = 1: the score rises by 60 / sqrt(128) * log2(e) * ... along the keys
+    v = rng.normal(size=(L, nkv, hd)).astype(np.float32)
+    q = rng.normal(size=(L, nq, hd)).astype(np.float32) * 0.05
+    q[:, :, 0] = 8.0
+    r16 = lambda a: torch.from_numpy(a).to(torch.bfloat16).float().numpy()
+    q, k, v = r16(q), r16(k), r16(v)
+    ref = P.causal_attention(q, k, v, 0)
+    kc, vc, pages = _paged(k, v, page, 50, 4)
+    G = nq // nkv
+    tiles = list(range(0, L * G, 256))
+    dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+    out = torch.empty((L, nq * hd), dtype=torch.bfloat16, device=DEV)
+    ops.attention_tc(torch.from_numpy(q.reshape(L, -1)).to(torch.bfloat16).to(DEV),
+                     torch.from_numpy(kc).to(torch.bfloat16).to(DEV), torch.from_numpy(vc).to(torch.bfloat16).to(DEV), out,
+                     dev([0] * len(tiles)), dev(tiles), dev([0, L]), dev([L]), dev(pages[None, :]), page,
+                     nq, nkv, hd, 0, 1.0 / math.sqrt(hd), rows_per_tile=256)
+    assert ops.attention_tc_error() == 0
+    got = out.float().cpu().numpy().reshape(L, nq, hd)
+    assert np.isfinite(got).all()
+    np.testing.assert_allclose(got, ref, rtol=0, atol=1e-2 * np.abs(ref).max())
 
 
 @pytest.mark.parametrize("nq,nkv,window,page,slices,slice_len", [(32, 8, 0, 16, 1, 1 << 24), (32, 8, 0, 16, 3, 128), (8, 1, 0, 8, 2, 256),
