@@ -129,7 +129,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const uint32_t tmem = *tmem_slot_ptr;
     pdl_wait();
 
-    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, slice = blockIdx.z;   // late tiles see the most keys
+    // blocks are handed out in the order of blockIdx.x: the kv heads of a tile follow each other and
+    // late tiles, which see the most keys, come first - across all kv heads
+    const int kvh = blockIdx.x % p.nkv, tile = (int)(gridDim.x / p.nkv) - 1 - (int)(blockIdx.x / p.nkv), slice = blockIdx.z;
     const int slice_len = p.slice_len_ptr ? *p.slice_len_ptr : p.slice_len;
     const int seq = p.tile_seq[tile], row0 = p.tile_row0[tile];
     const int G = p.nq / p.nkv;
@@ -464,7 +466,7 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
     KESTREL_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tc: %d query heads over %d kv heads", nq, nkv);
     KESTREL_REQUIRE(slices >= 1 && slice_len > 0 && slice_len % AT_BN == 0, "attention_tc: slice length %d must be a positive multiple of %d", slice_len, AT_BN);
     KESTREL_REQUIRE(slices == 1 || (part_o && part_ml), "attention_tc: %d slices without scratch", slices);
-    KESTREL_REQUIRE(nkv <= 65535 && slices <= 65535, "attention_tc: grid too large");
+    KESTREL_REQUIRE((long long)tiles * nkv < (1ll << 31) && slices <= 65535, "attention_tc: grid too large");
     KESTREL_REQUIRE(kestrel_attention_tc_supported(hd, page_size), "attention_tc: pages of %d keys; the page size must be a multiple of 8 that divides 128 or is a multiple of it", page_size);
     KESTREL_REQUIRE(cache_pages > 0 && (long long)cache_pages * nkv * page_size < (1ll << 31), "attention_tc: a cache of %d pages is beyond the 32-bit row coordinate", cache_pages);
     CUtensorMap map_k, map_v;
@@ -487,7 +489,7 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
         if (e != cudaSuccess) return kestrel_fail(-3, "attention_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
         attr_set = true;
     }
-    kestrel_launch(attention_tc_kernel, dim3(tiles, nkv, slices), dim3(AT_THREADS), smem, stream, map_k, map_v, p, cache_pages, rows_per_tile);
+    kestrel_launch(attention_tc_kernel, dim3((unsigned)((long long)tiles * nkv), 1, slices), dim3(AT_THREADS), smem, stream, map_k, map_v, p, cache_pages, rows_per_tile);
     rc = kestrel_check_launch("attention_tc");
     if (rc || slices == 1) return rc;
     return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, cu_seqlens, slices, hd, nq, nkv, stream);
