@@ -251,7 +251,7 @@ def main() -> int:
     clocks.active = True
     t0 = time.perf_counter()
     for _ in range(K):
-        llm.step()                               # ends with the read-back of the sampled ids
+        llm.step()                               # launches a step and reads back the ids of the one before
     torch.cuda.synchronize()
     e2e_secs = time.perf_counter() - t0
     clocks.active = False

@@ -60,14 +60,17 @@ class Engine:
         self.cache.release(rid)
 
     # ---- the step -----------------------------------------------------------------------
-    def step(self, entries: Sequence[Entry], reserved: bool = False, checked: bool = False) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[Entry], reserved: bool = False, checked: bool = False,
+             token_ids_dev: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs one batch.  Unknown requests are admitted.  Returns float32 logits
         [number of wanted places, vocab] on the device, in the order of entries and of each
         entry's ``want``; None if nothing was wanted.  If pages run out, `OutOfPages` is raised
         before anything runs; no request's length changes (pages that earlier entries of
         the same call had reserved stay with those requests for their next step).
         ``reserved``: the caller has reserved the pages already; ``checked``: it has checked that
-        every token id lies inside the vocabulary."""
+        every token id lies inside the vocabulary.  ``token_ids_dev`` (int32 on the device, one id
+        per entry; decode-only steps of a captured model) stands for the entries' token ids when
+        the host does not know them yet: the ids the previous step sampled."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None
@@ -100,9 +103,12 @@ class Engine:
             for rid in admitted:
                 self.cache.release(rid)
             raise
-        if self.graphs is not None and all(len(e.tokens) == 1 for e in entries):
+        decode_only = self.graphs is not None and all(len(e.tokens) == 1 for e in entries)
+        if token_ids_dev is not None and not decode_only:
+            raise ValueError("token ids on the device stand for one token per entry of a captured decode step")
+        if decode_only:
             # decode tokens only: replay the captured step of this batch-size bucket
-            logits, batch, replayed = self.graphs.run(entries)
+            logits, batch, replayed = self.graphs.run(entries, token_ids_dev)
             self.graph_launches += replayed
             if any(len(e.want) == 0 for e in entries):
                 keep = [i for i, e in enumerate(entries) if len(e.want)]

@@ -13,7 +13,7 @@ traced.  A model takes part only if all its parts declare ``graph_safe``.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -157,13 +157,17 @@ class DecodeGraphs:
         self._graphs[size] = ((first, rest), batch, logits)
         return self._graphs[size]
 
-    def run(self, entries: Sequence[Entry]):
+    def run(self, entries: Sequence[Entry], token_ids_dev: Optional[torch.Tensor] = None):
         """Replays the bucket's graph for these one-token entries; returns (logits of the
-        first len(entries) rows, static batch, kernels replayed)."""
+        first len(entries) rows, static batch, kernels replayed).  ``token_ids_dev`` (int32 on the
+        device, one id per entry) replaces the entries' token ids: the ids the previous step
+        sampled, which the host has not read yet."""
         size = self.bucket(len(entries))
         g = self._graphs.get(size) or self._capture(size)
         graphs, batch, logits = g
         batch.fill(entries, self.cache)
+        if token_ids_dev is not None:
+            batch.token_ids[:len(entries)].copy_(token_ids_dev[:len(entries)], non_blocking=True)
         for graph in graphs:
             graph.replay()
         return logits[:len(entries)], batch, self.launches_per_replay[size]

@@ -8,6 +8,12 @@ until a stop token or the token limit (src/serve/vllm_server.c:1130-1595, 1595-1
 src/serve/vllm_batch.c:303-493).  Here the scheduler builds mixed steps, every step is one
 call of `Engine.step`, and tokens are picked on the device; per step the host sends the
 step's description and reads back one token id per request that produced one.
+
+Decode steps run ahead of the host: when every running request is decoding and nothing waits,
+`step` launches the next step BEFORE it has read the ids the last one sampled - those go from the
+sampler's output to the next step's input on the device - and reads them while the new step
+runs.  A stop token is therefore seen one step late: the stopped request has one more token
+computed, which is thrown away, and its pages are given back then.
 """
 from __future__ import annotations
 
@@ -41,6 +47,19 @@ class _Live:
     params: SamplingParams
     seed: int
     stop_ids: frozenset
+    sampled: int = 0            # tokens sampled so far, those the host has not read yet included
+
+
+@dataclass
+class _InFlight:
+    """A step whose sampled ids are still on their way to the host."""
+    lives: List[_Live]
+    ids_dev: torch.Tensor       # int32 [len(lives)] on the device
+    ids_host: torch.Tensor      # pinned; filled when `done` has passed
+    done: torch.cuda.Event
+    decode_only: bool           # every entry of the step was a single decode token
+    counted: bool = False       # the scheduler already counts these tokens
+    discard: set = field(default_factory=set)      # requests that ended before this step's token was read
 
 
 @dataclass
@@ -75,6 +94,10 @@ class LLM:
         self._live: Dict[int, _Live] = {}
         self._next_id = 0
         self.stats = StepStats()
+        self._ahead: Optional[_InFlight] = None
+        self._pinned = [torch.empty(opts.batch_max + 8, dtype=torch.int32).pin_memory() for _ in range(3)]
+        self._pinned_turn = 0
+        self.run_ahead = True           # False: every step's ids are read before the next step is built
 
     # ---- requests -----------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -99,6 +122,8 @@ class LLM:
         lv = self._live.pop(rid, None)
         if lv is None:
             return None
+        if self._ahead is not None:
+            self._ahead.discard.add(rid)
         self.scheduler.finish(rid)
         lv.out.finish_reason = "abort"
         return lv.out
@@ -108,12 +133,18 @@ class LLM:
 
     # ---- one step -----------------------------------------------------------------------
     def step(self) -> List[RequestOutput]:
-        """Schedules and runs one step; returns the requests that finished in it."""
+        """Schedules and runs one step; returns the requests found finished in this call (a
+        decode step's tokens are read during the next call, see the module text)."""
+        prev, self._ahead = self._ahead, None
+        if prev is not None and self._can_run_ahead(prev):
+            return self._step_ahead(prev)
+        finished = self._finalize(prev, None) if prev is not None else []
         plan = self.scheduler.schedule()
         for rid in self.scheduler.preempted():
             self._live[rid].out.preemptions += 1
+            self._live[rid].sampled = len(self._live[rid].out.token_ids)
         if not plan:
-            return []
+            return finished
         entries, sampling = [], []
         for s in plan:
             lv = self._live[s.rid]
@@ -127,31 +158,95 @@ class LLM:
             entries.append(Entry(s.rid, piece, (s.count - 1,) if s.wants_token else ()))
             if s.wants_token:
                 sampling.append(lv)
-            if s.start < len(lv.out.prompt_token_ids):
-                self.stats.prompt_tokens += min(s.start + s.count, len(lv.out.prompt_token_ids)) - s.start
+            if s.start < n_prompt:
+                self.stats.prompt_tokens += min(s.start + s.count, n_prompt) - s.start
         logits = self.engine.step(entries, reserved=True, checked=True)    # prompts were checked on arrival
         self.scheduler.step_done()
         self.stats.steps += 1
         self.stats.h2d_bytes += self.engine.last_batch.bytes_h2d
-        finished: List[RequestOutput] = []
         if sampling:
-            ids_dev = self.sampler.sample(logits, [lv.params for lv in sampling], [lv.seed for lv in sampling],
-                                          [len(lv.out.token_ids) for lv in sampling])
-            ids = ids_dev.cpu().tolist()          # the step's only read-back: one id per request
-            self.stats.d2h_bytes += 4 * len(ids)
-            for lv, tok in zip(sampling, ids):
-                rid = lv.out.request_id
-                lv.out.token_ids.append(int(tok))
-                self.stats.generated_tokens += 1
-                at_limit = self.scheduler.on_token(rid)
-                if int(tok) in lv.stop_ids:
-                    lv.out.finish_reason = "stop"
-                elif at_limit or len(lv.out.token_ids) >= lv.params.max_tokens:
-                    lv.out.finish_reason = "length"
-                if lv.out.finish_reason:
-                    self.scheduler.finish(rid)
-                    finished.append(lv.out)
-                    del self._live[rid]
+            decode_only = all(s.count == 1 and s.wants_token for s in plan)
+            flight = self._sample(logits, sampling, decode_only)
+            if decode_only and self.run_ahead and self.engine.graphs is not None:
+                self._ahead = flight            # read while the next step runs
+            else:
+                finished += self._finalize(flight, None)
+        return finished
+
+    def _sample(self, logits: torch.Tensor, lives: List[_Live], decode_only: bool) -> _InFlight:
+        """Picks one token per request on the device and starts their copy to the host."""
+        ids_dev = self.sampler.sample(logits, [lv.params for lv in lives], [lv.seed for lv in lives],
+                                      [lv.sampled for lv in lives])
+        for lv in lives:
+            lv.sampled += 1
+        host = self._pinned[self._pinned_turn]
+        self._pinned_turn = (self._pinned_turn + 1) % len(self._pinned)
+        host[:len(lives)].copy_(ids_dev, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        self.stats.d2h_bytes += 4 * len(lives)
+        return _InFlight(lives, ids_dev, host, done, decode_only)
+
+    def _finalize(self, flight: _InFlight, newer: Optional[_InFlight]) -> List[RequestOutput]:
+        """Waits for a step's ids, appends them and ends the requests that are over; a request
+        that ends is struck from ``newer``, the step launched after this one."""
+        flight.done.synchronize()
+        ids = flight.ids_host[:len(flight.lives)].tolist()          # the step's only read-back: one id per request
+        finished: List[RequestOutput] = []
+        for lv, tok in zip(flight.lives, ids):
+            rid = lv.out.request_id
+            if rid in flight.discard or self._live.get(rid) is not lv:
+                continue
+            lv.out.token_ids.append(int(tok))
+            self.stats.generated_tokens += 1
+            at_limit = False if flight.counted else self.scheduler.on_token(rid)
+            if int(tok) in lv.stop_ids:
+                lv.out.finish_reason = "stop"
+            elif at_limit or len(lv.out.token_ids) >= lv.params.max_tokens:
+                lv.out.finish_reason = "length"
+            if lv.out.finish_reason:
+                self.scheduler.finish(rid)
+                finished.append(lv.out)
+                del self._live[rid]
+                if newer is not None:
+                    newer.discard.add(rid)
+        return finished
+
+    def _can_run_ahead(self, prev: _InFlight) -> bool:
+        """Whether the step after ``prev`` is known without prev's ids: every running request
+        decoded in prev and goes on for at least one more token, nothing waits, and pages for one
+        more token of each are there (so that the scheduler preempts nobody)."""
+        if not (self.run_ahead and prev.decode_only and self.engine.graphs is not None):
+            return False
+        if self.scheduler.num_waiting or self.scheduler.num_running != len(prev.lives):
+            return False
+        for lv in prev.lives:
+            rid = lv.out.request_id
+            if rid in prev.discard or self._live.get(rid) is not lv:
+                return False
+            if lv.sampled >= lv.params.max_tokens:           # the token in flight is its last
+                return False
+        cache = self.engine.cache
+        return all(cache.free_pages(g) >= len(prev.lives) for g in range(cache.num_groups))
+
+    def _step_ahead(self, prev: _InFlight) -> List[RequestOutput]:
+        """Launches the next decode step on the ids ``prev`` left on the device, then reads them."""
+        for lv in prev.lives:
+            if self.scheduler.on_token(lv.out.request_id):
+                raise RuntimeError("run-ahead: a request reached its token limit unexpectedly")
+        prev.counted = True
+        plan = self.scheduler.schedule()
+        if [s.rid for s in plan] != [lv.out.request_id for lv in prev.lives] or \
+                any(s.count != 1 or not s.wants_token for s in plan) or self.scheduler.preempted():
+            raise RuntimeError("run-ahead: the scheduler built another step than the one foreseen")
+        entries = [Entry(s.rid, (0,), (0,)) for s in plan]          # the ids are on the device
+        logits = self.engine.step(entries, reserved=True, checked=True, token_ids_dev=prev.ids_dev)
+        self.scheduler.step_done()
+        self.stats.steps += 1
+        self.stats.h2d_bytes += self.engine.last_batch.bytes_h2d
+        flight = self._sample(logits, prev.lives, True)
+        finished = self._finalize(prev, flight)
+        self._ahead = flight if self._live else None                 # all ended: the extra tokens are dropped
         return finished
 
     # ---- whole runs ---------------------------------------------------------------------

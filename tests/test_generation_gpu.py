@@ -87,6 +87,52 @@ def test_stop_token_ends_a_request(model_dirs):
     assert cut.finish_reason == "stop" and cut.token_ids == free[:k + 1]
 
 
+def test_decode_steps_that_run_ahead_change_no_token(model_dirs):
+    """bfloat16 with captured decode steps: the next step is launched before the host has read
+    the last one's ids.  Requests that stop at different times (a stop token found one step late,
+    different token limits, one request joining later) give the same ids as with every step read
+    back at once, nothing is left in the cache, and a stopped request's extra token is dropped."""
+    from kestrel_llm_b200 import LLM, SamplingParams
+    prompts = list(R.random_requests(509, (7, 40, 3, 90), seed=11).values())
+
+    def run(run_ahead, params, late=None):
+        llm = LLM(model_dirs["B"]["bfloat16"], dtype="bfloat16", page_size=16, batch_max=4, max_tokens=2048,
+                  prefill_batch=64, max_step_tokens=128)
+        llm.run_ahead = run_ahead
+        rids = [llm.add_request(p, sp) for p, sp in zip(prompts, params)]
+        done, steps = {}, 0
+        while llm.has_unfinished():
+            for o in llm.step():
+                done[o.request_id] = o
+            steps += 1
+            if late is not None and steps == 12:            # a request arrives while the others decode
+                rids.append(llm.add_request(late[0], late[1]))
+        assert llm.engine.cache.live_requests() == 0
+        llm.engine.cache.check()
+        return [done[r] for r in rids], llm
+
+    free = [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True) for n in (40, 25, 33, 40)]
+    base, _ = run(False, free)
+    ahead, llm = run(True, free)
+    assert [o.token_ids for o in ahead] == [o.token_ids for o in base]
+    assert [len(o.token_ids) for o in ahead] == [40, 25, 33, 40]
+    assert llm.stats.generated_tokens == 138
+    # stop tokens taken from the free run, at different depths; temperature sampling for one request
+    stops = [SamplingParams(temperature=0.0, max_tokens=40, stop_token_ids=(base[0].token_ids[17],)),
+             SamplingParams(temperature=0.0, max_tokens=25, ignore_eos=True),
+             SamplingParams(temperature=0.9, top_k=20, seed=5, max_tokens=33, ignore_eos=True),
+             SamplingParams(temperature=0.0, max_tokens=40, stop_token_ids=(base[3].token_ids[5], base[3].token_ids[30]))]
+    late = (prompts[1][:20], SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    b2, _ = run(False, stops, late)
+    a2, llm2 = run(True, stops, late)
+    assert [o.token_ids for o in a2] == [o.token_ids for o in b2]
+    assert [o.finish_reason for o in a2] == [o.finish_reason for o in b2]
+    assert a2[0].finish_reason == "stop" and a2[3].finish_reason == "stop" and a2[1].finish_reason == "length"
+    assert a2[0].token_ids[-1] == base[0].token_ids[17] and len(a2[0].token_ids) <= 18
+    # ids thrown away were still copied: more bytes read back than tokens kept
+    assert llm2.stats.d2h_bytes >= 4 * llm2.stats.generated_tokens
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(model_dirs, dtype, record_property):
     """Four prompt tokens, then 300 tokens one by one: every position against the plain
