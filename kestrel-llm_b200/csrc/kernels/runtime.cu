@@ -1,5 +1,5 @@
 // Error reporting shared by all entry points, and the library's identity.
-#include "common.cuh"
+#include "tcgen05.cuh"
 #include <stdarg.h>
 #include <stdio.h>
 
@@ -33,4 +33,42 @@ KESTREL_API int kestrel_device_arch(void) {
     cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
     cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
     return major * 10 + minor;
+}
+
+// ------------------------------------------------------------------------------------------
+// What the kernels' bounded waits do when nothing ever arrives: one block waits on an mbarrier
+// that no one completes, with the same wait the tensor-core kernels use.  The wait gives up
+// after its limit (about two seconds), the kernel records that and returns; the context stays
+// usable.  Returns 1 if the wait gave up, 0 if it claimed success, negative on an API error;
+// *elapsed_ms is the kernel's duration.
+// ------------------------------------------------------------------------------------------
+__global__ void wait_probe_kernel(int *result) {
+    __shared__ __align__(8) unsigned long long barrier_word;
+    const uint32_t bar = smem_u32(&barrier_word);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *result = mbar_wait(bar, 0) ? 0 : 1;
+    }
+}
+
+KESTREL_API int kestrel_wait_probe(float *elapsed_ms) {
+    int *flag = nullptr;
+    cudaEvent_t a, b;
+    if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) return kestrel_fail(-3, "wait_probe: no memory");
+    cudaMemset(flag, 0xff, sizeof(int));
+    cudaEventCreate(&a);
+    cudaEventCreate(&b);
+    cudaEventRecord(a, 0);
+    wait_probe_kernel<<<1, 32>>>(flag);
+    cudaEventRecord(b, 0);
+    cudaError_t e = cudaDeviceSynchronize();
+    int result = -1;
+    if (e == cudaSuccess) e = cudaMemcpy(&result, flag, sizeof(int), cudaMemcpyDeviceToHost);
+    if (elapsed_ms) cudaEventElapsedTime(elapsed_ms, a, b);
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    cudaFree(flag);
+    if (e != cudaSuccess) return kestrel_fail(-3, "wait_probe: %s", cudaGetErrorString(e));
+    return result;
 }

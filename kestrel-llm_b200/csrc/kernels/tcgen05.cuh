@@ -4,7 +4,7 @@
 #include "common.cuh"
 #include <cuda.h>
 
-#define TC_WAIT_LIMIT (1u << 22)
+#define TC_WAIT_LIMIT (1u << 19)        // polls of a wait; a poll that finds nothing sleeps a few microseconds: about two seconds
 
 // Host: tensor map of a bf16 matrix [rows, cols] with row stride ld elements, boxes of box_rows
 // rows by 64 columns, 128-byte swizzle (cached by its arguments; defined in gemm_tcgen05.cu).
@@ -18,8 +18,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// false if the barrier did not flip within the limit.  Each poll may sleep for at most the given
-// hint (in nanoseconds), so the limit is also a limit in time: about a second.
+// false if the barrier did not flip within the limit.  A poll that finds the phase incomplete
+// sleeps for a time of the hardware's choosing (measured: about 4 us, whatever the hint), so the
+// limit is also a limit in time.
 #ifndef TC_WAIT_HINT_NS
 #define TC_WAIT_HINT_NS 250u
 #endif

@@ -537,6 +537,32 @@ def attention_tc_supported(hd: int, page_size: int) -> bool:
     return bool(library().kestrel_attention_tc_supported(int(hd), int(page_size)))
 
 
+def raise_on_kernel_error() -> None:
+    """Reads the error words of the kernels with bounded waits (matrix product, the two attention
+    kernels) and raises if one of them gave up a wait: its output is not to be trusted.
+    Synchronises the device; callers use it where they synchronise anyway."""
+    lib = library()
+    bad = [(name, code) for name, code in (("gemm_tcgen05", lib.kestrel_gemm_tc_error()),
+                                           ("attention_tc", lib.kestrel_attention_tc_error()),
+                                           ("attention_decode", lib.kestrel_attention_decode_error())) if code]
+    if bad:
+        raise KernelError("a bounded wait ran out in " + ", ".join(f"{n} (wait {c})" for n, c in bad) +
+                          ": the step's results are invalid")
+
+
+def wait_probe():
+    """Runs one block that waits, with the kernels' bounded wait, on a barrier nobody completes.
+    Returns (gave_up, milliseconds): the wait must give up within seconds and leave the
+    device usable."""
+    ms = ctypes.c_float(0.0)
+    fn = library().kestrel_wait_probe
+    fn.argtypes, fn.restype = [ctypes.POINTER(ctypes.c_float)], _i
+    rc = fn(ctypes.byref(ms))
+    if rc < 0:
+        raise KernelError(library().kestrel_last_error().decode("utf-8", "replace"))
+    return rc == 1, float(ms.value)
+
+
 def attention_tc_error() -> int:
     """Error word of the tcgen05 attention kernel's bounded waits (0 = none); synchronises the device."""
     return library().kestrel_attention_tc_error()

@@ -24,6 +24,7 @@ from typing import Dict, List, Optional, Sequence, Union
 import torch
 
 from ..config.engine_options import EngineOptions
+from ..csrc import ops
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from ..weights.loader import load_model
@@ -273,4 +274,5 @@ class LLM:
                     raise RuntimeError("the scheduler found nothing to run although requests are waiting")
         torch.cuda.synchronize(self.model.device)
         self.stats.seconds += time.perf_counter() - t0
+        ops.raise_on_kernel_error()             # a kernel that gave up a bounded wait: no tokens are better than wrong ones
         return [done[r] for r in rids]

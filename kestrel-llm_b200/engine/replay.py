@@ -21,7 +21,9 @@ import sys
 def replay_stdin(model_dir: str, dtype: str, out_dir: str, max_tokens: int, page_size: int = 16,
                  stream=None) -> int:
     import torch
+
     from ..config import EngineOptions
+    from ..csrc import ops
     from ..weights import load_model
     from .batch import Entry
     from .engine import Engine
@@ -52,6 +54,7 @@ def replay_stdin(model_dir: str, dtype: str, out_dir: str, max_tokens: int, page
             logits.detach().to(torch.float32).cpu().numpy().astype("<f4").tofile(os.path.join(out_dir, f"{step}.f32"))
         else:
             torch.cuda.synchronize()
+        ops.raise_on_kernel_error()             # a kernel that gave up a bounded wait: no logits are better than wrong ones
         for name in rec.get("end", []):
             if name in ids:
                 if engine.cache.is_live(ids[name]):

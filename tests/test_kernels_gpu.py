@@ -734,6 +734,21 @@ def test_sample_against_plain_sampler(V):
     assert uniform_for(5, 3) == uniform_for(5, 3) and uniform_for(5, 3) != uniform_for(5, 4) != uniform_for(6, 4)
 
 
+def test_a_wait_that_nothing_ends_gives_up():
+    """The tensor-core kernels' mbarrier waits are bounded: on a barrier that nobody completes the
+    wait returns after its limit (seconds, not minutes), the kernel reports it, and the
+    device goes on working - here the next product is right."""
+    ops = _ops()
+    gave_up, ms = ops.wait_probe()
+    assert gave_up and 1.0 < ms < 10000.0, f"gave up: {gave_up}, after {ms:.0f} ms"
+    print(f"the wait gave up after {ms:.0f} ms")
+    x, xr = _rand((8, 256), torch.bfloat16, 31)
+    w, wr = _rand((128, 256), torch.bfloat16, 32, 0.05)
+    got = ops.gemm_tc(x, w).sum(0).cpu().numpy()
+    ops.raise_on_kernel_error()
+    np.testing.assert_allclose(got, xr.astype(np.float64) @ wr.astype(np.float64).T, rtol=0, atol=1e-3)
+
+
 def test_kernels_refuse_host_tensors():
     ops = _ops()
     with pytest.raises(ops.KernelError, match="CUDA device only"):
