@@ -395,12 +395,19 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, ui
 }
 
 #define TCP_BN 256          // tokens of a pair's tile (128 loaded by each rank)
+#ifndef TCP_EPI_GROUPS
+#define TCP_EPI_GROUPS 4    // epilogue warps per TMEM lane quarter; each takes 256 / TCP_EPI_GROUPS token columns
+#endif
+#define TCP_THREADS (64 + 128 * TCP_EPI_GROUPS)     // loader, MMA issuer, 4 x TCP_EPI_GROUPS epilogue warps
 
 // MODE PARTIAL: float32 [T, N], two accumulators (the epilogue overlaps the next tile).
 // MODE SWIGLU : gate rows n and up rows up_row_offset + n, two accumulators that fill TMEM (no
 //               overlap), bfloat16 silu(gate) * up out; 48 KB a stage for twice the MMAs.
+// The epilogue is spread over 16 warps a CTA (four per TMEM lane quarter, 64 token columns
+// each): where it does not overlap the next tile it is on the critical path, and four warps
+// alone, one per scheduler, run it at the pace of their own dependent instructions.
 template <int MODE>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TCP_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     void *__restrict__ out, int T, int N, int K, long long ldo, int stages, int tiles_n, int tiles_total,
                     int up_row_offset) {
@@ -432,7 +439,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (warp == 0) {
         if (lane < stages) { mbar_init(full_bar(lane), 1); mbar_init(empty_bar(lane), 1); }
         if (lane >= 28 && lane < 30) mbar_init(acc_full(lane - 28), 1);
-        if (lane >= 30) mbar_init(acc_empty(lane - 30), 8);              // four epilogue warps of each rank
+        if (lane >= 30) mbar_init(acc_empty(lane - 30), 8 * TCP_EPI_GROUPS);    // the epilogue warps of both ranks
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
@@ -512,8 +519,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             tc_fence_after();
             uint32_t d = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)b * ACC_COLS;
             int valid = min(TCP_BN, T - t0);
+            const int c_begin = ((warp - 2) >> 2) * (TCP_BN / TCP_EPI_GROUPS);      // each group of four warps its columns
 #pragma unroll 1
-            for (int c = 0; c < TCP_BN; c += 16) {
+            for (int c = c_begin; c < c_begin + TCP_BN / TCP_EPI_GROUPS; c += 16) {
                 if (c >= valid) break;
                 float g[16];
                 tc_ld16(d + c, g);
@@ -721,7 +729,7 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    cfg.blockDim = dim3(TC_THREADS);
+    cfg.blockDim = dim3(TCP_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cfg.attrs = attr;
