@@ -13,10 +13,12 @@ import tiny_configs
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": (5, 11, 17, 40, 70), "B": (1, 33, 70, 129, 47, 90), "C": (3, 50, 97, 130, 64, 81)}
+LENGTHS = {"A": (5, 11, 17, 40, 70), "B": (1, 33, 70, 129, 47, 90), "C": (3, 50, 97, 130, 64, 81),
+           "D": (2, 45, 131, 200, 77), "E": (9, 64, 150, 129)}
 # more requests than fit the pool at once, so that finished requests' pages are used again
 LENGTHS_MIXED = {"A": (5, 11, 17, 40, 70, 64, 33, 90, 25, 70, 48), "B": (1, 33, 70, 129, 47, 90, 16, 65, 120, 31),
-                 "C": (3, 50, 97, 130, 64, 81, 17, 111, 49, 128)}
+                 "C": (3, 50, 97, 130, 64, 81, 17, 111, 49, 128), "D": (2, 45, 131, 200, 77, 33, 160, 90, 64),
+                 "E": (9, 64, 150, 129, 40, 100, 65, 31)}
 DTYPES = ("float32", "bfloat16")
 
 
@@ -38,19 +40,19 @@ def _run(model_dirs, name, dtype, family, record_property, lengths=None, graphs=
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_prompts(model_dirs, name, dtype, record_property):
     _run(model_dirs, name, dtype, R.trace_whole, record_property)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_last_tokens_one_by_one(model_dirs, name, dtype, record_property):
     _run(model_dirs, name, dtype, R.trace_tail_decode, record_property)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("family", ["tail", "mixed"])
 def test_decode_steps_replayed_from_cuda_graphs(model_dirs, name, dtype, family, record_property):
     """The same traces with decode-only steps captured once per batch-size bucket and replayed
@@ -64,13 +66,13 @@ def test_decode_steps_replayed_from_cuda_graphs(model_dirs, name, dtype, family,
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_portions_of_changing_size(model_dirs, name, dtype, record_property):
     _run(model_dirs, name, dtype, R.trace_portions, record_property)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_mixed_with_page_reuse(model_dirs, name, dtype, record_property):
     engine = _run(model_dirs, name, dtype, R.trace_mixed, record_property, lengths=LENGTHS_MIXED[name])
     # the pool was so small that pages were handed out more often than there are pages
