@@ -1,5 +1,5 @@
 """The engine against the plain implementation under every way of cutting the work, in
-float32 and in bfloat16, for three tiny configurations (GPU)."""
+float32 and in bfloat16, for five tiny configurations (GPU)."""
 import json
 import os
 import subprocess
