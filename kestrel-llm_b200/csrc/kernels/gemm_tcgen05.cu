@@ -410,7 +410,7 @@ template <int MODE>
 __global__ void __launch_bounds__(TCP_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     void *__restrict__ out, int T, int N, int K, long long ldo, int stages, int tiles_n, int tiles_total,
-                    int up_row_offset) {
+                    int up_row_offset, int accumulate) {
     pdl_launch_dependents();
     constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
@@ -539,6 +539,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                 } else if (n < N) {
                     float *o = (float *)out;
+                    if (accumulate) {           // out is the residual stream: the product is added to it in place
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj)
+                            if (c + jj < valid) g[jj] += o[(size_t)(t0 + c + jj) * ldo + n];
+                    }
 #pragma unroll
                     for (int jj = 0; jj < 16; ++jj)
                         if (c + jj < valid) o[(size_t)(t0 + c + jj) * ldo + n] = g[jj];
@@ -717,7 +722,7 @@ static int launch_tc_persistent(const CUtensorMap &mw, const CUtensorMap &mx, vo
 
 template <int MODE>
 static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *out, int T, int N, int K, long long ldo,
-                          int up_off, cudaStream_t stream) {
+                          int up_off, int accumulate, cudaStream_t stream) {
     const int STAGE_BYTES = (MODE == TC_SWIGLU ? 2 : 1) * TC_BM * TC_BK * 2 + (TCP_BN / 2) * TC_BK * 2;
     int stages = (200 * 1024) / STAGE_BYTES;
     if (stages > 8) stages = 8;
@@ -753,7 +758,7 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
     if (total > 0x7fffffff) return kestrel_fail(-2, "gemm_tc: too many tiles");
     int pairs = total < max_clusters ? (int)total : max_clusters;
     cfg.gridDim = dim3(2 * pairs);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<MODE>, mw, mx, out, T, N, K, ldo, stages, tiles_n, (int)total, up_off);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<MODE>, mw, mx, out, T, N, K, ldo, stages, tiles_n, (int)total, up_off, accumulate);
     if (e != cudaSuccess) return kestrel_fail(-3, "gemm_tc_pair: %s", cudaGetErrorString(e));
     return kestrel_check_launch("gemm_tc_pair");
 }
@@ -770,7 +775,7 @@ static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, in
     if (persistent && g_pairs) {
         rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, TCP_BN / 2);
         if (rc) return rc;
-        rc = launch_tc_pair<MODE>(mw, mx, out, T, N, K, ldo, up_off, stream);
+        rc = launch_tc_pair<MODE>(mw, mx, out, T, N, K, ldo, up_off, 0, stream);
         if (rc <= 0) return rc;            // 1 = pairs cannot be scheduled: go on with one CTA per tile
     }
     rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, bn);
@@ -808,6 +813,21 @@ KESTREL_API int kestrel_gemm_tc_w(const void *x, const void *w, float *out, int 
 KESTREL_API int kestrel_gemm_tc(const void *x, const void *w, float *out, int T, int N, int K, long long ldx,
                                 long long ldw, long long ldo, int splits, long long slice_stride, cudaStream_t stream) {
     return kestrel_gemm_tc_w(x, w, out, T, N, K, ldx, ldw, ldo, splits, slice_stride, 0, stream);
+}
+
+// residual float32 [T, N] += x w^T, in the product's epilogue (many tokens on CTA pairs only).
+// Returns 0 when done, 1 when this product cannot do it (few tokens, or pairs cannot be
+// scheduled): the caller then takes the product as slices and lets their consumer add them.
+KESTREL_API int kestrel_gemm_tc_add(const void *x, const void *w, float *residual, int T, int N, int K, long long ldx,
+                                    long long ldw, long long ldo, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (T <= 256 || !g_persistent || !g_pairs || !kestrel_gemm_tc_supported(x, w, T, N, K, ldx, ldw)) return 1;
+    CUtensorMap mw, mx;
+    int rc = kestrel_tensor_map_bf16(&mw, w, N, K, ldw, TC_BM);
+    if (rc) return rc;
+    rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, TCP_BN / 2);
+    if (rc) return rc;
+    return launch_tc_pair<TC_PARTIAL>(mw, mx, residual, T, N, K, ldo, 0, 1, stream);
 }
 
 // out bf16 [T, ff] = silu(x Wg^T) * (x Wu^T), w bf16 [2 ff, K] with the gate rows first;

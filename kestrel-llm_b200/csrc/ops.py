@@ -69,6 +69,7 @@ def _declare(lib) -> None:
         "kestrel_gemm_tc_w": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _ll, _i, _vp],
         "kestrel_gemm_tc_swiglu": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
         "kestrel_gemm_tc_swiglu_w": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp],
+        "kestrel_gemm_tc_add": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
         "kestrel_gemm_tc_error": [],
         "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _vp, _f, _vp],
@@ -394,6 +395,25 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
         out = out.unsqueeze(0)
     gemm_plain(x, w, out[0])
     return out
+
+
+def linear_add_into(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> bool:
+    """residual += x w^T inside the product's epilogue, where the product can do that (bfloat16,
+    many tokens, one pass over K); False if it cannot - nothing has run then and the caller takes
+    the product as slices."""
+    if x.dtype != torch.bfloat16 or not gemm_tc_supported(x, w):
+        return False
+    _need(residual, "linear_add_into.residual", torch.float32, 2)
+    T, K = x.shape
+    N = w.shape[0]
+    if residual.shape != (T, N):
+        raise KernelError(f"linear_add_into: residual {tuple(residual.shape)} for T={T}, N={N}")
+    rc = library().kestrel_gemm_tc_add(x.data_ptr(), w.data_ptr(), residual.data_ptr(), T, N, K, x.stride(0), w.stride(0),
+                                       residual.stride(0), _stream())
+    if rc == 1:
+        return False
+    _check(rc)
+    return True
 
 
 def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, weights_static: bool = False) -> torch.Tensor:

@@ -63,7 +63,7 @@ class GroupedQueryAttention(Mixer):
                       WeightSlot(p + "k_norm.weight", self.k_norm, "norm")]
         return slots
 
-    def forward(self, x: torch.Tensor, batch, cache) -> ops.Partials:
+    def forward(self, x: torch.Tensor, batch, cache, residual: Optional[torch.Tensor] = None) -> Optional[ops.Partials]:
         T = x.shape[0]
         qkv = self.qkv.forward(x)
         q = torch.empty((T, self.heads * self.head_dim), dtype=self.dtype, device=x.device)
@@ -76,4 +76,4 @@ class GroupedQueryAttention(Mixer):
         a = torch.empty_like(q)
         ops.attention(q, cache.k, cache.v, batch, table, cache.page_size, a, self.heads, self.kv_heads,
                       self.head_dim, self.window, self.scale)
-        return self.out.forward(a)
+        return self.out.forward(a, residual=residual)

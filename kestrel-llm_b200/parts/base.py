@@ -92,7 +92,10 @@ class Mixer(Part):
 
     ``cache_spec()`` says what it keeps per request.  ``forward(x, batch, cache)`` takes the
     normed activations [T, width] of this step's tokens and the layer's `LayerCache`, reads and
-    updates the cache for exactly these tokens, and returns Partials [S, T, width]."""
+    updates the cache for exactly these tokens, and returns Partials [S, T, width].  A mixer
+    whose ``forward`` has a fourth parameter ``residual`` is given the float32 residual stream
+    [T, width] and may add its result to it itself (the last product's epilogue); it then returns
+    None."""
 
     def cache_spec(self) -> CacheSpec:
         return None
@@ -102,7 +105,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """Token-wise transformation: ``forward(x, batch)`` -> Partials [S, T, width]."""
+    """Token-wise transformation: ``forward(x, batch)`` -> Partials [S, T, width]; with a third
+    parameter ``residual`` it may add its result to the residual stream itself and return None,
+    as a mixer may."""
 
     def forward(self, x: torch.Tensor, batch):
         raise NotImplementedError

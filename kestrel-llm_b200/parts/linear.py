@@ -25,6 +25,10 @@ class Linear(Part):
         self.weight = torch.empty((out_features, in_features), dtype=dtype, device=device)
         self.bias = torch.empty((out_features,), dtype=torch.float32, device=device) if bias else None
 
-    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> ops.Partials:
-        """x [T, in] in the weight's dtype -> Partials [S, T, out]."""
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                residual: Optional[torch.Tensor] = None) -> Optional[ops.Partials]:
+        """x [T, in] in the weight's dtype -> Partials [S, T, out].  With ``residual`` (float32
+        [T, out]) the product may add itself to it in its epilogue; it then returns None."""
+        if residual is not None and self.bias is None and out is None and ops.linear_add_into(x, self.weight, residual):
+            return None
         return ops.Partials(ops.linear(x, self.weight, out, weights_static=True), self.bias)

@@ -3,7 +3,7 @@
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -31,7 +31,6 @@ class GatedMLP(FeedForward):
                 WeightSlot(p + "up_proj.weight", self.gate_up.weight[ff:]),
                 WeightSlot(p + "down_proj.weight", self.down.weight)]
 
-    def forward(self, x: torch.Tensor, batch) -> ops.Partials:
-        T = x.shape[0]
+    def forward(self, x: torch.Tensor, batch, residual: Optional[torch.Tensor] = None) -> Optional[ops.Partials]:
         act = ops.gate_up_swiglu(x, self.gate_up.weight, self.intermediate, weights_static=True)
-        return self.down.forward(act)
+        return self.down.forward(act, residual=residual)

@@ -70,6 +70,24 @@ def test_gemm_tcgen05(T, N, K, splits):
     np.testing.assert_allclose(got, plain.cpu().numpy(), rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max() + 1e-7)
 
 
+@pytest.mark.parametrize("T,N,K", [(300, 384, 512), (2048, 1100, 1096), (700, 4096, 256)])
+def test_gemm_tcgen05_adds_into_the_residual(T, N, K):
+    """The many-token product with the residual add in its epilogue: residual += x w^T gives the
+    bits of the product as a slice added afterwards; a few-token product declines."""
+    ops = _ops()
+    x, xr = _rand((T, K), torch.bfloat16, T + 1)
+    w, wr = _rand((N, K), torch.bfloat16, N + 1, 0.05)
+    res, rr = _rand((T, N), torch.float32, 9)
+    want = res + ops.gemm_tc(x, w, splits=1)[0]
+    assert ops.linear_add_into(x, w, res)
+    assert ops.gemm_tc_error() == 0
+    assert torch.equal(res, want)
+    ref = rr.astype(np.float64) + xr.astype(np.float64) @ wr.astype(np.float64).T
+    np.testing.assert_allclose(res.cpu().numpy(), ref, rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max())
+    few = torch.zeros((8, N), device=DEV)
+    assert not ops.linear_add_into(x[:8].contiguous(), w, few) and float(few.abs().max()) == 0.0
+
+
 def test_gemm_tcgen05_static_weights_wait_for_the_activations():
     """With weights_static the product fetches weight tiles before the kernel in front of it has
     ended; the activations, which that kernel writes, must still be the new ones.  A chain of
