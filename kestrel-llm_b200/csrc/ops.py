@@ -373,6 +373,18 @@ def gemm_tc_set_tuning(overhead_kb: int = -1, ctas_per_sm: int = 0) -> None:
     fn(int(overhead_kb), int(ctas_per_sm))
 
 
+def gemm_tc_set_many_token_path(pairs: bool = True, persistent: bool = True, swiglu_tile: int = 256) -> None:
+    """Which kernel a many-token product (more than 256 tokens) takes: CTA pairs (the default),
+    else one persistent CTA per SM (what runs where pairs cannot be scheduled; ``swiglu_tile``
+    128 or 256 tokens for its SwiGLU form), else one tile per CTA.  For tests of the fall-backs."""
+    lib = library()
+    for name, v in (("kestrel_gemm_tc_set_pairs", 1 if pairs else 0), ("kestrel_gemm_tc_set_persistent", 1 if persistent else 0),
+                    ("kestrel_gemm_tc_set_swiglu_tile", int(swiglu_tile))):
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = None, [_i]
+        fn(v)
+
+
 def gemm_tc_error() -> int:
     """Error word of the tcgen05 kernels' bounded waits (0 = none); synchronises the device."""
     return library().kestrel_gemm_tc_error()

@@ -88,6 +88,30 @@ def test_gemm_tcgen05_adds_into_the_residual(T, N, K):
     assert not ops.linear_add_into(x[:8].contiguous(), w, few) and float(few.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("pairs,persistent,tile", [(False, True, 256), (False, True, 128), (False, False, 256)])
+def test_gemm_tcgen05_fallbacks_for_many_tokens(pairs, persistent, tile):
+    """The kernels a many-token product takes where CTA pairs cannot be scheduled (one persistent
+    CTA per SM) or are switched off altogether (one tile per CTA), plain and with the SwiGLU epilogue."""
+    ops = _ops()
+    T, N, K, ff = 700, 1100, 520, 648
+    x, xr = _rand((T, K), torch.bfloat16, 41)
+    w, wr = _rand((N, K), torch.bfloat16, 42, 0.05)
+    w2, w2r = _rand((2 * ff, K), torch.bfloat16, 43, 0.1)
+    act = torch.empty((T, ff), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc_set_many_token_path(pairs, persistent, tile)
+    try:
+        got = ops.gemm_tc(x, w, splits=1)[0].cpu().numpy()
+        ops.gemm_tc_swiglu(x, w2, act)
+        assert ops.gemm_tc_error() == 0
+    finally:
+        ops.gemm_tc_set_many_token_path()
+    ref = xr.astype(np.float64) @ wr.astype(np.float64).T
+    np.testing.assert_allclose(got, ref, rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max())
+    y = xr.astype(np.float64) @ w2r.astype(np.float64).T
+    ref2 = (y[:, :ff] / (1 + np.exp(-y[:, :ff]))) * y[:, ff:]
+    np.testing.assert_allclose(act.float().cpu().numpy(), ref2, rtol=1e-2, atol=1e-2 * np.abs(ref2).max())
+
+
 def test_gemm_tcgen05_static_weights_wait_for_the_activations():
     """With weights_static the product fetches weight tiles before the kernel in front of it has
     ended; the activations, which that kernel writes, must still be the new ones.  A chain of
