@@ -632,8 +632,15 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
             # context 4,096: a second wave of CTAs costs more than longer slices), at least 256 keys
             # a slice.  A captured step fixes the number for a nominal context and lets the slice
             # length (a multiple of 128) follow the real one through the table on the device.
-            most = library().kestrel_attention_decode_cluster_slices() if use_decode else 32     # a cluster merges up to 8
-            cand = max(1, min(slots // ctas, -(-tl.max_kv // 256), most))
+            cand = max(1, min(slots // ctas, -(-tl.max_kv // 256), 32))
+            if use_decode:
+                # up to 8 slices are merged inside the kernel by a cluster; more go through scratch
+                # and a second kernel, which pays only where 8 slices would still be long
+                # (measured: one request at 32,768 keys 74 us with 8 slices, 48 us with 32; at 8,192
+                # keys 22 us against 31 us)
+                merged = library().kestrel_attention_decode_cluster_slices()
+                if cand > merged and tl.max_kv <= 2048 * merged:
+                    cand = merged
             slice_len = -(-(-(-tl.max_kv // cand)) // 128) * 128
             slices = -(-tl.max_kv // slice_len)
             if tl.slice_len_table is not None:

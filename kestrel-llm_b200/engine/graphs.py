@@ -28,7 +28,7 @@ HEAD_GRAPH_CALLS = 3          # layer calls in the first of a step's two graphs
 class StaticDecodeBatch:
     """The fixed-address twin of `StepBatch` for ``size`` requests of one token each."""
 
-    def __init__(self, size: int, cache, device):
+    def __init__(self, size: int, cache, device, nominal_kv: int):
         B, W, G = size, cache.max_blocks, cache.num_groups
         self.size = size
         self.num_tokens = self.num_seqs = self.num_logit_rows = B
@@ -62,7 +62,7 @@ class StaticDecodeBatch:
         self.max_count = 1
         self.null_page = cache.null_page
         # context for which the captured attention launch picks its number of slices
-        self.nominal_kv = max(256, min(cache.max_blocks * cache.page_size, 4096))
+        self.nominal_kv = nominal_kv
         self.bytes_h2d = int(total * 4)
         self._slice_counts = np.arange(1, MAX_SLICES + 1, dtype=np.int64)
         self.fill([], cache)
@@ -122,8 +122,19 @@ class DecodeGraphs:
             self.sizes.append(s)
             s *= 2
         self.sizes.append(batch_max)
-        self._graphs: Dict[int, tuple] = {}
-        self.launches_per_replay: Dict[int, int] = {}
+        self._graphs: Dict[tuple, tuple] = {}
+        self.launches_per_replay: Dict[tuple, int] = {}
+
+    # A captured step fixes how many slices its attention cuts the key range into; the slice
+    # length follows the real contexts through device memory.  So that short and very long
+    # contexts get a count that suits them, steps are captured per class of the longest context.
+    KV_CLASSES = (1024, 2048, 4096, 8192, 16384)
+
+    def kv_class(self, max_kv: int) -> int:
+        for c in self.KV_CLASSES:
+            if max_kv <= c:
+                return c
+        return max(self.KV_CLASSES[-1] * 2, self.cache.max_blocks * self.cache.page_size)
 
     def bucket(self, n: int) -> int:
         for s in self.sizes:
@@ -131,9 +142,9 @@ class DecodeGraphs:
                 return s
         raise ValueError(f"{n} requests exceed the largest bucket {self.sizes[-1]}")
 
-    def _capture(self, size: int):
+    def _capture(self, size: int, nominal_kv: int):
         dev = self.model.device
-        batch = StaticDecodeBatch(size, self.cache, dev)
+        batch = StaticDecodeBatch(size, self.cache, dev, nominal_kv)
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):               # one uncaptured run: loads modules, sets attributes
@@ -153,9 +164,9 @@ class DecodeGraphs:
         with torch.cuda.graph(rest, pool=first.pool()):
             x, pending = self.model.forward_calls(x, pending, batch, self.cache, head_calls, n_calls)
             logits = self.model.forward_head(x, pending, batch)
-        self.launches_per_replay[size] = ops.launches - before
-        self._graphs[size] = ((first, rest), batch, logits)
-        return self._graphs[size]
+        self.launches_per_replay[(size, nominal_kv)] = ops.launches - before
+        self._graphs[(size, nominal_kv)] = ((first, rest), batch, logits)
+        return self._graphs[(size, nominal_kv)]
 
     def run(self, entries: Sequence[Entry], token_ids_dev: Optional[torch.Tensor] = None):
         """Replays the bucket's graph for these one-token entries; returns (logits of the
@@ -163,11 +174,12 @@ class DecodeGraphs:
         device, one id per entry) replaces the entries' token ids: the ids the previous step
         sampled, which the host has not read yet."""
         size = self.bucket(len(entries))
-        g = self._graphs.get(size) or self._capture(size)
+        nominal = self.kv_class(1 + max(self.cache.length(e.rid) for e in entries))
+        g = self._graphs.get((size, nominal)) or self._capture(size, nominal)
         graphs, batch, logits = g
         batch.fill(entries, self.cache)
         if token_ids_dev is not None:
             batch.token_ids[:len(entries)].copy_(token_ids_dev[:len(entries)], non_blocking=True)
         for graph in graphs:
             graph.replay()
-        return logits[:len(entries)], batch, self.launches_per_replay[size]
+        return logits[:len(entries)], batch, self.launches_per_replay[(size, nominal)]

@@ -76,6 +76,49 @@ def test_temperature_sampling_does_not_depend_on_the_batch(model_dirs):
     assert other.token_ids != together[1].token_ids
 
 
+def test_decoding_far_into_a_long_context(tmp_path):
+    """17,000 tokens of context, head size 128: the captured decode step of that context class
+    cuts the key range into more slices than a cluster merges (scratch and a merge kernel inside
+    the graph), and a second, short request decodes beside it.  The logits agree with the
+    uncaptured engine's (which picks its slices per step) within bfloat16 rounding, and with
+    themselves from one class of context to the next."""
+    import torch
+    from kestrel_llm_b200.config import Qwen3Config
+    from kestrel_llm_b200.weights import write_random_model
+    raw = dict(tiny_configs.D, max_position_embeddings=20000, num_hidden_layers=2)
+    raw.pop("sliding_window"); raw.pop("use_sliding_window"); raw.pop("layer_types")
+    model_dir = str(tmp_path / "long")
+    write_random_model(Qwen3Config.from_dict(raw), 3, model_dir, "bfloat16")
+    rng = np.random.default_rng(4)
+    long_req = rng.integers(0, raw["vocab_size"], size=17003).tolist()
+    short_req = rng.integers(0, raw["vocab_size"], size=40).tolist()
+    steps = []
+    n, chunk = 0, 2048
+    while n < 17000:
+        k = min(chunk, 17000 - n)
+        steps.append({"entries": [{"id": "long", "tokens": long_req[n:n + k], "want": []}], "end": []})
+        n += k
+    steps.append({"entries": [{"id": "short", "tokens": short_req[:37], "want": []}], "end": []})
+    for i in range(3):
+        steps.append({"entries": [{"id": "long", "tokens": [long_req[17000 + i]], "want": [0]},
+                                  {"id": "short", "tokens": [short_req[37 + i]], "want": [0]}], "end": []})
+    steps[-1]["end"] = ["long", "short"]
+    results = []
+    for graphs in (False, True):
+        engine = R.make_engine(model_dir, "bfloat16", 17003 + 64 + 128, graphs=graphs)
+        results.append(R.run_trace(engine, steps))
+        if graphs:
+            assert engine.graph_launches > 0
+            assert any(k[1] > 16384 for k in engine.graphs._graphs), "the long context has a class of its own"
+        torch.cuda.synchronize()
+    for name in ("long", "short"):
+        for pos, row in results[0][name].items():
+            other = results[1][name][pos]
+            assert np.isfinite(row).all() and np.isfinite(other).all()
+            err = float(np.abs(row - other).max()) / float(np.abs(row).max())
+            assert err <= R.TOL["bfloat16"], f"{name} position {pos}: captured and uncaptured steps differ by {err:.3e}"
+
+
 def test_stop_token_ends_a_request(model_dirs):
     from kestrel_llm_b200 import LLM, SamplingParams
     prompt = R.random_requests(256, (9,), seed=5)["r0"]
