@@ -606,10 +606,12 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
     gives positions, seq_of_token, per-request lengths and the tiling of rows.
 
     float32 takes the plain kernel (one block per token and head, order of sums fixed per
-    token).  bfloat16 takes the tensor-core kernel: requests with at most 16 (token, head) rows
-    per kv head - decode tokens - in KEYS mode with the key range cut into slices so that the
-    grid fills the GPU, the others - prompt portions - on the tcgen05 kernel when the head size
-    is 128 (and the page size fits its TMA boxes) and in ROWS mode of the mma.sync kernel otherwise."""
+    token).  bfloat16 takes the tensor-core kernels.  Requests with at most 16 (token, head) rows
+    per kv head - decode tokens - have their key range cut into slices so that the grid fills the
+    GPU, and run on the kernel with the TMA loader warp (head size 64 or 128) or in KEYS mode of
+    the mma.sync kernel.  The others - prompt portions - run on the tcgen05 kernel (head size
+    128) or in ROWS mode of the mma.sync kernel.  The TMA-fed kernels also need a page size their
+    boxes fit."""
     if q.dtype != torch.bfloat16 or hd % 8 or hd > 256:
         attention_plain(q, k_cache, v_cache, batch.positions, batch.seq_of_token, block_table, page_size,
                         out, nq, nkv, hd, window, scale)

@@ -1,12 +1,14 @@
 """Decode steps as CUDA graphs.
 
-A step in which every request brings one token launches some 330 kernels at Qwen3-8B size,
+A step in which every request brings one token launches some 290 kernels at Qwen3-8B size,
 each a few microseconds long; launched one by one from the host they take longer to launch
-than to run.  Such a step is therefore captured once per batch-size bucket (1, 2, 4 ... up to
-``batch_max``) and replayed: the host fills ONE pinned int32 buffer (token ids, positions,
-lengths, slots, slice lengths of the attention kernel, block tables), copies it to the
-buffer's fixed device twin, and replays the graph.  Buckets are padded with dummy requests of
-one token at position 0 whose keys and values go to the cache's null page.
+than to run.  Such a step is therefore captured - once per batch-size bucket (1, 2, 4 ... up to
+``batch_max``) and class of the longest context, as two graphs of which the second is submitted
+while the first runs - and replayed: the host fills ONE pinned int32 buffer (token ids,
+positions, lengths, slots, slice lengths of the attention kernel, block tables) through one
+native call, copies it to the buffer's fixed device twin, and replays the graphs.  Buckets are
+padded with dummy requests of one token at position 0 whose keys and values go to the cache's
+null page.
 
 The captured kernels are the same ones an uncaptured step launches; nothing is compiled or
 traced.  A model takes part only if all its parts declare ``graph_safe``.
