@@ -5,8 +5,10 @@
 // (request, kv head) - at most 16 - and one slice of the key range; its four consumer warps
 // share the rows, each takes 16 keys of every 64-key tile (mma.sync.m16n8k16, float32 softmax
 // statistics and accumulators in registers) and the four running (max, sum, out) states are
-// merged in warp order at the end; the slices of a key range (up to 8) are the CTAs of a cluster
-// and merge their results over distributed shared memory.  What differs further is how the tiles arrive: a fifth warp fetches
+// merged in warp order at the end; up to 4 slices of a key range are the CTAs of a cluster and
+// merge their results over distributed shared memory, more go through scratch and
+// attention_merge_kernel (clusters of 8 were measured to be placed badly among the kernels of a
+// step: twice the time at 4 requests).  What differs further is how the tiles arrive: a fifth warp fetches
 // them with TMA (boxes of one page - or 64 keys of a larger page - by 64 dims, 128-byte swizzle)
 // into a ring of stages and runs ahead of the consumers as far as the ring allows; full/empty
 // mbarriers couple the two sides, so no warp issues copies between its products and the CTA
@@ -32,7 +34,9 @@
 #define AD_STAGES 3               // stages of the ring: 3 x 32 KB at head size 128, two CTAs per SM
 #endif
 #define AD_PANEL (AD_BN * 128)  // bytes of a panel: 64 keys x 64 dims
-#define AD_MAX_CLUSTER 8        // slices merged by one cluster (the portable cluster size)
+#ifndef AD_MAX_CLUSTER
+#define AD_MAX_CLUSTER 4        // slices merged by one cluster
+#endif
 
 __device__ int g_ad_error = 0;
 

@@ -376,34 +376,68 @@ attention_mma_kernel(const AttnParams p) {
 }
 
 // out[row] = sum over slices of part_o * 2^(m - M) / sum of l * 2^(m - M), slices in ascending
-// order, for the rows of the listed tiles (16 rows each at most); one block per (tile, kv head)
-__global__ void attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
-                                       __nv_bfloat16 *__restrict__ out, const int *__restrict__ tile_seq,
-                                       const int *__restrict__ tile_row0, const int *__restrict__ cu_seqlens,
-                                       int slices, int hd, int nq, int nkv) {
+// order, for the rows of the listed tiles (16 rows each at most); one block per (tile, kv head,
+// row of the tile).  The slices' weights are worked out once per row into shared memory; then
+// every thread adds its dims over the slices with AMG_UNROLL loads in flight (a row's slices
+// are few and far apart in memory: a loop of dependent loads would cost a memory latency each).
+#define AMG_THREADS 128
+#define AMG_MAX_SLICES 1024
+#define AMG_UNROLL 8
+__global__ void __launch_bounds__(AMG_THREADS)
+attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
+                       __nv_bfloat16 *__restrict__ out, const int *__restrict__ tile_seq,
+                       const int *__restrict__ tile_row0, const int *__restrict__ cu_seqlens,
+                       int slices, int hd, int nq, int nkv) {
     pdl_launch_dependents();
+    __shared__ float f_s[AMG_MAX_SLICES];
+    __shared__ float red[AMG_THREADS / 32];
+    __shared__ float inv_l;
+    const int tile = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+    const int tid = threadIdx.x;
+    const int seq = tile_seq[tile], row0 = tile_row0[tile];
+    const int G = nq / nkv;
+    const int tok_begin = cu_seqlens[seq];
+    const int n_rows = (cu_seqlens[seq + 1] - tok_begin) * G;
+    if (r >= min(16, n_rows - row0)) return;
+    const int row = row0 + r;
+    const size_t qrow = (size_t)(tok_begin + row / G) * nq + kvh * G + row % G;
+    const float *ml = part_ml + qrow * slices * 2;
     pdl_wait();
-    int tile = blockIdx.x, kvh = blockIdx.y;
-    int seq = tile_seq[tile], row0 = tile_row0[tile];
-    int G = nq / nkv;
-    int tok_begin = cu_seqlens[seq];
-    int n_rows = (cu_seqlens[seq + 1] - tok_begin) * G;
-    int rows_here = min(16, n_rows - row0);
-    for (int idx = threadIdx.x; idx < rows_here * hd; idx += blockDim.x) {
-        int r = idx / hd, d = idx % hd;
-        int row = row0 + r;
-        size_t qrow = (size_t)(tok_begin + row / G) * nq + kvh * G + row % G;
-        const float *ml = part_ml + qrow * slices * 2;
-        float M = -INFINITY;
-        for (int s = 0; s < slices; ++s) M = fmaxf(M, ml[2 * s]);
-        float L = 0.f, acc = 0.f;
-        for (int s = 0; s < slices; ++s) {
-            float ms = ml[2 * s];
-            if (ms == -INFINITY) continue;
-            float f = exp2f(ms - M);
-            L += ml[2 * s + 1] * f;
-            acc += part_o[(qrow * slices + s) * hd + d] * f;
+    float mx = -INFINITY;
+    for (int s = tid; s < slices; s += AMG_THREADS) mx = fmaxf(mx, ml[2 * s]);
+    mx = warp_max(mx);
+    if ((tid & 31) == 0) red[tid >> 5] = mx;
+    __syncthreads();
+    float M = red[0];
+#pragma unroll
+    for (int w = 1; w < AMG_THREADS / 32; ++w) M = fmaxf(M, red[w]);
+    for (int s = tid; s < slices; s += AMG_THREADS) {
+        float ms = ml[2 * s];
+        f_s[s] = ms == -INFINITY ? 0.f : exp2f(ms - M);
+    }
+    __syncthreads();
+    if (tid == 0) {             // the sum of the weights in ascending order, as the rows' own sums
+        float L = 0.f;
+        for (int s = 0; s < slices; ++s)
+            if (f_s[s] != 0.f) L += ml[2 * s + 1] * f_s[s];
+        inv_l = L;
+    }
+    __syncthreads();
+    const float L = inv_l;
+    const float *po = part_o + qrow * slices * hd;
+    for (int d = tid; d < hd; d += AMG_THREADS) {
+        float acc = 0.f;
+        int s = 0;
+        for (; s + AMG_UNROLL <= slices; s += AMG_UNROLL) {
+            float v[AMG_UNROLL];
+#pragma unroll
+            for (int u = 0; u < AMG_UNROLL; ++u) v[u] = po[(size_t)(s + u) * hd + d];
+#pragma unroll
+            for (int u = 0; u < AMG_UNROLL; ++u)
+                if (f_s[s + u] != 0.f) acc += v[u] * f_s[s + u];
         }
+        for (; s < slices; ++s)
+            if (f_s[s] != 0.f) acc += po[(size_t)s * hd + d] * f_s[s];
         out[qrow * hd + d] = __float2bfloat16_rn(acc / L);
     }
 }
@@ -429,7 +463,9 @@ static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream)
 KESTREL_API int kestrel_attention_merge(const float *part_o, const float *part_ml, void *out, const int *tile_seq,
                                         const int *tile_row0, int tiles, const int *cu_seqlens, int slices, int hd,
                                         int nq, int nkv, cudaStream_t stream) {
-    kestrel_launch(attention_merge_kernel, dim3(tiles, nkv), dim3(256), 0, stream, part_o, part_ml, (__nv_bfloat16 *)out,
+    KESTREL_REQUIRE(slices >= 1 && slices <= AMG_MAX_SLICES, "attention_merge: %d slices; the kernel merges up to %d", slices, AMG_MAX_SLICES);
+    KESTREL_REQUIRE(tiles <= 0x7fffffff && nkv <= 65535, "attention_merge: grid too large");
+    kestrel_launch(attention_merge_kernel, dim3(tiles, nkv, 16), dim3(AMG_THREADS), 0, stream, part_o, part_ml, (__nv_bfloat16 *)out,
                    tile_seq, tile_row0, cu_seqlens, slices, hd, nq, nkv);
     return kestrel_check_launch("attention_merge");
 }
@@ -482,9 +518,7 @@ KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const 
     if (rc) return rc;
     if (slices > 1) {
         KESTREL_REQUIRE(keys, "attention_mma: slices are merged for tiles of 16 rows only");
-        kestrel_launch(attention_merge_kernel, dim3(dim3(tiles, nkv)), dim3(256), 0, stream, part_o, part_ml, (__nv_bfloat16 *)out, tile_seq, tile_row0,
-                                                                  cu_seqlens, slices, hd, nq, nkv);
-        return kestrel_check_launch("attention_merge");
+        return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, cu_seqlens, slices, hd, nq, nkv, stream);
     }
     return 0;
 }

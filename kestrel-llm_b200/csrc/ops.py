@@ -520,7 +520,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      slices: int = 1, slice_len: int = 1 << 30, slice_len_dev: Optional[torch.Tensor] = None) -> None:
     """Attention of decode tokens (tiles of at most 16 rows) with a TMA loader warp in front of
     four mma.sync warps, head size 64 or 128; the key range is cut into ``slices`` slices of
-    ``slice_len`` keys (a multiple of 64) that are merged in ascending order (up to 8 inside the
+    ``slice_len`` keys (a multiple of 64) that are merged in ascending order (up to 4 inside the
     kernel, by the CTAs of a cluster; more through scratch and a second kernel), and
     ``slices * slice_len`` must reach the longest request.  The cache tensors are
     [pages, kv heads, page size, head size], contiguous (``attention_decode_supported``).  Keys
@@ -631,18 +631,14 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
             slots = library().kestrel_attention_decode_slots(hd) if use_decode else library().kestrel_attention_mma_slots(hd)
             ctas = max(1, tl.count * nkv)
             # As many slices as still let every CTA be resident at once (measured at batch 1 to 64,
-            # context 4,096: a second wave of CTAs costs more than longer slices), at least 256 keys
-            # a slice.  A captured step fixes the number for a nominal context and lets the slice
-            # length (a multiple of 128) follow the real one through the table on the device.
-            cand = max(1, min(slots // ctas, -(-tl.max_kv // 256), 32))
-            if use_decode:
-                # up to 8 slices are merged inside the kernel by a cluster; more go through scratch
-                # and a second kernel, which pays only where 8 slices would still be long
-                # (measured: one request at 32,768 keys 74 us with 8 slices, 48 us with 32; at 8,192
-                # keys 22 us against 31 us)
-                merged = library().kestrel_attention_decode_cluster_slices()
-                if cand > merged and tl.max_kv <= 2048 * merged:
-                    cand = merged
+            # contexts 2,048 to 65,536: a second wave of CTAs costs more than longer slices), at
+            # least 128 keys a slice (256 for the mma.sync kernel).  A captured step fixes the
+            # number for a nominal context and lets the slice length (a multiple of 128) follow the
+            # real one through the table on the device.
+            cand = max(1, min(slots // ctas, -(-tl.max_kv // (128 if use_decode else 256)), 32))
+            # (The decode kernel merges up to 4 slices inside a cluster, more through scratch and a
+            # second kernel of a few microseconds.  Measured, one request: 8,192 keys 21.7 us with 8
+            # slices, 12.2 us with 32; 32,768 keys 72.8 against 27.3 us.)
             slice_len = -(-(-(-tl.max_kv // cand)) // 128) * 128
             slices = -(-tl.max_kv // slice_len)
             if tl.slice_len_table is not None:

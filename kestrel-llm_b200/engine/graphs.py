@@ -130,7 +130,7 @@ class DecodeGraphs:
     # A captured step fixes how many slices its attention cuts the key range into; the slice
     # length follows the real contexts through device memory.  So that short and very long
     # contexts get a count that suits them, steps are captured per class of the longest context.
-    KV_CLASSES = (1024, 2048, 4096, 8192, 16384)
+    KV_CLASSES = (1024, 2048, 4096)
 
     def kv_class(self, max_kv: int) -> int:
         for c in self.KV_CLASSES:

@@ -499,6 +499,15 @@ def test_attention_decode_tokens(nq, nkv, hd, window, page, slices, slice_len):
               slices=slices, slice_len=slice_len, seed=hd + 7, decode=True)
 
 
+def test_attention_decode_merges_many_slices():
+    """37 slices of 64 keys through scratch and the merge kernel (its unrolled loop and the
+    remainder), some of them empty for the shorter requests."""
+    _mma_case(8, 2, 128, 0, 16, lens_new=(1, 1, 2), lens_ctx=(2330, 70, 1000), rows_per_tile=16, slices=37, slice_len=64,
+              seed=11, decode=True)
+    _mma_case(6, 1, 64, 0, 32, lens_new=(1, 1), lens_ctx=(1100, 5), rows_per_tile=16, slices=9, slice_len=128,
+              seed=12, decode=True)
+
+
 def test_attention_decode_takes_short_portions_too():
     """Tiles of up to 16 rows need not be single tokens: portions of two to four tokens."""
     _mma_case(8, 2, 128, 0, 16, lens_new=(4, 2, 3), lens_ctx=(100, 0, 130), rows_per_tile=16, slices=1, slice_len=1 << 24,
