@@ -451,7 +451,7 @@ KESTREL_API int kestrel_attention_decode(const void *q, const void *k_cache, con
     if (cluster) rc = hd == 64 ? launch_decode<64, true>(mk, mv, p, tiles, cache_pages, stream) : launch_decode<128, true>(mk, mv, p, tiles, cache_pages, stream);
     else rc = hd == 64 ? launch_decode<64, false>(mk, mv, p, tiles, cache_pages, stream) : launch_decode<128, false>(mk, mv, p, tiles, cache_pages, stream);
     if (rc || slices == 1 || cluster) return rc;
-    return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, cu_seqlens, slices, hd, nq, nkv, stream);
+    return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, 16, cu_seqlens, slices, hd, nq, nkv, stream);
 }
 
 // Error word of the kernel's bounded waits: 0 = none, 1 = the loader waited for a free stage,

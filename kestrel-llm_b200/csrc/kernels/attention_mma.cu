@@ -376,8 +376,8 @@ attention_mma_kernel(const AttnParams p) {
 }
 
 // out[row] = sum over slices of part_o * 2^(m - M) / sum of l * 2^(m - M), slices in ascending
-// order, for the rows of the listed tiles (16 rows each at most); one block per (tile, kv head,
-// row of the tile).  The slices' weights are worked out once per row into shared memory; then
+// order, for the rows of the listed tiles (rows_per_tile = gridDim.z rows each at most); one
+// block per (tile, kv head, row of the tile).  The slices' weights are worked out once per row into shared memory; then
 // every thread adds its dims over the slices with AMG_UNROLL loads in flight (a row's slices
 // are few and far apart in memory: a loop of dependent loads would cost a memory latency each).
 #define AMG_THREADS 128
@@ -398,7 +398,7 @@ attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict
     const int G = nq / nkv;
     const int tok_begin = cu_seqlens[seq];
     const int n_rows = (cu_seqlens[seq + 1] - tok_begin) * G;
-    if (r >= min(16, n_rows - row0)) return;
+    if (r >= min((int)gridDim.z, n_rows - row0)) return;
     const int row = row0 + r;
     const size_t qrow = (size_t)(tok_begin + row / G) * nq + kvh * G + row % G;
     const float *ml = part_ml + qrow * slices * 2;
@@ -459,13 +459,15 @@ static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream)
     return kestrel_check_launch("attention_mma");
 }
 
-// merges the slices of the listed tiles (at most 16 rows each) into out; also used by attention_tc.cu
+// merges the slices of the listed tiles (at most rows_per_tile rows each) into out; also used by
+// attention_decode.cu and attention_tc.cu
 KESTREL_API int kestrel_attention_merge(const float *part_o, const float *part_ml, void *out, const int *tile_seq,
-                                        const int *tile_row0, int tiles, const int *cu_seqlens, int slices, int hd,
-                                        int nq, int nkv, cudaStream_t stream) {
+                                        const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, int slices,
+                                        int hd, int nq, int nkv, cudaStream_t stream) {
+    KESTREL_REQUIRE(rows_per_tile >= 1 && rows_per_tile <= 65535, "attention_merge: tiles of %d rows", rows_per_tile);
     KESTREL_REQUIRE(slices >= 1 && slices <= AMG_MAX_SLICES, "attention_merge: %d slices; the kernel merges up to %d", slices, AMG_MAX_SLICES);
     KESTREL_REQUIRE(tiles <= 0x7fffffff && nkv <= 65535, "attention_merge: grid too large");
-    kestrel_launch(attention_merge_kernel, dim3(tiles, nkv, 16), dim3(AMG_THREADS), 0, stream, part_o, part_ml, (__nv_bfloat16 *)out,
+    kestrel_launch(attention_merge_kernel, dim3(tiles, nkv, rows_per_tile), dim3(AMG_THREADS), 0, stream, part_o, part_ml, (__nv_bfloat16 *)out,
                    tile_seq, tile_row0, cu_seqlens, slices, hd, nq, nkv);
     return kestrel_check_launch("attention_merge");
 }
@@ -518,7 +520,7 @@ KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const 
     if (rc) return rc;
     if (slices > 1) {
         KESTREL_REQUIRE(keys, "attention_mma: slices are merged for tiles of 16 rows only");
-        return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, cu_seqlens, slices, hd, nq, nkv, stream);
+        return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, 16, cu_seqlens, slices, hd, nq, nkv, stream);
     }
     return 0;
 }

@@ -22,5 +22,5 @@ struct AttnParams {
 
 // attention_mma.cu: merges the key-range slices of the listed tiles (at most 16 rows each) into out
 extern "C" int kestrel_attention_merge(const float *part_o, const float *part_ml, void *out, const int *tile_seq,
-                                       const int *tile_row0, int tiles, const int *cu_seqlens, int slices, int hd,
-                                       int nq, int nkv, cudaStream_t stream);
+                                       const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, int slices,
+                                       int hd, int nq, int nkv, cudaStream_t stream);

@@ -449,10 +449,21 @@ KESTREL_API int kestrel_attention_tc_supported(int hd, int page_size) {
     return hd == AT_HD && page_size > 0 && page_size % 8 == 0 && (AT_BN % page_size == 0 || page_size % AT_BN == 0);
 }
 
+// CTAs of this kernel that run at once: one per SM (shared memory and the 512 TMEM columns)
+KESTREL_API int kestrel_attention_tc_slots(void) {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sms = n;
+    }
+    return sms;
+}
+
 // Tiles of rows_per_tile rows, up to 256 (tile_seq / tile_row0 list them), head size 128;
-// cache_pages is the number of pages the cache tensors hold.  With slices > 1 (tiles of at
-// most 16 rows: decode tokens) every CTA takes a slice of slice_len keys, a multiple of 128 -
-// or the value at slice_len_ptr on the device - and the slices are merged in ascending order;
+// cache_pages is the number of pages the cache tensors hold.  With slices > 1 (few tiles far
+// into a long context) every CTA takes a slice of slice_len keys, a multiple of 128 - or the
+// value at slice_len_ptr on the device - and the slices are merged in ascending order;
 // part_o / part_ml are scratch of T * nq * slices * 128 and T * nq * slices * 2 floats.
 KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const void *v_cache, void *out,
                                      float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
@@ -492,7 +503,7 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
     kestrel_launch(attention_tc_kernel, dim3((unsigned)((long long)tiles * nkv), 1, slices), dim3(AT_THREADS), smem, stream, map_k, map_v, p, cache_pages, rows_per_tile);
     rc = kestrel_check_launch("attention_tc");
     if (rc || slices == 1) return rc;
-    return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, cu_seqlens, slices, hd, nq, nkv, stream);
+    return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, rows_per_tile, cu_seqlens, slices, hd, nq, nkv, stream);
 }
 
 // Error word of the kernel's bounded waits: 0 = none, else the number of the wait that gave up

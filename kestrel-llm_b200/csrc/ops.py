@@ -76,6 +76,7 @@ def _declare(lib) -> None:
         "kestrel_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
                                  _i, _i, _i, _i, _vp, _f, _vp],
         "kestrel_attention_tc_supported": [_i, _i],
+        "kestrel_attention_tc_slots": [],
         "kestrel_attention_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                      _i, _i, _i, _i, _i, _vp, _f, _vp],
         "kestrel_attention_decode_supported": [_i, _i],
@@ -109,7 +110,15 @@ def _p(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    """The current device's current stream as a raw handle.  Asked for at every launch, so it
+    takes torch's two C calls where they exist (a step of a few tokens is bound by the host)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -482,7 +491,7 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
                  slices: int = 1, slice_len: int = 1 << 30, slice_len_dev: Optional[torch.Tensor] = None,
                  rows_per_tile: int = 128) -> None:
     """tcgen05 attention of the listed tiles, head size 128: tiles of ``rows_per_tile`` rows, up
-    to 256 (prompt portions), or tiles of at most 16 rows (decode tokens) with the key range cut into
+    to 256 (prompt portions; 16 for decode tokens); the key range may be cut into
     ``slices`` slices of ``slice_len`` keys (a multiple of 128) that are merged in ascending
     order; ``slices * slice_len`` must reach the longest request.  The cache tensors are
     [pages, kv heads, page size, 128], contiguous, with a page size the kernel's page-wise TMA
@@ -652,8 +661,19 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
     if plan.large is not None:
         tl = plan.large
         if use_tc:
+            # Few tiles far into a long context (a portion of a long prompt) leave SMs idle, one
+            # CTA per SM: the key range is then cut into slices of at least 2,048 keys, merged
+            # through scratch.
+            slices, slice_len = 1, no_split
+            ctas = tl.count * nkv
+            sms = library().kestrel_attention_tc_slots()
+            if window <= 0 and 2 * ctas <= sms and tl.max_kv >= 4096:
+                cand = min(sms // ctas, tl.max_kv // 2048, 16)
+                slice_len = -(-(-(-tl.max_kv // cand)) // 128) * 128
+                slices = -(-tl.max_kv // slice_len)
             attention_tc(q, k_cache, v_cache, out, tl.seq, tl.row0, batch.cu_seqlens, batch.kv_lens, block_table,
-                         page_size, nq, nkv, hd, window, scale, rows_per_tile=rows_large)
+                         page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split,
+                         rows_per_tile=rows_large)
         else:
             attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, rows_large, batch.cu_seqlens, batch.kv_lens,
                           block_table, page_size, nq, nkv, hd, window, scale, 1, no_split)

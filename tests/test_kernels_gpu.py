@@ -381,6 +381,15 @@ def test_attention_tcgen05_prompt_portions(nq, nkv, window, page, rows):
               slices=1, slice_len=0, seed=nq, tc=True)
 
 
+@pytest.mark.parametrize("nq,nkv,page,rows,slices,slice_len", [(8, 2, 16, 256, 3, 256), (4, 1, 32, 128, 5, 128), (6, 2, 128, 256, 2, 384)])
+def test_attention_tcgen05_prompt_portions_in_slices(nq, nkv, page, rows, slices, slice_len):
+    """Portions deep into their contexts with the key range cut into slices that are merged:
+    some slices lie wholly before a portion, one holds its diagonal, later ones are empty for the
+    shorter request."""
+    _mma_case(nq, nkv, 128, 0, page, lens_new=(70, 130, 3), lens_ctx=(500, 90, 0), rows_per_tile=rows,
+              slices=slices, slice_len=slice_len, seed=nq + 21, tc=True)
+
+
 def test_attention_tcgen05_rescales_when_the_maximum_grows():
     """Scores that grow steeply along the keys: the running reference has to move (and the output
     accumulated so far be rescaled) at almost every key tile."""
