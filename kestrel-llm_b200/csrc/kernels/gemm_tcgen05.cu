@@ -186,7 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ------------------------------------------------------------------- persistent kernel
-// Many tokens (T > 256): one CTA per SM walks over output tiles (tile = blockIdx.x + i *
+// Many tokens (T > 128): one CTA per SM walks over output tiles (tile = blockIdx.x + i *
 // gridDim.x) and keeps TWO accumulators in TMEM (2 x 256 columns), so that the epilogue warps
 // drain tile i while the MMA thread already accumulates tile i+1 and the loader runs ahead
 // across tile boundaries.  PARTIAL uses tiles of 128 features x 256 tokens.  SWIGLU uses tiles
@@ -400,7 +400,10 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, ui
 #endif
 #define TCP_THREADS (64 + 128 * TCP_EPI_GROUPS)     // loader, MMA issuer, 4 x TCP_EPI_GROUPS epilogue warps
 
-// MODE PARTIAL: float32 [T, N], two accumulators (the epilogue overlaps the next tile).
+// MODE PARTIAL: float32 [T, N], two accumulators (the epilogue overlaps the next tile).  The K
+//               range may be cut into slices (tile index = slice * tiles_nt + output tile), each
+//               written to its own float32 plane slice_stride elements apart: a few hundred
+//               tokens give fewer output tiles than there are CTA pairs.
 // MODE SWIGLU : gate rows n and up rows up_row_offset + n, two accumulators that fill TMEM (no
 //               overlap), bfloat16 silu(gate) * up out; 48 KB a stage for twice the MMAs.
 // The epilogue is spread over 16 warps a CTA (four per TMEM lane quarter, 64 token columns
@@ -410,7 +413,7 @@ template <int MODE>
 __global__ void __launch_bounds__(TCP_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     void *__restrict__ out, int T, int N, int K, long long ldo, int stages, int tiles_n, int tiles_total,
-                    int up_row_offset, int accumulate) {
+                    int up_row_offset, int accumulate, int tiles_nt, int kb_per_split, long long slice_stride) {
     pdl_launch_dependents();
     constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
@@ -463,9 +466,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = pair; tile < tiles_total && ok; tile += n_pairs) {
-                int n0 = (tile % tiles_n) * 256 + (int)rank * TC_BM;
-                int t0 = (tile / tiles_n) * TCP_BN + (int)rank * (TCP_BN / 2);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int split = tile / tiles_nt, tw = tile % tiles_nt;       // a tile of the output and its slice of K
+                int n0 = (tw % tiles_n) * 256 + (int)rank * TC_BM;
+                int t0 = (tw / tiles_n) * TCP_BN + (int)rank * (TCP_BN / 2);
+                const int kb_end = min(num_kb, (split + 1) * kb_per_split);
+                for (int kb = split * kb_per_split; kb < kb_end; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1)) { atomicExch(&g_tc_error, 1); ok = false; break; }
                     uint32_t leader_full = map_to_rank(full_bar(stage), 0);
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
@@ -490,14 +495,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (!mbar_wait(acc_empty(b), acc_phase ^ 1)) { atomicExch(&g_tc_error, 4); ok = false; break; }
                 tc_fence_after();
                 uint32_t d = tmem + (uint32_t)b * ACC_COLS;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int split = tile / tiles_nt;
+                const int kb_begin = split * kb_per_split, kb_end = min(num_kb, (split + 1) * kb_per_split);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase)) { atomicExch(&g_tc_error, 2); ok = false; break; }
                     tc_fence_after();
                     uint32_t sa = base + (uint32_t)stage * STAGE_BYTES;
                     uint64_t da = smem_desc(sa), db = smem_desc(sa + A_TILES * A_BYTES);
 #pragma unroll
                     for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
-                        uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
+                        uint32_t acc = (kb > kb_begin || k4 > 0) ? 1u : 0u;
                         tc_mma_pair(d, da + 2 * k4, db + 2 * k4, IDESC, acc);
                         if (MODE == TC_SWIGLU) tc_mma_pair(d + TCP_BN, smem_desc(sa + A_BYTES) + 2 * k4, db + 2 * k4, IDESC, acc);
                     }
@@ -513,8 +520,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (int tile = pair; tile < tiles_total; tile += n_pairs, ++j) {
             int b = j % NBUF;
             uint32_t acc_phase = (uint32_t)(j / NBUF) & 1u;
-            int n = (tile % tiles_n) * 256 + (int)rank * TC_BM + 32 * q + lane;
-            int t0 = (tile / tiles_n) * TCP_BN;
+            const int split = tile / tiles_nt, tw = tile % tiles_nt;
+            int n = (tw % tiles_n) * 256 + (int)rank * TC_BM + 32 * q + lane;
+            int t0 = (tw / tiles_n) * TCP_BN;
             if (!mbar_wait(acc_full(b), acc_phase)) { if (lane == 0) atomicExch(&g_tc_error, 3); break; }
             tc_fence_after();
             uint32_t d = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)b * ACC_COLS;
@@ -538,7 +546,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             }
                     }
                 } else if (n < N) {
-                    float *o = (float *)out;
+                    float *o = (float *)out + (size_t)split * slice_stride;
                     if (accumulate) {           // out is the residual stream: the product is added to it in place
 #pragma unroll
                         for (int jj = 0; jj < 16; ++jj)
@@ -626,19 +634,26 @@ KESTREL_API int kestrel_gemm_tc_supported(const void *x, const void *w, int T, i
     return 1;
 }
 
-// Tuning of few-token products (T <= 256), which stream the weights once and are bound by HBM:
+// Tuning of few-token products (T <= 128), which stream the weights once and are bound by HBM:
 // g_ctas_per_sm CTAs share an SM's shared memory for their stages; a CTA costs about
 // g_overhead_kb k-blocks of time beyond its own k-blocks (launch, barrier set-up, TMEM
 // allocation, first tensor-map fetch, pipeline fill, epilogue).
 static int g_swiglu_bn = 256;      // token tile of the persistent SwiGLU product: 256 (one accumulator pair) or 128 (two)
 static int g_pairs = 1;            // many-token PARTIAL products on CTA pairs (cta_group::2)
 static int g_persistent = 1;       // many-token products on the persistent kernel (0: one tile per CTA)
+static int g_pair_min_tokens = 128; // products of more tokens run on CTA pairs (measured: from 129 tokens on they win)
+static int g_pair_overhead_kb = 12;
 static int g_overhead_kb = 6;
 static int g_ctas_per_sm = 2;
 
 KESTREL_API void kestrel_gemm_tc_set_persistent(int on) { g_persistent = on ? 1 : 0; }
 KESTREL_API void kestrel_gemm_tc_set_pairs(int on) { g_pairs = on ? 1 : 0; }
 KESTREL_API void kestrel_gemm_tc_set_swiglu_tile(int bn) { if (bn == 128 || bn == 256) g_swiglu_bn = bn; }
+
+KESTREL_API void kestrel_gemm_tc_set_pair_tuning(int min_tokens, int overhead_kb) {
+    if (min_tokens >= 0) g_pair_min_tokens = min_tokens;
+    if (overhead_kb >= 0) g_pair_overhead_kb = overhead_kb;
+}
 
 KESTREL_API void kestrel_gemm_tc_set_tuning(int overhead_kb, int ctas_per_sm) {
     if (overhead_kb >= 0) g_overhead_kb = overhead_kb;
@@ -649,11 +664,28 @@ KESTREL_API void kestrel_gemm_tc_set_tuning(int overhead_kb, int ctas_per_sm) {
 // number that minimises waves x (overhead + k-blocks per slice) over the GPU's 148 SMs.
 // Many-token products are not split.
 KESTREL_API int kestrel_gemm_tc_splits(int T, int N, int K) {
-    if (T > 256) return 1;
+    if (T > g_pair_min_tokens) {
+        // many tokens on CTA pairs: tiles of 256 x 256 over 74 pairs.  A slice costs about
+        // g_pair_overhead_kb k-blocks beyond its own (pipeline fill, the last tile's epilogue, its
+        // float32 plane written and read back); K is cut only where that fills idle pairs.
+        if (!g_pairs || !g_persistent) return 1;
+        long long tiles = (long long)((N + 255) / 256) * ((T + TCP_BN - 1) / TCP_BN);
+        int total_kb = (K + TC_BK - 1) / TC_BK;
+        int best = 1;
+        long long best_cost = -1;
+        for (int s = 1; s <= 8; ++s) {
+            int per = (total_kb + s - 1) / s;
+            if (s > 1 && (per < 16 || (total_kb + per - 1) / per != s)) continue;
+            long long waves = (tiles * s + 73) / 74;
+            long long cost = waves * (g_pair_overhead_kb + per);
+            if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+        }
+        return best;
+    }
     int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
     long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
     int total_kb = (K + TC_BK - 1) / TC_BK;
-    int slots = 148 * g_ctas_per_sm;
+    int slots = 148 * (bn <= 64 ? g_ctas_per_sm : 1);          // wider token tiles take an SM's shared memory alone
     int best = 1;
     long long best_cost = -1;
     int max_s = total_kb / 4 > 0 ? total_kb / 4 : 1;          // at least 4 k-blocks (256 columns) a slice
@@ -665,7 +697,7 @@ KESTREL_API int kestrel_gemm_tc_splits(int T, int N, int K) {
         long long waves = (tiles * s + slots - 1) / slots;
         // a CTA also writes its float32 slice [bn, 128] and the consumer reads it back: bn / 16
         // k-blocks' worth of bytes (a k-block of weights is 16 KB)
-        long long cost = waves * (g_overhead_kb + bn / 16 + per) * g_ctas_per_sm;
+        long long cost = waves * (g_overhead_kb + bn / 16 + per) * (bn <= 64 ? g_ctas_per_sm : 1);
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
     }
     return best;
@@ -722,7 +754,7 @@ static int launch_tc_persistent(const CUtensorMap &mw, const CUtensorMap &mx, vo
 
 template <int MODE>
 static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *out, int T, int N, int K, long long ldo,
-                          int up_off, int accumulate, cudaStream_t stream) {
+                          int up_off, int accumulate, int splits, long long slice_stride, cudaStream_t stream) {
     const int STAGE_BYTES = (MODE == TC_SWIGLU ? 2 : 1) * TC_BM * TC_BK * 2 + (TCP_BN / 2) * TC_BK * 2;
     int stages = (200 * 1024) / STAGE_BYTES;
     if (stages > 8) stages = 8;
@@ -754,11 +786,15 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
     }
     if (max_clusters == 0) return 1;       // not an error: tells the caller to fall back
     int tiles_n = (N + 255) / 256, tiles_t = (T + TCP_BN - 1) / TCP_BN;
-    long long total = (long long)tiles_n * tiles_t;
+    long long tiles_nt = (long long)tiles_n * tiles_t, total = tiles_nt * splits;
     if (total > 0x7fffffff) return kestrel_fail(-2, "gemm_tc: too many tiles");
+    if (splits > 1 && (MODE != TC_PARTIAL || accumulate)) return kestrel_fail(-2, "gemm_tc_pair: only plain float32 slices can be cut along K");
+    int total_kb = (K + TC_BK - 1) / TC_BK;
+    int per = (total_kb + splits - 1) / splits;
     int pairs = total < max_clusters ? (int)total : max_clusters;
     cfg.gridDim = dim3(2 * pairs);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<MODE>, mw, mx, out, T, N, K, ldo, stages, tiles_n, (int)total, up_off, accumulate);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<MODE>, mw, mx, out, T, N, K, ldo, stages, tiles_n, (int)total, up_off, accumulate,
+                                       (int)tiles_nt, per, slice_stride);
     if (e != cudaSuccess) return kestrel_fail(-3, "gemm_tc_pair: %s", cudaGetErrorString(e));
     return kestrel_check_launch("gemm_tc_pair");
 }
@@ -767,7 +803,7 @@ template <int MODE>
 static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, int w_rows, int K, long long ldx, long long ldw,
                        long long ldo, int splits, long long slice_stride, int up_off, int early_w, cudaStream_t stream) {
     int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
-    bool persistent = T > 256 && splits == 1 && g_persistent;
+    bool persistent = T > g_pair_min_tokens && g_persistent && (splits == 1 || (g_pairs && MODE == TC_PARTIAL));
     if (persistent && MODE == TC_SWIGLU) bn = g_swiglu_bn;
     CUtensorMap mw, mx;
     int rc = kestrel_tensor_map_bf16(&mw, w, w_rows, K, ldw, TC_BM);
@@ -775,9 +811,10 @@ static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, in
     if (persistent && g_pairs) {
         rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, TCP_BN / 2);
         if (rc) return rc;
-        rc = launch_tc_pair<MODE>(mw, mx, out, T, N, K, ldo, up_off, 0, stream);
+        rc = launch_tc_pair<MODE>(mw, mx, out, T, N, K, ldo, up_off, 0, splits, slice_stride, stream);
         if (rc <= 0) return rc;            // 1 = pairs cannot be scheduled: go on with one CTA per tile
     }
+    if (splits > 1) persistent = false;    // the one-CTA persistent kernel does not cut K
     rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, bn);
     if (rc) return rc;
     if (persistent) {
@@ -821,13 +858,14 @@ KESTREL_API int kestrel_gemm_tc(const void *x, const void *w, float *out, int T,
 KESTREL_API int kestrel_gemm_tc_add(const void *x, const void *w, float *residual, int T, int N, int K, long long ldx,
                                     long long ldw, long long ldo, cudaStream_t stream) {
     if (T == 0) return 0;
-    if (T <= 256 || !g_persistent || !g_pairs || !kestrel_gemm_tc_supported(x, w, T, N, K, ldx, ldw)) return 1;
+    if (T <= g_pair_min_tokens || !g_persistent || !g_pairs || !kestrel_gemm_tc_supported(x, w, T, N, K, ldx, ldw)) return 1;
+    if (kestrel_gemm_tc_splits(T, N, K) > 1) return 1;      // too few output tiles for the CTA pairs: cut along K, as slices
     CUtensorMap mw, mx;
     int rc = kestrel_tensor_map_bf16(&mw, w, N, K, ldw, TC_BM);
     if (rc) return rc;
     rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, TCP_BN / 2);
     if (rc) return rc;
-    return launch_tc_pair<TC_PARTIAL>(mw, mx, residual, T, N, K, ldo, 0, 1, stream);
+    return launch_tc_pair<TC_PARTIAL>(mw, mx, residual, T, N, K, ldo, 0, 1, 1, 0, stream);
 }
 
 // out bf16 [T, ff] = silu(x Wg^T) * (x Wu^T), w bf16 [2 ff, K] with the gate rows first;

@@ -47,6 +47,10 @@ KESTREL_API int kestrel_linear_bf16_noalloc(const void *x, const void *w, const 
                     "linear_noalloc: K=%d, ldx=%lld, ldw=%lld must be multiples of 8 and x, w 16-byte aligned", K, ldx, ldw);
     int splits = kestrel_gemm_tc_splits(T, N, K);
     unsigned long long need = (unsigned long long)splits * (unsigned long long)T * (unsigned long long)N;
+    if (need > NOALLOC_FLOATS && splits > 1) {       // one slice is always possible, if slower
+        splits = 1;
+        need = (unsigned long long)T * (unsigned long long)N;
+    }
     KESTREL_REQUIRE(need <= NOALLOC_FLOATS,
                     "linear_noalloc: %d slices of T=%d x N=%d float32 need %llu bytes of scratch; the built-in array holds %u",
                     splits, T, N, need * 4ull, (unsigned)KESTREL_NOALLOC_SCRATCH_BYTES);

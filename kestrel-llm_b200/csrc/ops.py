@@ -382,8 +382,16 @@ def gemm_tc_set_tuning(overhead_kb: int = -1, ctas_per_sm: int = 0) -> None:
     fn(int(overhead_kb), int(ctas_per_sm))
 
 
+def gemm_tc_set_pair_tuning(min_tokens: int = -1, overhead_kb: int = -1) -> None:
+    """Tuning of many-token products on CTA pairs: products of more than ``min_tokens`` tokens
+    take them; a K slice is priced at ``overhead_kb`` k-blocks beyond its own (see gemm_tcgen05.cu)."""
+    fn = library().kestrel_gemm_tc_set_pair_tuning
+    fn.restype, fn.argtypes = None, [_i, _i]
+    fn(int(min_tokens), int(overhead_kb))
+
+
 def gemm_tc_set_many_token_path(pairs: bool = True, persistent: bool = True, swiglu_tile: int = 256) -> None:
-    """Which kernel a many-token product (more than 256 tokens) takes: CTA pairs (the default),
+    """Which kernel a many-token product (more than 128 tokens) takes: CTA pairs (the default),
     else one persistent CTA per SM (what runs where pairs cannot be scheduled; ``swiglu_tile``
     128 or 256 tokens for its SwiGLU form), else one tile per CTA.  For tests of the fall-backs."""
     lib = library()

@@ -51,7 +51,9 @@ def test_gemm_plain_is_the_same_for_any_batch():
 
 @pytest.mark.parametrize("T,N,K,splits", [(1, 509, 96, None), (8, 4096, 4096, None), (37, 200, 96, 1), (130, 96, 200, 1),
                                           (65, 1000, 776, 3), (16, 128, 64, 1), (17, 129, 72, 1), (300, 640, 512, None),
-                                          (2048, 384, 256, 1), (64, 6144, 1024, 2), (3, 260, 4096, None), (600, 40000, 512, 1), (257, 129, 8, 1)])
+                                          (2048, 384, 256, 1), (64, 6144, 1024, 2), (3, 260, 4096, None), (600, 40000, 512, 1), (257, 129, 8, 1),
+                                          (300, 640, 2048, 2), (512, 4096, 4096, None), (200, 1100, 3080, 3), (1000, 520, 4096, 4),
+                                          (129, 6144, 4096, None), (128, 6144, 4096, None)])
 def test_gemm_tcgen05(T, N, K, splits):
     """The tensor-core product against the CUDA-core product of the same bfloat16 operands."""
     ops = _ops()
@@ -101,12 +103,14 @@ def test_gemm_tcgen05_fallbacks_for_many_tokens(pairs, persistent, tile):
     ops.gemm_tc_set_many_token_path(pairs, persistent, tile)
     try:
         got = ops.gemm_tc(x, w, splits=1)[0].cpu().numpy()
+        cut = ops.gemm_tc(x, w, splits=3).sum(0).cpu().numpy()          # K in slices: one tile per CTA, whatever the setting
         ops.gemm_tc_swiglu(x, w2, act)
         assert ops.gemm_tc_error() == 0
     finally:
         ops.gemm_tc_set_many_token_path()
     ref = xr.astype(np.float64) @ wr.astype(np.float64).T
     np.testing.assert_allclose(got, ref, rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max())
+    np.testing.assert_allclose(cut, ref, rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max())
     y = xr.astype(np.float64) @ w2r.astype(np.float64).T
     ref2 = (y[:, :ff] / (1 + np.exp(-y[:, :ff]))) * y[:, ff:]
     np.testing.assert_allclose(act.float().cpu().numpy(), ref2, rtol=1e-2, atol=1e-2 * np.abs(ref2).max())
