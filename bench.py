@@ -105,6 +105,7 @@ class ClockSampler:
 
 
 def main() -> int:
+    global CONTEXT, PREFILL_TOKENS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -113,6 +114,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="context length at which the decode steps end (default 4096)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the prefill step (default 2048)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -124,6 +127,7 @@ def main() -> int:
         print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported (no multi-GPU path exists)")
         return 2
     W, K = max(3, args.warmup), max(1, args.steps)
+    CONTEXT, PREFILL_TOKENS = max(256, args.context), max(16, args.prefill_tokens)      # the defaults unless asked otherwise
 
     import numpy as np
     import torch
@@ -145,8 +149,9 @@ def main() -> int:
     model = resolve_architecture(cfg.architecture).build(cfg, torch.bfloat16, dev)
     fill_random_(model, 0)
     max_batch = 64 if not args.skip_points else max(args.batch, 1)
-    opts = EngineOptions(dtype="bfloat16", page_size=16, batch_max=max_batch, max_model_len=CONTEXT + 64,
-                         max_tokens=max_batch * (CONTEXT + 64), max_step_tokens=max(PREFILL_TOKENS, max_batch),
+    longest = max(CONTEXT, PREFILL_TOKENS) + 64
+    opts = EngineOptions(dtype="bfloat16", page_size=16, batch_max=max_batch, max_model_len=longest,
+                         max_tokens=max(max_batch * (CONTEXT + 64), longest), max_step_tokens=max(PREFILL_TOKENS, max_batch),
                          prefill_batch=PREFILL_TOKENS)
     llm = LLM(model, dtype="bfloat16", options=opts)
     engine = llm.engine
@@ -263,7 +268,7 @@ def main() -> int:
 
     achieved = main_pt["bytes_step"] / (main_pt["ms"] / 1000.0) / 1e9
     rec = {
-        "metric": "decode tokens/s, Qwen3-8B bf16, batch 8, context 4096", "value": round(main_pt["tok_s"], 2),
+        "metric": f"decode tokens/s, Qwen3-8B bf16, batch {args.batch}, context {CONTEXT}", "value": round(main_pt["tok_s"], 2),
         "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(main_pt["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights, uniform random token ids, cache of the context filled with random values",

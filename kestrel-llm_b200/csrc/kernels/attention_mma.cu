@@ -382,14 +382,14 @@ attention_mma_kernel(const AttnParams p) {
 // are few and far apart in memory: a loop of dependent loads would cost a memory latency each).
 #define AMG_THREADS 128
 #define AMG_MAX_SLICES 1024
-#define AMG_UNROLL 8
+#define AMG_UNROLL 16
 __global__ void __launch_bounds__(AMG_THREADS)
 attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
                        __nv_bfloat16 *__restrict__ out, const int *__restrict__ tile_seq,
                        const int *__restrict__ tile_row0, const int *__restrict__ cu_seqlens,
                        int slices, int hd, int nq, int nkv) {
     pdl_launch_dependents();
-    __shared__ float f_s[AMG_MAX_SLICES];
+    __shared__ float f_s[AMG_MAX_SLICES], lf_s[AMG_MAX_SLICES];
     __shared__ float red[AMG_THREADS / 32];
     __shared__ float inv_l;
     const int tile = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
@@ -412,14 +412,15 @@ attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict
 #pragma unroll
     for (int w = 1; w < AMG_THREADS / 32; ++w) M = fmaxf(M, red[w]);
     for (int s = tid; s < slices; s += AMG_THREADS) {
-        float ms = ml[2 * s];
-        f_s[s] = ms == -INFINITY ? 0.f : exp2f(ms - M);
+        float2 v = *reinterpret_cast<const float2 *>(ml + 2 * s);
+        float f = v.x == -INFINITY ? 0.f : exp2f(v.x - M);
+        f_s[s] = f;
+        lf_s[s] = f != 0.f ? v.y * f : 0.f;
     }
     __syncthreads();
     if (tid == 0) {             // the sum of the weights in ascending order, as the rows' own sums
         float L = 0.f;
-        for (int s = 0; s < slices; ++s)
-            if (f_s[s] != 0.f) L += ml[2 * s + 1] * f_s[s];
+        for (int s = 0; s < slices; ++s) L += lf_s[s];
         inv_l = L;
     }
     __syncthreads();
