@@ -114,6 +114,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length at which the decode steps end (default 4096)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the prefill step (default 2048)")
     args = ap.parse_args()
@@ -150,7 +151,7 @@ def main() -> int:
     fill_random_(model, 0)
     max_batch = 64 if not args.skip_points else max(args.batch, 1)
     longest = max(CONTEXT, PREFILL_TOKENS) + 64
-    opts = EngineOptions(dtype="bfloat16", page_size=16, batch_max=max_batch, max_model_len=longest,
+    opts = EngineOptions(dtype="bfloat16", page_size=args.page_size, batch_max=max_batch, max_model_len=longest,
                          max_tokens=max(max_batch * (CONTEXT + 64), longest), max_step_tokens=max(PREFILL_TOKENS, max_batch),
                          prefill_batch=PREFILL_TOKENS)
     llm = LLM(model, dtype="bfloat16", options=opts)
@@ -276,7 +277,7 @@ def main() -> int:
         "config": {"model": "Qwen3-8B shape", "layers": L, "layers_of_model": full_layers, "hidden": cfg.hidden_size,
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
-                   "seq_len": CONTEXT, "page_size": 16, "parallelism": "single GPU",
+                   "seq_len": CONTEXT, "page_size": args.page_size, "parallelism": "single GPU",
                    "cache_flush": "inputs larger than L2: each step streams all weights and cache from HBM",
                    "peaks": pk["source"]},
         "e2e": e2e, "gpu_launches": int(main_pt["launches"]), "prefill": prefill,
