@@ -324,6 +324,14 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                                     uniform.data_ptr(), out.data_ptr(), _stream()))
 
 
+def sample_set_cluster(on: bool = True) -> None:
+    """Whether `sample` may take the kernel that keeps a row in the shared memory of a cluster
+    (the default); off: always the one-block kernel over global memory.  For tests of the latter."""
+    fn = library().kestrel_sample_set_cluster
+    fn.restype, fn.argtypes = None, [_i]
+    fn(1 if on else 0)
+
+
 def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether the tcgen05 product takes these operands: bfloat16, K and both row strides
     multiples of 8 elements, bases 16-byte aligned (the TMA rules)."""

@@ -763,24 +763,36 @@ def test_argmax_first_maximum_wins():
     assert got[:4] == [77, V - 1, 0, 0] and got[4] == int(l[4].argmax())
 
 
-@pytest.mark.parametrize("V", [509, 151936])
-def test_sample_against_plain_sampler(V):
+@pytest.mark.parametrize("V,cluster,reps", [(509, True, 3), (509, False, 3), (9001, True, 2), (40000, True, 2), (151936, True, 3),
+                                            (151936, False, 1), (262144, True, 1)])
+def test_sample_against_plain_sampler(V, cluster, reps):
+    """Temperature, top-k, min-p and top-p against the plain sampler, on the kernel that keeps a
+    row in the shared memory of a cluster (1, 2 and 8 CTAs; with and without room for the
+    probabilities) and on the one-block kernel over global memory.  Rows are flat (random
+    logits) or peaked (a few tokens far above the rest, as a trained model gives them)."""
     ops = _ops()
     from kestrel_llm_b200.sampling import uniform_for
     rng = np.random.default_rng(V)
     rows = [(0.8, 0, 0.0, 1.0), (1.0, 20, 0.0, 1.0), (0.7, 0, 0.05, 1.0), (1.3, 0, 0.0, 0.9), (0.9, 50, 0.02, 0.8),
-            (0.0, 0, 0.0, 1.0), (1.0, 0, 0.0, 0.0), (2.0, 1, 0.0, 1.0), (0.5, 0, 0.0, 0.3)] * 3
+            (0.0, 0, 0.0, 1.0), (1.0, 0, 0.0, 0.0), (2.0, 1, 0.0, 1.0), (0.5, 0, 0.0, 0.3), (1.0, 3, 0.0, 0.999)] * reps
     R = len(rows)
     logits = (rng.normal(size=(R, V)) * 3).astype(np.float32)
+    for r in range(1, R, 2):            # every other row peaked: five tokens 8 to 12 above the rest
+        logits[r, rng.choice(V, size=5, replace=False)] += rng.uniform(8, 12, size=5).astype(np.float32)
     u = np.array([uniform_for(123, i) for i in range(R)], dtype=np.float32)
     assert ((u > 0) & (u <= 1)).all()
     dev = lambda a, dt: torch.tensor(a, dtype=dt, device=DEV)
-    out = torch.empty(R, dtype=torch.int32, device=DEV)
-    ops.sample(torch.from_numpy(logits).to(DEV), dev([r[0] for r in rows], torch.float32),
-               dev([r[1] for r in rows], torch.int32), dev([r[3] for r in rows], torch.float32),
-               dev([r[2] for r in rows], torch.float32), torch.from_numpy(u).to(DEV), out)
-    got = out.cpu().tolist()
+    out = torch.full((R,), -7, dtype=torch.int32, device=DEV)
+    ops.sample_set_cluster(cluster)
+    try:
+        ops.sample(torch.from_numpy(logits).to(DEV), dev([r[0] for r in rows], torch.float32),
+                   dev([r[1] for r in rows], torch.int32), dev([r[3] for r in rows], torch.float32),
+                   dev([r[2] for r in rows], torch.float32), torch.from_numpy(u).to(DEV), out)
+        got = out.cpu().tolist()
+    finally:
+        ops.sample_set_cluster(True)
     for r, (temp, tk, mp, tp) in enumerate(rows):
+        assert 0 <= got[r] < V, f"row {r}: no token written ({got[r]})"
         if temp <= 0 or tp <= 0:
             assert got[r] == P.greedy(logits[r])
             continue
@@ -796,6 +808,37 @@ def test_sample_against_plain_sampler(V):
             assert abs(edge - target) <= 1e-5 * c[-1], f"row {r}: got {got[r]}, plain {want}"
     # a draw depends on (seed, index) only
     assert uniform_for(5, 3) == uniform_for(5, 3) and uniform_for(5, 3) != uniform_for(5, 4) != uniform_for(6, 4)
+
+
+@pytest.mark.parametrize("V", [1000, 151936])
+def test_sample_odd_rows(V):
+    """Rows that a sampler must not stumble over: all logits equal (every token kept, the draw
+    walks the indices), -inf almost everywhere, NaN everywhere (first maximum = index 0 as a
+    strict scan gives), top-k beyond ties at the cut; and a row's token does not depend on the
+    rows beside it."""
+    ops = _ops()
+    dev = lambda a, dt: torch.tensor(a, dtype=dt, device=DEV)
+    logits = np.zeros((5, V), dtype=np.float32)
+    logits[1, :] = -np.inf; logits[1, V - 3] = 1.0; logits[1, 7] = 0.5
+    logits[2, :] = np.nan
+    logits[3, :] = -1.0; logits[3, [5, V // 2, V - 1]] = 2.0                 # three equal maxima, top-k 2: all three stay
+    logits[4] = np.random.default_rng(1).normal(size=V).astype(np.float32) * 4
+    temps, tks, tps, mps = [1.0, 1.0, 1.0, 1.0, 0.7], [0, 0, 0, 2, 40], [1.0, 0.95, 0.9, 1.0, 0.9], [0.0, 0.0, 0.0, 0.0, 0.01]
+    u = np.array([0.5, 0.9, 0.3, 0.99, 0.42], dtype=np.float32)
+    out = torch.full((5,), -7, dtype=torch.int32, device=DEV)
+    args = lambda sel: (torch.from_numpy(logits[sel]).to(DEV), dev([temps[i] for i in sel], torch.float32), dev([tks[i] for i in sel], torch.int32),
+                        dev([tps[i] for i in sel], torch.float32), dev([mps[i] for i in sel], torch.float32), torch.from_numpy(u[sel]).to(DEV))
+    ops.sample(*args([0, 1, 2, 3, 4]), out)
+    got = out.cpu().tolist()
+    assert abs(got[0] - (V // 2 - 1)) <= 1                      # uniform: the index at half the mass
+    assert got[1] == V - 3                                      # p(7) = 0.38, p(V - 3) = 0.62; u = 0.9 lands in the latter
+    assert got[2] == 0
+    assert got[3] == V - 1                                      # three tokens of 1/3 each (all of the tie stay); u = 0.99: the last
+    alone = torch.full((1,), -7, dtype=torch.int32, device=DEV)
+    ops.sample(*args([4]), alone)
+    assert int(alone[0]) == got[4]
+    p = P.sample_probs(logits[4], 0.7, 40, 0.01, 0.9)
+    assert p[got[4]] > 0
 
 
 def test_a_wait_that_nothing_ends_gives_up():
