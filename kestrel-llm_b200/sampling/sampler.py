@@ -35,8 +35,29 @@ def uniform_for(seed: int, index: int) -> float:
 
 
 class Sampler:
+    RING = 4        # pinned buffers for the rows' options; a buffer is reused only after its copy has run
+
     def __init__(self, device):
         self.device = torch.device(device)
+        self._ring: List[torch.Tensor] = []
+        self._ring_done: List[object] = []
+        self._turn = 0
+
+    def _pinned(self, rows: int) -> np.ndarray:
+        """A pinned float32 [5, rows] view whose last copy to the device has completed."""
+        if not self._ring or self._ring[0].shape[1] < rows:
+            cap = max(64, 1 << (rows - 1).bit_length())
+            for ev in self._ring_done:
+                if ev is not None:
+                    ev.synchronize()
+            self._ring = [torch.empty((5, cap), dtype=torch.float32).pin_memory() for _ in range(self.RING)]
+            self._ring_done = [None] * self.RING
+        t = self._turn
+        self._turn = (t + 1) % self.RING
+        if self._ring_done[t] is not None:
+            self._ring_done[t].synchronize()
+        self._current = t
+        return self._ring[t].numpy()[:, :rows]
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                indices: Sequence[int]) -> torch.Tensor:
@@ -47,7 +68,7 @@ class Sampler:
         if all(p.greedy for p in params):
             ops.argmax(logits, out)
             return out
-        host = np.empty((5, R), dtype=np.float32)
+        host = self._pinned(R) if self.device.type == "cuda" else np.empty((5, R), dtype=np.float32)
         ks = np.empty((R,), dtype=np.int32)
         for r, (p, s, i) in enumerate(zip(params, seeds, indices)):
             host[0, r] = p.temperature if not p.greedy else 0.0
@@ -56,6 +77,13 @@ class Sampler:
             host[3, r] = uniform_for(s, i)
             ks[r] = p.top_k
         host[4] = ks.view(np.float32)
-        dev = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
+        if self.device.type == "cuda":
+            dev = torch.empty((5, R), dtype=torch.float32, device=self.device)
+            dev.copy_(self._ring[self._current][:, :R], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._ring_done[self._current] = ev
+        else:
+            dev = torch.from_numpy(host).to(self.device)
         ops.sample(logits, dev[0], dev[4].view(torch.int32), dev[1], dev[2], dev[3], out)
         return out
