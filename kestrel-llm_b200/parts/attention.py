@@ -20,7 +20,6 @@ from .linear import Linear
 
 
 class GroupedQueryAttention(Mixer):
-    graph_safe = True
 
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype,
                  device, prefix: str, position: Optional[PositionEncoding], qk_norm_eps: Optional[float],
@@ -44,6 +43,8 @@ class GroupedQueryAttention(Mixer):
         else:
             self.q_norm = self.k_norm = None
         self.scale = 1.0 / math.sqrt(head_dim)
+        # a captured decode step tiles every request's rows (token, head) into one tile of 16
+        self.graph_safe = heads // kv_heads <= 16
 
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.kv_heads, self.head_dim, self.window)

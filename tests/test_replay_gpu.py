@@ -14,7 +14,7 @@ import tiny_configs
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": (5, 11, 17, 40, 70), "B": (1, 33, 70, 129, 47, 90), "C": (3, 50, 97, 130, 64, 81),
-           "D": (2, 45, 131, 200, 77), "E": (9, 64, 150, 129)}
+           "D": (2, 45, 131, 200, 77), "E": (9, 64, 150, 129), "F": (4, 40, 150, 66)}
 # more requests than fit the pool at once, so that finished requests' pages are used again
 LENGTHS_MIXED = {"A": (5, 11, 17, 40, 70, 64, 33, 90, 25, 70, 48), "B": (1, 33, 70, 129, 47, 90, 16, 65, 120, 31),
                  "C": (3, 50, 97, 130, 64, 81, 17, 111, 49, 128), "D": (2, 45, 131, 200, 77, 33, 160, 90, 64),
@@ -43,6 +43,15 @@ def _run(model_dirs, name, dtype, family, record_property, lengths=None, graphs=
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_prompts(model_dirs, name, dtype, record_property):
     _run(model_dirs, name, dtype, R.trace_whole, record_property)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("family", [R.trace_whole, R.trace_tail_decode])
+def test_more_heads_per_kv_head_than_a_decode_tile_holds(model_dirs, dtype, family, record_property):
+    """18 query heads on one kv head: a token's rows do not fit the 16-row tiles, so decode
+    tokens run on the kernels for prompt portions and the model's steps are not captured."""
+    engine = _run(model_dirs, "F", dtype, family, record_property, graphs=True)
+    assert engine.graphs is None and engine.graph_launches == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
