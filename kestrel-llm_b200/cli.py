@@ -11,6 +11,8 @@ Names and meanings taken over from the reference (src/main.c:4491-4850):
   --batch-max N          live requests (main.c:4805)
   --max-queued N         waiting requests before admission refuses (main.c:4802)
   --top-k N, --min-p X   sampling filters (main.c:4567-4573)
+  --repetition-penalty P, --repetition-window N   the harness's penalty on the last N generated
+                         tokens (main.c:3741-3782; defaults from VLLM_STREAM_REPPEN / VLLM_STREAM_REPWIN)
 Added for this engine: --dtype, --prompt-ids, --prompt-file, --random-prompts N:LEN:SEED,
 --temperature, --top-p, --seed, --ignore-eos, --page-size, --max-tokens, --max-model-len,
 --max-step-tokens, --random-weights SEED with --config FILE (writes the folder to --model
@@ -27,6 +29,27 @@ import sys
 import time
 
 
+def _repetition_options(args):
+    """Penalty and window as the reference reads them (main.c:3741-3752): a penalty counts only
+    if 1 < p < 1000, a window only if 1 <= n <= 64; otherwise off and 32."""
+    pen, win = 1.0, 32
+    raw = args.repetition_penalty if args.repetition_penalty is not None else os.environ.get("VLLM_STREAM_REPPEN", "")
+    try:
+        p = float(raw)
+        if 1.0 < p < 1e3:
+            pen = p
+    except (TypeError, ValueError):
+        pass
+    raw = args.repetition_window if args.repetition_window is not None else os.environ.get("VLLM_STREAM_REPWIN", "")
+    try:
+        w = int(raw)
+        if 1 <= w <= 64:
+            win = w
+    except (TypeError, ValueError):
+        pass
+    return pen, win
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="kestrel", description="Qwen3 dense decoder on one B200")
     ap.add_argument("--model", required=True)
@@ -41,6 +64,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--min-p", type=float, default=0.0)
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--temperature", type=float, default=0.0)
+    # the reference takes these two from the environment (main.c:3741-3752); the flags override it
+    ap.add_argument("--repetition-penalty", type=float, default=None, help="default: VLLM_STREAM_REPPEN, else off")
+    ap.add_argument("--repetition-window", type=int, default=None, help="default: VLLM_STREAM_REPWIN, else 32")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--ignore-eos", action="store_true")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
@@ -103,8 +129,12 @@ def main(argv=None) -> int:
     prompts = _prompts(args, c.vocab_size)
     if args.stream_ctx > 0:
         prompts = [(p * (args.stream_ctx // len(p) + 1))[:args.stream_ctx] for p in prompts]
+    rep_pen, rep_win = _repetition_options(args)
     sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
-                        max_tokens=args.stream_n, seed=args.seed, ignore_eos=args.ignore_eos)
+                        max_tokens=args.stream_n, seed=args.seed, ignore_eos=args.ignore_eos,
+                        repetition_penalty=rep_pen, repetition_window=rep_win)
+    mode = "greedy" if sp.greedy else "sampling"
+    print(f"[STREAM] decode mode: {mode}{'+reppen' if sp.penalised else ''} (rep_pen={rep_pen:.3f} win={rep_win})", flush=True)
     if args.warmup:
         tw = time.perf_counter()
         llm.generate(prompts[:1], SamplingParams(max_tokens=8, ignore_eos=True))

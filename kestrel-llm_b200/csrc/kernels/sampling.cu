@@ -529,6 +529,40 @@ static int sample_cluster_shape(int V, int R, int *slice, int *store_p) {
     return 0;
 }
 
+// ------------------------------------------------------------------------------------------
+// Repetition penalty of the reference's streaming harness (src/main.c:3741-3782): for each of
+// the last `window` tokens a request generated, most recent first, the token's logit l becomes
+// l / p if l >= 0, else l * p - once per occurrence, so a token that appears twice in the window
+// is penalised twice.  history int32 [R, width]: row r holds that request's last tokens (entries
+// beyond counts[r], or outside the vocabulary, are skipped); penalty float [R], <= 1 = off.
+// One thread a row: the steps on one token follow each other, and there are 64 at most.
+// ------------------------------------------------------------------------------------------
+__global__ void repetition_penalty_kernel(float *__restrict__ logits, long long ld, int V, const int *__restrict__ history,
+                                          int width, const int *__restrict__ counts, const float *__restrict__ penalty, int R) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    float p = penalty[r];
+    if (!(p > 1.0f)) return;
+    float *row = logits + (size_t)r * ld;
+    int n = min(counts[r], width);
+    for (int h = 0; h < n; ++h) {
+        int tok = history[(size_t)r * width + h];
+        if (tok < 0 || tok >= V) continue;
+        float l = row[tok];
+        row[tok] = l >= 0.0f ? l / p : l * p;
+    }
+}
+
+KESTREL_API int kestrel_repetition_penalty(float *logits, long long ld, int R, int V, const int *history, int width,
+                                           const int *counts, const float *penalty, cudaStream_t stream) {
+    if (R == 0) return 0;
+    KESTREL_REQUIRE(R > 0 && V > 0 && width > 0, "repetition_penalty: bad sizes R=%d V=%d width=%d", R, V, width);
+    kestrel_launch(repetition_penalty_kernel, dim3((R + 63) / 64), dim3(64), 0, stream, logits, ld, V, history, width, counts, penalty, R);
+    return kestrel_check_launch("repetition_penalty");
+}
+
 static int g_sample_cluster = 1;    // 0: always the one-block kernel (for tests of it)
 KESTREL_API void kestrel_sample_set_cluster(int on) { g_sample_cluster = on ? 1 : 0; }
 

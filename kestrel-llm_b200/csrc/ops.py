@@ -324,6 +324,23 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                                     uniform.data_ptr(), out.data_ptr(), _stream()))
 
 
+def repetition_penalty(logits: torch.Tensor, history: torch.Tensor, counts: torch.Tensor, penalty: torch.Tensor) -> None:
+    """In place: for each of the first counts[r] tokens of history[r] (int32 [R, width], a request's
+    last generated tokens), logits[r, token] becomes l / penalty[r] if l >= 0, else l * penalty[r] -
+    once per occurrence; rows with penalty <= 1 are left alone."""
+    _need(logits, "repetition_penalty.logits", torch.float32, 2)
+    _need(history, "repetition_penalty.history", torch.int32, 2)
+    _need(counts, "repetition_penalty.counts", torch.int32, 1)
+    _need(penalty, "repetition_penalty.penalty", torch.float32, 1)
+    R, V = logits.shape
+    if history.shape[0] != R or counts.shape[0] != R or penalty.shape[0] != R:
+        raise KernelError("repetition_penalty: one row of history, one count and one penalty per row of logits")
+    fn = library().kestrel_repetition_penalty
+    fn.restype, fn.argtypes = _i, [_vp, _ll, _i, _i, _vp, _i, _vp, _vp, _vp]
+    _check(fn(logits.data_ptr(), logits.stride(0), R, V, history.data_ptr(), history.shape[1], counts.data_ptr(),
+              penalty.data_ptr(), _stream()))
+
+
 def sample_set_cluster(on: bool = True) -> None:
     """Whether `sample` may take the kernel that keeps a row in the shared memory of a cluster
     (the default); off: always the one-block kernel over global memory.  For tests of the latter."""

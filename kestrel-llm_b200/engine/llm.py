@@ -177,7 +177,7 @@ class LLM:
     def _sample(self, logits: torch.Tensor, lives: List[_Live], decode_only: bool) -> _InFlight:
         """Picks one token per request on the device and starts their copy to the host."""
         ids_dev = self.sampler.sample(logits, [lv.params for lv in lives], [lv.seed for lv in lives],
-                                      [lv.sampled for lv in lives])
+                                      [lv.sampled for lv in lives], [lv.out.token_ids for lv in lives])
         for lv in lives:
             lv.sampled += 1
         host = self._pinned[self._pinned_turn]
@@ -226,6 +226,8 @@ class LLM:
             if rid in prev.discard or self._live.get(rid) is not lv:
                 return False
             if lv.sampled >= lv.params.max_tokens:           # the token in flight is its last
+                return False
+            if lv.params.penalised:                          # the penalty needs that token on the host
                 return False
         cache = self.engine.cache
         return all(cache.free_pages(g) >= len(prev.lives) for g in range(cache.num_groups))

@@ -9,7 +9,7 @@ and can be repeated.
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -60,11 +60,29 @@ class Sampler:
         return self._ring[t].numpy()[:, :rows]
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-               indices: Sequence[int]) -> torch.Tensor:
+               indices: Sequence[int], generated: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
         """logits float32 [R, V]; row r belongs to a request with ``params[r]``, ``seeds[r]``,
-        generating its ``indices[r]``-th token.  Returns int32 [R] on the device."""
+        generating its ``indices[r]``-th token; ``generated[r]`` are the tokens it has generated so
+        far (needed by rows with a repetition penalty, which changes ``logits`` in place).
+        Returns int32 [R] on the device."""
         R = logits.shape[0]
         out = torch.empty((R,), dtype=torch.int32, device=self.device)
+        if any(p.penalised for p in params):
+            if generated is None:
+                raise ValueError("a repetition penalty needs the tokens generated so far")
+            W = 64
+            hist = np.full((R, W), -1, dtype=np.int32)
+            counts = np.zeros((R,), dtype=np.int32)
+            pen = np.ones((R,), dtype=np.float32)
+            for r, (p, g) in enumerate(zip(params, generated)):
+                if not p.penalised:
+                    continue
+                last = list(g[-p.repetition_window:])[::-1]       # most recent first, as the reference walks them
+                hist[r, :len(last)] = last
+                counts[r] = len(last)
+                pen[r] = p.repetition_penalty
+            ops.repetition_penalty(logits, torch.from_numpy(hist).to(self.device), torch.from_numpy(counts).to(self.device),
+                                   torch.from_numpy(pen).to(self.device))
         if all(p.greedy for p in params):
             ops.argmax(logits, out)
             return out

@@ -259,6 +259,23 @@ def greedy(logits: np.ndarray) -> int:
     return best
 
 
+def repetition_penalty(logits: np.ndarray, generated, penalty: float, window: int = 32) -> np.ndarray:
+    """The streaming harness's penalty (src/main.c:3741-3752 options, 3768-3782 loop): a copy of
+    the logits in which, for each of the last ``window`` generated tokens, most recent first, the
+    token's logit l is replaced by l / penalty if l >= 0, else l * penalty - once per occurrence."""
+    out = np.array(logits, dtype=F32, copy=True)
+    if not penalty > 1.0:
+        return out
+    cnt = min(len(generated), window)
+    for h in range(cnt):
+        tid = generated[len(generated) - 1 - h]
+        if tid < 0 or tid >= out.shape[0]:
+            continue
+        l = out[tid]
+        out[tid] = F32(l / F32(penalty)) if l >= 0 else F32(l * F32(penalty))
+    return out
+
+
 def sample_probs(logits: np.ndarray, temperature: float, top_k: int = 0, min_p: float = 0.0,
                  top_p: float = 1.0) -> np.ndarray:
     """Filtered, unnormalised probabilities in the reference's order: softmax((l-max)/T)

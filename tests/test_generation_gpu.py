@@ -48,6 +48,34 @@ def test_greedy_generation(model_dirs, name, lengths, n_new, chunk, dtype):
     assert [o.token_ids for o in again] == [o.token_ids for o in outs]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_with_a_repetition_penalty(model_dirs, dtype):
+    """The harness's repetition penalty on the last generated tokens, greedy, beside a request
+    without one (which still runs ahead of the host when it is alone): every token is the first
+    maximum of the plain implementation's penalised logits."""
+    from kestrel_llm_b200 import LLM, SamplingParams
+    prompts = list(R.random_requests(tiny_configs.A["vocab_size"], (9, 21), seed=6).values())
+    llm = LLM(model_dirs["A"][dtype], dtype=dtype, page_size=16, batch_max=4, max_tokens=1024)
+    sps = [SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True, repetition_penalty=1.8, repetition_window=6),
+           SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)]
+    outs = llm.generate(prompts, sps)
+    cfg, W = P.read_model(model_dirs["A"]["float32"])
+    toks, gen = list(prompts[0]), []
+    for got in outs[0].token_ids:
+        logits = P.repetition_penalty(P.forward_logits(cfg, W, toks)[-1], gen, 1.8, 6)
+        want = P.greedy(logits)
+        if got != want:
+            assert float(logits[want] - logits[got]) <= R.TOL[dtype] * float(np.abs(logits).max()), \
+                f"token {got} instead of {want} after {len(gen)} generated tokens"
+        toks.append(got)
+        gen.append(got)
+    _check_greedy(model_dirs["A"]["float32"], prompts[1], outs[1].token_ids, dtype)
+    plain = llm.generate(prompts[:1], SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))[0].token_ids
+    assert plain != outs[0].token_ids, "the penalty changed nothing: the test shows nothing"
+    with pytest.raises(ValueError, match="repetition_window"):
+        SamplingParams(repetition_window=65)
+
+
 def test_temperature_sampling_does_not_depend_on_the_batch(model_dirs):
     """Config B's workload: temperature 0.8, seed 4, 16 tokens, portions of 24 beside decodes.
     A request's tokens are the same alone and in company, and follow the plain sampler fed with

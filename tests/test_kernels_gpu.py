@@ -810,6 +810,33 @@ def test_sample_against_plain_sampler(V, cluster, reps):
     assert uniform_for(5, 3) == uniform_for(5, 3) and uniform_for(5, 3) != uniform_for(5, 4) != uniform_for(6, 4)
 
 
+def test_repetition_penalty_against_the_plain_one():
+    """Rows with and without a penalty, windows shorter and longer than what was generated, a
+    token twice in the window (penalised twice), negative and positive logits, ids outside the
+    vocabulary skipped."""
+    ops = _ops()
+    V, W = 5003, 64
+    rng = np.random.default_rng(8)
+    logits = (rng.normal(size=(5, V)) * 4).astype(np.float32)
+    gens = [list(rng.integers(0, V, size=50)), [7, 7, 9, 7], [], list(rng.integers(0, V, size=10)), [3, V + 5, -2, 4]]
+    gens[0][-3] = gens[0][-1]
+    pens, wins = [1.3, 2.0, 1.5, 1.0, 1.1], [32, 64, 8, 5, 64]
+    hist = np.full((5, W), -1, dtype=np.int32)
+    counts = np.zeros(5, dtype=np.int32)
+    for r, (g, w) in enumerate(zip(gens, wins)):
+        last = [int(x) for x in g[-w:]][::-1]
+        hist[r, :len(last)] = last
+        counts[r] = len(last)
+    dev_logits = torch.from_numpy(logits).to(DEV)
+    ops.repetition_penalty(dev_logits, torch.from_numpy(hist).to(DEV), torch.from_numpy(counts).to(DEV),
+                           torch.tensor(pens, dtype=torch.float32, device=DEV))
+    got = dev_logits.cpu().numpy()
+    for r in range(5):
+        want = P.repetition_penalty(logits[r], [int(x) for x in gens[r]], pens[r], wins[r])
+        np.testing.assert_array_equal(got[r], want)
+    assert (got[3] == logits[3]).all() and (got[1] != logits[1]).sum() == 2
+
+
 @pytest.mark.parametrize("V", [1000, 151936])
 def test_sample_odd_rows(V):
     """Rows that a sampler must not stumble over: all logits equal (every token kept, the draw

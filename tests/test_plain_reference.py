@@ -55,3 +55,26 @@ def test_plain_sampling_filters():
     assert (p > 0).tolist() == [True, True, True, False, False]
     p = P.sample_probs(l, 1.0)
     assert P.sample_from(p, 0.49) == 0 and P.sample_from(p, 0.51) == 1 and P.sample_from(p, 1.0) == 4
+
+
+def test_plain_repetition_penalty_and_its_options(monkeypatch):
+    """A token twice among the last generated ones is penalised twice; positive logits are
+    divided, negative ones multiplied; tokens before the window are left alone.  The command
+    line takes penalty and window from the flags, else from the reference's two environment
+    variables, and ignores values outside the reference's ranges (main.c:3741-3752)."""
+    l = np.array([2.0, -1.0, 4.0, 0.5, -3.0], dtype=np.float32)
+    out = P.repetition_penalty(l, [4, 0, 2, 0, 1], 2.0, 4)
+    np.testing.assert_array_equal(out, np.array([0.5, -2.0, 2.0, 0.5, -3.0], dtype=np.float32))
+    np.testing.assert_array_equal(P.repetition_penalty(l, [0, 1], 1.0, 4), l)
+    from kestrel_llm_b200.cli import _repetition_options, build_parser
+    args = build_parser().parse_args(["--model", "x"])
+    monkeypatch.delenv("VLLM_STREAM_REPPEN", raising=False)
+    monkeypatch.delenv("VLLM_STREAM_REPWIN", raising=False)
+    assert _repetition_options(args) == (1.0, 32)
+    monkeypatch.setenv("VLLM_STREAM_REPPEN", "1.25")
+    monkeypatch.setenv("VLLM_STREAM_REPWIN", "70")          # outside 1..64: the default stays
+    assert _repetition_options(args) == (1.25, 32)
+    args = build_parser().parse_args(["--model", "x", "--repetition-penalty", "1.5", "--repetition-window", "8"])
+    assert _repetition_options(args) == (1.5, 8)
+    args = build_parser().parse_args(["--model", "x", "--repetition-penalty", "0.9"])
+    assert _repetition_options(args) == (1.0, 32)
