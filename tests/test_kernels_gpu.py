@@ -116,6 +116,30 @@ def test_gemm_tcgen05_fallbacks_for_many_tokens(pairs, persistent, tile):
     np.testing.assert_allclose(act.float().cpu().numpy(), ref2, rtol=1e-2, atol=1e-2 * np.abs(ref2).max())
 
 
+def test_gemm_tcgen05_tuning_moves_the_kernel_not_the_result():
+    """The tuning knobs choose among kernels and numbers of K slices; whatever they choose, the
+    product is the same within float32 rounding: CTA pairs already from 65 tokens on, a slice
+    priced at nothing (many slices) or at a fortune (one)."""
+    ops = _ops()
+    T, N, K = 100, 1100, 2048
+    x, xr = _rand((T, K), torch.bfloat16, 51)
+    w, wr = _rand((N, K), torch.bfloat16, 52, 0.05)
+    ref = xr.astype(np.float64) @ wr.astype(np.float64).T
+    seen = set()
+    try:
+        for min_tokens, pair_kb, few_kb in ((128, 12, 6), (64, 12, 6), (64, 0, 6), (64, 1000, 6), (128, 12, 0), (128, 12, 1000)):
+            ops.gemm_tc_set_pair_tuning(min_tokens, pair_kb)
+            ops.gemm_tc_set_tuning(few_kb, 0)
+            out = ops.gemm_tc(x, w)
+            seen.add(out.shape[0])
+            np.testing.assert_allclose(out.sum(0).cpu().numpy(), ref, rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max())
+        assert ops.gemm_tc_error() == 0
+    finally:
+        ops.gemm_tc_set_pair_tuning(128, 12)
+        ops.gemm_tc_set_tuning(6, 2)
+    assert len(seen) > 1, "the knobs never changed the number of slices"
+
+
 def test_gemm_tcgen05_static_weights_wait_for_the_activations():
     """With weights_static the product fetches weight tiles before the kernel in front of it has
     ended; the activations, which that kernel writes, must still be the new ones.  A chain of
