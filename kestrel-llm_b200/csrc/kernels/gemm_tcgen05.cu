@@ -703,6 +703,13 @@ KESTREL_API int kestrel_gemm_tc_splits(int T, int N, int K) {
     return best;
 }
 
+// What `linear` asks before a product, in one call: 0 if the operands do not fit the TMA rules,
+// else the number of K slices the product should be cut into.
+KESTREL_API int kestrel_gemm_tc_plan(const void *x, const void *w, int T, int N, int K, long long ldx, long long ldw) {
+    if (!kestrel_gemm_tc_supported(x, w, T, N, K, ldx, ldw)) return 0;
+    return kestrel_gemm_tc_splits(T, N, K);
+}
+
 template <int BN, int MODE>
 static int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, void *out, int T, int N, int K, int splits,
                      long long slice_stride, long long ldo, int up_off, int early_w, cudaStream_t stream) {

@@ -63,6 +63,7 @@ def _declare(lib) -> None:
         "kestrel_gemm_plain": [_vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
         "kestrel_attention_plain": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _i,
                                     _f, _vp],
+        "kestrel_gemm_tc_plan": [_vp, _vp, _i, _i, _i, _ll, _ll],
         "kestrel_gemm_tc_supported": [_vp, _vp, _i, _i, _i, _ll, _ll],
         "kestrel_gemm_tc_splits": [_i, _i, _i],
         "kestrel_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _ll, _vp],
@@ -123,6 +124,8 @@ def _stream():
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:
+    if t.is_cuda and t.is_contiguous() and (dtype is None or t.dtype == dtype) and (dims is None or t.dim() == dims):
+        return
     if not t.is_cuda:
         raise KernelError(f"{name}: tensor is on {t.device}; the kernels run on a CUDA device only")
     if not t.is_contiguous():
@@ -441,8 +444,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
     product when its tiling rules hold (see `gemm_tc_supported`) and the CUDA-core one
     otherwise."""
     T, N = x.shape[0], w.shape[0]
-    if gemm_tc_supported(x, w):
-        return gemm_tc(x, w, out, weights_static=weights_static)
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2:
+        # one question to the library: do the operands fit, and into how many K slices
+        plan = library().kestrel_gemm_tc_plan(x.data_ptr(), w.data_ptr(), T, N, x.shape[1], x.stride(0), w.stride(0))
+        if plan > 0:
+            return gemm_tc(x, w, out, splits=plan if out is None else None, weights_static=weights_static)
     if out is None:
         out = torch.empty((1, T, N), dtype=torch.float32, device=x.device)
     elif out.dim() == 2:
@@ -455,13 +461,15 @@ def linear_add_into(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) ->
     """residual += x w^T inside the product's epilogue, where the product can do that (bfloat16,
     many tokens, one pass over K); False if it cannot - nothing has run then and the caller takes
     the product as slices."""
-    if x.dtype != torch.bfloat16 or not gemm_tc_supported(x, w):
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
+    _need(x, "linear_add_into.x", torch.bfloat16, 2)
+    _need(w, "linear_add_into.w", torch.bfloat16, 2)
     _need(residual, "linear_add_into.residual", torch.float32, 2)
     T, K = x.shape
     N = w.shape[0]
-    if residual.shape != (T, N):
-        raise KernelError(f"linear_add_into: residual {tuple(residual.shape)} for T={T}, N={N}")
+    if w.shape[1] != K or residual.shape != (T, N):
+        raise KernelError(f"linear_add_into: x {tuple(x.shape)}, w {tuple(w.shape)}, residual {tuple(residual.shape)}")
     rc = library().kestrel_gemm_tc_add(x.data_ptr(), w.data_ptr(), residual.data_ptr(), T, N, K, x.stride(0), w.stride(0),
                                        residual.stride(0), _stream())
     if rc == 1:
