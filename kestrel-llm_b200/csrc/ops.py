@@ -410,6 +410,14 @@ def gemm_tc_set_tuning(overhead_kb: int = -1, ctas_per_sm: int = 0) -> None:
     fn(int(overhead_kb), int(ctas_per_sm))
 
 
+def gemm_tc_set_wide(on: bool = True, more_than_tokens: int = -1) -> None:
+    """Whether products of more than ``more_than_tokens`` (32) and at most 128 tokens take two
+    weight tiles a CTA (the default).  For tests and measurements of the one-tile kernel."""
+    fn = library().kestrel_gemm_tc_set_wide
+    fn.restype, fn.argtypes = None, [_i, _i]
+    fn(1 if on else 0, int(more_than_tokens))
+
+
 def gemm_tc_set_pair_tuning(min_tokens: int = -1, overhead_kb: int = -1) -> None:
     """Tuning of many-token products on CTA pairs: products of more than ``min_tokens`` tokens
     take them; a K slice is priced at ``overhead_kb`` k-blocks beyond its own (see gemm_tcgen05.cu)."""

@@ -140,6 +140,29 @@ def test_gemm_tcgen05_tuning_moves_the_kernel_not_the_result():
     assert len(seen) > 1, "the knobs never changed the number of slices"
 
 
+@pytest.mark.parametrize("T,N,K,splits", [(33, 512, 512, 2), (64, 768, 1096, 3), (65, 256, 520, 1), (100, 1280, 2048, 4), (128, 6144, 1024, 2)])
+def test_gemm_tcgen05_two_weight_tiles_a_cta(T, N, K, splits):
+    """33 to 128 tokens: a CTA takes rows n and N / 2 + n of the weights against one token tile.
+    The same bits as one tile a CTA gives (each output element is the same chain of MMAs), and a
+    width that is no multiple of 256 takes one tile a CTA."""
+    ops = _ops()
+    x, xr = _rand((T, K), torch.bfloat16, T)
+    w, wr = _rand((N, K), torch.bfloat16, N, 0.05)
+    try:
+        ops.gemm_tc_set_wide(False)
+        one = ops.gemm_tc(x, w, splits=splits)
+        ops.gemm_tc_set_wide(True)
+        two = ops.gemm_tc(x, w, splits=splits)
+        odd = ops.gemm_tc(x, w[:N - 128].contiguous(), splits=splits)       # N - 128 is no multiple of 256
+    finally:
+        ops.gemm_tc_set_wide(True)
+    assert ops.gemm_tc_error() == 0
+    assert torch.equal(one, two)
+    assert torch.equal(odd, one[:, :, :N - 128])
+    ref = xr.astype(np.float64) @ wr.astype(np.float64).T
+    np.testing.assert_allclose(two.sum(0).cpu().numpy(), ref, rtol=0, atol=2e-6 * math.sqrt(K) * np.abs(ref).max() + 1e-7)
+
+
 def test_gemm_tcgen05_static_weights_wait_for_the_activations():
     """With weights_static the product fetches weight tiles before the kernel in front of it has
     ended; the activations, which that kernel writes, must still be the new ones.  A chain of
