@@ -269,3 +269,21 @@ def test_command_line(model_dirs):
     ids = [int(t) for t in line[0].split(":", 1)[1].split()]
     assert len(ids) == 6
     _check_greedy(model_dirs["A"]["float32"], [5, 17, 3, 200], ids, "float32")
+    assert "[STREAM] decode mode: greedy (rep_pen=1.000 win=32)" in p.stdout
+    # the reference's environment variable switches the repetition penalty on, a flag overrides the window
+    env = dict(os.environ, VLLM_STREAM_REPPEN="1.7")
+    q = subprocess.run([sys.executable, os.path.join(root, "bin", "kestrel"), "--model", model_dirs["A"]["bfloat16"],
+                        "--stream-test", "--stream-n", "12", "--prompt-ids", "5,17,3,200", "--dtype", "float32",
+                        "--repetition-window", "5"], capture_output=True, text=True, timeout=600, env=env)
+    assert q.returncode == 0, q.stderr[-2000:]
+    assert "[STREAM] decode mode: greedy+reppen (rep_pen=1.700 win=5)" in q.stdout
+    line = [l for l in q.stdout.splitlines() if l.startswith("[STREAM] TOKIDS:")]
+    got = [int(t) for t in line[0].split(":", 1)[1].split()]
+    cfg, W = P.read_model(model_dirs["A"]["float32"])
+    toks, gen = [5, 17, 3, 200], []
+    for g in got:
+        logits = P.repetition_penalty(P.forward_logits(cfg, W, toks)[-1], gen, 1.7, 5)
+        want = P.greedy(logits)
+        assert g == want or float(logits[want] - logits[g]) <= R.TOL["float32"] * float(np.abs(logits).max())
+        toks.append(g)
+        gen.append(g)
