@@ -17,6 +17,7 @@ import numpy as np
 import torch
 
 from ..csrc import build as _build
+from ..csrc import cdecl as _cdecl
 from ..parts.base import CacheSpec, FixedStateSpec, PagedKVSpec
 
 
@@ -35,32 +36,9 @@ def host_library() -> ctypes.CDLL:
     """The native host runtime (cache manager and scheduler), built on first use."""
     global _host
     if _host is None:
-        lib = ctypes.CDLL(_build.build_host())
-        vp, i, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-        ip = ctypes.POINTER(ctypes.c_int)
-        llp = ctypes.POINTER(ctypes.c_longlong)
-        sig = {
-            "kcache_create": (vp, [i, ip, ip, i, i, i]), "kcache_destroy": (None, [vp]),
-            "kcache_admit": (i, [vp, ll]), "kcache_can_reserve": (i, [vp, ll, i]),
-            "kcache_reserve": (i, [vp, ll, i]), "kcache_commit": (i, [vp, ll, i]),
-            "kcache_release": (i, [vp, ll]), "kcache_length": (i, [vp, ll]), "kcache_slot": (i, [vp, ll]),
-            "kcache_num_blocks": (i, [vp, ll, i]), "kcache_block_table": (i, [vp, ll, i, vp, i]),
-            "kcache_describe_decode": (i, [vp, vp, i, i, i, vp, vp, vp, vp, vp]),
-            "kcache_free_pages": (i, [vp, i]), "kcache_num_pages": (i, [vp, i]),
-            "kcache_num_groups": (i, [vp]), "kcache_page_size": (i, [vp]),
-            "kcache_live_requests": (i, [vp]), "kcache_free_slots": (i, [vp]),
-            "kcache_pages_handed_out": (ll, [vp]), "kcache_pages_given_back": (ll, [vp]),
-            "kcache_check": (i, [vp]),
-            "ksched_create": (vp, [vp, i, i, i, i, i]), "ksched_destroy": (None, [vp]),
-            "ksched_add": (i, [vp, ll, i, i]), "ksched_schedule": (i, [vp, llp, ip, ip, ip, i]),
-            "ksched_preempted": (i, [vp, llp, i]), "ksched_step_done": (i, [vp]),
-            "ksched_on_token": (i, [vp, ll]), "ksched_finish": (i, [vp, ll]),
-            "ksched_num_running": (i, [vp]), "ksched_num_waiting": (i, [vp]),
-            "ksched_num_preemptions": (ll, [vp]), "ksched_known": (i, [vp, ll]),
-        }
-        for name, (res, args) in sig.items():
-            fn = getattr(lib, name)
-            fn.restype, fn.argtypes = res, args
+        # global symbols: the kernel library, loaded later, calls the cache manager of this one
+        lib = ctypes.CDLL(_build.build_host(), mode=ctypes.RTLD_GLOBAL)
+        _cdecl.declare(lib, ("kcache_", "ksched_", "kbatch_"))
         _host = lib
     return _host
 
@@ -91,7 +69,8 @@ class PageTable:
         n = len(windows)
         W = (ctypes.c_int * max(1, n))(*windows)
         P = (ctypes.c_int * max(1, n))(*num_pages)
-        self._h = self._lib.kcache_create(n, W, P, page_size, max_requests, max_blocks_per_request)
+        self._h = self._lib.kcache_create(n, ctypes.addressof(W), ctypes.addressof(P), page_size, max_requests,
+                                          max_blocks_per_request)
         if not self._h:
             raise CacheError("cache manager: bad sizes")
         self.page_size = page_size
@@ -176,7 +155,7 @@ class PageTable:
         longest length after the step."""
         bad = ctypes.c_int(0)
         rc = self._lib.kcache_describe_decode(self._h, rids.ctypes.data, rids.shape[0], batch, width, pos.ctypes.data,
-                                              kv.ctypes.data, slot.ctypes.data, tables.ctypes.data, ctypes.byref(bad))
+                                              kv.ctypes.data, slot.ctypes.data, tables.ctypes.data, ctypes.addressof(bad))
         if rc < 0:
             raise CacheError(self._explain(rc, int(rids[bad.value])))
         return rc
@@ -186,6 +165,15 @@ class PageTable:
         row = np.empty(max(n, 1), dtype=np.int32)
         self.block_table_into(rid, group, row)
         return row[:n].tolist()
+
+    def take_admitted(self) -> List[Tuple[int, int]]:
+        """(request, slot) of every admission since the last call, whoever made it (this object's
+        `admit` or the native scheduler): the owner of per-slot device state clears those slots."""
+        cap = self.max_requests + 8
+        ids = (ctypes.c_longlong * cap)()
+        slots = (ctypes.c_int * cap)()
+        n = self._lib.kcache_take_admitted(self._h, ctypes.addressof(ids), ctypes.addressof(slots), cap)
+        return [(int(ids[i]), int(slots[i])) for i in range(min(n, cap))]
 
     def free_pages(self, group: int) -> int:
         return self._lib.kcache_free_pages(self._h, group)
@@ -243,6 +231,7 @@ class CacheManager(PageTable):
         self.groups = [GroupInfo(w, num_pages, tuple(m)) for w, m in zip(windows, members)]
         self.specs = list(specs)
         self.null_page = num_pages
+        self.spare_slot = max_requests
         self.dtype, self.device = dtype, torch.device(device)
         self.k: List[Optional[torch.Tensor]] = []
         self.v: List[Optional[torch.Tensor]] = []
@@ -258,7 +247,9 @@ class CacheManager(PageTable):
             elif isinstance(sp, FixedStateSpec):
                 self.k.append(None)
                 self.v.append(None)
-                self.state.append(torch.zeros((max_requests,) + tuple(sp.shape), dtype=sp.dtype, device=device))
+                # one slot more than there are requests: the spare slot, which padding rows of a
+                # captured step use so that they never touch a live request's state
+                self.state.append(torch.zeros((max_requests + 1,) + tuple(sp.shape), dtype=sp.dtype, device=device))
             else:
                 self.k.append(None)
                 self.v.append(None)
@@ -266,10 +257,21 @@ class CacheManager(PageTable):
 
     def admit(self, rid: int) -> int:
         slot = super().admit(rid)
-        for st in self.state:                 # a new request starts from zero state
-            if st is not None:
-                st[slot].zero_()
+        self.clear_admitted()
         return slot
+
+    def clear_admitted(self) -> None:
+        """A new request starts from zero state: clears the state slot of every request admitted
+        since the last call, by `admit` here or by the native scheduler on its own (a slot that a
+        finished or preempted request left keeps that request's state until then).  The engine
+        calls this before every step."""
+        new = self.take_admitted()
+        if not new or not any(st is not None for st in self.state):
+            return
+        for _rid, slot in new:
+            for st in self.state:
+                if st is not None:
+                    st[slot].zero_()
 
     def layer(self, index: int, writable: bool = True) -> LayerCache:
         return LayerCache(index, self.layer_group[index], self.page_size, self.k[index], self.v[index],

@@ -1,10 +1,11 @@
 """Builds the package's two native libraries in-tree, at first use.
 
+* ``libkestrel_host.so`` - the C++ host runtime under ``csrc/host`` (cache manager, scheduler,
+  packer of a step's description), compiled by g++; it needs no GPU and no CUDA toolkit.
 * ``libkestrel_cuda.so`` - every ``.cu`` under ``csrc/kernels`` compiled by nvcc for sm_100a
   (``-gencode arch=compute_100a,code=sm_100a``); kernels take raw pointers and a stream, so no
-  framework headers are needed and a file compiles in seconds.
-* ``libkestrel_host.so`` - the C++ host runtime under ``csrc/host`` (cache manager,
-  scheduler), compiled by g++; it needs no GPU and no CUDA toolkit.
+  framework headers are needed and a file compiles in seconds.  It holds the step runner too,
+  which calls the cache manager, so it links against ``libkestrel_host.so`` (found beside it).
 
 A library is rebuilt when the hash of its sources changes.  The build folder is
 ``csrc/_build`` inside the package; if the package folder cannot be written (a read-only
@@ -25,6 +26,7 @@ from typing import List
 _HERE = os.path.dirname(os.path.abspath(__file__))
 KERNEL_DIR = os.path.join(_HERE, "kernels")
 HOST_DIR = os.path.join(_HERE, "host")
+HEADER = os.path.join(os.path.dirname(_HERE), "include", "kestrel.h")     # the one C header of both libraries
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
@@ -91,9 +93,10 @@ def _fresh(lib: str, stamp: str, digest: str) -> bool:
 
 def build_cuda(verbose: bool = True) -> str:
     """Path of libkestrel_cuda.so, compiling it if its sources changed."""
-    out = build_dir()
+    host_lib = build_host(verbose)
+    out = os.path.dirname(host_lib)
     srcs = _sources(KERNEL_DIR, (".cu",))
-    deps = srcs + _sources(KERNEL_DIR, (".cuh", ".h"))
+    deps = srcs + _sources(KERNEL_DIR, (".cuh", ".h")) + [HEADER]
     flags = NVCC_FLAGS + os.environ.get("KESTREL_NVCC_EXTRA", "").split()      # e.g. -DAM_KEYS_STAGES=2 for experiments
     digest = _digest(deps, flags)
     lib = os.path.join(out, "libkestrel_cuda.so")
@@ -116,7 +119,8 @@ def build_cuda(verbose: bool = True) -> str:
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
         objs = list(ex.map(one, srcs))
     tmp = lib + f".tmp{os.getpid()}"
-    _run([nvcc, "-shared", "-o", tmp] + objs, "link libkestrel_cuda.so")
+    _run([nvcc, "-shared", "-o", tmp] + objs + ["-L" + out, "-lkestrel_host", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"],
+         "link libkestrel_cuda.so")
     os.replace(tmp, lib)
     for o in objs:
         os.remove(o)
@@ -131,7 +135,7 @@ def build_host(verbose: bool = True) -> str:
     """Path of libkestrel_host.so, compiling it if its sources changed."""
     out = build_dir()
     srcs = _sources(HOST_DIR, (".cpp",))
-    deps = srcs + _sources(HOST_DIR, (".h", ".hpp"))
+    deps = srcs + _sources(HOST_DIR, (".h", ".hpp")) + [HEADER]
     digest = _digest(deps, GXX_FLAGS)
     lib = os.path.join(out, "libkestrel_host.so")
     stamp = lib + ".stamp"

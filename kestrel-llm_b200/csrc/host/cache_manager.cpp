@@ -25,7 +25,7 @@
 #include <unordered_map>
 #include <vector>
 
-#define KAPI extern "C" __attribute__((visibility("default")))
+#include "../../include/kestrel.h"
 
 namespace {
 
@@ -52,6 +52,7 @@ struct Cache {
     std::vector<Group> groups;
     std::vector<int> free_slots;           // stack
     std::unordered_map<long long, Request> live;
+    std::vector<std::pair<long long, int>> admitted;   // (id, slot) of admissions not yet taken by the owner of the device state
     long long pages_handed_out = 0, pages_given_back = 0;
 };
 
@@ -82,7 +83,7 @@ void give_back(Cache &c, int gi, int page) {
 
 }  // namespace
 
-KAPI void *kcache_create(int n_groups, const int *windows, const int *num_pages, int page_size,
+KESTREL_API void *kcache_create(int n_groups, const int *windows, const int *num_pages, int page_size,
                          int max_requests, int max_blocks_per_request) {
     if (n_groups < 0 || page_size <= 0 || max_requests <= 0 || max_blocks_per_request <= 0) return nullptr;
     Cache *c = new Cache();
@@ -102,10 +103,10 @@ KAPI void *kcache_create(int n_groups, const int *windows, const int *num_pages,
     return c;
 }
 
-KAPI void kcache_destroy(void *h) { delete (Cache *)h; }
+KESTREL_API void kcache_destroy(void *h) { delete (Cache *)h; }
 
 // slot of the new request, -1 if no slot is free, -2 if the id is live already
-KAPI int kcache_admit(void *h, long long id) {
+KESTREL_API int kcache_admit(void *h, long long id) {
     Cache &c = *(Cache *)h;
     if (c.live.count(id)) return -2;
     if (c.free_slots.empty()) return -1;
@@ -115,12 +116,28 @@ KAPI int kcache_admit(void *h, long long id) {
     c.free_slots.pop_back();
     r.table.resize(c.groups.size());
     r.first_live.assign(c.groups.size(), 0);
+    const int slot = r.slot;
     c.live.emplace(id, std::move(r));
-    return c.live[id].slot;
+    c.admitted.emplace_back(id, slot);
+    return slot;
+}
+
+// The requests admitted since the last call, whoever admitted them (the caller, or the scheduler
+// on its own): whoever owns per-slot state on the device clears those slots before the next
+// step runs.  Writes up to cap (id, slot) pairs and forgets all of them; returns how many there were.
+KESTREL_API int kcache_take_admitted(void *h, long long *ids, int *slots, int cap) {
+    Cache &c = *(Cache *)h;
+    int n = (int)c.admitted.size();
+    for (int i = 0; i < n && i < cap; ++i) {
+        if (ids) ids[i] = c.admitted[i].first;
+        if (slots) slots[i] = c.admitted[i].second;
+    }
+    c.admitted.clear();
+    return n;
 }
 
 // 1 if reserve(id, n_new) would succeed, 0 if pages are short, negative on misuse
-KAPI int kcache_can_reserve(void *h, long long id, int n_new) {
+KESTREL_API int kcache_can_reserve(void *h, long long id, int n_new) {
     Cache &c = *(Cache *)h;
     auto it = c.live.find(id);
     if (it == c.live.end()) return -3;
@@ -134,7 +151,7 @@ KAPI int kcache_can_reserve(void *h, long long id, int n_new) {
 
 // Pages for positions [length, length + n_new) in every group.  0 = done, -1 = pages short
 // (nothing changed), -3 = unknown request, -4 = longer than max_blocks_per_request allows.
-KAPI int kcache_reserve(void *h, long long id, int n_new) {
+KESTREL_API int kcache_reserve(void *h, long long id, int n_new) {
     Cache &c = *(Cache *)h;
     auto it = c.live.find(id);
     if (it == c.live.end()) return -3;
@@ -168,7 +185,7 @@ KAPI int kcache_reserve(void *h, long long id, int n_new) {
 }
 
 // length += n_new (must be reserved); windowed groups give back what fell out of reach
-KAPI int kcache_commit(void *h, long long id, int n_new) {
+KESTREL_API int kcache_commit(void *h, long long id, int n_new) {
     Cache &c = *(Cache *)h;
     auto it = c.live.find(id);
     if (it == c.live.end()) return -3;
@@ -190,7 +207,7 @@ KAPI int kcache_commit(void *h, long long id, int n_new) {
     return 0;
 }
 
-KAPI int kcache_release(void *h, long long id) {
+KESTREL_API int kcache_release(void *h, long long id) {
     Cache &c = *(Cache *)h;
     auto it = c.live.find(id);
     if (it == c.live.end()) return -3;
@@ -203,19 +220,19 @@ KAPI int kcache_release(void *h, long long id) {
     return 0;
 }
 
-KAPI int kcache_length(void *h, long long id) {
+KESTREL_API int kcache_length(void *h, long long id) {
     Cache &c = *(Cache *)h;
     auto it = c.live.find(id);
     return it == c.live.end() ? -3 : it->second.length;
 }
 
-KAPI int kcache_slot(void *h, long long id) {
+KESTREL_API int kcache_slot(void *h, long long id) {
     Cache &c = *(Cache *)h;
     auto it = c.live.find(id);
     return it == c.live.end() ? -3 : it->second.slot;
 }
 
-KAPI int kcache_num_blocks(void *h, long long id, int group) {
+KESTREL_API int kcache_num_blocks(void *h, long long id, int group) {
     Cache &c = *(Cache *)h;
     auto it = c.live.find(id);
     if (it == c.live.end()) return -3;
@@ -225,7 +242,7 @@ KAPI int kcache_num_blocks(void *h, long long id, int group) {
 
 // copies min(n, blocks) entries of the request's table in `group` (page id, or -1 where the
 // page was given back); pads the rest of `out` with -1; returns the number of blocks
-KAPI int kcache_block_table(void *h, long long id, int group, int *out, int n) {
+KESTREL_API int kcache_block_table(void *h, long long id, int group, int *out, int n) {
     Cache &c = *(Cache *)h;
     auto it = c.live.find(id);
     if (it == c.live.end()) return -3;
@@ -241,7 +258,7 @@ KAPI int kcache_block_table(void *h, long long id, int group, int *out, int n) {
 // positions (the length so far), lengths after the step, state slots, and every group's block
 // table rows [G][B][W] (-1 beyond a request's pages).  Rows n..B-1 are left untouched.  Returns
 // the longest length after the step, or a negative error (then *bad is the request's index).
-KAPI int kcache_describe_decode(void *h, const long long *ids, int n, int B, int W, int *pos, int *kv, int *slot,
+KESTREL_API int kcache_describe_decode(void *h, const long long *ids, int n, int B, int W, int *pos, int *kv, int *slot,
                                 int *tables, int *bad) {
     Cache &c = *(Cache *)h;
     const int G = (int)c.groups.size();
@@ -265,29 +282,30 @@ KAPI int kcache_describe_decode(void *h, const long long *ids, int n, int B, int
     return longest;
 }
 
-KAPI int kcache_free_pages(void *h, int group) {
+KESTREL_API int kcache_free_pages(void *h, int group) {
     Cache &c = *(Cache *)h;
     if (group < 0 || group >= (int)c.groups.size()) return -6;
     return (int)c.groups[group].free_stack.size();
 }
 
-KAPI int kcache_num_pages(void *h, int group) {
+KESTREL_API int kcache_num_pages(void *h, int group) {
     Cache &c = *(Cache *)h;
     if (group < 0 || group >= (int)c.groups.size()) return -6;
     return c.groups[group].num_pages;
 }
 
-KAPI int kcache_num_groups(void *h) { return (int)((Cache *)h)->groups.size(); }
-KAPI int kcache_page_size(void *h) { return ((Cache *)h)->page_size; }
-KAPI int kcache_live_requests(void *h) { return (int)((Cache *)h)->live.size(); }
-KAPI int kcache_free_slots(void *h) { return (int)((Cache *)h)->free_slots.size(); }
-KAPI long long kcache_pages_handed_out(void *h) { return ((Cache *)h)->pages_handed_out; }
-KAPI long long kcache_pages_given_back(void *h) { return ((Cache *)h)->pages_given_back; }
+KESTREL_API int kcache_num_groups(void *h) { return (int)((Cache *)h)->groups.size(); }
+KESTREL_API int kcache_page_size(void *h) { return ((Cache *)h)->page_size; }
+KESTREL_API int kcache_max_blocks(void *h) { return ((Cache *)h)->max_blocks; }
+KESTREL_API int kcache_live_requests(void *h) { return (int)((Cache *)h)->live.size(); }
+KESTREL_API int kcache_free_slots(void *h) { return (int)((Cache *)h)->free_slots.size(); }
+KESTREL_API long long kcache_pages_handed_out(void *h) { return ((Cache *)h)->pages_handed_out; }
+KESTREL_API long long kcache_pages_given_back(void *h) { return ((Cache *)h)->pages_given_back; }
 
 // Invariants: every page of every group is on the free stack exactly once or in exactly one
 // live table exactly once; slots likewise.  0 if they hold, else a negative code that says
 // which one broke.
-KAPI int kcache_check(void *h) {
+KESTREL_API int kcache_check(void *h) {
     Cache &c = *(Cache *)h;
     for (size_t gi = 0; gi < c.groups.size(); ++gi) {
         const Group &g = c.groups[gi];

@@ -26,18 +26,7 @@
 #include <unordered_map>
 #include <vector>
 
-#define KAPI extern "C" __attribute__((visibility("default")))
-
-extern "C" {
-int kcache_admit(void *h, long long id);
-int kcache_can_reserve(void *h, long long id, int n_new);
-int kcache_reserve(void *h, long long id, int n_new);
-int kcache_release(void *h, long long id);
-int kcache_num_pages(void *h, int group);
-int kcache_num_groups(void *h);
-int kcache_page_size(void *h);
-int kcache_free_slots(void *h);
-}
+#include "../../include/kestrel.h"
 
 namespace {
 
@@ -96,7 +85,7 @@ bool preempt_youngest(Sched &s, std::vector<int> &entry_of_running, std::vector<
 
 }  // namespace
 
-KAPI void *ksched_create(void *cache, int max_step_tokens, int prefill_chunk, int batch_max,
+KESTREL_API void *ksched_create(void *cache, int max_step_tokens, int prefill_chunk, int batch_max,
                          int max_queued, int max_model_len) {
     if (!cache || max_step_tokens <= 0 || prefill_chunk <= 0 || batch_max <= 0 || max_model_len <= 0) return nullptr;
     Sched *s = new Sched();
@@ -109,11 +98,11 @@ KAPI void *ksched_create(void *cache, int max_step_tokens, int prefill_chunk, in
     return s;
 }
 
-KAPI void ksched_destroy(void *h) { delete (Sched *)h; }
+KESTREL_API void ksched_destroy(void *h) { delete (Sched *)h; }
 
 // 0 = queued; -1 = waiting queue full; -2 = prompt + max_new_tokens exceeds max_model_len or
 // what the page pool can ever hold; -3 = empty prompt or duplicate id
-KAPI int ksched_add(void *h, long long id, int prompt_len, int max_new_tokens) {
+KESTREL_API int ksched_add(void *h, long long id, int prompt_len, int max_new_tokens) {
     Sched &s = *(Sched *)h;
     if (prompt_len <= 0 || max_new_tokens < 0) return -3;
     for (const Req &r : s.running) if (r.id == id) return -3;
@@ -133,7 +122,7 @@ KAPI int ksched_add(void *h, long long id, int prompt_len, int max_new_tokens) {
 // ids[e]; wants[e] = 1 if the entry ends with the request's last known token, whose logits
 // pick the next token.  Pages for every entry are reserved.  Returns the number of entries
 // (0 = nothing to do), or -7 if the previous step was not completed.
-KAPI int ksched_schedule(void *h, long long *ids_out, int *starts_out, int *counts_out, int *wants_out, int cap) {
+KESTREL_API int ksched_schedule(void *h, long long *ids_out, int *starts_out, int *counts_out, int *wants_out, int cap) {
     Sched &s = *(Sched *)h;
     if (s.step_in_flight) return -7;
     s.preempted.clear();
@@ -228,7 +217,7 @@ KAPI int ksched_schedule(void *h, long long *ids_out, int *starts_out, int *coun
 }
 
 // ids that the last schedule() call sent back to the waiting queue
-KAPI int ksched_preempted(void *h, long long *out, int cap) {
+KESTREL_API int ksched_preempted(void *h, long long *out, int cap) {
     Sched &s = *(Sched *)h;
     int n = std::min(cap, (int)s.preempted.size());
     for (int i = 0; i < n; ++i) out[i] = s.preempted[i];
@@ -237,7 +226,7 @@ KAPI int ksched_preempted(void *h, long long *out, int cap) {
 
 // The step that schedule() built has run: its tokens are in the cache.  The caller commits
 // the cache manager itself (it owns the device side); this only moves the counters.
-KAPI int ksched_step_done(void *h) {
+KESTREL_API int ksched_step_done(void *h) {
     Sched &s = *(Sched *)h;
     for (Req &r : s.running) {
         r.computed += r.scheduled;
@@ -249,7 +238,7 @@ KAPI int ksched_step_done(void *h) {
 
 // A token was sampled for the request: it has one more known token.  Returns 1 if the
 // request has now reached its token limit (the caller finishes it), 0 otherwise.
-KAPI int ksched_on_token(void *h, long long id) {
+KESTREL_API int ksched_on_token(void *h, long long id) {
     Sched &s = *(Sched *)h;
     for (Req &r : s.running)
         if (r.id == id) {
@@ -260,7 +249,7 @@ KAPI int ksched_on_token(void *h, long long id) {
 }
 
 // The request is over (stop token, token limit or abort): pages and slot are given back.
-KAPI int ksched_finish(void *h, long long id) {
+KESTREL_API int ksched_finish(void *h, long long id) {
     Sched &s = *(Sched *)h;
     for (size_t i = 0; i < s.running.size(); ++i)
         if (s.running[i].id == id) {
@@ -276,10 +265,10 @@ KAPI int ksched_finish(void *h, long long id) {
     return -3;
 }
 
-KAPI int ksched_num_running(void *h) { return (int)((Sched *)h)->running.size(); }
-KAPI int ksched_num_waiting(void *h) { return (int)((Sched *)h)->waiting.size(); }
-KAPI long long ksched_num_preemptions(void *h) { return ((Sched *)h)->n_preemptions; }
-KAPI int ksched_known(void *h, long long id) {
+KESTREL_API int ksched_num_running(void *h) { return (int)((Sched *)h)->running.size(); }
+KESTREL_API int ksched_num_waiting(void *h) { return (int)((Sched *)h)->waiting.size(); }
+KESTREL_API long long ksched_num_preemptions(void *h) { return ((Sched *)h)->n_preemptions; }
+KESTREL_API int ksched_known(void *h, long long id) {
     Sched &s = *(Sched *)h;
     for (const Req &r : s.running) if (r.id == id) return r.known;
     for (const Req &r : s.waiting) if (r.id == id) return r.known;

@@ -86,7 +86,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int pos_begin = kv_len - n_tok;             // position of the request's first token of this step
     const int rows_here = min(16, n_tok * G - row0);
     const int *table = p.block_table + (size_t)seq * p.table_stride;
-    const int slice_len = p.slice_len_ptr ? *p.slice_len_ptr : p.slice_len;
+    const int slice_len = attn_slice_len(p);
     const int first_tok = row0 / G, last_tok = (row0 + rows_here - 1) / G;
     int k_hi = min(pos_begin + last_tok + 1, (slice + 1) * slice_len);          // exclusive
     const int k_first = max(p.window > 0 ? max(0, pos_begin + first_tok - p.window + 1) : 0, slice * slice_len);
@@ -407,22 +407,22 @@ KESTREL_API int kestrel_attention_decode_supported(int hd, int page_size) {
     return (hd == 64 || hd == 128) && page_size > 0 && page_size % 8 == 0 && (AD_BN % page_size == 0 || page_size % AD_BN == 0);
 }
 
-// CTAs of the kernel that the GPU's 148 SMs hold at once, by shared memory
+// CTAs of the kernel that the GPU's SMs hold at once, by shared memory
 KESTREL_API int kestrel_attention_decode_slots(int hd) {
     size_t smem = hd == 64 ? decode_smem<64>() : decode_smem<128>();
     int per_sm = (int)((227 * 1024) / (smem + 1024));
-    return 148 * (per_sm < 1 ? 1 : per_sm);
+    return kestrel_sms() * (per_sm < 1 ? 1 : per_sm);
 }
 
 // Tiles of at most 16 rows (tile_seq / tile_row0): decode tokens.  The key range is cut into
-// `slices` slices of slice_len keys, a multiple of 64 - or the value at slice_len_ptr on the
-// device - which are merged in ascending order; part_o / part_ml are scratch of T * nq * slices
-// * hd and T * nq * slices * 2 floats.  cache_pages is the number of pages the cache tensors hold.
+// `slices` slices of slice_len keys, a multiple of 64 - or a length that follows the longest
+// request at max_kv_ptr on the device - which are merged in ascending order; part_o / part_ml
+// are scratch of T * nq * slices * hd and T * nq * slices * 2 floats.  cache_pages is the number of pages the cache tensors hold.
 KESTREL_API int kestrel_attention_decode(const void *q, const void *k_cache, const void *v_cache, void *out,
                                          float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
                                          int tiles, const int *cu_seqlens, const int *kv_lens, const int *block_table,
                                          int table_width, int table_stride, int page_size, int cache_pages, int T, int nq,
-                                         int nkv, int hd, int window, int slices, int slice_len, const int *slice_len_ptr,
+                                         int nkv, int hd, int window, int slices, int slice_len, const int *max_kv_ptr,
                                          float scale, cudaStream_t stream) {
     if (T == 0 || tiles == 0) return 0;
     KESTREL_REQUIRE(kestrel_attention_decode_supported(hd, page_size),
@@ -444,7 +444,7 @@ KESTREL_API int kestrel_attention_decode(const void *q, const void *k_cache, con
     p.out = (__nv_bfloat16 *)out; p.part_o = part_o; p.part_ml = part_ml; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
     p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.block_table = block_table; p.table_width = table_width;
     p.table_stride = table_stride; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window;
-    p.slices = slices; p.slice_len = slice_len; p.slice_len_ptr = slice_len_ptr;
+    p.slices = slices; p.slice_len = slice_len; p.max_kv_ptr = max_kv_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
     // up to AD_MAX_CLUSTER slices are merged inside the kernel by a cluster; more go through scratch
     const bool cluster = slices > 1 && slices <= AD_MAX_CLUSTER;

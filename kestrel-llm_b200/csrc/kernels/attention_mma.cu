@@ -68,7 +68,7 @@ attention_mma_kernel(const AttnParams p) {
     const int n_rows = n_tok * G;
     const int rows_here = min(BM, n_rows - row0);
     const int *table = p.block_table + (size_t)seq * p.table_stride;
-    const int slice_len = p.slice_len_ptr ? *p.slice_len_ptr : p.slice_len;
+    const int slice_len = attn_slice_len(p);
 
     // key range of this CTA: what its rows may see, cut to the slice, on 64-key tile boundaries
     const int first_tok = row0 / G, last_tok = (row0 + rows_here - 1) / G;
@@ -476,25 +476,26 @@ KESTREL_API int kestrel_attention_merge(const float *part_o, const float *part_m
 // rows (token, head) of a ROWS-mode tile for this head size
 KESTREL_API int kestrel_attention_mma_rows_per_tile(int hd) { return hd <= 128 ? 64 * AM_ROWS_MT : 64; }
 
-// CTAs of the KEYS-mode kernel that the GPU's 148 SMs hold at once, by shared memory and threads
+// CTAs of the KEYS-mode kernel that the GPU's SMs hold at once, by shared memory and threads
 KESTREL_API int kestrel_attention_mma_slots(int hd) {
     int HD = hd <= 32 ? 32 : hd <= 64 ? 64 : hd <= 128 ? 128 : 256;
     size_t smem = (size_t)(16 + 2 * AM_KEYS_STAGES * AM_BN) * (HD + 8) * 2 + 1024;
     int per_sm = (int)((227 * 1024) / smem);
     if (per_sm > 2048 / AM_THREADS) per_sm = 2048 / AM_THREADS;
     if (per_sm < 1) per_sm = 1;
-    return 148 * per_sm;
+    return kestrel_sms() * per_sm;
 }
 
 // rows_per_tile must be 16 (KEYS mode) or 64 (ROWS mode); tile_seq / tile_row0 describe the
 // tiles.  part_o / part_ml are scratch for slices > 1: float32 [T * nq * slices * hd] and
-// [T * nq * slices * 2].  slice_len_ptr, if given, points to the slice length on the device (a
-// multiple of 64) and overrides slice_len, so that a captured launch can follow the context.
+// [T * nq * slices * 2].  max_kv_ptr, if given, points to the longest request's length on the
+// device; the slice length then follows it instead of slice_len, so that a captured launch can
+// follow the context.
 KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const void *v_cache, void *out,
                                       float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
                                       int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens,
                                       const int *block_table, int table_stride, int page_size, int T, int nq,
-                                      int nkv, int hd, int window, int slices, int slice_len, const int *slice_len_ptr,
+                                      int nkv, int hd, int window, int slices, int slice_len, const int *max_kv_ptr,
                                       float scale, cudaStream_t stream) {
     if (T == 0 || tiles == 0) return 0;
     KESTREL_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_mma: %d query heads over %d kv heads", nq, nkv);
@@ -510,7 +511,7 @@ KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const 
     p.out = (__nv_bfloat16 *)out; p.part_o = part_o; p.part_ml = part_ml; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
     p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.block_table = block_table; p.table_stride = table_stride;
     p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = slices; p.slice_len = slice_len;
-    p.slice_len_ptr = slice_len_ptr;
+    p.max_kv_ptr = max_kv_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
     bool keys = rows_per_tile == 16;
     int rc;

@@ -132,7 +132,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     // blocks are handed out in the order of blockIdx.x: the kv heads of a tile follow each other and
     // late tiles, which see the most keys, come first - across all kv heads
     const int kvh = blockIdx.x % p.nkv, tile = (int)(gridDim.x / p.nkv) - 1 - (int)(blockIdx.x / p.nkv), slice = blockIdx.z;
-    const int slice_len = p.slice_len_ptr ? *p.slice_len_ptr : p.slice_len;
+    const int slice_len = attn_slice_len(p);
     const int seq = p.tile_seq[tile], row0 = p.tile_row0[tile];
     const int G = p.nq / p.nkv;
     const int tok_begin = p.cu_seqlens[seq], n_tok = p.cu_seqlens[seq + 1] - tok_begin;
@@ -450,26 +450,18 @@ KESTREL_API int kestrel_attention_tc_supported(int hd, int page_size) {
 }
 
 // CTAs of this kernel that run at once: one per SM (shared memory and the 512 TMEM columns)
-KESTREL_API int kestrel_attention_tc_slots(void) {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        sms = n;
-    }
-    return sms;
-}
+KESTREL_API int kestrel_attention_tc_slots(void) { return kestrel_sms(); }
 
 // Tiles of rows_per_tile rows, up to 256 (tile_seq / tile_row0 list them), head size 128;
 // cache_pages is the number of pages the cache tensors hold.  With slices > 1 (few tiles far
-// into a long context) every CTA takes a slice of slice_len keys, a multiple of 128 - or the
-// value at slice_len_ptr on the device - and the slices are merged in ascending order;
+// into a long context) every CTA takes a slice of slice_len keys, a multiple of 128 - or of a
+// length that follows the longest request at max_kv_ptr on the device - and the slices are merged in ascending order;
 // part_o / part_ml are scratch of T * nq * slices * 128 and T * nq * slices * 2 floats.
 KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const void *v_cache, void *out,
                                      float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
                                      int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table,
                                      int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd,
-                                     int window, int slices, int slice_len, const int *slice_len_ptr, float scale,
+                                     int window, int slices, int slice_len, const int *max_kv_ptr, float scale,
                                      cudaStream_t stream) {
     if (T == 0 || tiles == 0) return 0;
     KESTREL_REQUIRE(hd == AT_HD, "attention_tc: head size %d; this kernel is built for %d", hd, AT_HD);
@@ -491,7 +483,7 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
     p.out = (__nv_bfloat16 *)out; p.part_o = part_o; p.part_ml = part_ml; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
     p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.block_table = block_table; p.table_width = table_width; p.table_stride = table_stride;
     p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = slices; p.slice_len = slice_len;
-    p.slice_len_ptr = slice_len_ptr;
+    p.max_kv_ptr = max_kv_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
     size_t smem = 12 * AT_PANEL + 8 * B_COUNT + 16 + 2 * 768 * 4 + 1024;
     static bool attr_set = false;

@@ -11,11 +11,17 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#define KESTREL_API extern "C" __attribute__((visibility("default")))
-
-enum { KESTREL_F32 = 0, KESTREL_BF16 = 1 };
+// every exported entry point is declared in the package's one C header; a definition that
+// differs from its declaration there does not compile
+#include "../../include/kestrel.h"
 
 int kestrel_fail(int code, const char *fmt, ...);
+// multiprocessors of the current device (cost models and grids size themselves by it); a
+// B200's 148 where no device can be asked, as when a cost model is called on a host without one
+static inline int kestrel_sms() {
+    int n = kestrel_sm_count();
+    return n > 0 ? n : 148;
+}
 int kestrel_check_launch(const char *what);
 
 #define KESTREL_REQUIRE(cond, ...)                       \

@@ -253,21 +253,25 @@ KESTREL_API int kestrel_swiglu(const float *partial, int S, long long slice_stri
 //   q head : + bias, per-head RMSNorm (if q_norm_w), rotation, -> q_out [T, nq*hd]
 //   k head : + bias, per-head RMSNorm (if k_norm_w), rotation, -> K page slot of the token
 //   v head : + bias                                           -> V page slot of the token
-// Rotation pairs dimension j with j + rot/2 inside the first `rot` dimensions of a head
-// (rot = head size for Qwen3); angle = (float)pos * inv_freq[j], cosf/sinf in float32.
+// Rotation turns pairs of dimensions inside the first `rot` dimensions of a head (rot = head size
+// for Qwen3) by angle = (float)pos * inv_freq[j], cosf/sinf in float32, both multiplied by
+// rot_scale (1 for Qwen3).  rot_mode 0 pairs dimension j with j + rot/2 (rotate-half, the
+// reference's pairing, st.c:8963-8989); rot_mode 1 pairs 2j with 2j + 1 (interleaved).
 // The page of a token is block_table[seq, pos / page_size]; cache planes are laid out
 // [page][kv_head][slot][hd].  One warp per (token, head).
 // ------------------------------------------------------------------------------------------
-#define PREP_MAX_PER_LANE 8   // head size up to 512
+#define PREP_MAX_PER_LANE 8   // head size up to 8 * 32 = 256
 
 // rotation when half the rotary size is HP * 32: the pair (j, j + half) sits in registers c and c + HP
 template <int HP>
-__device__ __forceinline__ void rotate_in_registers(float *x, int pos, const float *__restrict__ inv_freq, int lane) {
+__device__ __forceinline__ void rotate_in_registers(float *x, int pos, const float *__restrict__ inv_freq, int lane, float rot_scale) {
 #pragma unroll
     for (int c = 0; c < HP; ++c) {
         float ang = (float)pos * inv_freq[lane + 32 * c];
         float sn, cs;
         sincosf(ang, &sn, &cs);
+        sn *= rot_scale;
+        cs *= rot_scale;
         float lo = x[c], hi = x[c + HP];
         x[c] = lo * cs - hi * sn;
         x[c + HP] = hi * cs + lo * sn;
@@ -278,7 +282,7 @@ template <typename T>
 __global__ void attn_prepare_kernel(const float *__restrict__ partial, int S, size_t slice_stride,
                                     const float *__restrict__ bias, const float *__restrict__ q_norm_w,
                                     const float *__restrict__ k_norm_w, float norm_eps,
-                                    const float *__restrict__ inv_freq, int rot,
+                                    const float *__restrict__ inv_freq, int rot, int rot_mode, float rot_scale,
                                     const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                                     const int *__restrict__ block_table, int table_stride, int page_size,
                                     T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out,
@@ -343,13 +347,14 @@ __global__ void attn_prepare_kernel(const float *__restrict__ partial, int S, si
     int pos = positions[t];
     if ((is_q || is_k) && rot > 0) {
         int half = rot >> 1;
-        if ((half & 31) == 0) {
+        if (rot_mode == 0 && (half & 31) == 0 && half <= 128) {
             // element lane + 32 c pairs with lane + 32 (c + half / 32): both are in this lane
+            // (half = 32, 64, 96 or 128: the entry point refuses head sizes beyond 256)
             switch (half >> 5) {
-                case 1: rotate_in_registers<1>(x, pos, inv_freq, lane); break;
-                case 2: rotate_in_registers<2>(x, pos, inv_freq, lane); break;
-                case 3: rotate_in_registers<3>(x, pos, inv_freq, lane); break;
-                default: rotate_in_registers<4>(x, pos, inv_freq, lane); break;
+                case 1: rotate_in_registers<1>(x, pos, inv_freq, lane, rot_scale); break;
+                case 2: rotate_in_registers<2>(x, pos, inv_freq, lane, rot_scale); break;
+                case 3: rotate_in_registers<3>(x, pos, inv_freq, lane, rot_scale); break;
+                case 4: rotate_in_registers<4>(x, pos, inv_freq, lane, rot_scale); break;
             }
         } else {
             // the partner lives in another lane: exchange through a per-warp row of shared memory
@@ -365,12 +370,16 @@ __global__ void attn_prepare_kernel(const float *__restrict__ partial, int S, si
             for (int c = 0; c < PREP_MAX_PER_LANE; ++c) {
                 int i = lane + 32 * c;
                 if (i < rot) {
-                    int j = i < half ? i : i - half;
+                    // pair index j; its first member `lo`, its second `hi`
+                    int j = rot_mode == 0 ? (i < half ? i : i - half) : (i >> 1);
+                    bool first = rot_mode == 0 ? i < half : !(i & 1);
                     float ang = (float)pos * inv_freq[j];
                     float sn, cs;
                     sincosf(ang, &sn, &cs);
-                    float lo = st[j], hi = st[j + half];
-                    x[c] = i < half ? lo * cs - hi * sn : hi * cs + lo * sn;
+                    sn *= rot_scale;
+                    cs *= rot_scale;
+                    float lo = rot_mode == 0 ? st[j] : st[2 * j], hi = rot_mode == 0 ? st[j + half] : st[2 * j + 1];
+                    x[c] = first ? lo * cs - hi * sn : hi * cs + lo * sn;
                 }
             }
         }
@@ -405,7 +414,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice_stride,
                           const float *__restrict__ bias, const float *__restrict__ q_norm_w,
-                          const float *__restrict__ k_norm_w, float norm_eps, const float *__restrict__ inv_freq,
+                          const float *__restrict__ k_norm_w, float norm_eps, const float *__restrict__ inv_freq, float rot_scale,
                           const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                           const int *__restrict__ block_table, int table_stride, int page_size,
                           T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out,
@@ -421,8 +430,8 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
         float ang = (float)pos * inv_freq[threadIdx.x];
         float sn, cs;
         sincosf(ang, &sn, &cs);
-        cs_s[threadIdx.x] = cs;
-        sn_s[threadIdx.x] = sn;
+        cs_s[threadIdx.x] = cs * rot_scale;
+        sn_s[threadIdx.x] = sn * rot_scale;
     }
     __syncthreads();
     int heads = nq + 2 * nkv;
@@ -474,7 +483,7 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
 
 KESTREL_API int kestrel_attn_prepare(const float *partial, int S, long long slice_stride,
                                      const float *bias, const float *q_norm_w, const float *k_norm_w,
-                                     float norm_eps, const float *inv_freq, int rot,
+                                     float norm_eps, const float *inv_freq, int rot, int rot_mode, float rot_scale,
                                      const int *positions, const int *seq_of_token,
                                      const int *block_table, int table_stride, int page_size,
                                      void *k_cache, void *v_cache, void *q_out, int dtype, int T,
@@ -483,32 +492,33 @@ KESTREL_API int kestrel_attn_prepare(const float *partial, int S, long long slic
     KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0, "attn_prepare: bad sizes");
     KESTREL_REQUIRE(hd <= 32 * PREP_MAX_PER_LANE, "attn_prepare: head size %d exceeds %d", hd, 32 * PREP_MAX_PER_LANE);
     KESTREL_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "attn_prepare: rotary size %d does not fit head size %d", rot, hd);
+    KESTREL_REQUIRE(rot_mode == 0 || rot_mode == 1, "attn_prepare: rotation mode %d is neither 0 (rotate-half) nor 1 (interleaved)", rot_mode);
     KESTREL_REQUIRE(page_size > 0, "attn_prepare: page size %d", page_size);
     long long warps = (long long)T * (nq + 2 * nkv);
     unsigned blocks = (unsigned)((warps + 3) / 4);
-    bool fast = hd == 128 && rot == 128 && slice_stride % 4 == 0 && (nq + 2 * nkv + 7) / 8 <= 65535 &&
+    bool fast = hd == 128 && rot == 128 && rot_mode == 0 && slice_stride % 4 == 0 && (nq + 2 * nkv + 7) / 8 <= 65535 &&
                 ((((uintptr_t)partial | (uintptr_t)bias | (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)q_out |
                    (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0);
     if (fast) {
         dim3 grid(T, (nq + 2 * nkv + 7) / 8);
         if (dtype == KESTREL_F32)
             kestrel_launch(attn_prepare_hd128_kernel<float>, grid, dim3(256), 0, stream, partial, S, (size_t)slice_stride, bias, q_norm_w,
-                           k_norm_w, norm_eps, inv_freq, positions, seq_of_token, block_table, table_stride, page_size,
+                           k_norm_w, norm_eps, inv_freq, rot_scale, positions, seq_of_token, block_table, table_stride, page_size,
                            (float *)k_cache, (float *)v_cache, (float *)q_out, nq, nkv, write_kv);
         else if (dtype == KESTREL_BF16)
             kestrel_launch(attn_prepare_hd128_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, partial, S, (size_t)slice_stride, bias,
-                           q_norm_w, k_norm_w, norm_eps, inv_freq, positions, seq_of_token, block_table, table_stride, page_size,
+                           q_norm_w, k_norm_w, norm_eps, inv_freq, rot_scale, positions, seq_of_token, block_table, table_stride, page_size,
                            (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, nq, nkv, write_kv);
         else
             return kestrel_fail(-2, "attn_prepare: unknown dtype %d", dtype);
         return kestrel_check_launch("attn_prepare");
     }
     if (dtype == KESTREL_F32)
-        kestrel_launch(attn_prepare_kernel<float>, dim3(blocks), dim3(128), 0, stream, partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, positions,
+        kestrel_launch(attn_prepare_kernel<float>, dim3(blocks), dim3(128), 0, stream, partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, rot_mode, rot_scale, positions,
             seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache,
             (float *)q_out, T, nq, nkv, hd, write_kv);
     else if (dtype == KESTREL_BF16)
-        kestrel_launch(attn_prepare_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, positions,
+        kestrel_launch(attn_prepare_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, partial, S, (size_t)slice_stride, bias, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, rot_mode, rot_scale, positions,
             seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)k_cache,
             (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, T, nq, nkv, hd, write_kv);
     else

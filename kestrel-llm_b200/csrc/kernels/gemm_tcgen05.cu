@@ -670,7 +670,7 @@ KESTREL_API void kestrel_gemm_tc_set_tuning(int overhead_kb, int ctas_per_sm) {
 }
 
 // Slices into which a product of T tokens and N output features splits its K range: the
-// number that minimises waves x (overhead + k-blocks per slice) over the GPU's 148 SMs.
+// number that minimises waves x (overhead + k-blocks per slice) over the GPU's SMs.
 // Many-token products are not split.
 // 33 to 128 tokens: the token tile is half as large as the weight tile or as large, so a third to
 // a half of what an SM takes in is the same activations for every CTA.  A CTA then takes two
@@ -683,18 +683,19 @@ static bool tc_wide(int T, int N) { return g_wide && T > g_wide_min && T <= 128 
 
 KESTREL_API int kestrel_gemm_tc_splits(int T, int N, int K) {
     if (T > g_pair_min_tokens) {
-        // many tokens on CTA pairs: tiles of 256 x 256 over 74 pairs.  A slice costs about
+        // many tokens on CTA pairs: tiles of 256 x 256 over the pairs of SMs.  A slice costs about
         // g_pair_overhead_kb k-blocks beyond its own (pipeline fill, the last tile's epilogue, its
         // float32 plane written and read back); K is cut only where that fills idle pairs.
         if (!g_pairs || !g_persistent) return 1;
         long long tiles = (long long)((N + 255) / 256) * ((T + TCP_BN - 1) / TCP_BN);
         int total_kb = (K + TC_BK - 1) / TC_BK;
+        const int pairs = kestrel_sms() / 2;
         int best = 1;
         long long best_cost = -1;
         for (int s = 1; s <= 8; ++s) {
             int per = (total_kb + s - 1) / s;
             if (s > 1 && (per < 16 || (total_kb + per - 1) / per != s)) continue;
-            long long waves = (tiles * s + 73) / 74;
+            long long waves = (tiles * s + pairs - 1) / pairs;
             long long cost = waves * (g_pair_overhead_kb + per);
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
         }
@@ -704,7 +705,7 @@ KESTREL_API int kestrel_gemm_tc_splits(int T, int N, int K) {
     const bool wide = tc_wide(T, N);
     long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn) / (wide ? 2 : 1);
     int total_kb = (K + TC_BK - 1) / TC_BK;
-    int slots = 148 * (bn <= 64 && !wide ? g_ctas_per_sm : 1);          // wider token tiles take an SM's shared memory alone
+    int slots = kestrel_sms() * (bn <= 64 && !wide ? g_ctas_per_sm : 1);          // wider token tiles take an SM's shared memory alone
     int best = 1;
     long long best_cost = -1;
     int max_s = total_kb / 4 > 0 ? total_kb / 4 : 1;          // at least 4 k-blocks (256 columns) a slice
@@ -772,7 +773,8 @@ static int launch_tc_persistent(const CUtensorMap &mw, const CUtensorMap &mx, vo
     int tiles_n = (N + TC_BM - 1) / TC_BM, tiles_t = (T + BN - 1) / BN;
     long long total = (long long)tiles_n * tiles_t;
     if (total > 0x7fffffff) return kestrel_fail(-2, "gemm_tc: too many tiles");
-    int grid = total < 148 ? (int)total : 148;
+    const int sms = kestrel_sms();
+    int grid = total < sms ? (int)total : sms;
     kestrel_launch(gemm_tc_persistent_kernel<BN, MODE>, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, out, T, N, K, ldo,
                    stages, up_off, tiles_n, (int)total);
     return kestrel_check_launch("gemm_tc_persistent");
@@ -800,7 +802,7 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
     if (max_clusters < 0) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return kestrel_fail(-3, "gemm_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-        cfg.gridDim = dim3(148);
+        cfg.gridDim = dim3(kestrel_sms());
         int n = 0;
         e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<MODE>, &cfg);
         if (e != cudaSuccess || n < 1) {

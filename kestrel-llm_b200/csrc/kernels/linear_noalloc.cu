@@ -4,13 +4,7 @@
 #include "linear_noalloc.h"
 #include "common.cuh"
 
-// entry points of the other translation units that do the work
-extern "C" int kestrel_gemm_tc_supported(const void *x, const void *w, int T, int N, int K, long long ldx, long long ldw);
-extern "C" int kestrel_gemm_tc_splits(int T, int N, int K);
-extern "C" int kestrel_gemm_tc(const void *x, const void *w, float *out, int T, int N, int K, long long ldx,
-                               long long ldw, long long ldo, int splits, long long slice_stride, cudaStream_t stream);
-extern "C" int kestrel_reduce_partials(const float *partial, int S, long long slice_stride, const float *bias,
-                                       void *out, int out_dtype, int T, int width, cudaStream_t stream);
+// (the entry points of the other translation units that do the work are declared in kestrel.h)
 
 #define NOALLOC_FLOATS (KESTREL_NOALLOC_SCRATCH_BYTES / sizeof(float))
 #define NOALLOC_MAX_DEVICES 64

@@ -35,6 +35,31 @@ KESTREL_API int kestrel_device_arch(void) {
     return major * 10 + minor;
 }
 
+// Streaming multiprocessors of the current device, asked once per device; cost models and grids
+// size themselves by it.
+KESTREL_API int kestrel_sm_count(void) {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return kestrel_fail(-3, "no CUDA device");
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+        return kestrel_fail(-3, "cannot read the device's multiprocessor count");
+    if (dev >= 0 && dev < 64) cached[dev] = n;
+    return n;
+}
+
+// Error words of all kernels with bounded waits in one call: bit 0 the tensor-core product,
+// bit 1 the prompt-portion attention, bit 2 the decode attention.  Synchronises the device and
+// clears the words.
+KESTREL_API int kestrel_kernel_errors(void) {
+    int bits = 0;
+    if (kestrel_gemm_tc_error() != 0) bits |= 1;
+    if (kestrel_attention_tc_error() != 0) bits |= 2;
+    if (kestrel_attention_decode_error() != 0) bits |= 4;
+    return bits;
+}
+
 // ------------------------------------------------------------------------------------------
 // What the kernels' bounded waits do when nothing ever arrives: one block waits on an mbarrier
 // that no one completes, with the same wait the tensor-core kernels use.  The wait gives up

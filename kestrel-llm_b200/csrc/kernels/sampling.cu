@@ -522,7 +522,7 @@ static int sample_cluster_shape(int V, int R, int *slice, int *store_p) {
         bool last = cl == SC_MAX_CLUSTER;
         if (!last && S > 8192) continue;               // more CTAs while a slice is long
         // many rows: two CTAs on an SM, if leaving the probabilities out lets them fit
-        bool crowded = (long long)R * cl > 148 && (size_t)S * 8 > 100 * 1024 && (size_t)S * 4 <= 100 * 1024;
+        bool crowded = (long long)R * cl > kestrel_sms() && (size_t)S * 8 > 100 * 1024 && (size_t)S * 4 <= 100 * 1024;
         if (!crowded && (size_t)S * 8 <= SC_SMEM_LIMIT) { *slice = S; *store_p = 1; return cl; }
         if ((size_t)S * 4 <= SC_SMEM_LIMIT) { *slice = S; *store_p = 0; return cl; }
     }

@@ -14,6 +14,7 @@ from typing import Optional
 import torch
 
 from . import build as _build
+from . import cdecl as _cdecl
 
 F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
@@ -32,10 +33,11 @@ def library() -> ctypes.CDLL:
     if _lib is None:
         path = _build.build_cuda()
         try:
+            # the kernel library calls the host runtime (cache manager), which is found beside it
+            ctypes.CDLL(_build.build_host(verbose=False), mode=ctypes.RTLD_GLOBAL)
             lib = ctypes.CDLL(path)
         except OSError as e:
             raise KernelError(f"cannot load {path}: {e}") from None
-        lib.kestrel_last_error.restype = ctypes.c_char_p
         _declare(lib)
         _lib = lib
         if os.environ.get("KESTREL_PDL", "1") == "0":      # for A/B measurements only
@@ -52,49 +54,8 @@ _vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_fl
 
 
 def _declare(lib) -> None:
-    sig = {
-        "kestrel_device_arch": [],
-        "kestrel_embed": [_vp, _i, _vp, _vp, _i, _i, _vp],
-        "kestrel_add_rmsnorm": [_vp, _vp, _i, _ll, _vp, _vp, _vp, _f, _vp, _i, _i, _i, _i, _vp],
-        "kestrel_swiglu": [_vp, _i, _ll, _vp, _i, _i, _i, _vp],
-        "kestrel_attn_prepare": [_vp, _i, _ll, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _vp, _i, _i,
-                                 _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
-        "kestrel_reduce_partials": [_vp, _i, _ll, _vp, _vp, _i, _i, _i, _vp],
-        "kestrel_gemm_plain": [_vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
-        "kestrel_attention_plain": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _i,
-                                    _f, _vp],
-        "kestrel_gemm_tc_plan": [_vp, _vp, _i, _i, _i, _ll, _ll],
-        "kestrel_gemm_tc_supported": [_vp, _vp, _i, _i, _i, _ll, _ll],
-        "kestrel_gemm_tc_splits": [_i, _i, _i],
-        "kestrel_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _ll, _vp],
-        "kestrel_gemm_tc_w": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _ll, _i, _vp],
-        "kestrel_gemm_tc_swiglu": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
-        "kestrel_gemm_tc_swiglu_w": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp],
-        "kestrel_gemm_tc_add": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
-        "kestrel_gemm_tc_error": [],
-        "kestrel_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                                  _i, _i, _i, _i, _vp, _f, _vp],
-        "kestrel_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
-                                 _i, _i, _i, _i, _vp, _f, _vp],
-        "kestrel_attention_tc_supported": [_i, _i],
-        "kestrel_attention_tc_slots": [],
-        "kestrel_attention_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                     _i, _i, _i, _i, _i, _vp, _f, _vp],
-        "kestrel_attention_decode_supported": [_i, _i],
-        "kestrel_attention_decode_slots": [_i],
-        "kestrel_attention_decode_cluster_slices": [],
-        "kestrel_attention_decode_error": [],
-        "kestrel_attention_tc_error": [],
-        "kestrel_attention_mma_slots": [_i],
-        "kestrel_attention_mma_rows_per_tile": [_i],
-        "kestrel_argmax": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp],
-        "kestrel_argmax_chunks": [_i],
-        "kestrel_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
-    }
-    for name, args in sig.items():
-        fn = getattr(lib, name)
-        fn.argtypes = args
-        fn.restype = _i
+    """Argument and result types of every exported function, from the package's C header."""
+    _cdecl.declare(lib, ("kestrel_", "kprog_", "krunner_"))
 
 
 launches = 0     # kernels launched through this module since import (graph replays are counted by their runner)
@@ -145,7 +106,6 @@ def _code(t: torch.Tensor, name: str) -> int:
 def set_pdl(on: bool) -> None:
     """Programmatic dependent launch for all kernels of the library (default on)."""
     fn = library().kestrel_set_pdl
-    fn.restype, fn.argtypes = None, [_i]
     fn(1 if on else 0)
 
 
@@ -244,8 +204,10 @@ def attn_prepare(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: Opti
                  norm_eps: float, inv_freq: Optional[torch.Tensor], rotary_dim: int,
                  positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                  page_size: int, k_cache: torch.Tensor, v_cache: torch.Tensor, q_out: torch.Tensor,
-                 nq: int, nkv: int, hd: int, write_kv: bool = True) -> None:
-    """Bias, per-head RMSNorm, rotation; q to q_out, K and V into their cache pages."""
+                 nq: int, nkv: int, hd: int, write_kv: bool = True, rot_mode: int = 0, rot_scale: float = 1.0) -> None:
+    """Bias, per-head RMSNorm, rotation; q to q_out, K and V into their cache pages.  ``rot_mode``
+    0 pairs dimension j with j + rotary_dim / 2 (rotate-half), 1 pairs 2j with 2j + 1
+    (interleaved); ``rot_scale`` multiplies cos and sin."""
     _need(q_out, "attn_prepare.q_out", dims=2)
     _need(positions, "attn_prepare.positions", torch.int32, 1)
     _need(seq_of_token, "attn_prepare.seq_of_token", torch.int32, 1)
@@ -259,7 +221,7 @@ def attn_prepare(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: Opti
         raise KernelError("attn_prepare: rotation asked for without frequencies")
     _check(library().kestrel_attn_prepare(
         qkv.data.data_ptr(), qkv.slices, qkv.slice_stride, _p(qkv.bias), _p(q_norm_w), _p(k_norm_w),
-        float(norm_eps), _p(inv_freq), int(rotary_dim), positions.data_ptr(), seq_of_token.data_ptr(),
+        float(norm_eps), _p(inv_freq), int(rotary_dim), int(rot_mode), float(rot_scale), positions.data_ptr(), seq_of_token.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), int(page_size), k_cache.data_ptr(),
         v_cache.data_ptr(), q_out.data_ptr(), _code(q_out, "attn_prepare.q_out"), T, nq, nkv, hd,
         1 if write_kv else 0, _stream()))
@@ -339,7 +301,6 @@ def repetition_penalty(logits: torch.Tensor, history: torch.Tensor, counts: torc
     if history.shape[0] != R or counts.shape[0] != R or penalty.shape[0] != R:
         raise KernelError("repetition_penalty: one row of history, one count and one penalty per row of logits")
     fn = library().kestrel_repetition_penalty
-    fn.restype, fn.argtypes = _i, [_vp, _ll, _i, _i, _vp, _i, _vp, _vp, _vp]
     _check(fn(logits.data_ptr(), logits.stride(0), R, V, history.data_ptr(), history.shape[1], counts.data_ptr(),
               penalty.data_ptr(), _stream()))
 
@@ -348,7 +309,6 @@ def sample_set_cluster(on: bool = True) -> None:
     """Whether `sample` may take the kernel that keeps a row in the shared memory of a cluster
     (the default); off: always the one-block kernel over global memory.  For tests of the latter."""
     fn = library().kestrel_sample_set_cluster
-    fn.restype, fn.argtypes = None, [_i]
     fn(1 if on else 0)
 
 
@@ -406,7 +366,6 @@ def gemm_tc_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, 
 def gemm_tc_set_tuning(overhead_kb: int = -1, ctas_per_sm: int = 0) -> None:
     """Tuning of the split heuristic of few-token products (see gemm_tcgen05.cu)."""
     fn = library().kestrel_gemm_tc_set_tuning
-    fn.restype, fn.argtypes = None, [_i, _i]
     fn(int(overhead_kb), int(ctas_per_sm))
 
 
@@ -414,7 +373,6 @@ def gemm_tc_set_wide(on: bool = True, more_than_tokens: int = -1) -> None:
     """Whether products of more than ``more_than_tokens`` (32) and at most 128 tokens take two
     weight tiles a CTA (the default).  For tests and measurements of the one-tile kernel."""
     fn = library().kestrel_gemm_tc_set_wide
-    fn.restype, fn.argtypes = None, [_i, _i]
     fn(1 if on else 0, int(more_than_tokens))
 
 
@@ -422,7 +380,6 @@ def gemm_tc_set_pair_tuning(min_tokens: int = -1, overhead_kb: int = -1) -> None
     """Tuning of many-token products on CTA pairs: products of more than ``min_tokens`` tokens
     take them; a K slice is priced at ``overhead_kb`` k-blocks beyond its own (see gemm_tcgen05.cu)."""
     fn = library().kestrel_gemm_tc_set_pair_tuning
-    fn.restype, fn.argtypes = None, [_i, _i]
     fn(int(min_tokens), int(overhead_kb))
 
 
@@ -434,7 +391,6 @@ def gemm_tc_set_many_token_path(pairs: bool = True, persistent: bool = True, swi
     for name, v in (("kestrel_gemm_tc_set_pairs", 1 if pairs else 0), ("kestrel_gemm_tc_set_persistent", 1 if persistent else 0),
                     ("kestrel_gemm_tc_set_swiglu_tile", int(swiglu_tile))):
         fn = getattr(lib, name)
-        fn.restype, fn.argtypes = None, [_i]
         fn(v)
 
 
@@ -503,7 +459,7 @@ def attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   tile_seq: torch.Tensor, tile_row0: torch.Tensor, rows_per_tile: int, cu_seqlens: torch.Tensor,
                   kv_lens: torch.Tensor, block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int,
                   window: int, scale: float, slices: int = 1, slice_len: int = 1 << 30,
-                  slice_len_dev: Optional[torch.Tensor] = None) -> None:
+                  max_kv_dev: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention (mma.sync) of the tiles listed in tile_seq / tile_row0; rows of
     other requests in ``out`` are left alone.  With ``slices`` > 1 the key range is cut into
     slices of ``slice_len`` keys (a multiple of 64) that are merged in ascending order;
@@ -528,7 +484,7 @@ def attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
         tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, rows_per_tile, cu_seqlens.data_ptr(), kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), int(page_size), T, nq, nkv, hd, int(window), int(slices),
-        slice_len, _p(slice_len_dev), float(scale), _stream()))
+        slice_len, _p(max_kv_dev), float(scale), _stream()))
     if slices > 1:
         global launches
         launches += 1          # the merge kernel
@@ -537,7 +493,7 @@ def attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
 def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                  tile_seq: torch.Tensor, tile_row0: torch.Tensor, cu_seqlens: torch.Tensor, kv_lens: torch.Tensor,
                  block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int, window: int, scale: float,
-                 slices: int = 1, slice_len: int = 1 << 30, slice_len_dev: Optional[torch.Tensor] = None,
+                 slices: int = 1, slice_len: int = 1 << 30, max_kv_dev: Optional[torch.Tensor] = None,
                  rows_per_tile: int = 128) -> None:
     """tcgen05 attention of the listed tiles, head size 128: tiles of ``rows_per_tile`` rows, up
     to 256 (prompt portions; 16 for decode tokens); the key range may be cut into
@@ -566,7 +522,7 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
         tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, int(rows_per_tile), cu_seqlens.data_ptr(), kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], block_table.stride(0), int(page_size), int(k_cache.shape[0]), T, nq, nkv, hd,
-        int(window), int(slices), slice_len, _p(slice_len_dev), float(scale), _stream()))
+        int(window), int(slices), slice_len, _p(max_kv_dev), float(scale), _stream()))
     if slices > 1:
         global launches
         launches += 1          # the merge kernel
@@ -575,7 +531,7 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
 def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                      tile_seq: torch.Tensor, tile_row0: torch.Tensor, cu_seqlens: torch.Tensor, kv_lens: torch.Tensor,
                      block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int, window: int, scale: float,
-                     slices: int = 1, slice_len: int = 1 << 30, slice_len_dev: Optional[torch.Tensor] = None) -> None:
+                     slices: int = 1, slice_len: int = 1 << 30, max_kv_dev: Optional[torch.Tensor] = None) -> None:
     """Attention of decode tokens (tiles of at most 16 rows) with a TMA loader warp in front of
     four mma.sync warps, head size 64 or 128; the key range is cut into ``slices`` slices of
     ``slice_len`` keys (a multiple of 64) that are merged in ascending order (up to 4 inside the
@@ -606,7 +562,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
         tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, cu_seqlens.data_ptr(), kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], block_table.stride(0), int(page_size), int(k_cache.shape[0]), T,
-        nq, nkv, hd, int(window), int(slices), slice_len, _p(slice_len_dev), float(scale), _stream()))
+        nq, nkv, hd, int(window), int(slices), slice_len, _p(max_kv_dev), float(scale), _stream()))
     if scratch:
         global launches
         launches += 1          # the merge kernel
@@ -645,9 +601,7 @@ def wait_probe():
     Returns (gave_up, milliseconds): the wait must give up within seconds and leave the
     device usable."""
     ms = ctypes.c_float(0.0)
-    fn = library().kestrel_wait_probe
-    fn.argtypes, fn.restype = [ctypes.POINTER(ctypes.c_float)], _i
-    rc = fn(ctypes.byref(ms))
+    rc = library().kestrel_wait_probe(ctypes.addressof(ms))
     if rc < 0:
         raise KernelError(library().kestrel_last_error().decode("utf-8", "replace"))
     return rc == 1, float(ms.value)
@@ -658,71 +612,163 @@ def attention_tc_error() -> int:
     return library().kestrel_attention_tc_error()
 
 
-def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch, block_table: torch.Tensor,
-              page_size: int, out: torch.Tensor, nq: int, nkv: int, hd: int, window: int, scale: float) -> None:
-    """Causal attention of this step's queries over their requests' cache pages.  ``batch``
-    gives positions, seq_of_token, per-request lengths and the tiling of rows.
+class AttentionPlanner:
+    """What the attention kernels keep between the layers of a step: the tile lists of the
+    step's requests on the device (made once per step from the step's host description) and
+    scratch for key-range slices.  One planner serves all attention layers of a model; its
+    launches must stay on one stream."""
 
-    float32 takes the plain kernel (one block per token and head, order of sums fixed per
-    token).  bfloat16 takes the tensor-core kernels.  Requests with at most 16 (token, head) rows
-    per kv head - decode tokens - have their key range cut into slices so that the grid fills the
-    GPU, and run on the kernel with the TMA loader warp (head size 64 or 128) or in KEYS mode of
-    the mma.sync kernel.  The others - prompt portions - run on the tcgen05 kernel (head size
-    128) or in ROWS mode of the mma.sync kernel.  The TMA-fed kernels also need a page size their
-    boxes fit."""
-    if q.dtype != torch.bfloat16 or hd % 8 or hd > 256:
-        attention_plain(q, k_cache, v_cache, batch.positions, batch.seq_of_token, block_table, page_size,
-                        out, nq, nkv, hd, window, scale)
-        return
-    use_tc = attention_tc_supported(hd, page_size)
-    rows_large = 256 if use_tc else library().kestrel_attention_mma_rows_per_tile(hd)
-    plan = batch.attention_plan(nq // nkv, rows_large)
-    no_split = (1 << 30) // 128 * 128
-    # Decode tokens: the kernel with the TMA loader warp where the head size and the page size
-    # fit it, else the KEYS mode of the mma.sync kernel.  (The tcgen05 kernel is built for tiles
-    # full of rows, one CTA per SM; it can run decode tokens, slices included, and is tested so.)
-    if plan.small is not None:
-        tl = plan.small
-        use_decode = attention_decode_supported(hd, page_size) and nq // nkv <= 16
-        slices, slice_len, slice_dev = 1, no_split, None
-        if window <= 0:         # a window is short; only full-length key ranges are cut into slices
-            slots = library().kestrel_attention_decode_slots(hd) if use_decode else library().kestrel_attention_mma_slots(hd)
-            ctas = max(1, tl.count * nkv)
-            # As many slices as still let every CTA be resident at once (measured at batch 1 to 64,
-            # contexts 2,048 to 65,536: a second wave of CTAs costs more than longer slices), at
-            # least 128 keys a slice (256 for the mma.sync kernel).  A captured step fixes the
-            # number for a nominal context and lets the slice length (a multiple of 128) follow the
-            # real one through the table on the device.
-            cand = max(1, min(slots // ctas, -(-tl.max_kv // (128 if use_decode else 256)), 32))
-            # (The decode kernel merges up to 4 slices inside a cluster, more through scratch and a
-            # second kernel of a few microseconds.  Measured, one request: 8,192 keys 21.7 us with 8
-            # slices, 12.2 us with 32; 32,768 keys 72.8 against 27.3 us.)
-            slice_len = -(-(-(-tl.max_kv // cand)) // 128) * 128
-            slices = -(-tl.max_kv // slice_len)
-            if tl.slice_len_table is not None:
-                slice_dev = tl.slice_len_table[slices:slices + 1] if slices > 1 else None
-        if use_decode:
-            attention_decode(q, k_cache, v_cache, out, tl.seq, tl.row0, batch.cu_seqlens, batch.kv_lens, block_table,
-                             page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
-        else:
-            attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, 16, batch.cu_seqlens, batch.kv_lens, block_table,
-                          page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split, slice_dev)
-    if plan.large is not None:
-        tl = plan.large
-        if use_tc:
-            # Few tiles far into a long context (a portion of a long prompt) leave SMs idle, one
-            # CTA per SM: the key range is then cut into slices of at least 2,048 keys, merged
-            # through scratch.
-            slices, slice_len = 1, no_split
-            ctas = tl.count * nkv
-            sms = library().kestrel_attention_tc_slots()
-            if window <= 0 and 2 * ctas <= sms and tl.max_kv >= 4096:
-                cand = min(sms // ctas, tl.max_kv // 2048, 16)
-                slice_len = -(-(-(-tl.max_kv // cand)) // 128) * 128
-                slices = -(-tl.max_kv // slice_len)
-            attention_tc(q, k_cache, v_cache, out, tl.seq, tl.row0, batch.cu_seqlens, batch.kv_lens, block_table,
-                         page_size, nq, nkv, hd, window, scale, slices, slice_len if slices > 1 else no_split,
-                         rows_per_tile=rows_large)
-        else:
-            attention_mma(q, k_cache, v_cache, out, tl.seq, tl.row0, rows_large, batch.cu_seqlens, batch.kv_lens,
-                          block_table, page_size, nq, nkv, hd, window, scale, 1, no_split)
+    def __init__(self, max_tokens: int = 4096, max_seqs: int = 256):
+        self._lib = library()
+        self._h = self._lib.kestrel_attn_planner_create(int(max_tokens), int(max_seqs))
+        if not self._h:
+            raise KernelError(self._lib.kestrel_last_error().decode("utf-8", "replace"))
+
+    @property
+    def handle(self):
+        return self._h
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.kestrel_attn_planner_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def attention(planner: Optional[AttentionPlanner], q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch,
+              group: int, page_size: int, out: torch.Tensor, nq: int, nkv: int, hd: int, window: int, scale: float) -> None:
+    """Causal attention of this step's queries over their requests' cache pages.  ``batch``
+    is the step's description: its packed int32 buffer on the host (``host``) and on the device
+    (``device_buffer``), the buffer's ``layout``, a ``serial`` that changes with every step, and
+    ``captured`` (the launch is being recorded for replay).  Which kernel takes which requests,
+    the tiling of their rows and the cutting of key ranges into slices are decided natively
+    (csrc/kernels/attention_dispatch.cu); float32 always takes the plain kernel."""
+    _need(q, "attention.q", dims=2)
+    _need(out, "attention.out", q.dtype, 2)
+    _need(k_cache, "attention.k_cache", q.dtype, 4)
+    _need(v_cache, "attention.v_cache", q.dtype, 4)
+    if q.shape[1] != nq * hd or out.shape != q.shape:
+        raise KernelError("attention: shapes differ")
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or v_cache.shape != k_cache.shape:
+        raise KernelError(f"attention: cache of shape {tuple(k_cache.shape)}, expected [pages, {nkv}, {page_size}, {hd}]")
+    if q.shape[0] != batch.num_tokens:
+        raise KernelError(f"attention: {q.shape[0]} query rows for a step of {batch.num_tokens} tokens")
+    lib = library()
+    global launches
+    rc = lib.kestrel_attention(planner.handle if planner is not None else None, int(batch.serial), batch.host.ctypes.data,
+                               batch.device_buffer.data_ptr(), batch.layout.ctypes.data, int(group), 1 if batch.captured else 0,
+                               q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _code(q, "attention.q"),
+                               int(k_cache.shape[0]), int(page_size), nq, nkv, hd, int(window), float(scale), _stream())
+    if rc != 0:
+        raise KernelError(lib.kestrel_last_error().decode("utf-8", "replace"))
+    launches += lib.kestrel_attn_planner_last_launches(planner.handle) if planner is not None else 1
+
+
+# ---- the step program and its runner ---------------------------------------------------------
+PHASES = {name[4:].lower(): value for name, value in _cdecl.constants().items() if name.startswith("KPH_") and name != "KPH_COUNT"}
+PHASE_COUNT = _cdecl.constants()["KPH_COUNT"]
+
+
+class StepProgram:
+    """A model's step as a list of kernel-level operations (csrc/kernels/step_program.cu).  Parts
+    write their operations into it once, in the order in which they run (`emit` methods); the
+    methods below return registers - small integers that name activations - or raise."""
+
+    def __init__(self, dtype: torch.dtype):
+        self._lib = library()
+        self.dtype = dtype
+        self._h = self._lib.kprog_create(_DT[dtype])
+        if not self._h:
+            raise KernelError(self._lib.kestrel_last_error().decode("utf-8", "replace"))
+        self._keep = []          # tensors the program points into
+
+    @property
+    def handle(self):
+        return self._h
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.kprog_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _reg(self, rc: int) -> int:
+        if rc < 0:
+            raise KernelError(self._lib.kestrel_last_error().decode("utf-8", "replace"))
+        return rc
+
+    def _ptr(self, t: Optional[torch.Tensor], name: str, dtype=None):
+        if t is None:
+            return None
+        _need(t, name, dtype)
+        self._keep.append(t)
+        return t.data_ptr()
+
+    def begin_call(self) -> None:
+        self._reg(self._lib.kprog_begin_call(self._h))
+
+    def embed(self, table: torch.Tensor) -> int:
+        _need(table, "program.embed.table", dims=2)
+        return self._reg(self._lib.kprog_embed(self._h, self._ptr(table, "table"), _code(table, "table"), table.shape[1]))
+
+    def add_rmsnorm(self, residual: int, delta: Optional[int], weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                    logit_rows: bool = False, phase: str = "norm") -> int:
+        return self._reg(self._lib.kprog_add_rmsnorm(self._h, residual, -1 if delta is None else delta,
+                                                     self._ptr(weight, "norm weight", torch.float32), float(eps), weight.shape[0],
+                                                     _DT[out_dtype], 1 if logit_rows else 0, PHASES[phase]))
+
+    def linear(self, x: int, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, add_to: Optional[int] = None,
+               phase: str = "other") -> int:
+        _need(weight, "program.linear.weight", self.dtype, 2)
+        return self._reg(self._lib.kprog_linear(self._h, x, self._ptr(weight, "weight"), weight.stride(0), weight.shape[0],
+                                                weight.shape[1], self._ptr(bias, "bias", torch.float32),
+                                                -1 if add_to is None else add_to, PHASES[phase]))
+
+    def gate_up_swiglu(self, x: int, weight: torch.Tensor, ff: int, phase: str = "gate_up") -> int:
+        _need(weight, "program.gate_up.weight", self.dtype, 2)
+        if weight.shape[0] != 2 * ff:
+            raise KernelError("program.gate_up_swiglu: the weight has not 2 x ff rows")
+        return self._reg(self._lib.kprog_gate_up_swiglu(self._h, x, self._ptr(weight, "weight"), weight.stride(0), ff,
+                                                        weight.shape[1], PHASES[phase]))
+
+    def attn_prepare(self, qkv: int, q_norm_w, k_norm_w, norm_eps: float, inv_freq, rotary_dim: int, rot_mode: int,
+                     rot_scale: float, group: int, page_size: int, k_cache: torch.Tensor, v_cache: torch.Tensor, nq: int,
+                     nkv: int, hd: int, write_kv: bool, phase: str = "rope") -> int:
+        return self._reg(self._lib.kprog_attn_prepare(
+            self._h, qkv, self._ptr(q_norm_w, "q_norm", torch.float32), self._ptr(k_norm_w, "k_norm", torch.float32),
+            float(norm_eps), self._ptr(inv_freq, "inv_freq", torch.float32), int(rotary_dim), int(rot_mode), float(rot_scale),
+            int(group), int(page_size), self._ptr(k_cache, "k_cache", self.dtype), self._ptr(v_cache, "v_cache", self.dtype),
+            nq, nkv, hd, 1 if write_kv else 0, PHASES[phase]))
+
+    def attention(self, q: int, planner: Optional[AttentionPlanner], group: int, page_size: int, k_cache: torch.Tensor,
+                  v_cache: torch.Tensor, nq: int, nkv: int, hd: int, window: int, scale: float, phase: str = "attn") -> int:
+        if planner is not None:
+            self._keep.append(planner)
+        return self._reg(self._lib.kprog_attention(
+            self._h, q, planner.handle if planner is not None else None, int(group), int(page_size), int(k_cache.shape[0]),
+            self._ptr(k_cache, "k_cache", self.dtype), self._ptr(v_cache, "v_cache", self.dtype), nq, nkv, hd, int(window),
+            float(scale), PHASES[phase]))
+
+    def logits(self, x: int, weight: torch.Tensor, phase: str = "lm_head") -> None:
+        _need(weight, "program.logits.weight", self.dtype, 2)
+        self._reg(self._lib.kprog_logits(self._h, x, self._ptr(weight, "weight"), weight.stride(0), weight.shape[0],
+                                         weight.shape[1], PHASES[phase]))
+
+    @property
+    def num_ops(self) -> int:
+        return self._lib.kprog_num_ops(self._h)
+
+
+def kernel_errors() -> int:
+    """Bits of the kernels whose bounded waits ran out since the last call (0 = none); synchronises."""
+    return library().kestrel_kernel_errors()

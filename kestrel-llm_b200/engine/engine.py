@@ -37,9 +37,10 @@ class Engine:
         page = options.page_size
         if options.num_pages:
             num_pages = options.num_pages
+        elif options.max_tokens:
+            num_pages = (options.max_tokens + page - 1) // page
         else:
-            max_tokens = options.max_tokens or options.batch_max * self.max_model_len
-            num_pages = (max_tokens + page - 1) // page
+            num_pages = self._pages_that_fit(model, options, page)
         self.cache = CacheManager(model.cache_specs(), model.dtype, dev, page, num_pages,
                                   options.batch_max, self.max_model_len)
         self.vocab_size = model.vocab_size
@@ -47,8 +48,47 @@ class Engine:
         if options.cuda_graphs and getattr(model, "graph_safe", False):
             from .graphs import DecodeGraphs
             self.graphs = DecodeGraphs(model, self.cache, options.batch_max)
+        # Steps that are not replayed from a graph run from the model's step program, one native
+        # call a step, if every part of the model wrote itself into one; else by the parts' forward.
+        self.runner = None
+        if options.native_step and hasattr(model, "step_program"):
+            program = model.step_program(self.cache)
+            if program is not None:
+                from .runner import StepRunner
+                self.runner = StepRunner(program, self.cache, options.max_step_tokens, options.batch_max,
+                                         guards=options.debug_guards)
+        self.profile = None
+        if options.profile:
+            from .profile import PhaseProfile
+            self.profile = PhaseProfile()
         self.steps_run = 0
         self.graph_launches = 0      # kernels replayed from CUDA graphs (not counted by ops.launches)
+        self.native_launches = 0     # kernels launched by the native runner (not counted by ops.launches)
+        self.last_h2d_bytes = 0
+
+    def _pages_that_fit(self, model, options: EngineOptions, page: int) -> int:
+        """Pages per cache group when no size is given: what the chosen share of the device's free
+        memory holds (the weights are loaded already), at most batch_max requests of
+        max_model_len tokens; the choice is printed."""
+        import sys
+        from ..parts.base import PagedKVSpec
+        want = options.batch_max * self.max_model_len
+        esize = torch.empty((), dtype=model.dtype).element_size()
+        per_token = sum(2 * sp.kv_heads * sp.head_dim * esize for sp in model.cache_specs() if isinstance(sp, PagedKVSpec))
+        if per_token == 0:
+            return max(1, (want + page - 1) // page)
+        free, _total = torch.cuda.mem_get_info(model.device)
+        # room for activations of the largest step beside the cache
+        reserve = 2 << 30
+        fit = int(max(0, free * options.memory_fraction - reserve) // per_token)
+        tokens = min(want, fit)
+        if tokens < self.max_model_len:
+            raise RuntimeError(f"the device has room for a cache of {fit} tokens ({per_token} bytes a token), less than one "
+                               f"request of max_model_len {self.max_model_len}; lower max_model_len")
+        if tokens < want:
+            print(f"[kestrel] cache: {tokens} tokens ({tokens * per_token / 2**30:.1f} GiB) fit the device's free memory; "
+                  f"{options.batch_max} requests of {self.max_model_len} tokens would need {want}", file=sys.stderr, flush=True)
+        return (tokens + page - 1) // page
 
     # ---- requests -----------------------------------------------------------------------
     def admit(self, rid: int) -> int:
@@ -103,21 +143,27 @@ class Engine:
             for rid in admitted:
                 self.cache.release(rid)
             raise
-        decode_only = self.graphs is not None and all(len(e.tokens) == 1 for e in entries)
+        self.cache.clear_admitted()       # state slots of requests admitted since the last step, by whomever
+        decode_only = self.graphs is not None and self.profile is None and all(len(e.tokens) == 1 for e in entries)
         if token_ids_dev is not None and not decode_only:
             raise ValueError("token ids on the device stand for one token per entry of a captured decode step")
         if decode_only:
             # decode tokens only: replay the captured step of this batch-size bucket
             logits, batch, replayed = self.graphs.run(entries, token_ids_dev)
             self.graph_launches += replayed
+            self.last_h2d_bytes = batch.bytes_h2d
             if any(len(e.want) == 0 for e in entries):
                 keep = [i for i, e in enumerate(entries) if len(e.want)]
                 logits = logits[torch.tensor(keep, dtype=torch.long, device=logits.device)] if keep else None
+        elif self.runner is not None:
+            logits = self.runner.step(entries, self.vocab_size, profile=self.profile)
+            self.native_launches += self.runner.last_launches
+            self.last_h2d_bytes = self.runner.last_h2d_bytes
         else:
             batch = StepBatch(entries, self.cache, self.model.device)
             logits = self.model.forward(batch, self.cache)
+            self.last_h2d_bytes = batch.bytes_h2d
         for e in entries:
             self.cache.commit(e.rid, len(e.tokens))
         self.steps_run += 1
-        self.last_batch = batch
         return logits

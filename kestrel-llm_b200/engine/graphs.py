@@ -5,8 +5,8 @@ each a few microseconds long; launched one by one from the host they take longer
 than to run.  Such a step is therefore captured - once per batch-size bucket (1, 2, 4 ... up to
 ``batch_max``) and class of the longest context, as two graphs of which the second is submitted
 while the first runs - and replayed: the host fills ONE pinned int32 buffer (token ids,
-positions, lengths, slots, slice lengths of the attention kernel, block tables) through one
-native call, copies it to the buffer's fixed device twin, and replays the graphs.  Buckets are
+positions, lengths, slots, the longest context, block tables) through one native call, copies
+it to the buffer's fixed device twin, and replays the graphs.  Buckets are
 padded with dummy requests of one token at position 0 whose keys and values go to the cache's
 null page.
 
@@ -21,52 +21,72 @@ import numpy as np
 import torch
 
 from ..csrc import ops
-from .batch import AttentionPlan, Entry, TileList
+from ..csrc import cdecl as _cdecl
+from .batch import LAYOUT_INTS, Entry, next_serial
 
-MAX_SLICES = 32
+_K = _cdecl.constants()
 HEAD_GRAPH_CALLS = 3          # layer calls in the first of a step's two graphs
 
 
 class StaticDecodeBatch:
-    """The fixed-address twin of `StepBatch` for ``size`` requests of one token each."""
+    """The fixed-address twin of `StepBatch` for ``size`` requests of one token each: the same
+    sections in one int32 buffer at one device address, refilled for every replay."""
+
+    captured = True             # launches made with it are recorded and replayed with other contents
 
     def __init__(self, size: int, cache, device, nominal_kv: int):
         B, W, G = size, cache.max_blocks, cache.num_groups
         self.size = size
         self.num_tokens = self.num_seqs = self.num_logit_rows = B
         self.table_width = W
-        o_tok, o_pos, o_kv, o_slot = 0, B, 2 * B, 3 * B
-        o_misc = 4 * B
-        o_tab = o_misc + MAX_SLICES + 1
+        o_tok, o_pos, o_seq = 0, B, 2 * B
+        o_cu = 3 * B
+        o_kv = o_cu + B + 1
+        o_slot = o_kv + B
+        o_rows = o_slot + B
+        o_maxkv = o_rows + B
+        o_tab = o_maxkv + 1
         total = o_tab + G * B * W
-        self._o = (o_tok, o_pos, o_kv, o_slot, o_misc, o_tab)
+        self._o = (o_tok, o_pos, o_kv, o_slot, o_maxkv, o_tab)
+        layout = np.zeros(LAYOUT_INTS, dtype=np.int32)
+        for name, v in (("KB_NUM_TOKENS", B), ("KB_NUM_SEQS", B), ("KB_NUM_ROWS", B), ("KB_TABLE_WIDTH", W), ("KB_NUM_GROUPS", G),
+                        ("KB_MAX_COUNT", 1), ("KB_MAX_KV_LEN", nominal_kv), ("KB_TOTAL_INTS", total), ("KB_O_TOKEN_IDS", o_tok),
+                        ("KB_O_POSITIONS", o_pos), ("KB_O_SEQ_OF_TOKEN", o_seq), ("KB_O_CU_SEQLENS", o_cu), ("KB_O_KV_LENS", o_kv),
+                        ("KB_O_SLOTS", o_slot), ("KB_O_ROWS", o_rows), ("KB_O_MAX_KV", o_maxkv), ("KB_O_TABLES", o_tab)):
+            layout[_K[name]] = v
+        self.layout = layout
         # a ring of pinned buffers: a buffer is rewritten only after the copy that read it is done
         self._ring = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(3)]
         self._ring_np = [t.numpy() for t in self._ring]
+        for h in self._ring_np:             # what never changes: request i is token i, and its logits are row i
+            h[o_seq:o_seq + B] = np.arange(B)
+            h[o_cu:o_cu + B + 1] = np.arange(B + 1)
+            h[o_rows:o_rows + B] = np.arange(B)
         self._ring_done = [None, None, None]
         self._turn = 0
+        self.host = self._ring_np[0]
+        self.serial = next_serial()
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)
-        ar = torch.arange(B + 1, dtype=torch.int32, device=device)
+        self.device_buffer = self.dev
         self.token_ids = self.dev[o_tok:o_tok + B]
         self.positions = self.dev[o_pos:o_pos + B]
+        self.seq_of_token = self.dev[o_seq:o_seq + B]
+        self.cu_seqlens = self.dev[o_cu:o_cu + B + 1]
         self.kv_lens = self.dev[o_kv:o_kv + B]
         self.slots = self.dev[o_slot:o_slot + B]
-        self.slice_len_table = self.dev[o_misc:o_misc + MAX_SLICES + 1]
-        self.seq_of_token = ar[:B].contiguous()
-        self.cu_seqlens = ar
-        self.logit_rows = ar[:B].contiguous()
-        self._tile_row0 = torch.zeros(B, dtype=torch.int32, device=device)
+        self.logit_rows = self.dev[o_rows:o_rows + B]
         self._tables = [self.dev[o_tab + g * B * W: o_tab + (g + 1) * B * W].view(B, W) for g in range(G)]
         self.counts = [1] * B
         self.cu_seqlens_host = list(range(B + 1))
-        self.slots_host: List[int] = [0] * B
+        self.slots_host: List[int] = [cache.spare_slot] * B
         self.kv_lens_host: List[int] = [1] * B
         self.max_count = 1
         self.null_page = cache.null_page
-        # context for which the captured attention launch picks its number of slices
-        self.nominal_kv = nominal_kv
+        self.spare_slot = cache.spare_slot
+        # the context for which a recorded launch plans (the slices of an attention kernel, say);
+        # the real longest context is on the device, at KB_O_MAX_KV
+        self.max_kv_len = nominal_kv
         self.bytes_h2d = int(total * 4)
-        self._slice_counts = np.arange(1, MAX_SLICES + 1, dtype=np.int64)
         self.fill([], cache)
 
     @property
@@ -76,14 +96,9 @@ class StaticDecodeBatch:
     def block_table(self, group: int) -> torch.Tensor:
         return self._tables[group]
 
-    def attention_plan(self, group_size: int, rows_large: int = 64) -> AttentionPlan:
-        if group_size > 16:
-            raise RuntimeError("a captured decode step needs at most 16 query heads per kv head")
-        return AttentionPlan(TileList(self.seq_of_token, self._tile_row0, self.size, self.nominal_kv, self.slice_len_table), None)
-
     def fill(self, entries: Sequence[Entry], cache) -> None:
         """Writes this step's values into the pinned buffer and starts its copy to the device."""
-        o_tok, o_pos, o_kv, o_slot, o_misc, o_tab = self._o
+        o_tok, o_pos, o_kv, o_slot, o_maxkv, o_tab = self._o
         B, W, G = self.size, self.table_width, cache.num_groups
         turn = self._turn
         self._turn = (turn + 1) % len(self._ring)
@@ -97,16 +112,19 @@ class StaticDecodeBatch:
             rids = np.fromiter((e.rid for e in entries), dtype=np.int64, count=n)
             max_kv = cache.describe_decode(rids, B, W, h[o_pos:o_pos + B], h[o_kv:o_kv + B], h[o_slot:o_slot + B],
                                            h[o_tab:o_tab + G * B * W])
-        if n < B:                       # dummy requests: one token at position 0 on the null page
+        if n < B:                       # dummy requests: one token at position 0 on the null page, state in the spare slot
             h[o_tok + n:o_tok + B] = 0
             h[o_pos + n:o_pos + B] = 0
             h[o_kv + n:o_kv + B] = 1
-            h[o_slot + n:o_slot + B] = 0
+            h[o_slot + n:o_slot + B] = self.spare_slot
             for g in range(G):
                 for i in range(n, B):
                     h[o_tab + (g * B + i) * W] = self.null_page
-        # slice length for every number of slices: max_kv / s rounded up to a multiple of 128
-        h[o_misc + 1:o_misc + MAX_SLICES + 1] = np.maximum(128, -(-(-(-max_kv // self._slice_counts)) // 128) * 128)
+        h[o_maxkv] = max_kv
+        self.host = h
+        self.serial = next_serial()
+        self.slots_host = h[o_slot:o_slot + B].tolist()
+        self.kv_lens_host = h[o_kv:o_kv + B].tolist()
         self.dev.copy_(self._ring[turn], non_blocking=True)
         ev = self._ring_done[turn] or torch.cuda.Event()
         ev.record()
@@ -127,9 +145,10 @@ class DecodeGraphs:
         self._graphs: Dict[tuple, tuple] = {}
         self.launches_per_replay: Dict[tuple, int] = {}
 
-    # A captured step fixes how many slices its attention cuts the key range into; the slice
-    # length follows the real contexts through device memory.  So that short and very long
-    # contexts get a count that suits them, steps are captured per class of the longest context.
+    # A captured launch fixes what its part decided on the host from the context it was recorded
+    # for (an attention kernel its number of key-range slices; their length follows the real
+    # contexts through device memory).  So that short and very long contexts get decisions that
+    # suit them, steps are captured per class of the longest context.
     KV_CLASSES = (1024, 2048, 4096)
 
     def kv_class(self, max_kv: int) -> int:

@@ -164,7 +164,7 @@ class LLM:
         logits = self.engine.step(entries, reserved=True, checked=True)    # prompts were checked on arrival
         self.scheduler.step_done()
         self.stats.steps += 1
-        self.stats.h2d_bytes += self.engine.last_batch.bytes_h2d
+        self.stats.h2d_bytes += self.engine.last_h2d_bytes
         if sampling:
             decode_only = all(s.count == 1 and s.wants_token for s in plan)
             flight = self._sample(logits, sampling, decode_only)
@@ -246,7 +246,7 @@ class LLM:
         logits = self.engine.step(entries, reserved=True, checked=True, token_ids_dev=prev.ids_dev)
         self.scheduler.step_done()
         self.stats.steps += 1
-        self.stats.h2d_bytes += self.engine.last_batch.bytes_h2d
+        self.stats.h2d_bytes += self.engine.last_h2d_bytes
         flight = self._sample(logits, prev.lives, True)
         finished = self._finalize(prev, flight)
         self._ahead = flight if self._live else None                 # all ended: the extra tokens are dropped

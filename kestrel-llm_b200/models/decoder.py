@@ -84,6 +84,28 @@ class DecoderModel(Part):
         slots += self.final_norm.weight_slots() + self.lm_head.weight_slots()
         return slots
 
+    def step_program(self, cache):
+        """The whole step as a `StepProgram` for the native runner, or None if some part of the
+        model has no ``emit`` (it then runs by the walk below).  ``cache`` is the `CacheManager`
+        whose layers the program's attention operations point into."""
+        from ..csrc import ops
+        pos_ok = self.position is None or type(self.position).add_to_embedding is PositionEncoding.add_to_embedding
+        blocks_ok = all(getattr(b, "emit", None) is not None and getattr(b, "emits", False) for b in self.blocks)
+        if not (pos_ok and blocks_ok and all(getattr(p, "emit", None) is not None
+                                              for p in (self.embedding, self.final_norm, self.lm_head))):
+            return None
+        prog = ops.StepProgram(self.dtype)
+        x = self.embedding.emit(prog)
+        pending = None
+        for call in self.order:
+            lc = cache.layer(call.cache, call.writes_cache) if call.cache >= 0 else None
+            prog.begin_call()
+            pending = self.blocks[call.block].emit(prog, x, pending, lc)
+        prog.begin_call()
+        n = self.final_norm.emit(prog, x, pending, self.dtype, logit_rows=True)
+        self.lm_head.emit(prog, n)
+        return prog
+
     def forward(self, batch, cache) -> Optional[torch.Tensor]:
         """Runs this step's tokens through every layer call; returns float32 logits
         [len(batch.logit_rows), vocab], or None if no logits are wanted."""

@@ -13,6 +13,7 @@ import torch
 
 from ..config.model_config import Qwen3Config
 from ..config.registry import register_architecture
+from ..csrc import ops
 from ..parts import (GatedMLP, GroupedQueryAttention, LMHead, PreNormBlock, RMSNorm, RotaryHalf,
                      TokenEmbedding)
 from .decoder import DecoderModel, LayerCall
@@ -22,13 +23,14 @@ def build_qwen3(config: Qwen3Config, dtype: torch.dtype, device) -> DecoderModel
     c = config
     emb = TokenEmbedding(c.vocab_size, c.hidden_size, dtype, device, "model.embed_tokens.weight")
     rope = RotaryHalf(c.head_dim, c.rope_theta, device)
+    planner = ops.AttentionPlanner() if dtype == torch.bfloat16 and torch.device(device).type == "cuda" else None
     blocks = []
     for i in range(c.num_hidden_layers):
         p = f"model.layers.{i}."
         mixer = GroupedQueryAttention(c.hidden_size, c.num_attention_heads, c.num_key_value_heads,
                                       c.head_dim, dtype, device, p + "self_attn.", rope,
                                       qk_norm_eps=c.qk_norm_eps, bias=c.attention_bias,
-                                      window=c.layer_window(i))
+                                      window=c.layer_window(i), planner=planner)
         ffn = GatedMLP(c.hidden_size, c.intermediate_size, dtype, device, p + "mlp.", c.hidden_act)
         blocks.append(PreNormBlock(RMSNorm(c.hidden_size, c.rms_norm_eps, device, p + "input_layernorm.weight"),
                                    mixer,

@@ -23,7 +23,7 @@ class GroupedQueryAttention(Mixer):
 
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype,
                  device, prefix: str, position: Optional[PositionEncoding], qk_norm_eps: Optional[float],
-                 bias: bool = False, window: int = 0):
+                 bias: bool = False, window: int = 0, planner: Optional[ops.AttentionPlanner] = None):
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
         if head_dim % 2 or head_dim > 256:
@@ -43,7 +43,12 @@ class GroupedQueryAttention(Mixer):
         else:
             self.q_norm = self.k_norm = None
         self.scale = 1.0 / math.sqrt(head_dim)
-        # a captured decode step tiles every request's rows (token, head) into one tile of 16
+        # What the attention kernels keep from layer to layer of a step (tile lists, slice
+        # scratch).  The layers of a model share one; a layer built alone gets its own.
+        self.planner = planner
+        if planner is None and dtype == torch.bfloat16 and torch.device(device).type == "cuda":
+            self.planner = ops.AttentionPlanner()
+        # a recorded decode step needs every request's rows (token, head) to fit one tile of the decode kernels
         self.graph_safe = heads // kv_heads <= 16
 
     def cache_spec(self) -> PagedKVSpec:
@@ -69,12 +74,22 @@ class GroupedQueryAttention(Mixer):
         qkv = self.qkv.forward(x)
         q = torch.empty((T, self.heads * self.head_dim), dtype=self.dtype, device=x.device)
         rot = self.position.rotary() if self.position is not None else None
-        inv_freq, rot_dim = rot if rot is not None else (None, 0)
         table = batch.block_table(cache.group)
-        ops.attn_prepare(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, inv_freq, rot_dim,
-                         batch.positions, batch.seq_of_token, table, cache.page_size, cache.k, cache.v,
-                         q, self.heads, self.kv_heads, self.head_dim, write_kv=cache.writable)
+        ops.attn_prepare(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, rot.inv_freq if rot else None,
+                         rot.dim if rot else 0, batch.positions, batch.seq_of_token, table, cache.page_size, cache.k, cache.v,
+                         q, self.heads, self.kv_heads, self.head_dim, write_kv=cache.writable,
+                         rot_mode=rot.mode if rot else 0, rot_scale=rot.scale if rot else 1.0)
         a = torch.empty_like(q)
-        ops.attention(q, cache.k, cache.v, batch, table, cache.page_size, a, self.heads, self.kv_heads,
+        ops.attention(self.planner, q, cache.k, cache.v, batch, cache.group, cache.page_size, a, self.heads, self.kv_heads,
                       self.head_dim, self.window, self.scale)
         return self.out.forward(a, residual=residual)
+
+    def emit(self, prog, x: int, residual: Optional[int], cache) -> int:
+        qkv = self.qkv.emit(prog, x, phase="qkv")
+        rot = self.position.rotary() if self.position is not None else None
+        q = prog.attn_prepare(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, rot.inv_freq if rot else None,
+                              rot.dim if rot else 0, rot.mode if rot else 0, rot.scale if rot else 1.0, cache.group,
+                              cache.page_size, cache.k, cache.v, self.heads, self.kv_heads, self.head_dim, cache.writable)
+        a = prog.attention(q, self.planner, cache.group, cache.page_size, cache.k, cache.v, self.heads, self.kv_heads,
+                           self.head_dim, self.window, self.scale)
+        return self.out.emit(prog, a, residual=residual, phase="o")

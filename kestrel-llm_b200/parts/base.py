@@ -63,15 +63,45 @@ class Part:
     def weight_slots(self) -> List[WeightSlot]:
         return []
 
+    # A part may also offer ``emit``: it writes the kernel-level operations of its forward pass
+    # into a `StepProgram` (csrc/ops.py), once, when the engine is made, and returns the
+    # program's register of its result.  The operations must be the ones ``forward`` launches,
+    # in the same order.  If every part of a model offers it, steps run from that program through
+    # the native runner (one call a step); otherwise they walk the parts' ``forward``.  The
+    # signatures mirror ``forward`` with registers in place of tensors:
+    #   Norm.emit(prog, residual, delta, out_dtype, logit_rows=False) -> register
+    #   Mixer.emit(prog, x, residual, layer_cache) -> register of a product, still to be added
+    #   FeedForward.emit(prog, x, residual) -> register of a product
+    #   Block.emit(prog, residual, pending, layer_cache) -> pending register
+    emit = None
+
+
+@dataclass(frozen=True)
+class Rotation:
+    """How a mixer turns queries and keys by position: pair j of the first ``dim`` dimensions of a
+    head is turned by the angle position * inv_freq[j].  ``pairing`` "half" pairs dimension j
+    with j + dim/2 (the reference's, st.c:8963-8989), "interleaved" pairs 2j with 2j + 1;
+    ``scale`` multiplies cos and sin (1 for plain rotary encodings)."""
+    inv_freq: torch.Tensor      # float32 [dim / 2] on the device
+    dim: int
+    pairing: str = "half"
+    scale: float = 1.0
+
+    @property
+    def mode(self) -> int:
+        if self.pairing not in ("half", "interleaved"):
+            raise ValueError(f"rotation pairing '{self.pairing}' is neither 'half' nor 'interleaved'")
+        return 0 if self.pairing == "half" else 1
+
 
 class PositionEncoding(Part):
     """How positions enter the model.
 
-    ``rotary()`` returns (inv_freq float32 [rot/2] on the device, rot) for mixers that rotate
-    queries and keys, or None.  ``add_to_embedding(x, batch)`` lets an absolute encoding add
-    to the embedded tokens; the default does nothing."""
+    ``rotary()`` returns a `Rotation` for mixers that rotate queries and keys, or None.
+    ``add_to_embedding(x, batch)`` lets an absolute encoding add to the embedded tokens; the
+    default does nothing."""
 
-    def rotary(self) -> Optional[Tuple[torch.Tensor, int]]:
+    def rotary(self) -> Optional[Rotation]:
         return None
 
     def add_to_embedding(self, x: torch.Tensor, batch) -> None:

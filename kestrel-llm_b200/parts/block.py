@@ -36,3 +36,15 @@ class PreNormBlock(Block):
         n = self.norm2.add_forward(residual, a, self.dtype)            # a is None if the mixer added itself
         f = self.ffn.forward(n, batch, residual=residual) if self._ffn_adds else self.ffn.forward(n, batch)
         return residual, f
+
+    @property
+    def emits(self) -> bool:
+        return all(getattr(p, "emit", None) is not None for p in self.parts())
+
+    def emit(self, prog, residual: int, pending, cache) -> int:
+        """This block's operations in a step program; returns the register of what is still to be
+        added to the residual stream (the feed-forward's product)."""
+        n = self.norm1.emit(prog, residual, pending, self.dtype)
+        a = self.mixer.emit(prog, n, residual if self._mixer_adds else None, cache)
+        n = self.norm2.emit(prog, residual, a, self.dtype)
+        return self.ffn.emit(prog, n, residual if self._ffn_adds else None)

@@ -30,6 +30,9 @@ class TokenEmbedding(Part):
         ops.embed(self.weight, token_ids, out)
         return out
 
+    def emit(self, prog) -> int:
+        return prog.embed(self.weight)
+
 
 class LMHead(Part):
     graph_safe = True
@@ -50,3 +53,6 @@ class LMHead(Part):
         product returns slices that a consumer kernel sums; the logits have no such consumer)."""
         logits = torch.empty((1, x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
         return ops.linear(x, self.weight, logits, weights_static=True)[0]
+
+    def emit(self, prog, x: int) -> None:
+        prog.logits(x, self.weight)

@@ -32,3 +32,8 @@ class Linear(Part):
         if residual is not None and self.bias is None and out is None and ops.linear_add_into(x, self.weight, residual):
             return None
         return ops.Partials(ops.linear(x, self.weight, out, weights_static=True), self.bias)
+
+    def emit(self, prog, x: int, residual: Optional[int] = None, phase: str = "other") -> int:
+        """The same product in a step program: register of float32 slices (empty if the product
+        added itself to ``residual``)."""
+        return prog.linear(x, self.weight, self.bias, add_to=residual, phase=phase)

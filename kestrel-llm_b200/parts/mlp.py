@@ -34,3 +34,7 @@ class GatedMLP(FeedForward):
     def forward(self, x: torch.Tensor, batch, residual: Optional[torch.Tensor] = None) -> Optional[ops.Partials]:
         act = ops.gate_up_swiglu(x, self.gate_up.weight, self.intermediate, weights_static=True)
         return self.down.forward(act, residual=residual)
+
+    def emit(self, prog, x: int, residual: Optional[int]) -> int:
+        act = prog.gate_up_swiglu(x, self.gate_up.weight, self.intermediate)
+        return self.down.emit(prog, act, residual=residual, phase="down")

@@ -31,3 +31,6 @@ class RMSNorm(Norm):
         out = torch.empty((n, self.width), dtype=out_dtype, device=residual.device)
         ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows=rows)
         return out
+
+    def emit(self, prog, residual: int, delta: Optional[int], out_dtype: torch.dtype, logit_rows: bool = False) -> int:
+        return prog.add_rmsnorm(residual, delta, self.weight, self.eps, out_dtype, logit_rows=logit_rows)

@@ -120,12 +120,13 @@ def trace_mixed(reqs: Dict[str, List[int]], live_max: int = 4, tail: int = 12,
 # ---- running a trace in-process ---------------------------------------------------------------
 
 def make_engine(model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, batch_max: int = 8,
-                graphs: bool = False):
+                graphs: bool = False, native: bool = True, guards: bool = False):
     from kestrel_llm_b200.config import EngineOptions
     from kestrel_llm_b200.engine import Engine
     from kestrel_llm_b200.weights import load_model
     opts = EngineOptions(dtype=dtype, page_size=page_size, batch_max=batch_max,
-                         num_pages=max(1, (max_tokens + page_size - 1) // page_size), cuda_graphs=graphs)
+                         num_pages=max(1, (max_tokens + page_size - 1) // page_size), cuda_graphs=graphs,
+                         native_step=native, debug_guards=guards)
     model = load_model(model_dir, dtype, opts.device)
     return Engine(model, opts)
 

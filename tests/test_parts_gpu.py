@@ -50,8 +50,9 @@ def test_norm_part(dtype):
 def test_rotary_part_matches_the_plain_angles():
     from kestrel_llm_b200.parts import RotaryHalf
     r = RotaryHalf(48, 50000.0, DEV)
-    inv, rot = r.rotary()
-    assert rot == 48 and inv.dtype == torch.float32
+    spec = r.rotary()
+    inv, rot = spec.inv_freq, spec.dim
+    assert rot == 48 and inv.dtype == torch.float32 and spec.pairing == "half" and spec.scale == 1.0
     cos, sin = P.rope_angles([1], 48, 50000.0)
     np.testing.assert_array_equal(np.cos(inv.cpu().numpy().astype(np.float32)), cos[0])
     with pytest.raises(ValueError):
