@@ -1,14 +1,24 @@
 #!/usr/bin/env python3
-"""Benchmark of the engine on one B200: decode tokens a second at batch 8 (the headline),
-at batch 1 and 64, prefill of 2,048 tokens, and the same decode through the Python entry
-point with host tokens in and out.
+"""Benchmark of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+    python bench.py --workload mix14b | 32b
 
+Default run (the headline): decode tokens a second at batch 8, at batch 1 and 64, prefill of
+2,048 tokens, and the same decode through the Python entry point with host tokens in and out.
 Model: the sizes of Qwen3-8B (36 layers, width 4096, 32/8 heads of 128, feed-forward 12288,
 vocabulary 151936), bfloat16, random weights; prompts are uniform random token ids.  A step is
-one decode step of the whole batch at a context that ends at 4,096 tokens.  `--layers` runs
-fewer layers of the same sizes (the record names both numbers); layer sizes never shrink.
+one decode step of the whole batch at a context that ends at 4,096 tokens; the ids a step picks
+are the next step's input (on the device), and the cache pages are handed out in a scattered
+order, as after long serving.  `--layers` runs fewer layers of the same sizes (the record names
+both numbers); layer sizes never shrink.
+
+`--workload mix14b`: 32 requests with prompts of 128 to 2,048 tokens (seed-fixed) and 256 greedy
+tokens each at the sizes of Qwen3-14B, through `LLM.add_request` / `LLM.step`, prompt portions
+of 512 tokens mixed with decode tokens.  `--workload 32b`: 16 requests of 1,024 + 128 tokens at
+the sizes of Qwen3-32B (64 query heads of 128 on a width of 5,120).  Each prints one JSON line
+with total, prompt and generated tokens a second, the time of all steps on the device, the
+wall-clock time over it, and the steps' fraction of their roofline.
 
 Timing: CUDA events on the launching stream around exactly K steps after W warm-up steps, with
 a synchronize on both sides.  Every step streams all weights (15 GB) and the live requests'
@@ -33,6 +43,20 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidd
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
                 attention_bias=False, max_position_embeddings=40960, hidden_act="silu")
+QWEN3_14B = dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
+# The reference cannot run this benchmark.  It is a CMake C11 project ("Neither 'setup.py' nor
+# 'pyproject.toml' found" is pip's answer), its engine reads only its own quantized VQF files,
+# and its one bfloat16-free route to the same numbers, the float32 CPU forward that
+# tests/golden compiles, takes 35 ms a token and layer at these layer sizes on this machine's
+# 8 cores (measured: 24 tokens through one layer, less 4 tokens through it, over 20) - 1.4 s a
+# token for 36 layers and the output head - and prefills token by token
+# (src/model/vllm_safetensors.c:17964-17971): the 8 x 2,048 prompt tokens of this benchmark
+# alone would take more than six hours, and the float32 weights 33 GB of host memory.
+REFERENCE_UNAVAILABLE = ("the reference is a CPU-only C11 engine (CMake, no Python package: pip install finds no setup.py or "
+                         "pyproject.toml) that loads only its own quantized VQF files; its float32 forward, the one path "
+                         "that takes these weights, was compiled and measured here at 35 ms per token and layer of this "
+                         "size on 8 cores = 1.4 s a token, prefill token by token: batch 8 x context 4,096 would take hours")
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -104,6 +128,123 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def run_workload(args) -> int:
+    """A whole workload through the scheduler: requests are added to `LLM`, `LLM.step` is called
+    until all are done; every step leaves CUDA events, from which the time on the device and the
+    host's share follow."""
+    import numpy as np
+    import torch
+    from kestrel_llm_b200 import LLM, SamplingParams
+    from kestrel_llm_b200.config import EngineOptions, Qwen3Config
+    from kestrel_llm_b200.config.registry import resolve_architecture
+    from kestrel_llm_b200.weights import fill_random_
+
+    if args.workload == "mix14b":
+        raw, label = dict(QWEN3_14B), "Qwen3-14B shape"
+        n_req, gen = args.requests or 32, args.generate or 256
+        rng = np.random.default_rng(14)
+        lengths = rng.integers(128, 2049, size=n_req).tolist()
+        chunk = 512
+        what = f"{n_req} requests, prompts of 128 to 2,048 tokens (seed 14), {gen} greedy tokens each, prompt portions of {chunk} mixed with decode tokens"
+    else:
+        raw, label = dict(QWEN3_32B), "Qwen3-32B shape"
+        n_req, gen = args.requests or 16, args.generate or 128
+        rng = np.random.default_rng(32)
+        lengths = [1024] * n_req
+        chunk = 512
+        what = f"{n_req} requests of 1,024 prompt tokens, {gen} greedy tokens each, prompt portions of {chunk} mixed with decode tokens"
+    full_layers = raw["num_hidden_layers"]
+    if args.layers:
+        raw["num_hidden_layers"] = min(args.layers, full_layers)
+    cfg = Qwen3Config.from_dict(raw)
+    L = cfg.num_hidden_layers
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    model = resolve_architecture(cfg.architecture).build(cfg, torch.bfloat16, dev)
+    fill_random_(model, 0)
+    longest = max(lengths) + gen + 64
+    opts = EngineOptions(dtype="bfloat16", page_size=args.page_size, batch_max=n_req, max_model_len=longest,
+                         max_tokens=sum(l + gen + 64 for l in lengths), max_step_tokens=chunk + n_req, prefill_batch=chunk)
+    llm = LLM(model, dtype="bfloat16", options=opts)
+    llm.engine.cache.shuffle_free(0)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lengths]
+    sp = SamplingParams(temperature=0.0, max_tokens=gen, ignore_eos=True)
+    pk = peaks()
+    # warm-up: a short run of the same kind, so that modules are loaded, graphs of the first buckets are captured and
+    # the workspace has its size
+    llm.generate([p[:300] for p in prompts[:min(4, n_req)]], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    llm.warm_up()
+    clocks = ClockSampler(0)
+    llm.record_steps = True
+    llm.step_records.clear()
+    for p in prompts:
+        llm.add_request(p, sp)
+    contexts = []           # per step: (tokens, sum over entries of count * (start + (count + 1) / 2), live context tokens)
+    sched_plan = llm.scheduler.schedule
+    seen = []
+
+    def watching():
+        plan = sched_plan()
+        seen.append(plan)
+        return plan
+    llm.scheduler.schedule = watching
+    torch.cuda.synchronize()
+    clocks.active = True
+    t0 = time.perf_counter()
+    done = llm.run_until_done()
+    wall = time.perf_counter() - t0
+    clocks.active = False
+    clocks.close()
+    llm.scheduler.schedule = sched_plan
+    recs = llm.step_records
+    dev_ms = [r.start.elapsed_time(r.end) for r in recs]
+    device_s = sum(dev_ms) / 1000.0
+    n_prompt, n_gen = sum(lengths), sum(len(o.token_ids) for o in done.values())
+    # the steps' bound: every weight once, the live requests' cache, and the arithmetic, whichever is larger
+    per_layer = (cfg.q_size + 2 * cfg.kv_size) * cfg.hidden_size + cfg.hidden_size * cfg.q_size + 3 * cfg.intermediate_size * cfg.hidden_size
+    weight_bytes = 2 * (L * per_layer + cfg.vocab_size * cfg.hidden_size)
+    kv_bytes_per_token = L * 2 * cfg.kv_size * 2
+    plans = [p for p in seen if p]
+    ideal_s, prefill_dev, decode_dev, mixed = 0.0, 0.0, 0.0, 0
+    for plan, ms in zip(plans, dev_ms):
+        T = sum(s.count for s in plan)
+        ctx = sum(s.start + s.count for s in plan)
+        pairs = sum(s.count * (s.start + (s.count + 1) / 2.0) for s in plan)
+        flops = 2.0 * T * L * per_layer + 2.0 * sum(1 for s in plan if s.wants_token) * cfg.vocab_size * cfg.hidden_size \
+            + L * 4.0 * cfg.num_attention_heads * cfg.head_dim * pairs
+        byts = weight_bytes + ctx * kv_bytes_per_token
+        ideal_s += max(byts / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops_sustained"] * 1e12))
+        if all(s.count == 1 for s in plan):
+            decode_dev += ms
+        else:
+            prefill_dev += ms
+            mixed += 1 if any(s.count == 1 for s in plan) else 0
+    m = [o.metrics for o in done.values()]
+    rec = {
+        "metric": f"tokens/s (prompt + generated) of the workload, {label} bf16", "value": round((n_prompt + n_gen) / wall, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": len(recs), "warmup": 1, "ms_per_step": round(1000 * wall / max(1, len(recs)), 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights, uniform random token ids; " + what, "impl": "ours", "workload": args.workload,
+        "config": {"model": label, "layers": L, "layers_of_model": full_layers, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "requests": n_req, "generate": gen,
+                   "prompt_tokens": n_prompt, "prefill_batch": chunk, "max_step_tokens": opts.max_step_tokens,
+                   "page_size": args.page_size, "pages": "scattered", "parallelism": "single GPU", "peaks": pk["source"]},
+        "wall_s": round(wall, 4), "device_s": round(device_s, 4), "wall_over_device": round(wall / device_s, 4),
+        "prompt_tok_s": round(n_prompt / wall, 1), "generated_tok_s": round(n_gen / wall, 1),
+        "steps_with_prompt_portions": {"steps": sum(1 for p in plans if any(s.count > 1 for s in p)), "of_them_mixed": mixed,
+                                       "device_ms": round(prefill_dev, 2)},
+        "decode_only_steps": {"steps": sum(1 for p in plans if all(s.count == 1 for s in p)), "device_ms": round(decode_dev, 2)},
+        "roofline": {"bound": "per step max(bytes / HBM, flops / sustained bf16)", "ideal_s": round(ideal_s, 4),
+                     "frac_of_device_time": round(ideal_s / device_s, 4), "frac_of_wall": round(ideal_s / wall, 4)},
+        "requests": {"ttft_ms_mean": round(sum(x.ttft_ms for x in m) / len(m), 1), "ttft_ms_max": round(max(x.ttft_ms for x in m), 1),
+                     "tpot_ms_mean": round(sum(x.tpot_ms for x in m) / len(m), 2), "preemptions": int(llm.scheduler.num_preemptions)},
+        "gpu_launches": int(llm.engine.native_launches + llm.engine.graph_launches), "clocks": clocks.summary(),
+    }
+    print(json.dumps(rec))
+    return 0
+
+
 def main() -> int:
     global CONTEXT, PREFILL_TOKENS
     ap = argparse.ArgumentParser()
@@ -117,16 +258,19 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length at which the decode steps end (default 4096)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the prefill step (default 2048)")
+    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "mix14b", "32b"],
+                    help="decode8b: the headline run; mix14b / 32b: whole workloads through the scheduler")
+    ap.add_argument("--requests", type=int, default=0, help="requests of a workload (0: 32 for mix14b, 16 for 32b)")
+    ap.add_argument("--generate", type=int, default=0, help="tokens to generate per request of a workload (0: 256 / 128)")
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "not installable offline: pip finds neither setup.py nor pyproject.toml (a CMake C11 "
-                          "project), and the engine is CPU-only and loads only its own quantized VQF files, "
-                          "not bfloat16 safetensors"}))
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported (no multi-GPU path exists)")
         return 2
+    if args.workload != "decode8b":
+        return run_workload(args)
     W, K = max(3, args.warmup), max(1, args.steps)
     CONTEXT, PREFILL_TOKENS = max(256, args.context), max(16, args.prefill_tokens)      # the defaults unless asked otherwise
 
@@ -156,6 +300,7 @@ def main() -> int:
                          prefill_batch=PREFILL_TOKENS)
     llm = LLM(model, dtype="bfloat16", options=opts)
     engine = llm.engine
+    engine.cache.shuffle_free(0)                     # pages in a scattered order, as after long serving
     for t in engine.cache.k + engine.cache.v:        # cache contents for the synthetic contexts
         if t is not None:
             t.normal_(0.0, 0.5)
@@ -191,19 +336,18 @@ def main() -> int:
             engine.admit(r)
             engine.cache.reserve(r, ctx0)       # a context of ctx0 tokens whose cache holds random values
             engine.cache.commit(r, ctx0)
-        toks = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)).to(dev)
-        nxt = torch.empty(B, dtype=torch.int32, device=dev)
-        state = {"toks": toks.cpu().tolist()}
+        nxt = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)).to(dev)
+        entries = [Entry(r, (0,), (0,)) for r in rids]       # the ids are on the device: those the step before picked
 
         def one():
-            logits = engine.step([Entry(r, [t], (0,)) for r, t in zip(rids, state["toks"])])
+            logits = engine.step(entries, token_ids_dev=nxt)
             ops.argmax(logits, nxt)
 
         for _ in range(W):
             one()
-        before = ops.launches + engine.graph_launches
+        before = ops.launches + engine.graph_launches + engine.native_launches
         secs = timed(one, K)
-        launched = ops.launches + engine.graph_launches - before
+        launched = ops.launches + engine.graph_launches + engine.native_launches - before
         for r in rids:
             engine.release(r)
         mean_ctx = ctx0 + W + (K - 1) / 2.0 + 1
@@ -281,6 +425,7 @@ def main() -> int:
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
                    "seq_len": CONTEXT, "page_size": args.page_size, "parallelism": "single GPU",
                    "cache_flush": "inputs larger than L2: each step streams all weights and cache from HBM",
+                   "pages": "scattered", "token_feedback": "device",
                    "peaks": pk["source"]},
         "e2e": e2e, "gpu_launches": int(main_pt["launches"]), "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",

@@ -175,6 +175,11 @@ class PageTable:
         n = self._lib.kcache_take_admitted(self._h, ctypes.addressof(ids), ctypes.addressof(slots), cap)
         return [(int(ids[i]), int(slots[i])) for i in range(min(n, cap))]
 
+    def shuffle_free(self, seed: int = 0) -> None:
+        """Free pages in a pseudo-random order fixed by ``seed``: the scattered layout a pool has
+        after long serving, from the start (benchmarks, tests)."""
+        self._lib.kcache_shuffle_free(self._h, int(seed))
+
     def free_pages(self, group: int) -> int:
         return self._lib.kcache_free_pages(self._h, group)
 

@@ -79,6 +79,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-step-tokens", type=int, default=2048)
     ap.add_argument("--random-weights", type=int, default=None, metavar="SEED")
     ap.add_argument("--config", default=None, help="config.json for --random-weights")
+    ap.add_argument("--profile", action="store_true", help="time every step's phases on the device and print [DEC-SINGLE] / [PREFILL-TIMING] lines")
+    ap.add_argument("--debug-guards", action="store_true", help="check every step's description on the device and guard words behind every activation")
+    ap.add_argument("--cuda-graphs", type=int, default=1, help="0: launch decode steps kernel by kernel instead of replaying captured graphs")
     ap.add_argument("--replay", action="store_true")
     ap.add_argument("--out", default=None)
     return ap
@@ -116,13 +119,15 @@ def main(argv=None) -> int:
         print(f"[STREAM] random weights (seed {args.random_weights}) written to {args.model}", flush=True)
     if args.replay:
         from .engine.replay import replay_stdin
-        return replay_stdin(args.model, args.dtype, args.out or "trace_out", args.max_tokens or 4096, args.page_size)
+        return replay_stdin(args.model, args.dtype, args.out or "trace_out", args.max_tokens or 4096, args.page_size,
+                            cuda_graphs=bool(args.cuda_graphs))
 
     t0 = time.perf_counter()
     llm = LLM(args.model, dtype=args.dtype, page_size=args.page_size, batch_max=args.batch_max,
               max_queued=max(args.max_queued, 1), prefill_batch=args.prefill_batch,
               max_step_tokens=args.max_step_tokens, max_tokens=args.max_tokens,
-              max_model_len=args.max_model_len, seed=args.seed)
+              max_model_len=args.max_model_len, seed=args.seed, profile=args.profile, debug_guards=args.debug_guards,
+              cuda_graphs=bool(args.cuda_graphs))
     c = llm.model.config
     print(f"[STREAM] load OK ({time.perf_counter() - t0:.2f}s): dim={c.hidden_size} layers={c.num_hidden_layers} "
           f"heads={c.num_attention_heads} kv={c.num_key_value_heads} vocab={c.vocab_size} dtype={args.dtype}", flush=True)
@@ -146,19 +151,16 @@ def main(argv=None) -> int:
     for p in prompts:
         llm.add_request(p, sp)
     t1 = time.perf_counter()
-    done = {}
-    first = True
-    t_prefill = None
-    while llm.has_unfinished():
-        fin = llm.step()
-        if first and llm.stats.generated_tokens >= len(prompts):
+    state = {"t_prefill": None}
+
+    def after_step(finished):
+        if state["t_prefill"] is None and llm.stats.generated_tokens >= len(prompts):
             torch.cuda.synchronize()
-            t_prefill = time.perf_counter() - t1
-            first = False
-        for o in fin:
-            done[o.request_id] = o
-    torch.cuda.synchronize()
+            state["t_prefill"] = time.perf_counter() - t1
+
+    done = llm.run_until_done(after_step)         # raises if a kernel gave up a wait or nothing can run
     total = time.perf_counter() - t1
+    t_prefill = state["t_prefill"]
     t_prefill = t_prefill if t_prefill is not None else total
     print(f"[STREAM] prefill {n_prompt} tokens in {t_prefill:.3f}s ({n_prompt / max(t_prefill, 1e-9):.0f} tok/s) [batch]", flush=True)
     mode = "greedy" if sp.greedy else f"sample T={sp.temperature} top_p={sp.top_p} top_k={sp.top_k} min_p={sp.min_p}"
@@ -169,6 +171,14 @@ def main(argv=None) -> int:
     t_dec = max(total - t_prefill, 1e-9)
     if n_dec > 0:
         print(f"[STREAM] decoded {n_dec} tokens, {1000 * t_dec / n_dec:.2f} ms/tok ({n_dec / t_dec:.2f} tok/s)", flush=True)
+    for rid in sorted(done):
+        m = done[rid].metrics
+        print(f"[STREAM] metrics request={rid} prompt_tokens={m.prompt_tokens} n_tokens={m.n_tokens} prefill_ms={m.prefill_ms:.1f} "
+              f"ttft_ms={m.ttft_ms:.1f} tpot_ms={m.tpot_ms:.2f} total_ms={m.total_ms:.1f} finish={done[rid].finish_reason}", flush=True)
+    occ = llm.cache_occupancy()
+    for i, g in enumerate(occ["groups"]):
+        print(f"[STREAM] cache group {i}: window={g['window']} pages={g['pages']} free={g['free']} page_size={occ['page_size']} "
+              f"preemptions={llm.scheduler.num_preemptions}", flush=True)
     return 0
 
 

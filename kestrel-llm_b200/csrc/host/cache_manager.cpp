@@ -282,6 +282,22 @@ KESTREL_API int kcache_describe_decode(void *h, const long long *ids, int n, int
     return longest;
 }
 
+// Puts every group's free pages into a pseudo-random order (a fixed function of `seed`).  A
+// fresh pool hands pages out in ascending order, so that a request's pages lie one behind the
+// other; after minutes of serving they do not.  Benchmarks and tests call this to get the
+// scattered layout from the start.
+KESTREL_API int kcache_shuffle_free(void *h, long long seed) {
+    Cache &c = *(Cache *)h;
+    unsigned long long x = (unsigned long long)seed * 6364136223846793005ull + 1442695040888963407ull;
+    for (Group &g : c.groups)
+        for (size_t i = g.free_stack.size(); i > 1; --i) {
+            x = x * 6364136223846793005ull + 1442695040888963407ull;
+            size_t j = (size_t)((x >> 33) % i);
+            std::swap(g.free_stack[i - 1], g.free_stack[j]);
+        }
+    return 0;
+}
+
 KESTREL_API int kcache_free_pages(void *h, int group) {
     Cache &c = *(Cache *)h;
     if (group < 0 || group >= (int)c.groups.size()) return -6;

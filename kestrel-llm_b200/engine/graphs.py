@@ -189,6 +189,20 @@ class DecodeGraphs:
         self._graphs[(size, nominal_kv)] = ((first, rest), batch, logits)
         return self._graphs[(size, nominal_kv)]
 
+    def capture_all(self, longest_context: int) -> int:
+        """Captures every bucket size at every class of context up to ``longest_context`` now, so
+        that no step of a later run pays for a capture (a server does this once, at start-up).
+        Returns the number of steps captured."""
+        classes = sorted({self.kv_class(c) for c in list(self.KV_CLASSES) + [longest_context] if c <= max(longest_context, self.KV_CLASSES[0])}
+                         | {self.kv_class(longest_context)})
+        made = 0
+        for size in self.sizes:
+            for nominal in classes:
+                if (size, nominal) not in self._graphs:
+                    self._capture(size, nominal)
+                    made += 1
+        return made
+
     def run(self, entries: Sequence[Entry], token_ids_dev: Optional[torch.Tensor] = None):
         """Replays the bucket's graph for these one-token entries; returns (logits of the
         first len(entries) rows, static batch, kernels replayed).  ``token_ids_dev`` (int32 on the

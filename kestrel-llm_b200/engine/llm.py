@@ -34,12 +34,26 @@ from .scheduler import Scheduler
 
 
 @dataclass
+class RequestMetrics:
+    """The six numbers the reference reports per request (VLLMMetrics,
+    include/serve/vllm_server.h:322-339, filled in src/serve/vllm_batch.c:419-426): wall-clock
+    milliseconds from the moment the request was added."""
+    prompt_tokens: int = 0
+    n_tokens: int = 0           # generated tokens
+    prefill_ms: float = 0.0     # start -> the step that finished the prompt has run
+    ttft_ms: float = 0.0        # start -> first token on the host
+    tpot_ms: float = 0.0        # mean time per token after the first
+    total_ms: float = 0.0       # start -> last token on the host
+
+
+@dataclass
 class RequestOutput:
     request_id: int
     prompt_token_ids: List[int]
     token_ids: List[int] = field(default_factory=list)
     finish_reason: Optional[str] = None       # "stop" | "length", as the reference reports them
     preemptions: int = 0
+    metrics: RequestMetrics = field(default_factory=RequestMetrics)
 
 
 @dataclass
@@ -49,6 +63,8 @@ class _Live:
     seed: int
     stop_ids: frozenset
     sampled: int = 0            # tokens sampled so far, those the host has not read yet included
+    t_start: float = 0.0        # perf_counter when the request was added
+    t_first: float = 0.0        # ... when its first token reached the host
 
 
 @dataclass
@@ -71,6 +87,18 @@ class StepStats:
     h2d_bytes: int = 0
     d2h_bytes: int = 0
     seconds: float = 0.0
+
+
+@dataclass
+class StepRecord:
+    """One step as `LLM.record_steps` keeps it: what ran, and CUDA events around its kernels
+    (their distance is the step's time on the device; the distance between the starts of
+    consecutive steps holds the host's share too)."""
+    tokens: int
+    requests: int
+    decode_only: bool
+    start: torch.cuda.Event
+    end: torch.cuda.Event
 
 
 class LLM:
@@ -98,7 +126,9 @@ class LLM:
         self._ahead: Optional[_InFlight] = None
         self._pinned = [torch.empty(opts.batch_max + 8, dtype=torch.int32).pin_memory() for _ in range(3)]
         self._pinned_turn = 0
-        self.run_ahead = True           # False: every step's ids are read before the next step is built
+        self.run_ahead = not opts.profile   # False: every step's ids are read before the next step is built
+        self.record_steps = False       # True: every step leaves a `StepRecord` in `step_records`
+        self.step_records: List[StepRecord] = []
 
     # ---- requests -----------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -115,7 +145,9 @@ class LLM:
         if not params.ignore_eos:
             stop |= set(self.model.config.eos_token_ids)
         seed = params.seed if params.seed is not None else (self.options.seed * 1000003 + rid)
-        self._live[rid] = _Live(RequestOutput(rid, prompt), params, seed, frozenset(stop))
+        lv = _Live(RequestOutput(rid, prompt), params, seed, frozenset(stop), t_start=time.perf_counter())
+        lv.out.metrics.prompt_tokens = len(prompt)
+        self._live[rid] = lv
         return rid
 
     def abort_request(self, rid: int) -> Optional[RequestOutput]:
@@ -128,6 +160,16 @@ class LLM:
         self.scheduler.finish(rid)
         lv.out.finish_reason = "abort"
         return lv.out
+
+    def warm_up(self) -> int:
+        """What a server does once before it takes requests: captures the decode step of every
+        batch-size bucket and class of context now, so that no request waits for a capture.
+        Returns the number of steps captured (0 if the model's steps are not captured)."""
+        if self.engine.graphs is None:
+            return 0
+        n = self.engine.graphs.capture_all(self.engine.max_model_len)
+        torch.cuda.synchronize(self.model.device)
+        return n
 
     def has_unfinished(self) -> bool:
         return bool(self._live)
@@ -161,6 +203,7 @@ class LLM:
                 sampling.append(lv)
             if s.start < n_prompt:
                 self.stats.prompt_tokens += min(s.start + s.count, n_prompt) - s.start
+        rec = self._begin_record(sum(s.count for s in plan), len(plan), all(s.count == 1 for s in plan))
         logits = self.engine.step(entries, reserved=True, checked=True)    # prompts were checked on arrival
         self.scheduler.step_done()
         self.stats.steps += 1
@@ -168,11 +211,34 @@ class LLM:
         if sampling:
             decode_only = all(s.count == 1 and s.wants_token for s in plan)
             flight = self._sample(logits, sampling, decode_only)
+            self._end_record(rec)
             if decode_only and self.run_ahead and self.engine.graphs is not None:
                 self._ahead = flight            # read while the next step runs
             else:
                 finished += self._finalize(flight, None)
+        else:
+            self._end_record(rec)
         return finished
+
+    def _begin_record(self, tokens: int, requests: int, decode_only: bool) -> Optional[StepRecord]:
+        if not self.record_steps:
+            return None
+        rec = StepRecord(tokens, requests, decode_only, torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        rec.start.record()
+        return rec
+
+    def _end_record(self, rec: Optional[StepRecord]) -> None:
+        if rec is not None:
+            rec.end.record()
+            self.step_records.append(rec)
+
+    def cache_occupancy(self) -> Dict[str, object]:
+        """Pages of every cache group in use, and live requests: what the reference's serving
+        loop watches as free memory before it admits (src/serve/vllm_server.c:82-101)."""
+        c = self.engine.cache
+        groups = [{"window": g.window, "pages": c.num_pages(i), "free": c.free_pages(i)} for i, g in enumerate(c.groups)]
+        return {"page_size": c.page_size, "groups": groups, "live_requests": c.live_requests(),
+                "running": self.scheduler.num_running, "waiting": self.scheduler.num_waiting}
 
     def _sample(self, logits: torch.Tensor, lives: List[_Live], decode_only: bool) -> _InFlight:
         """Picks one token per request on the device and starts their copy to the host."""
@@ -200,6 +266,14 @@ class LLM:
                 continue
             lv.out.token_ids.append(int(tok))
             self.stats.generated_tokens += 1
+            now = time.perf_counter()
+            m = lv.out.metrics
+            if lv.t_first == 0.0:
+                lv.t_first = now
+                m.prefill_ms = m.ttft_ms = (now - lv.t_start) * 1000.0
+            m.n_tokens = len(lv.out.token_ids)
+            m.total_ms = (now - lv.t_start) * 1000.0
+            m.tpot_ms = (now - lv.t_first) * 1000.0 / (m.n_tokens - 1) if m.n_tokens > 1 else m.ttft_ms
             at_limit = False if flight.counted else self.scheduler.on_token(rid)
             if int(tok) in lv.stop_ids:
                 lv.out.finish_reason = "stop"
@@ -243,11 +317,13 @@ class LLM:
                 any(s.count != 1 or not s.wants_token for s in plan) or self.scheduler.preempted():
             raise RuntimeError("run-ahead: the scheduler built another step than the one foreseen")
         entries = [Entry(s.rid, (0,), (0,)) for s in plan]          # the ids are on the device
+        rec = self._begin_record(len(plan), len(plan), True)
         logits = self.engine.step(entries, reserved=True, checked=True, token_ids_dev=prev.ids_dev)
         self.scheduler.step_done()
         self.stats.steps += 1
         self.stats.h2d_bytes += self.engine.last_h2d_bytes
         flight = self._sample(logits, prev.lives, True)
+        self._end_record(rec)
         finished = self._finalize(prev, flight)
         self._ahead = flight if self._live else None                 # all ended: the extra tokens are dropped
         return finished
@@ -264,17 +340,32 @@ class LLM:
                 raise ValueError("one SamplingParams per prompt, or one for all")
         t0 = time.perf_counter()
         rids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        done = self.run_until_done()
+        self.stats.seconds += time.perf_counter() - t0
+        return [done[r] for r in rids]
+
+    def run_until_done(self, on_step=None) -> Dict[int, RequestOutput]:
+        """Steps until no request is left; returns the finished requests by id.  ``on_step`` is
+        called after every step with the requests it found finished.  Raises if the scheduler
+        finds nothing to run although requests are live, and if a kernel gave up a bounded wait
+        (no tokens are better than wrong ones)."""
         done: Dict[int, RequestOutput] = {}
         idle = 0
         while self.has_unfinished():
+            before = self.engine.steps_run
             fin = self.step()
             for o in fin:
                 done[o.request_id] = o
-            if not fin and self.engine.steps_run == 0:
+            if on_step is not None:
+                on_step(fin)
+            if not fin and self.engine.steps_run == before:
                 idle += 1
                 if idle > 3:
                     raise RuntimeError("the scheduler found nothing to run although requests are waiting")
+            else:
+                idle = 0
         torch.cuda.synchronize(self.model.device)
-        self.stats.seconds += time.perf_counter() - t0
-        ops.raise_on_kernel_error()             # a kernel that gave up a bounded wait: no tokens are better than wrong ones
-        return [done[r] for r in rids]
+        ops.raise_on_kernel_error()
+        if self.engine.profile is not None and hasattr(self.engine.profile, "print_summary"):
+            self.engine.profile.print_summary()
+        return done

@@ -19,7 +19,9 @@ import sys
 
 
 def replay_stdin(model_dir: str, dtype: str, out_dir: str, max_tokens: int, page_size: int = 16,
-                 stream=None) -> int:
+                 stream=None, cuda_graphs: bool = False) -> int:
+    """``cuda_graphs``: steps of one token per request replay captured graphs, as generation's
+    decode steps do; off, every step launches its kernels one by one (the same kernels)."""
     import torch
 
     from ..config import EngineOptions
@@ -31,7 +33,7 @@ def replay_stdin(model_dir: str, dtype: str, out_dir: str, max_tokens: int, page
     stream = stream or sys.stdin
     os.makedirs(out_dir, exist_ok=True)
     opts = EngineOptions(dtype=dtype, page_size=page_size, batch_max=8,
-                         num_pages=max(1, (max_tokens + page_size - 1) // page_size), cuda_graphs=False)
+                         num_pages=max(1, (max_tokens + page_size - 1) // page_size), cuda_graphs=cuda_graphs)
     dtype = opts.normalised_dtype()
     model = load_model(model_dir, dtype, opts.device)
     engine = Engine(model, opts)

@@ -67,7 +67,8 @@ class StepRunner:
         self.last_h2d_bytes = int(self._lib.krunner_last_h2d_bytes(self._h))
         if profile is not None:
             self._lib.krunner_phase_ms(self._h, ctypes.addressof(self._phase))
-            profile.add(list(self._phase), int(counts.sum()), int(counts.max()) == 1)
+            profile.add(list(self._phase), int(counts.sum()), int(counts.max()) == 1,
+                        seq=max(self.cache.length(int(r)) for r in ids) + int(counts.max()))
         return logits
 
     @property

@@ -69,6 +69,8 @@ KESTREL_API long long kcache_pages_handed_out(void *h);
 KESTREL_API long long kcache_pages_given_back(void *h);
 /* ids of the requests admitted since the last call (their state slots are to be cleared); returns how many there were */
 KESTREL_API int kcache_take_admitted(void *h, long long *ids, int *slots, int cap);
+/* puts the free pages of every group into a pseudo-random order fixed by `seed` (the layout a pool has after long serving) */
+KESTREL_API int kcache_shuffle_free(void *h, long long seed);
 /* 0 if every page and slot is free exactly once or held exactly once, else a negative code naming the broken invariant */
 KESTREL_API int kcache_check(void *h);
 

@@ -1,5 +1,6 @@
-"""Makes tests/golden/reference_logits.npy: logits of the REFERENCE's own compiled float32
-forward pass on the tiny random model in tests/golden/tiny_model.
+"""Makes tests/golden/reference_logits_<name>.npy: logits of the REFERENCE's own compiled float32
+forward pass on the tiny random models in tests/golden/tiny_model_<name>, for two
+configurations that differ in every size.
 
     python tests/golden/make_reference_golden.py /path/to/kestrel-llm
 
@@ -11,9 +12,13 @@ an int8 shadow of the cache and reads that), and stores the logits after every t
 tests/test_plain_reference.py compares tests/plain_qwen3.py with the stored file, so the
 plain implementation is anchored on the reference's code, not only on its formulas.
 
+Each request is 100 tokens long: from 64 keys on the reference's float32 attention switches
+from its plain loop to the tiled online-softmax kernel (src/model/vllm_safetensors.c:16556-16562,
+9762-9859), so both of its attention paths are the oracle.
+
 Limits of the anchor: one token at a time only; no attention bias; the per-head norm's eps is
-the literal 1e-6 of the reference.  The model folder is written by this script as well (numpy
-generator, seed 7) so that the pair stays consistent.
+the literal 1e-6 of the reference.  The model folders are written by this script as well (numpy
+generator, seeds below) so that each pair stays consistent.
 """
 import json
 import os
@@ -25,11 +30,16 @@ import tempfile
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-CFG = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=32, num_hidden_layers=2,
-           num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=48, vocab_size=64,
-           max_position_embeddings=256, rope_theta=1000000.0, rms_norm_eps=1e-6, hidden_act="silu",
-           tie_word_embeddings=False, attention_bias=False, torch_dtype="bfloat16")
-TOKENS = [3, 61, 17, 17, 0, 42, 9, 33, 58, 21, 7, 12, 63, 1, 30, 45]
+BASE = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", max_position_embeddings=256, rms_norm_eps=1e-6,
+            hidden_act="silu", tie_word_embeddings=False, attention_bias=False, torch_dtype="bfloat16")
+# name -> (configuration, seed of the weights, seed of the tokens)
+CONFIGS = {
+    "a": (dict(BASE, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+               intermediate_size=48, vocab_size=64, rope_theta=1000000.0), 7, 70),
+    "b": (dict(BASE, hidden_size=96, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=2, head_dim=32,
+               intermediate_size=200, vocab_size=509, rope_theta=1000000.0), 8, 80),
+}
+N_TOKENS = 100
 
 
 def bf16_round(a):
@@ -38,9 +48,8 @@ def bf16_round(a):
     return u.view(np.float32)
 
 
-def make_weights():
-    rng = np.random.default_rng(7)
-    c = CFG
+def make_weights(c, seed):
+    rng = np.random.default_rng(seed)
     d, L, nh, nkv, hd, ff, V = (c["hidden_size"], c["num_hidden_layers"], c["num_attention_heads"],
                                 c["num_key_value_heads"], c["head_dim"], c["intermediate_size"], c["vocab_size"])
     W = {}
@@ -86,39 +95,8 @@ def write_safetensors_bf16(path, W):
             f.write(b)
 
 
-def main():
-    if len(sys.argv) < 2:
-        sys.exit("usage: make_reference_golden.py /path/to/kestrel-llm (a checkout of the reference)")
-    ref = sys.argv[1]
-    W = make_weights()
-    mdir = os.path.join(HERE, "tiny_model")
-    os.makedirs(mdir, exist_ok=True)
-    with open(os.path.join(mdir, "config.json"), "w") as f:
-        json.dump(CFG, f, indent=1)
-    write_safetensors_bf16(os.path.join(mdir, "model.safetensors"), W)
-
-    c = CFG
-    L = c["num_hidden_layers"]
-    tmp = tempfile.mkdtemp(prefix="kestrel_golden_")
-    flat = os.path.join(tmp, "in.bin")
-    with open(flat, "wb") as f:
-        f.write(struct.pack("<8i", L, c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"],
-                            c["head_dim"], c["intermediate_size"], c["vocab_size"], len(TOKENS)))
-        f.write(struct.pack("<2f", c["rope_theta"], c["rms_norm_eps"]))
-        f.write(struct.pack(f"<{len(TOKENS)}i", *TOKENS))
-
-        def put(a):
-            f.write(np.ascontiguousarray(a, dtype="<f4").tobytes())
-
-        def stack(suffix):
-            return np.concatenate([W[f"model.layers.{l}.{suffix}"].reshape(-1) for l in range(L)])
-
-        put(W["model.embed_tokens.weight"]); put(W["lm_head.weight"]); put(W["model.norm.weight"])
-        for s in ("input_layernorm.weight", "post_attention_layernorm.weight", "self_attn.q_proj.weight",
-                  "self_attn.k_proj.weight", "self_attn.v_proj.weight", "self_attn.o_proj.weight",
-                  "self_attn.q_norm.weight", "self_attn.k_norm.weight", "mlp.gate_proj.weight",
-                  "mlp.up_proj.weight", "mlp.down_proj.weight"):
-            put(stack(s))
+def build_probe(ref, tmp):
+    """Compiles the reference's model code and the harness; returns the executable."""
     incs = [f"-I{ref}/include/{d}" for d in ("common", "core", "serve", "model", "npu", "npu/rk3588", "media")]
     incs.append(f"-I{ref}/src/model")
     flags = "-std=gnu11 -O1 -D_GNU_SOURCE -mavx2 -mfma -ffp-contract=off -pthread -fopenmp -w".split()
@@ -134,14 +112,54 @@ def main():
         objs.append(o)
     exe = os.path.join(tmp, "probe")
     subprocess.run(["gcc", "-o", exe] + objs + ["-lm", "-pthread", "-fopenmp", "-ldl"], check=True)
-    out = os.path.join(tmp, "out.bin")
+    return exe
+
+
+def run_one(exe, tmp, name, c, wseed, tseed):
+    W = make_weights(c, wseed)
+    tokens = np.random.default_rng(tseed).integers(0, c["vocab_size"], size=N_TOKENS).tolist()
+    mdir = os.path.join(HERE, f"tiny_model_{name}")
+    os.makedirs(mdir, exist_ok=True)
+    with open(os.path.join(mdir, "config.json"), "w") as f:
+        json.dump(c, f, indent=1)
+    write_safetensors_bf16(os.path.join(mdir, "model.safetensors"), W)
+    L = c["num_hidden_layers"]
+    flat = os.path.join(tmp, f"in_{name}.bin")
+    with open(flat, "wb") as f:
+        f.write(struct.pack("<8i", L, c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"],
+                            c["head_dim"], c["intermediate_size"], c["vocab_size"], len(tokens)))
+        f.write(struct.pack("<2f", c["rope_theta"], c["rms_norm_eps"]))
+        f.write(struct.pack(f"<{len(tokens)}i", *tokens))
+
+        def put(a):
+            f.write(np.ascontiguousarray(a, dtype="<f4").tobytes())
+
+        def stack(suffix):
+            return np.concatenate([W[f"model.layers.{l}.{suffix}"].reshape(-1) for l in range(L)])
+
+        put(W["model.embed_tokens.weight"]); put(W["lm_head.weight"]); put(W["model.norm.weight"])
+        for s in ("input_layernorm.weight", "post_attention_layernorm.weight", "self_attn.q_proj.weight",
+                  "self_attn.k_proj.weight", "self_attn.v_proj.weight", "self_attn.o_proj.weight",
+                  "self_attn.q_norm.weight", "self_attn.k_norm.weight", "mlp.gate_proj.weight",
+                  "mlp.up_proj.weight", "mlp.down_proj.weight"):
+            put(stack(s))
+    out = os.path.join(tmp, f"out_{name}.bin")
     env = dict(os.environ, VLLM_KV_F32="1", VLLM_THREADS="1", OMP_NUM_THREADS="1")
     subprocess.run([exe, flat, out], check=True, env=env, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
-    logits = np.fromfile(out, dtype="<f4").reshape(len(TOKENS), c["vocab_size"])
-    np.save(os.path.join(HERE, "reference_logits.npy"), logits)
-    with open(os.path.join(HERE, "reference_tokens.json"), "w") as f:
-        json.dump(TOKENS, f)
-    print("wrote", logits.shape, "max |logit|", float(np.abs(logits).max()))
+    logits = np.fromfile(out, dtype="<f4").reshape(len(tokens), c["vocab_size"])
+    np.save(os.path.join(HERE, f"reference_logits_{name}.npy"), logits)
+    with open(os.path.join(HERE, f"reference_tokens_{name}.json"), "w") as f:
+        json.dump(tokens, f)
+    print(name, "wrote", logits.shape, "max |logit|", float(np.abs(logits).max()))
+
+
+def main():
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_reference_golden.py /path/to/kestrel-llm (a checkout of the reference)")
+    tmp = tempfile.mkdtemp(prefix="kestrel_golden_")
+    exe = build_probe(sys.argv[1], tmp)
+    for name, (c, wseed, tseed) in CONFIGS.items():
+        run_one(exe, tmp, name, c, wseed, tseed)
 
 
 if __name__ == "__main__":

@@ -1,25 +1,31 @@
 """The plain implementation against the reference's own compiled float32 forward pass.
 
-tests/golden/reference_logits.npy was written once by tests/golden/make_reference_golden.py,
+tests/golden/reference_logits_<name>.npy were written by tests/golden/make_reference_golden.py,
 which builds six of the reference's C files on the CPU and runs st_qwen_model_forward token by
-token on tests/golden/tiny_model.  This test needs neither the reference nor a GPU."""
+token on tests/golden/tiny_model_<name>: two configurations that differ in every size, 100
+tokens each, so that the reference's attention for fewer than 64 keys and its tiled kernel for
+more are both the oracle.  This test needs neither the reference nor a GPU."""
 import json
 import os
 
 import numpy as np
+import pytest
 
 import plain_qwen3 as P
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-def test_plain_matches_reference_code():
-    cfg, W = P.read_model(os.path.join(GOLD, "tiny_model"))
-    tokens = json.load(open(os.path.join(GOLD, "reference_tokens.json")))
-    ref = np.load(os.path.join(GOLD, "reference_logits.npy"))
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_plain_matches_reference_code(name):
+    cfg, W = P.read_model(os.path.join(GOLD, f"tiny_model_{name}"))
+    tokens = json.load(open(os.path.join(GOLD, f"reference_tokens_{name}.json")))
+    ref = np.load(os.path.join(GOLD, f"reference_logits_{name}.npy"))
+    assert len(tokens) >= 96                                     # beyond the reference's switch of attention kernels at 64 keys
     mine = P.forward_logits(cfg, W, tokens)
     assert mine.shape == ref.shape
-    assert np.abs(mine - ref).max() <= 2e-6 * max(1.0, np.abs(ref).max())
+    err = np.abs(mine - ref).max(axis=1)
+    assert err.max() <= 2e-6 * max(1.0, np.abs(ref).max()), f"first wrong position {int((err > 2e-6).argmax())}: {err.max():.2e}"
     assert (mine.argmax(1) == ref.argmax(1)).all()
     # the comparison can fail: a different rope base must show
     cfg2 = dict(cfg, rope_theta=10000.0)

@@ -107,9 +107,12 @@ def test_cuttings_agree_with_each_other(model_dirs, dtype):
                 assert err <= tol, f"request {rname} position {p}: cuttings differ by {err:.3e}"
 
 
+@pytest.mark.parametrize("graphs", [1, 0])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_trace_run_program(model_dirs, dtype, tmp_path):
-    """bin/trace_run as a user calls it: JSON lines in, <step>.f32 files and `done` lines out."""
+def test_trace_run_program(model_dirs, dtype, graphs, tmp_path):
+    """bin/trace_run as a user calls it: JSON lines in, <step>.f32 files and `done` lines out;
+    with decode steps replayed from captured graphs (the default, what generation runs) and
+    launched kernel by kernel."""
     name = "A"
     reqs = _requests(name)
     steps, max_tokens = R.trace_mixed(reqs, seed=3)
@@ -117,7 +120,7 @@ def test_trace_run_program(model_dirs, dtype, tmp_path):
     lines = "".join(json.dumps(dict(step=i, **s)) + "\n" for i, s in enumerate(steps))
     out = tmp_path / "out"
     p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model_dirs[name][dtype],
-                        "--dtype", dtype, "--out", str(out), "--max-tokens", str(max_tokens)],
+                        "--dtype", dtype, "--out", str(out), "--max-tokens", str(max_tokens), "--cuda-graphs", str(graphs)],
                        input=lines, capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
     assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
