@@ -13,7 +13,8 @@ Names and meanings taken over from the reference (src/main.c:4491-4850):
   --top-k N, --min-p X   sampling filters (main.c:4567-4573)
   --repetition-penalty P, --repetition-window N   the harness's penalty on the last N generated
                          tokens (main.c:3741-3782; defaults from VLLM_STREAM_REPPEN / VLLM_STREAM_REPWIN)
-Added for this engine: --dtype, --prompt-ids, --prompt-file, --random-prompts N:LEN:SEED,
+Added for this engine: --plugin MODULE (imported first; it may register architectures of its
+own), --profile, --debug-guards, --cuda-graphs 0|1, --dtype, --prompt-ids, --prompt-file, --random-prompts N:LEN:SEED,
 --temperature, --top-p, --seed, --ignore-eos, --page-size, --max-tokens, --max-model-len,
 --max-step-tokens, --random-weights SEED with --config FILE (writes the folder to --model
 first), --replay (reads a trace on standard input, as bin/trace_run does, with --out DIR).
@@ -79,6 +80,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-step-tokens", type=int, default=2048)
     ap.add_argument("--random-weights", type=int, default=None, metavar="SEED")
     ap.add_argument("--config", default=None, help="config.json for --random-weights")
+    ap.add_argument("--plugin", action="append", default=[], metavar="MODULE",
+                    help="import this module first; it may register architectures and parts of its own (may be given several times)")
     ap.add_argument("--profile", action="store_true", help="time every step's phases on the device and print [DEC-SINGLE] / [PREFILL-TIMING] lines")
     ap.add_argument("--debug-guards", action="store_true", help="check every step's description on the device and guard words behind every activation")
     ap.add_argument("--cuda-graphs", type=int, default=1, help="0: launch decode steps kernel by kernel instead of replaying captured graphs")
@@ -104,6 +107,9 @@ def _prompts(args, vocab: int):
 
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
+    import importlib
+    for name in args.plugin:                  # architectures and parts from outside the package register themselves on import
+        importlib.import_module(name)
     from . import LLM, SamplingParams
     from .config import EngineOptions, Qwen3Config, read_config_json, resolve_architecture, architecture_of
     from .weights import write_random_model
@@ -129,8 +135,11 @@ def main(argv=None) -> int:
               max_model_len=args.max_model_len, seed=args.seed, profile=args.profile, debug_guards=args.debug_guards,
               cuda_graphs=bool(args.cuda_graphs))
     c = llm.model.config
-    print(f"[STREAM] load OK ({time.perf_counter() - t0:.2f}s): dim={c.hidden_size} layers={c.num_hidden_layers} "
-          f"heads={c.num_attention_heads} kv={c.num_key_value_heads} vocab={c.vocab_size} dtype={args.dtype}", flush=True)
+    # sizes every architecture's configuration has; head counts where this one names them
+    heads = "".join(f" {tag}={getattr(c, key)}" for tag, key in (("heads", "num_attention_heads"), ("kv", "num_key_value_heads"))
+                    if hasattr(c, key))
+    print(f"[STREAM] load OK ({time.perf_counter() - t0:.2f}s): arch={c.architecture} dim={c.hidden_size} "
+          f"layers={c.num_hidden_layers}{heads} vocab={c.vocab_size} dtype={args.dtype}", flush=True)
     prompts = _prompts(args, c.vocab_size)
     if args.stream_ctx > 0:
         prompts = [(p * (args.stream_ctx // len(p) + 1))[:args.stream_ctx] for p in prompts]

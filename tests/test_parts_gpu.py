@@ -3,7 +3,6 @@ parts compose: a toy mixer with state of its own, a toy position encoding and a 
 feed-forward are defined HERE, registered, built and stepped without a change to the
 package; the order of layers is data (a block runs twice, a layer reads another's cache) (GPU)."""
 import math
-from dataclasses import dataclass
 
 import numpy as np
 import pytest
@@ -111,169 +110,90 @@ def test_block_embedding_and_head(model_dirs, dtype):
     np.testing.assert_allclose(lg, refl, rtol=0, atol=TOL[dtype] * np.abs(refl).max() + 1e-6)
 
 
-# ---- toy parts, defined in the test ----------------------------------------------------------
+# ---- toy parts, defined in the tests (tests/toy_architecture.py) ------------------------------
 
-def _toy_parts():
-    from kestrel_llm_b200.csrc import ops
-    from kestrel_llm_b200.parts import FeedForward, FixedStateSpec, Mixer, PositionEncoding, WeightSlot
-
-    class RunningMeanMixer(Mixer):
-        """out[t] = W * mean(x[0..t]) of the request: needs a running sum per request, kept in a
-        fixed-size state slot; no pages."""
-
-        def __init__(self, width, dtype, device, prefix):
-            self.width, self.dtype, self.prefix = width, dtype, prefix
-            self.weight = torch.empty((width, width), dtype=dtype, device=device)
-
-        def cache_spec(self):
-            return FixedStateSpec((self.width,), torch.float32)
-
-        def weight_slots(self):
-            return [WeightSlot(self.prefix + "mix.weight", self.weight)]
-
-        def forward(self, x, batch, cache):
-            outs = []
-            cu = batch.cu_seqlens_host
-            for i in range(batch.num_seqs):
-                b, e = cu[i], cu[i + 1]
-                slot = batch.slots_host[i]
-                cs = cache.state[slot] + torch.cumsum(x[b:e].float(), 0)
-                cache.state[slot] = cs[-1]
-                outs.append(cs / (batch.positions[b:e].float() + 1)[:, None])
-            mean = torch.cat(outs).to(self.dtype)
-            return ops.Partials(ops.linear(mean, self.weight))
-
-    class LearnedPositions(PositionEncoding):
-        """An absolute encoding: a table row per position, added to the embedded tokens."""
-
-        def __init__(self, max_pos, width, device):
-            self.table = torch.empty((max_pos, width), dtype=torch.float32, device=device)
-
-        def weight_slots(self):
-            return [WeightSlot("model.positions.weight", self.table)]
-
-        def add_to_embedding(self, x, batch):
-            x += self.table[batch.positions.long()]
-
-    class RoutedFeedForward(FeedForward):
-        """Two experts, each token goes to the one its router scores higher."""
-
-        def __init__(self, width, inner, dtype, device, prefix):
-            self.dtype, self.prefix = dtype, prefix
-            self.router = torch.empty((2, width), dtype=dtype, device=device)
-            self.up = [torch.empty((inner, width), dtype=dtype, device=device) for _ in range(2)]
-            self.down = [torch.empty((width, inner), dtype=dtype, device=device) for _ in range(2)]
-
-        def weight_slots(self):
-            s = [WeightSlot(self.prefix + "router.weight", self.router)]
-            for e in range(2):
-                s += [WeightSlot(f"{self.prefix}experts.{e}.up.weight", self.up[e]),
-                      WeightSlot(f"{self.prefix}experts.{e}.down.weight", self.down[e])]
-            return s
-
-        def forward(self, x, batch):
-            score = ops.linear(x, self.router).sum(0)
-            pick = score.argmax(1)
-            out = torch.zeros((x.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
-            for e in range(2):
-                idx = (pick == e).nonzero().flatten()
-                if idx.numel():
-                    h = torch.relu(ops.linear(x[idx].contiguous(), self.up[e]).sum(0)).to(self.dtype)
-                    out[idx] = ops.linear(h, self.down[e]).sum(0)
-            return ops.Partials(out)
-
-    return RunningMeanMixer, LearnedPositions, RoutedFeedForward
-
-
-@dataclass(frozen=True)
-class _ToyConfigBase:
-    pass
-
-
-def _register_toy():
-    from kestrel_llm_b200.config import Qwen3Config, register_architecture
-    from kestrel_llm_b200.models import DecoderModel, LayerCall
-    from kestrel_llm_b200.parts import (GatedMLP, GroupedQueryAttention, LMHead, PreNormBlock, RMSNorm,
-                                        TokenEmbedding)
-    Mean, Learned, Routed = _toy_parts()
-
-    def build(c, dtype, device):
-        emb = TokenEmbedding(c.vocab_size, c.hidden_size, dtype, device, "model.embed_tokens.weight")
-        pos = Learned(c.max_position_embeddings, c.hidden_size, device)
-        blocks = []
-        for i in range(c.num_hidden_layers):
-            p = f"model.layers.{i}."
-            if i % 2 == 0:
-                mixer = Mean(c.hidden_size, dtype, device, p)
-                ffn = Routed(c.hidden_size, c.intermediate_size, dtype, device, p + "moe.")
-            else:        # attention without rotation: positions come from the learned table
-                mixer = GroupedQueryAttention(c.hidden_size, c.num_attention_heads, c.num_key_value_heads,
-                                              c.head_dim, dtype, device, p + "self_attn.", None, None)
-                ffn = GatedMLP(c.hidden_size, c.intermediate_size, dtype, device, p + "mlp.")
-            blocks.append(PreNormBlock(RMSNorm(c.hidden_size, c.rms_norm_eps, device, p + "n1.weight"), mixer,
-                                       RMSNorm(c.hidden_size, c.rms_norm_eps, device, p + "n2.weight"), ffn, dtype))
-        order = [LayerCall(i, i) for i in range(c.num_hidden_layers)]
-        return DecoderModel(c, dtype, device, emb, pos, blocks, order,
-                            RMSNorm(c.hidden_size, c.rms_norm_eps, device, "model.norm.weight"),
-                            LMHead(c.vocab_size, c.hidden_size, dtype, device, "lm_head.weight"))
-
-    register_architecture("ToyStateForCausalLM", Qwen3Config, build)
-
-
-def _toy_reference(W, cfg, toks):
-    """The toy model, whole sequence, in numpy."""
-    T = len(toks)
-    pos = np.arange(T)
-    x = W["model.embed_tokens.weight"][toks] + W["model.positions.weight"][pos]
-    for i in range(cfg["num_hidden_layers"]):
-        p = f"model.layers.{i}."
-        n = P.rms_norm(x, W[p + "n1.weight"], cfg["rms_norm_eps"])
-        if i % 2 == 0:
-            mean = np.cumsum(n, 0) / (pos + 1)[:, None].astype(np.float32)
-            x = x + P.linear(mean.astype(np.float32), W[p + "mix.weight"])
-            n = P.rms_norm(x, W[p + "n2.weight"], cfg["rms_norm_eps"])
-            pick = P.linear(n, W[p + "moe.router.weight"]).argmax(1)
-            y = np.zeros_like(x)
-            for e in range(2):
-                h = np.maximum(P.linear(n, W[f"{p}moe.experts.{e}.up.weight"]), 0)
-                y[pick == e] = P.linear(h, W[f"{p}moe.experts.{e}.down.weight"])[pick == e]
-            x = x + y
-        else:
-            nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
-            a = p + "self_attn."
-            q = P.linear(n, W[a + "q_proj.weight"]).reshape(T, nh, hd)
-            k = P.linear(n, W[a + "k_proj.weight"]).reshape(T, nkv, hd)
-            v = P.linear(n, W[a + "v_proj.weight"]).reshape(T, nkv, hd)
-            x = x + P.linear(P.causal_attention(q, k, v).reshape(T, nh * hd), W[a + "o_proj.weight"])
-            n = P.rms_norm(x, W[p + "n2.weight"], cfg["rms_norm_eps"])
-            x = x + P.gated_mlp(n, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"], W[p + "mlp.down_proj.weight"])
-    return P.linear(P.rms_norm(x, W["model.norm.weight"], cfg["rms_norm_eps"]), W["lm_head.weight"])
+def _toy_folder(tmp_path, seed=11):
+    """The toy architecture written to a folder by the random-weights mode, from its own
+    configuration class; returns (folder, config.json dict, tensors)."""
+    import toy_architecture as toy
+    from kestrel_llm_b200.weights import write_random_model
+    cfg = toy.register().from_dict(dict(toy.RAW))
+    d = write_random_model(cfg, seed, str(tmp_path / "toy"), "float32")
+    pcfg, W = toy.read_folder(d)
+    assert set(pcfg) >= {"width", "depth", "rotary_scale"} and "hidden_size" not in pcfg     # its own keys
+    return d, pcfg, W
 
 
 def test_toy_architecture_is_registered_built_and_stepped(tmp_path):
-    """A mixer with state of its own, a feed-forward with routing and another position
-    encoding, none of them in the package: written to a folder by the random-weights mode,
-    loaded by name through the registry, stepped whole, token by token and in portions with
-    two requests interleaved; all agree with a numpy statement of the toy model."""
-    from kestrel_llm_b200.config import Qwen3Config
-    from kestrel_llm_b200.weights import write_random_model
-    _register_toy()
-    raw = dict(tiny_configs.B, architectures=["ToyStateForCausalLM"], num_hidden_layers=4, attention_bias=False,
-               max_position_embeddings=128)
-    cfg = Qwen3Config.from_dict(raw)
-    d = write_random_model(cfg, 11, str(tmp_path / "toy"), "float32")
-    pcfg, W = P.read_model(d)
-    reqs = R.random_requests(cfg.vocab_size, (40, 23, 64), seed=4)
-    refs = {n: _toy_reference(W, pcfg, t) for n, t in reqs.items()}
+    """A mixer with state of its own, a feed-forward with routing, a learned position table and
+    a rotation of another form (adjacent pairs, part of a head, scaled), with a configuration
+    class of their own, none of them in the package: written to a folder by the random-weights
+    mode, loaded by name through the registry, stepped whole, token by token and in portions with
+    several requests interleaved; all agree with a numpy statement of the toy model.  The model
+    has parts without a step program, so its steps walk the parts' forward methods."""
+    import toy_architecture as toy
+    d, pcfg, W = _toy_folder(tmp_path)
+    reqs = R.random_requests(pcfg["vocab"], (40, 23, 64), seed=4)
+    refs = {n: toy.reference_logits(W, pcfg, t) for n, t in reqs.items()}
     for family in (R.trace_whole, R.trace_tail_decode, R.trace_portions, R.trace_mixed):
         steps, max_tokens = family(reqs)
         engine = R.make_engine(d, "float32", max_tokens)
+        assert engine.runner is None
         assert [type(s).__name__ for s in engine.model.cache_specs()] == ["FixedStateSpec", "PagedKVSpec"] * 2
         got = R.run_trace(engine, steps)
         for n, toks in reqs.items():
             for p in range(len(toks)):
                 err = np.abs(got[n][p] - refs[n][p]).max() / np.abs(refs[n]).max()
                 assert err < 2e-5, f"{family.__name__}: request {n} position {p}: {err:.2e}"
+
+
+def test_toy_generation_reuses_state_slots_and_survives_preemption(tmp_path):
+    """Through `LLM.generate`, where the native scheduler admits requests on its own: more
+    requests than state slots, so slots are reused by later requests, and so few pages that
+    requests are preempted and start again from position 0.  A slot that kept its last owner's
+    running sum would change the tokens; they are those of the numpy model."""
+    import toy_architecture as toy
+    from kestrel_llm_b200 import LLM, SamplingParams
+    d, pcfg, W = _toy_folder(tmp_path)
+    prompts = list(R.random_requests(pcfg["vocab"], (21, 9, 30, 14, 25), seed=6).values())
+    sp = SamplingParams(temperature=0.0, max_tokens=14, ignore_eos=True)
+    want = [toy.greedy_continuation(W, pcfg, p, 14) for p in prompts]
+    roomy = LLM(d, dtype="float32", page_size=16, batch_max=2, max_tokens=512)
+    outs = roomy.generate(prompts, sp)
+    assert [o.token_ids for o in outs] == want
+    tight = LLM(d, dtype="float32", page_size=16, batch_max=3, num_pages=6)        # 96 tokens for up to 3 requests of up to 44
+    outs = tight.generate(prompts, sp)
+    assert tight.scheduler.num_preemptions > 0
+    assert [o.token_ids for o in outs] == want
+    tight.engine.cache.check()
+
+
+def test_toy_architecture_through_the_command_line(tmp_path):
+    """bin/kestrel in a process of its own: `--plugin` imports the module that registers the toy
+    architecture, `--random-weights` writes its folder from a config.json with the toy's own
+    keys, and the streaming harness prints the numpy model's greedy tokens."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import toy_architecture as toy
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg_file = tmp_path / "toy_config.json"
+    cfg_file.write_text(json.dumps(toy.RAW))
+    model_dir = tmp_path / "toy_cli"
+    prompt = R.random_requests(toy.RAW["vocab"], (19,), seed=2)["r0"]
+    env = dict(os.environ, PYTHONPATH=os.path.join(root, "tests") + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "kestrel"), "--plugin", "toy_architecture", "--model", str(model_dir),
+                        "--config", str(cfg_file), "--random-weights", "5", "--dtype", "float32", "--stream-test", "--stream-n", "10",
+                        "--prompt-ids", ",".join(str(t) for t in prompt), "--ignore-eos", "--max-tokens", "256", "--batch-max", "2"],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    line = [l for l in p.stdout.splitlines() if l.startswith("[STREAM] TOKIDS:")]
+    assert len(line) == 1
+    pcfg, W = toy.read_folder(str(model_dir))
+    # the folder stores bfloat16 (the command line's random-weights mode); the float32 engine widens it exactly
+    assert [int(t) for t in line[0].split(":")[1].split()] == toy.greedy_continuation(W, pcfg, prompt, 10)
+    assert any(l.startswith("[STREAM] metrics request=") for l in p.stdout.splitlines())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
