@@ -135,7 +135,7 @@ def build_host(verbose: bool = True) -> str:
     """Path of libkestrel_host.so, compiling it if its sources changed."""
     out = build_dir()
     srcs = _sources(HOST_DIR, (".cpp",))
-    deps = srcs + _sources(HOST_DIR, (".h", ".hpp")) + [HEADER]
+    deps = srcs + _sources(HOST_DIR, (".h", ".hpp")) + [HEADER, os.path.join(KERNEL_DIR, "step_checks.cuh")]
     digest = _digest(deps, GXX_FLAGS)
     lib = os.path.join(out, "libkestrel_host.so")
     stamp = lib + ".stamp"

@@ -17,6 +17,7 @@
 #include <algorithm>
 
 #include "../../include/kestrel.h"
+#include "../kernels/step_checks.cuh"
 
 namespace {
 
@@ -119,4 +120,21 @@ KESTREL_API int kbatch_pack(void *cache, int n, const long long *ids, const int 
     layout[KB_O_MAX_KV] = o_maxkv;
     layout[KB_O_TABLES] = o_tab;
     return (int)total;
+}
+
+// The predicate of the runner's debug guards, on the host: walks every token of a packed
+// description and returns 0 if the kernels can place it, else (rule << 16) | (token & 0xffff)
+// for the first token that breaks a rule (STEP_CHECK_* in csrc/kernels/step_checks.cuh: 1 token
+// id, 2 request index, 3 position, 4 block-table column, 5 page id, 6 token outside its request's
+// rows).  `pages` holds the number of pages of each group's tensors.  Tests hand this bad
+// descriptions; no kernel ever sees them.
+KESTREL_API int kbatch_check(const int *batch, const int *layout, int vocab, int page_size, const int *pages) {
+    if (!batch || !layout || !pages || page_size <= 0) return -2;
+    StepCheckLayout lay = step_check_layout(layout, vocab, page_size);
+    for (int g = 0; g < lay.num_groups && g < STEP_CHECK_MAX_GROUPS; ++g) lay.pages[g] = pages[g];
+    for (int t = 0; t < lay.num_tokens; ++t) {
+        int code = kestrel_check_token(batch, lay, t);
+        if (code) return code * 65536 + (t & 0xffff);
+    }
+    return 0;
 }

@@ -10,7 +10,10 @@
 //   2. what is left of the step's token budget goes to prompt portions of running requests,
 //      oldest first, each at most `prefill_chunk` tokens;
 //   3. then waiting requests are admitted in arrival order while a state slot is free, the
-//      live-request limit is not reached and pages for their first portion exist.
+//      live-request limit is not reached and free pages exist for all the tokens they have so
+//      far (their prompt, and what they had generated if they were preempted): a request that
+//      only its first portion fits would be preempted again a few steps later.  A request is not
+//      admitted by the same call that preempted it.
 //
 // When pages run out for a running request, the youngest running request (the last one
 // admitted) gives back everything it holds and returns to the FRONT of the waiting queue;
@@ -167,10 +170,11 @@ KESTREL_API int ksched_schedule(void *h, long long *ids_out, int *starts_out, in
     while (!s.waiting.empty() && budget > 0 && (int)s.running.size() < s.batch_max &&
            kcache_free_slots(s.cache) > 0) {
         Req r = s.waiting.front();
+        if (std::find(s.preempted.begin(), s.preempted.end(), r.id) != s.preempted.end()) break;
         int left = r.known - r.computed;
         int n = std::min(std::min(left, s.prefill_chunk), budget);
         if (kcache_admit(s.cache, r.id) < 0) break;
-        if (kcache_can_reserve(s.cache, r.id, n) != 1) {
+        if (kcache_can_reserve(s.cache, r.id, left) != 1) {
             kcache_release(s.cache, r.id);
             break;                      // arrival order is kept: nobody overtakes the head
         }

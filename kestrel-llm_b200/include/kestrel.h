@@ -126,6 +126,11 @@ KESTREL_API int kbatch_ints_needed(void *cache, int n, const long long *ids, con
  * Returns the ints written, or -2 bad argument, -3 unknown request, -9 buffer too small. */
 KESTREL_API int kbatch_pack(void *cache, int n, const long long *ids, const int *counts, const int *tokens, const int *want_counts, const int *wants, int table_width, int *out, int cap, int *layout);
 
+/* the check of the runner's debug guards, on the host: 0 if every token of the packed description can be placed by the kernels,
+ * else (rule << 16) | (token & 0xffff) for the first that cannot (rules: 1 token id, 2 request index, 3 position,
+ * 4 block-table column, 5 page id, 6 token outside its request's rows); pages[g] = pages of group g's tensors */
+KESTREL_API int kbatch_check(const int *batch, const int *layout, int vocab, int page_size, const int *pages);
+
 /* ============================================================================================
  * Kernel library (libkestrel_cuda.so): runtime
  * ========================================================================================== */

@@ -60,13 +60,20 @@ class SafetensorsFile:
             n = 1
             for s in shape:
                 n *= s
-            if b < 0 or e < b or self._base + e > size:
+            if e < b:
+                raise WeightsError(f"{path}: tensor '{name}' has its data_offsets in the wrong order ({b}, {e})")
+            if b < 0 or self._base + e > size:
                 raise WeightsError(f"{path}: tensor '{name}' lies outside the file "
                                    f"(offsets {b}..{e}, data section {size - self._base} bytes)")
             if e - b != n * _DTYPES[dt][1]:
                 raise WeightsError(f"{path}: tensor '{name}' of shape {list(shape)} {dt} needs "
                                    f"{n * _DTYPES[dt][1]} bytes, header gives {e - b}")
             self.entries[name] = (dt, shape, b, e)
+        # no byte of the data section may belong to two tensors
+        spans = sorted((b, e, name) for name, (_dt, _shape, b, e) in self.entries.items() if e > b)
+        for (b0, e0, n0), (b1, e1, n1) in zip(spans, spans[1:]):
+            if b1 < e0:
+                raise WeightsError(f"{path}: tensors '{n0}' (bytes {b0}..{e0}) and '{n1}' (bytes {b1}..{e1}) overlap")
 
     def names(self) -> List[str]:
         return list(self.entries)

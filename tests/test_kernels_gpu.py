@@ -302,6 +302,11 @@ def test_embed(dtype):
     np.testing.assert_array_equal(out.cpu().numpy(), tr[[300, 0, 17, 17]])
 
 
+def _r16(a):
+    """The values a bfloat16 tensor holds, as float32."""
+    return torch.from_numpy(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy()
+
+
 def _paged(dense_k, dense_v, page_size, num_pages, seed):
     """Scatter dense [L, nkv, hd] keys/values of ONE request into pages picked at random.
     Unused slots are filled with large numbers so that a read beyond the request shows."""
@@ -660,6 +665,43 @@ def test_attention_mma_window_edge():
         got = out.float().cpu().numpy().reshape(nq, hd)
         close = np.abs(got - v[spot]).max() < 3e-2
         assert close == inside, f"key at distance {offset} (window {window}): inside={inside}, output follows it={close}"
+
+
+@pytest.mark.parametrize("rows", [128, 256])
+def test_attention_tcgen05_window_edge(rows):
+    """The prompt-portion kernel at a window's edge: for the query in the LAST row of a row tile,
+    one key stands out; at distance window - 1 the output follows it, at distance window it must
+    not.  Pages that lie behind the window for every query of the portion are gone (-1)."""
+    ops = _ops()
+    ctx, new, nq, nkv, hd, page, window = 128, 272, 2, 2, 128, 16, 48
+    L = ctx + new
+    probe = rows - 1                                   # row of the portion under test (one row a token: nq == nkv)
+    for offset, inside in ((window - 1, True), (window, False)):
+        rng = np.random.default_rng(7)
+        k = rng.normal(size=(L, nkv, hd)).astype(np.float32) * 0.1
+        v = rng.normal(size=(L, nkv, hd)).astype(np.float32)
+        q = rng.normal(size=(new, nq, hd)).astype(np.float32) * 0.1
+        q[probe] = 4.0
+        spot = ctx + probe - offset
+        k[spot] = 4.0
+        kc, vc, pages = _paged(k, v, page, 40, 3)
+        pages = pages.copy()
+        pages[: (ctx - window + 1) // page] = -1      # behind the window of the portion's first query
+        dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+        tiles = list(range(0, new * (nq // nkv), rows))
+        out = torch.full((new, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.attention_tc(torch.from_numpy(q.reshape(new, -1)).to(torch.bfloat16).to(DEV),
+                         torch.from_numpy(kc).to(torch.bfloat16).to(DEV), torch.from_numpy(vc).to(torch.bfloat16).to(DEV),
+                         out, dev([0] * len(tiles)), dev(tiles), dev([0, new]), dev([L]), dev(pages[None, :]), page, nq, nkv, hd,
+                         window, 1.0 / math.sqrt(hd), rows_per_tile=rows)
+        assert ops.attention_tc_error() == 0
+        got = out.float().cpu().numpy().reshape(new, nq, hd)
+        assert np.isfinite(got).all()
+        close = np.abs(got[probe] - v[spot]).max() < 3e-2
+        assert close == inside, f"rows {rows}: key at distance {offset} (window {window}): inside={inside}, output follows it={close}"
+        # every other row agrees with the plain attention of the window
+        ref = P.causal_attention(np.concatenate([np.zeros((ctx, nq, hd), np.float32), _r16(q)]), _r16(k), _r16(v), window)[ctx:]
+        np.testing.assert_allclose(got, ref, rtol=0, atol=2e-2 * np.abs(ref).max())
 
 
 def test_attention_mma_refuses_odd_head_sizes():

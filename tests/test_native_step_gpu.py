@@ -61,3 +61,49 @@ def test_debug_guards_stay_quiet_on_valid_steps(model_dirs, name, dtype):
     for rname, toks in reqs.items():
         for p in range(len(toks)):
             assert np.array_equal(a[rname][p], b[rname][p])
+
+
+def test_profile_prints_the_reference_lines(model_dirs, capsys):
+    """`EngineOptions.profile`: every step's phases are timed on the device and printed in the
+    reference's formats - `[PREFILL-TIMING]` / `[PREFILL-KERNELS]` for steps with prompt portions,
+    `[DEC-SINGLE]` for steps of single tokens - and the tokens are those of the unprofiled run."""
+    import re
+    from kestrel_llm_b200 import LLM, SamplingParams
+    prompts = list(R.random_requests(509, (40, 9), seed=3).values())
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    plain = LLM(model_dirs["B"]["bfloat16"], dtype="bfloat16", max_tokens=512, batch_max=2).generate(prompts, sp)
+    capsys.readouterr()
+    llm = LLM(model_dirs["B"]["bfloat16"], dtype="bfloat16", max_tokens=512, batch_max=2, profile=True)
+    outs = llm.generate(prompts, sp)
+    err = capsys.readouterr().err
+    assert [o.token_ids for o in outs] == [o.token_ids for o in plain]
+    pre = re.findall(r"\[PREFILL-TIMING\] n=(\d+) total=([0-9.]+)ms \| GEMM=([0-9.]+)ms\(.*?\) ATTN=([0-9.]+)ms\(.*?\) OTHER=([0-9.]+)ms", err)
+    assert pre and int(pre[0][0]) == 49 and float(pre[0][1]) > 0 and float(pre[0][2]) > 0
+    from kestrel_llm_b200.csrc import ops
+    prof = llm.engine.profile            # the line prints tenths of a millisecond; the sums behind it are finer
+    assert all(prof.prefill_ms[ops.PHASES[k]] > 0 for k in ("qkv", "attn", "o", "gate_up", "down", "norm", "rope", "lm_head", "embed"))
+    assert "[PREFILL-KERNELS] QKV=" in err
+    dec = re.findall(r"\[DEC-SINGLE\] seq=(\d+) qkv=([0-9.]+) attn=([0-9.]+) o=([0-9.]+) gu=([0-9.]+) down=([0-9.]+) lm=([0-9.]+) nrm=([0-9.]+) rope=([0-9.]+)", err)
+    assert len(dec) == 5 and all(prof.decode_ms[ops.PHASES[k]] > 0 for k in ("qkv", "attn", "o", "gate_up", "down", "norm", "rope", "lm_head"))
+    assert llm.engine.profile.decode_steps == 5 and llm.engine.profile.prefill_steps == 1
+
+
+def test_request_metrics_and_cache_occupancy(model_dirs):
+    """Every finished request carries the reference's six numbers (VLLMMetrics), and the pool's
+    occupancy can be read while requests are live."""
+    from kestrel_llm_b200 import LLM, SamplingParams
+    llm = LLM(model_dirs["B"]["bfloat16"], dtype="bfloat16", max_tokens=512, batch_max=4, page_size=16)
+    prompts = list(R.random_requests(509, (30, 5, 64), seed=9).values())
+    rids = [llm.add_request(p, SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True)) for p, n in zip(prompts, (7, 1, 12))]
+    first = {o.request_id: o for o in llm.step()}          # the request that wants one token is over after the first step
+    occ = llm.cache_occupancy()
+    assert list(first) == [rids[1]] and occ["live_requests"] == 2 and occ["running"] == 2 and occ["waiting"] == 0
+    assert occ["groups"][0]["free"] < occ["groups"][0]["pages"] and occ["page_size"] == 16
+    done = {**first, **llm.run_until_done()}
+    for rid, p, n in zip(rids, prompts, (7, 1, 12)):
+        m = done[rid].metrics
+        assert m.prompt_tokens == len(p) and m.n_tokens == n == len(done[rid].token_ids)
+        assert 0 < m.prefill_ms <= m.ttft_ms <= m.total_ms
+        assert (m.tpot_ms == m.ttft_ms) if n == 1 else abs(m.tpot_ms * (n - 1) - (m.total_ms - m.ttft_ms)) < 1e-6
+    occ = llm.cache_occupancy()
+    assert occ["live_requests"] == 0 and occ["groups"][0]["free"] == occ["groups"][0]["pages"]

@@ -112,10 +112,11 @@ def test_pages_run_out_the_youngest_yields_and_is_computed_again():
 
 
 def test_stuck_prompts_resolve():
-    # two prompts admitted side by side fill the pool before either is complete
+    # two prompts admitted side by side fill the pool before either is complete: the second was
+    # admitted while its 20 tokens fitted what was free, but the first still grows
     pt, s = make(pages=8, page_size=4, budget=16, chunk=8)        # 32 tokens
     s.add(1, 28, 2)
-    s.add(2, 28, 2)
+    s.add(2, 20, 2)
     seen_preempt = False
     done = []
     for _ in range(40):
@@ -126,3 +127,22 @@ def test_stuck_prompts_resolve():
         done += run_step(pt, s, p)
     assert seen_preempt and done == [1, 2]
     assert pt.free_pages(0) == 8
+
+
+def test_a_request_is_admitted_only_if_all_its_tokens_fit_now():
+    """Admission asks for free pages for everything the request has so far, not for its first
+    portion only (it would be preempted a few steps later), and the call that preempts a
+    request does not admit it again."""
+    pt, s = make(pages=8, page_size=4, budget=16, chunk=8)        # 32 tokens
+    s.add(1, 28, 2)
+    s.add(2, 28, 2)                                               # its first portion would fit beside request 1, its 28 tokens do not
+    p = s.schedule()
+    assert [(e.rid, e.count) for e in p] == [(1, 8)] and s.num_waiting == 1
+    done = []
+    for _ in range(40):
+        done += run_step(pt, s, p)
+        p = s.schedule()
+        assert s.preempted() == []
+        if not p:
+            break
+    assert done == [1, 2] and s.num_preemptions == 0

@@ -153,6 +153,22 @@ def test_broken_files(model_dirs, tmp_path):
     (d / "model.safetensors").write_bytes(struct.pack("<Q", len(hj)) + hj + blob[8 + hlen:])
     with pytest.raises(WeightsError, match="unsupported dtype"):
         load_model(str(d), "bfloat16", "cpu")
+    # two tensors that share bytes, and a pair of offsets in the wrong order
+    hdr = json.loads(blob[8:8 + hlen])
+    names = [k for k in hdr if k != "__metadata__" and hdr[k]["data_offsets"][1] > hdr[k]["data_offsets"][0]]
+    size_of = lambda k: hdr[k]["data_offsets"][1] - hdr[k]["data_offsets"][0]
+    a, b2 = next((x, y) for i, x in enumerate(names) for y in names[i + 1:] if size_of(x) == size_of(y))
+    for label, edit, msg in (("overlap", lambda h: h[b2].__setitem__("data_offsets", list(h[a]["data_offsets"])), "overlap"),
+                             ("swapped", lambda h: h[a].__setitem__("data_offsets", h[a]["data_offsets"][::-1]), "wrong order")):
+        h2 = json.loads(blob[8:8 + hlen])
+        edit(h2)
+        hj = json.dumps(h2).encode()
+        d = tmp_path / label
+        os.makedirs(d)
+        shutil.copy(os.path.join(src, "config.json"), d / "config.json")
+        (d / "model.safetensors").write_bytes(struct.pack("<Q", len(hj)) + hj + blob[8 + hlen:])
+        with pytest.raises(WeightsError, match=msg):
+            load_model(str(d), "bfloat16", "cpu")
     e = tmp_path / "empty"
     os.makedirs(e)
     shutil.copy(os.path.join(src, "config.json"), e / "config.json")

@@ -40,14 +40,20 @@ def test_two_calls_in_a_row_match_the_allocating_route():
     ops, lib, fn = _symbol()
     torch.cuda.set_device(0)
     stream = torch.cuda.current_stream().cuda_stream
-    # (T, N, K, output dtype): split into several slices / one slice; float32 / bfloat16 out
-    for call, (T, N, K, out_dtype) in enumerate([(8, 4096, 4096, torch.float32), (40, 1000, 776, torch.bfloat16)]):
+    # (T, N, K, output dtype): split into several slices / one slice; float32 / bfloat16 out; then more than 128
+    # tokens with few output tiles (CTA pairs, K cut into slices), and a product whose slices would not fit the
+    # scratch (2 x 128 x 16,384 x 4 bytes = 16 MiB exactly fits; 3 slices would not), which runs as fewer
+    for call, (T, N, K, out_dtype) in enumerate([(8, 4096, 4096, torch.float32), (40, 1000, 776, torch.bfloat16),
+                                                 (300, 1024, 4096, torch.bfloat16), (128, 16384, 4096, torch.float32)]):
         x, w, b = _operands(T, N, K, 100 + call)
         out = torch.full((T, N), float("nan"), dtype=out_dtype, device=DEV)
         rc = fn(x.data_ptr(), w.data_ptr(), b.data_ptr(), out.data_ptr(), 0 if out_dtype == torch.float32 else 1,
                 T, N, K, x.stride(0), w.stride(0), stream)
         assert rc == 0, lib.kestrel_last_error().decode()
-        want = ops.Partials(ops.gemm_tc(x, w), b).reduce(out_dtype)      # scratch allocated per call
+        splits = lib.kestrel_gemm_tc_splits(T, N, K)
+        if splits * T * N * 4 > (16 << 20):
+            splits = 1                                                    # the entry point's fall-back: one slice always fits or is refused
+        want = ops.Partials(ops.gemm_tc(x, w, splits=splits), b).reduce(out_dtype)      # scratch allocated per call
         assert ops.gemm_tc_error() == 0
         assert torch.isfinite(out.float()).all()
         # same kernels, same order of sums: the two routes agree to the last bit; the bound below
