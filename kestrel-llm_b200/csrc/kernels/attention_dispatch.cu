@@ -250,7 +250,14 @@ KESTREL_API int kestrel_attention(void *planner, long long step_serial, const in
     KESTREL_REQUIRE(pl, "attention: the tensor-core kernels need a planner");
     const int gs = nq / nkv;
     const bool use_tc = kestrel_attention_tc_supported(hd, page_size) != 0;
-    const int rows_large = use_tc ? 256 : kestrel_attention_mma_rows_per_tile(hd);
+    // The tcgen05 kernel takes two row tiles of 128 a CTA, so that the tensor cores work on one
+    // while the other is in its softmax; with so few rows that CTAs of 256 would leave more than
+    // half of the SMs idle, one row tile a CTA and twice the CTAs is faster (measured, one request
+    // from position 0: 512 tokens 15.7 against 20.2 us, 256 tokens 11.6 against 15.7; 1,024 equal;
+    // 1,024 equal).  Far into a long context the few CTAs of 256 rows cut their key ranges into
+    // slices instead (below), which gains more.
+    int rows_large = use_tc ? 256 : kestrel_attention_mma_rows_per_tile(hd);
+    if (use_tc && layout[KB_MAX_KV_LEN] < 4096 && (long long)T * gs * nkv <= 128ll * kestrel_attention_tc_slots()) rows_large = 128;
     const Plan *plan = nullptr;
     int rc = plan_for(*pl, step_serial, batch_host, batch_dev, layout, gs, rows_large, captured != 0, stream, &plan);
     if (rc) return rc;

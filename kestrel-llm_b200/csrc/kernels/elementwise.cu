@@ -167,6 +167,78 @@ add_rmsnorm_vec_kernel(float *__restrict__ residual, const float *__restrict__ p
     }
 }
 
+// Many rows: one WARP per row, the row's vectors in registers (lane l holds vectors l, l + 32,
+// ...), no shared memory and no block barrier; all of a row's loads are in flight at once and
+// several rows a block keep the memory system busy, where one block per row waits out its own
+// chain of load, barrier, store (2,048 rows of 4,096: 17.4 us before).  The sums are the SAME
+// tree as above - vector i is virtual lane i mod 1024, its squares are added in the order x, y,
+// z, w, virtual lanes 32 g .. 32 g + 31 are combined by the same shuffle tree and the 32 group
+// sums in ascending order - so a row's bits do not depend on which variant ran.
+// NV: vectors per lane, 32 NV >= d / 4.
+template <typename TOut, int NV>
+__global__ void __launch_bounds__(128)
+add_rmsnorm_warp_kernel(float *__restrict__ residual, const float *__restrict__ partial, int S, size_t slice_stride,
+                        const float *__restrict__ bias, const int *__restrict__ rows, const float *__restrict__ w,
+                        float eps, TOut *__restrict__ out, int R, int d, int write_back) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (r >= R) return;
+    const int t = rows ? rows[r] : r;
+    const int d4 = d >> 2;
+    float4 *res = reinterpret_cast<float4 *>(residual + (size_t)t * d);
+    float4 x[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = 32 * j + lane;
+        x[j] = i < d4 ? res[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (partial) {
+        const float4 *p4 = reinterpret_cast<const float4 *>(partial + (size_t)t * d);
+        const float4 *bias4 = reinterpret_cast<const float4 *>(bias);
+        const size_t st4 = slice_stride >> 2;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = 32 * j + lane;
+            if (i >= d4) continue;
+            float4 delta = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < S; ++s) delta = add4(delta, p4[(size_t)s * st4 + i]);
+            if (bias) delta = add4(delta, bias4[i]);
+            x[j] = add4(x[j], delta);
+            if (write_back) res[i] = x[j];
+        }
+    }
+    float tot = 0.f;
+#pragma unroll
+    for (int g = 0; g < 32; ++g) {
+        float ss = 0.f;
+        if (g < NV) {
+            ss += x[g].x * x[g].x;
+            ss += x[g].y * x[g].y;
+            ss += x[g].z * x[g].z;
+            ss += x[g].w * x[g].w;
+        }
+        if (g + 32 < NV) {              // widths beyond 4096: the second vector of this virtual lane
+            ss += x[(g + 32) % NV].x * x[(g + 32) % NV].x;
+            ss += x[(g + 32) % NV].y * x[(g + 32) % NV].y;
+            ss += x[(g + 32) % NV].z * x[(g + 32) % NV].z;
+            ss += x[(g + 32) % NV].w * x[(g + 32) % NV].w;
+        }
+        tot += warp_sum(ss);
+    }
+    const float rinv = 1.0f / sqrtf(tot / (float)d + eps);
+    TOut *o = out + (size_t)r * d;
+    const float4 *w4 = reinterpret_cast<const float4 *>(w);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = 32 * j + lane;
+        if (i >= d4) continue;
+        const float4 g = w4[i];
+        store4(o + 4 * i, make_float4((x[j].x * rinv) * g.x, (x[j].y * rinv) * g.y, (x[j].z * rinv) * g.z, (x[j].w * rinv) * g.w));
+    }
+}
+
 template <typename TOut>
 static void launch_add_rmsnorm(float *residual, const float *partial, int S, long long slice_stride, const float *bias,
                                const int *rows, const float *w, float eps, TOut *out, int R, int d, int write_back,
@@ -177,7 +249,18 @@ static void launch_add_rmsnorm(float *residual, const float *partial, int S, lon
     bool vec = d % 4 == 0 && d >= 2048 && slice_stride % 4 == 0 &&
                ((((uintptr_t)residual | (uintptr_t)partial | (uintptr_t)bias | (uintptr_t)w) & 15) == 0) &&
                (((uintptr_t)out & 7) == 0);
-    if (vec && R >= 296) {
+    if (vec && R >= 1024 && d <= 48 * 128) {
+        // very many rows: a warp a row (widths up to 6144 fit a lane's registers; measured faster from about a thousand rows on)
+        const dim3 grid((R + 3) / 4), block(128);
+        if (d <= 16 * 128)
+            kestrel_launch(add_rmsnorm_warp_kernel<TOut, 16>, grid, block, 0, stream, residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, R, d, write_back);
+        else if (d <= 32 * 128)
+            kestrel_launch(add_rmsnorm_warp_kernel<TOut, 32>, grid, block, 0, stream, residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, R, d, write_back);
+        else if (d <= 40 * 128)
+            kestrel_launch(add_rmsnorm_warp_kernel<TOut, 40>, grid, block, 0, stream, residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, R, d, write_back);
+        else
+            kestrel_launch(add_rmsnorm_warp_kernel<TOut, 48>, grid, block, 0, stream, residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, R, d, write_back);
+    } else if (vec && R >= 296) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_vec_kernel<TOut, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kestrel_launch(add_rmsnorm_vec_kernel<TOut, 256>, dim3(R), dim3(256), smem, stream, residual, partial, S, (size_t)slice_stride, bias, rows, w, eps, out, d, write_back);

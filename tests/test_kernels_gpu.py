@@ -252,22 +252,33 @@ def test_add_rmsnorm(out_dtype, d):
     np.testing.assert_allclose(out3.float().cpu().numpy(), ref3, rtol=tol, atol=tol * np.abs(ref3).max())
 
 
-def test_add_rmsnorm_row_does_not_depend_on_the_batch():
-    """Few rows take the wide variant of the kernel, many rows the narrow one; a row's bits are the same."""
+@pytest.mark.parametrize("d,S,with_bias", [(4096, 5, False), (2048, 1, True), (5120, 3, True), (6144, 2, False), (3000, 4, True),
+                                          (8192, 1, False), (4096, 0, False)])
+def test_add_rmsnorm_row_does_not_depend_on_the_batch(d, S, with_bias):
+    """Few rows take the variant of the kernel that spreads a row over a whole block, many rows
+    the one that gives a row to a warp (widths up to 6144) or to a narrow block; a row's bits -
+    the norm in both storage types and the residual written back - are the same."""
     ops = _ops()
-    d, S = 4096, 5
     res, _ = _rand((400, d), torch.float32, 21)
-    part, _ = _rand((S, 400, d), torch.float32, 22, 0.3)
     w, _ = _rand((d,), torch.float32, 23)
-    many = torch.empty((400, d), dtype=torch.bfloat16, device=DEV)
-    r1 = res.clone()
-    ops.add_rmsnorm(r1, ops.Partials(part), w, 1e-6, many)
-    one = torch.empty((1, d), dtype=torch.float32, device=DEV)
-    many32 = torch.empty((400, d), dtype=torch.float32, device=DEV)
-    ops.add_rmsnorm(res.clone(), ops.Partials(part), w, 1e-6, many32)
-    r2 = res[123:124].clone()
-    ops.add_rmsnorm(r2, ops.Partials(part[:, 123:124].contiguous()), w, 1e-6, one)
-    assert torch.equal(one[0], many32[123]) and torch.equal(r2[0], r1[123])
+    delta = one_delta = None
+    if S:
+        part, _ = _rand((S, 400, d), torch.float32, 22, 0.3)
+        bias = _rand((d,), torch.float32, 24, 0.1)[0] if with_bias else None
+        delta = ops.Partials(part, bias)
+        one_delta = ops.Partials(part[:, 123:124].contiguous(), bias)
+    for dt in (torch.float32, torch.bfloat16):
+        many = torch.empty((400, d), dtype=dt, device=DEV)
+        r1 = res.clone()
+        ops.add_rmsnorm(r1, delta, w, 1e-6, many)
+        one = torch.empty((1, d), dtype=dt, device=DEV)
+        r2 = res[123:124].clone()
+        ops.add_rmsnorm(r2, one_delta, w, 1e-6, one)
+        assert torch.equal(one[0], many[123]) and torch.equal(r2[0], r1[123])
+        rows = torch.arange(399, -1, -1, dtype=torch.int32, device=DEV)        # many gathered rows
+        gathered = torch.empty((400, d), dtype=dt, device=DEV)
+        ops.add_rmsnorm(res.clone(), delta, w, 1e-6, gathered, rows=rows)
+        assert torch.equal(gathered[399 - 123], many[123])
 
 
 def test_add_rmsnorm_refuses_what_it_cannot_hold():
@@ -827,6 +838,62 @@ def test_attn_prepare(dtype, nq, nkv, hd, rot, bias, norm):
         for sl in range(page):
             if (pg, sl) not in written:
                 assert not kcn[pg, :, sl].any() and not vcn[pg, :, sl].any(), f"page {pg} slot {sl} was written"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,S,bias,interleaved", [(32, 8, 1, False, False), (5, 1, 3, True, False), (6, 2, 2, False, True)])
+def test_attn_prepare_token_does_not_depend_on_the_batch(dtype, nq, nkv, S, bias, interleaved):
+    """Head size 128 (the kernel of its own) and the general kernel with another rotation: a
+    token's queries, keys and values are the same bits in a step of 200 tokens and in a step of
+    3, and agree with the plain parts."""
+    ops = _ops()
+    td = DT[dtype]
+    hd, page, T = 128, 16, 200
+    width = (nq + 2 * nkv) * hd
+    part, pr = _rand((S, T, width), torch.float32, 31)
+    b, br = _rand((width,), torch.float32, 32, 0.2) if bias else (None, None)
+    qw, qwr = _rand((hd,), torch.float32, 33)
+    kw, kwr = _rand((hd,), torch.float32, 34)
+    inv = (np.float32(1) / np.power(np.float32(1e6), np.arange(hd // 2, dtype=np.float32) / np.float32(hd // 2))).astype(np.float32)
+    inv_d = torch.from_numpy(inv).to(DEV)
+    positions = (np.arange(T, dtype=np.int32) * 37) % 3000
+    pages = 3000 // page + 1
+    table = torch.from_numpy(np.random.default_rng(1).permutation(pages).astype(np.int32)[None, :]).to(DEV)
+    mode = 1 if interleaved else 0
+
+    def run(tokens):
+        n = len(tokens)
+        kc = torch.zeros((pages, nkv, page, hd), dtype=td, device=DEV)
+        vc = torch.zeros_like(kc)
+        q = torch.empty((n, nq * hd), dtype=td, device=DEV)
+        idx = torch.tensor(tokens, device=DEV)
+        ops.attn_prepare(ops.Partials(part[:, idx].contiguous(), b), qw, kw, 1e-6, inv_d, hd,
+                         torch.from_numpy(positions[tokens]).to(DEV), torch.zeros(n, dtype=torch.int32, device=DEV), table, page,
+                         kc, vc, q, nq, nkv, hd, rot_mode=mode)
+        return q, kc, vc
+
+    q_all, k_all, v_all = run(list(range(T)))
+    few = [150, 7, 63]
+    q_few, k_few, v_few = run(few)
+    tab = table[0].cpu().numpy()
+    for i, t in enumerate(few):
+        assert torch.equal(q_few[i], q_all[t])
+        pg, sl = tab[positions[t] // page], positions[t] % page
+        assert torch.equal(k_few[pg, :, sl], k_all[pg, :, sl]) and torch.equal(v_few[pg, :, sl], v_all[pg, :, sl])
+    # and against the plain parts
+    x = pr.sum(0) + (br if bias else 0)
+    qr = P.head_rms_norm(x[:, :nq * hd].reshape(T, nq, hd), qwr, 1e-6)
+    ang = positions.astype(np.float32)[:, None] * inv[None, :]
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    if interleaved:
+        ref = qr.copy()
+        a0, b0 = qr[..., 0::2], qr[..., 1::2]
+        ref[..., 0::2] = a0 * cos[:, None, :] - b0 * sin[:, None, :]
+        ref[..., 1::2] = b0 * cos[:, None, :] + a0 * sin[:, None, :]
+    else:
+        ref = P.rope(qr, cos, sin)
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    np.testing.assert_allclose(q_all.float().cpu().numpy().reshape(T, nq, hd), ref, rtol=tol, atol=tol * 4)
 
 
 def test_attn_prepare_refuses_odd_sizes():
