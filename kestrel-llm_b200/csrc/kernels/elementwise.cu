@@ -508,7 +508,29 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
     __shared__ float cs_s[64], sn_s[64];
     int t = blockIdx.x;
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int heads = nq + 2 * nkv;
+    int h = blockIdx.y * 8 + warp;
+    const bool live = h < heads;
+    // The head's values are asked for first: their loads are in flight while two warps turn the
+    // token's position into cosines and sines and the block meets at the barrier (the loads do
+    // not depend on the position; issued after the barrier, every block would wait out two
+    // memory latencies one behind the other).
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+        const float4 *row = reinterpret_cast<const float4 *>(partial + (size_t)t * heads * hd + (size_t)h * hd) + lane;
+        size_t st4 = slice_stride >> 2;
+        int s = 0;
+        for (; s + 4 <= S; s += 4) {
+            float4 a = row[(size_t)s * st4], b = row[(size_t)(s + 1) * st4], c = row[(size_t)(s + 2) * st4], e = row[(size_t)(s + 3) * st4];
+            x = add4(add4(add4(add4(x, a), b), c), e);
+        }
+        for (; s < S; ++s) x = add4(x, row[(size_t)s * st4]);
+    }
     int pos = positions[t];
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    int page = 0;
+    if (live && !is_q && write_kv)          // where the key or value goes: two dependent loads, begun before the barrier too
+        page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
     if (threadIdx.x < 64) {
         float ang = (float)pos * inv_freq[threadIdx.x];
         float sn, cs;
@@ -517,20 +539,8 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
         sn_s[threadIdx.x] = sn * rot_scale;
     }
     __syncthreads();
-    int heads = nq + 2 * nkv;
-    int h = blockIdx.y * 8 + warp;
-    if (h >= heads) return;
-    bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    if (!live) return;
     if (!is_q && !write_kv) return;
-    const float4 *row = reinterpret_cast<const float4 *>(partial + (size_t)t * heads * hd + (size_t)h * hd) + lane;
-    size_t st4 = slice_stride >> 2;
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-    int s = 0;
-    for (; s + 4 <= S; s += 4) {
-        float4 a = row[(size_t)s * st4], b = row[(size_t)(s + 1) * st4], c = row[(size_t)(s + 2) * st4], e = row[(size_t)(s + 3) * st4];
-        x = add4(add4(add4(add4(x, a), b), c), e);
-    }
-    for (; s < S; ++s) x = add4(x, row[(size_t)s * st4]);
     if (bias) x = add4(x, reinterpret_cast<const float4 *>(bias + (size_t)h * hd)[lane]);
     const float *nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
     if (nw) {
@@ -557,8 +567,6 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
         store4(q_out + ((size_t)t * nq + h) * hd + 4 * lane, x);
     } else {
         int kvh = is_k ? h - nq : h - nq - nkv;
-        int seq = seq_of_token[t];
-        int page = block_table[(size_t)seq * table_stride + pos / page_size];
         T *plane = is_k ? k_cache : v_cache;
         store4(plane + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd + 4 * lane, x);
     }

@@ -30,7 +30,13 @@
 #define TC_BK 64
 #define TC_THREADS 192
 
-enum { TC_PARTIAL = 0, TC_SWIGLU = 1, TC_PARTIAL2 = 2 };     // PARTIAL2: two weight tiles a CTA, as SWIGLU, both written as float32 slices
+enum { TC_PARTIAL = 0, TC_SWIGLU = 1, TC_PARTIAL2 = 2, TC_SWIGLU_T = 3 };     // PARTIAL2: two weight tiles a CTA, as SWIGLU, both written as float32 slices
+// SWIGLU_T (CTA pairs only): the roles of the operands swapped - tokens are the MMA's M operand,
+// the weights its N operand (128 gate rows from one rank, the 128 up rows of the same features
+// from the other) - so that ONE accumulator of 256 columns holds gate and up of a (token,
+// feature) in the same TMEM lane, two accumulators fit TMEM and the epilogue of a tile overlaps
+// the main loop of the next, and a tile is 256 tokens x 128 features: twice as many, half as
+// large, which fills the last round of tiles better.
 
 __device__ int g_tc_error = 0;
 
@@ -424,6 +430,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     void *__restrict__ out, int T, int N, int K, long long ldo, int stages, int tiles_n, int tiles_total,
                     int up_row_offset, int accumulate, int tiles_nt, int kb_per_split, long long slice_stride) {
     pdl_launch_dependents();
+    constexpr bool SWAP = MODE == TC_SWIGLU_T;
     constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = (TCP_BN / 2) * TC_BK * 2;
@@ -478,6 +485,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const int split = tile / tiles_nt, tw = tile % tiles_nt;       // a tile of the output and its slice of K
                 int n0 = (tw % tiles_n) * 256 + (int)rank * TC_BM;
                 int t0 = (tw / tiles_n) * TCP_BN + (int)rank * (TCP_BN / 2);
+                if (SWAP) n0 = (tw % tiles_n) * TC_BM + (rank ? up_row_offset : 0);     // this rank's half of the N operand: gate rows, or up rows
                 const int kb_end = min(num_kb, (split + 1) * kb_per_split);
                 for (int kb = split * kb_per_split; kb < kb_end; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1)) { atomicExch(&g_tc_error, 1); ok = false; break; }
@@ -485,9 +493,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
                     uint32_t sa = base + (uint32_t)stage * STAGE_BYTES;
                     int kc = kb * TC_BK;
-                    tma_load_2d_pair(sa, &map_w, leader_full, kc, n0);
-                    if (MODE == TC_SWIGLU) tma_load_2d_pair(sa + A_BYTES, &map_w, leader_full, kc, up_row_offset + n0);
-                    tma_load_2d_pair(sa + A_TILES * A_BYTES, &map_x, leader_full, kc, t0);
+                    if (SWAP) {              // tokens are the M operand (this rank's 128), weights the N operand (this rank's half)
+                        tma_load_2d_pair(sa, &map_x, leader_full, kc, t0);
+                        tma_load_2d_pair(sa + A_BYTES, &map_w, leader_full, kc, n0);
+                    } else {
+                        tma_load_2d_pair(sa, &map_w, leader_full, kc, n0);
+                        if (MODE == TC_SWIGLU) tma_load_2d_pair(sa + A_BYTES, &map_w, leader_full, kc, up_row_offset + n0);
+                        tma_load_2d_pair(sa + A_TILES * A_BYTES, &map_x, leader_full, kc, t0);
+                    }
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -535,6 +548,47 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (!mbar_wait(acc_full(b), acc_phase)) { if (lane == 0) atomicExch(&g_tc_error, 3); break; }
             tc_fence_after();
             uint32_t d = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)b * ACC_COLS;
+            if (SWAP) {
+                // lane = token, columns 0..127 = gate of 128 features, 128..255 = up of the same features;
+                // each group of four warps takes a quarter of the features
+                const int t = t0 + (int)rank * (TCP_BN / 2) + 32 * q + lane;
+                const int f0 = (tw % tiles_n) * TC_BM;
+                const int cf = ((warp - 2) >> 2) * (TC_BM / TCP_EPI_GROUPS);
+                __nv_bfloat16 *o = (__nv_bfloat16 *)out + (size_t)t * ldo + f0;
+#pragma unroll 1
+                for (int c = cf; c < cf + TC_BM / TCP_EPI_GROUPS; c += 16) {
+                    if (f0 + c >= N) break;
+                    float g[16], u[16];
+                    tc_ld16(d + c, g);
+                    tc_ld16(d + TC_BM + c, u);
+                    if (t < T) {
+                        if (f0 + c + 16 <= N && (ldo & 7) == 0) {          // 16 features of one token: two 16-byte stores
+                            uint32_t pk[8];
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                float a0 = __fdividef(g[2 * jj], 1.0f + __expf(-g[2 * jj])) * u[2 * jj];
+                                float a1 = __fdividef(g[2 * jj + 1], 1.0f + __expf(-g[2 * jj + 1])) * u[2 * jj + 1];
+                                __nv_bfloat162 h = __floats2bfloat162_rn(a0, a1);
+                                pk[jj] = *reinterpret_cast<uint32_t *>(&h);
+                            }
+                            uint4 *dst = reinterpret_cast<uint4 *>(o + c);
+                            dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                        } else {
+#pragma unroll
+                            for (int jj = 0; jj < 16; ++jj)
+                                if (f0 + c + jj < N) {
+                                    float a = __fdividef(g[jj], 1.0f + __expf(-g[jj]));
+                                    o[c + jj] = __float2bfloat16_rn(a * u[jj]);
+                                }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_rank(acc_empty(b), 0));
+                continue;
+            }
             int valid = min(TCP_BN, T - t0);
             const int c_begin = ((warp - 2) >> 2) * (TCP_BN / TCP_EPI_GROUPS);      // each group of four warps its columns
 #pragma unroll 1
@@ -647,6 +701,7 @@ KESTREL_API int kestrel_gemm_tc_supported(const void *x, const void *w, int T, i
 // g_ctas_per_sm CTAs share an SM's shared memory for their stages; a CTA costs about
 // g_overhead_kb k-blocks of time beyond its own k-blocks (launch, barrier set-up, TMEM
 // allocation, first tensor-map fetch, pipeline fill, epilogue).
+static int g_swiglu_swapped = 1;   // the SwiGLU product on CTA pairs with tokens as the M operand (TC_SWIGLU_T)
 static int g_swiglu_bn = 256;      // token tile of the persistent SwiGLU product: 256 (one accumulator pair) or 128 (two)
 static int g_pairs = 1;            // many-token PARTIAL products on CTA pairs (cta_group::2)
 static int g_persistent = 1;       // many-token products on the persistent kernel (0: one tile per CTA)
@@ -658,6 +713,7 @@ static int g_ctas_per_sm = 2;
 KESTREL_API void kestrel_gemm_tc_set_persistent(int on) { g_persistent = on ? 1 : 0; }
 KESTREL_API void kestrel_gemm_tc_set_pairs(int on) { g_pairs = on ? 1 : 0; }
 KESTREL_API void kestrel_gemm_tc_set_swiglu_tile(int bn) { if (bn == 128 || bn == 256) g_swiglu_bn = bn; }
+KESTREL_API void kestrel_gemm_tc_set_swiglu_swapped(int mode) { if (mode >= 0 && mode <= 2) g_swiglu_swapped = mode; }
 
 KESTREL_API void kestrel_gemm_tc_set_pair_tuning(int min_tokens, int overhead_kb) {
     if (min_tokens >= 0) g_pair_min_tokens = min_tokens;
@@ -813,7 +869,8 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
         }
     }
     if (max_clusters == 0) return 1;       // not an error: tells the caller to fall back
-    int tiles_n = (N + 255) / 256, tiles_t = (T + TCP_BN - 1) / TCP_BN;
+    // output tiles: 256 features x 256 tokens; with the operands swapped 128 features x 256 tokens
+    int tiles_n = MODE == TC_SWIGLU_T ? (N + TC_BM - 1) / TC_BM : (N + 255) / 256, tiles_t = (T + TCP_BN - 1) / TCP_BN;
     long long tiles_nt = (long long)tiles_n * tiles_t, total = tiles_nt * splits;
     if (total > 0x7fffffff) return kestrel_fail(-2, "gemm_tc: too many tiles");
     if (splits > 1 && (MODE != TC_PARTIAL || accumulate)) return kestrel_fail(-2, "gemm_tc_pair: only plain float32 slices can be cut along K");
@@ -825,6 +882,22 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
                                        (int)tiles_nt, per, slice_stride);
     if (e != cudaSuccess) return kestrel_fail(-3, "gemm_tc_pair: %s", cudaGetErrorString(e));
     return kestrel_check_launch("gemm_tc_pair");
+}
+
+// Which form the SwiGLU product takes on CTA pairs.  With the weights as the M operand a tile is
+// 256 features x 256 tokens (gate and up: four units of work) and its epilogue is not overlapped;
+// with the tokens as the M operand a tile is 128 features x 256 tokens (two units) and overlaps,
+// but it fetches a third more operand bytes per multiply-add and runs into the L2's bandwidth
+// when all pairs work (measured: a unit costs about 1.24 times as much).  The swapped form wins
+// where its finer tiles save a round: 8B sizes 384 to 512 tokens 95 -> 87 and 97 -> 90 us, 32B
+// sizes 256 tokens 131 -> 109 us; at 1,024 tokens of 8B size, where both take as many rounds of
+// work, it loses 166 -> 177 us and is not taken.  g_swiglu_swapped: 0 never, 1 by this rule, 2 always.
+static bool swiglu_swapped_wins(int T, int ff) {
+    if (g_swiglu_swapped != 1) return g_swiglu_swapped == 2;
+    const long long pairs = kestrel_sms() / 2, tt = (T + TCP_BN - 1) / TCP_BN;
+    const long long rounds_m = (((ff + 255) / 256) * tt + pairs - 1) / pairs;       // weights as M
+    const long long rounds_t = (((ff + 127) / 128) * tt + pairs - 1) / pairs;       // tokens as M
+    return rounds_t * 248 < rounds_m * 430;
 }
 
 template <int MODE>
@@ -839,7 +912,10 @@ static int dispatch_tc(const void *x, const void *w, void *out, int T, int N, in
     if (persistent && g_pairs) {
         rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, TCP_BN / 2);
         if (rc) return rc;
-        rc = launch_tc_pair<MODE>(mw, mx, out, T, N, K, ldo, up_off, 0, splits, slice_stride, stream);
+        if (MODE == TC_SWIGLU && swiglu_swapped_wins(T, N) && ((uintptr_t)out & 15) == 0 && ldo % 8 == 0)
+            rc = launch_tc_pair<TC_SWIGLU_T>(mw, mx, out, T, N, K, ldo, up_off, 0, 1, 0, stream);
+        else
+            rc = launch_tc_pair<MODE>(mw, mx, out, T, N, K, ldo, up_off, 0, splits, slice_stride, stream);
         if (rc <= 0) return rc;            // 1 = pairs cannot be scheduled: go on with one CTA per tile
     }
     if (splits > 1) persistent = false;    // the one-CTA persistent kernel does not cut K

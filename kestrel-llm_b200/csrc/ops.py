@@ -383,13 +383,16 @@ def gemm_tc_set_pair_tuning(min_tokens: int = -1, overhead_kb: int = -1) -> None
     fn(int(min_tokens), int(overhead_kb))
 
 
-def gemm_tc_set_many_token_path(pairs: bool = True, persistent: bool = True, swiglu_tile: int = 256) -> None:
+def gemm_tc_set_many_token_path(pairs: bool = True, persistent: bool = True, swiglu_tile: int = 256,
+                                swiglu_swapped: Optional[bool] = None) -> None:
     """Which kernel a many-token product (more than 128 tokens) takes: CTA pairs (the default),
     else one persistent CTA per SM (what runs where pairs cannot be scheduled; ``swiglu_tile``
-    128 or 256 tokens for its SwiGLU form), else one tile per CTA.  For tests of the fall-backs."""
+    128 or 256 tokens for its SwiGLU form), else one tile per CTA.  ``swiglu_swapped``: the
+    SwiGLU product on pairs takes the tokens as the M operand always (True), never (False), or
+    where its finer tiles save a round of tiles (None, the default).  For tests of every path."""
     lib = library()
     for name, v in (("kestrel_gemm_tc_set_pairs", 1 if pairs else 0), ("kestrel_gemm_tc_set_persistent", 1 if persistent else 0),
-                    ("kestrel_gemm_tc_set_swiglu_tile", int(swiglu_tile))):
+                    ("kestrel_gemm_tc_set_swiglu_tile", int(swiglu_tile)), ("kestrel_gemm_tc_set_swiglu_swapped", 1 if swiglu_swapped is None else (2 if swiglu_swapped else 0))):
         fn = getattr(lib, name)
         fn(v)
 

@@ -166,6 +166,8 @@ KESTREL_API int kestrel_linear_bf16_noalloc(const void *x, const void *w, const 
 KESTREL_API void kestrel_gemm_tc_set_persistent(int on);
 KESTREL_API void kestrel_gemm_tc_set_pairs(int on);
 KESTREL_API void kestrel_gemm_tc_set_swiglu_tile(int bn);
+/* the SwiGLU product on CTA pairs with the tokens as the M operand: 0 never, 1 where its finer tiles save a round (the default), 2 always */
+KESTREL_API void kestrel_gemm_tc_set_swiglu_swapped(int mode);
 KESTREL_API void kestrel_gemm_tc_set_pair_tuning(int min_tokens, int overhead_kb);
 KESTREL_API void kestrel_gemm_tc_set_tuning(int overhead_kb, int ctas_per_sm);
 KESTREL_API void kestrel_gemm_tc_set_wide(int on, int more_than_tokens);

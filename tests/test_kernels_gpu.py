@@ -207,6 +207,20 @@ def test_gemm_tcgen05_swiglu(T, ff, K):
     y = xr.astype(np.float64) @ wr.astype(np.float64).T
     ref = (y[:, :ff] / (1 + np.exp(-y[:, :ff]))) * y[:, ff:]
     np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=1e-2, atol=1e-2 * np.abs(ref).max())
+    if T > 128:
+        # on CTA pairs the product has two forms, weights or tokens as the MMA's M operand; which one
+        # runs follows the number of tiles, and both give the same bits
+        try:
+            forms = []
+            for swapped in (False, True):
+                ops.gemm_tc_set_many_token_path(swiglu_swapped=swapped)
+                o = torch.full((T, ff), float("nan"), dtype=torch.bfloat16, device=DEV)
+                ops.gemm_tc_swiglu(x, w, o)
+                forms.append(o)
+        finally:
+            ops.gemm_tc_set_many_token_path()
+        assert ops.gemm_tc_error() == 0
+        assert torch.equal(forms[0], forms[1]) and torch.equal(forms[0], out)
 
 
 def test_gemm_tcgen05_refuses_what_tma_cannot_address():
