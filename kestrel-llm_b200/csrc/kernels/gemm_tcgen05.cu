@@ -454,6 +454,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const uint32_t rank = cluster_rank();
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
+    // Output tile w of a slice: the token tiles of one feature tile follow each other, so the pairs
+    // that work at the same time share weight rows, which are then fetched from HBM once and found
+    // in L2 by the others (with the feature tile running fastest a round of 74 pairs touched 74
+    // weight tiles, more than L2 holds, and every token tile fetched the weights anew: 1.08 GB read
+    // for the 201 MB of a gate/up matrix at 2,048 tokens).  The activations of a step fit L2.
+    const int tiles_t = tiles_nt / tiles_n;
+    auto tile_n = [&](int w) { return w / tiles_t; };
+    auto tile_t = [&](int w) { return w % tiles_t; };
 
     if (warp == 0) {
         if (lane < stages) { mbar_init(full_bar(lane), 1); mbar_init(empty_bar(lane), 1); }
@@ -483,9 +491,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             bool ok = true;
             for (int tile = pair; tile < tiles_total && ok; tile += n_pairs) {
                 const int split = tile / tiles_nt, tw = tile % tiles_nt;       // a tile of the output and its slice of K
-                int n0 = (tw % tiles_n) * 256 + (int)rank * TC_BM;
-                int t0 = (tw / tiles_n) * TCP_BN + (int)rank * (TCP_BN / 2);
-                if (SWAP) n0 = (tw % tiles_n) * TC_BM + (rank ? up_row_offset : 0);     // this rank's half of the N operand: gate rows, or up rows
+                int n0 = tile_n(tw) * 256 + (int)rank * TC_BM;
+                int t0 = tile_t(tw) * TCP_BN + (int)rank * (TCP_BN / 2);
+                if (SWAP) n0 = tile_n(tw) * TC_BM + (rank ? up_row_offset : 0);     // this rank's half of the N operand: gate rows, or up rows
                 const int kb_end = min(num_kb, (split + 1) * kb_per_split);
                 for (int kb = split * kb_per_split; kb < kb_end; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1)) { atomicExch(&g_tc_error, 1); ok = false; break; }
@@ -543,8 +551,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             int b = j % NBUF;
             uint32_t acc_phase = (uint32_t)(j / NBUF) & 1u;
             const int split = tile / tiles_nt, tw = tile % tiles_nt;
-            int n = (tw % tiles_n) * 256 + (int)rank * TC_BM + 32 * q + lane;
-            int t0 = (tw / tiles_n) * TCP_BN;
+            int n = tile_n(tw) * 256 + (int)rank * TC_BM + 32 * q + lane;
+            int t0 = tile_t(tw) * TCP_BN;
             if (!mbar_wait(acc_full(b), acc_phase)) { if (lane == 0) atomicExch(&g_tc_error, 3); break; }
             tc_fence_after();
             uint32_t d = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)b * ACC_COLS;
@@ -552,7 +560,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 // lane = token, columns 0..127 = gate of 128 features, 128..255 = up of the same features;
                 // each group of four warps takes a quarter of the features
                 const int t = t0 + (int)rank * (TCP_BN / 2) + 32 * q + lane;
-                const int f0 = (tw % tiles_n) * TC_BM;
+                const int f0 = tile_n(tw) * TC_BM;
                 const int cf = ((warp - 2) >> 2) * (TC_BM / TCP_EPI_GROUPS);
                 __nv_bfloat16 *o = (__nv_bfloat16 *)out + (size_t)t * ldo + f0;
 #pragma unroll 1
@@ -886,18 +894,19 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
 
 // Which form the SwiGLU product takes on CTA pairs.  With the weights as the M operand a tile is
 // 256 features x 256 tokens (gate and up: four units of work) and its epilogue is not overlapped;
-// with the tokens as the M operand a tile is 128 features x 256 tokens (two units) and overlaps,
-// but it fetches a third more operand bytes per multiply-add and runs into the L2's bandwidth
-// when all pairs work (measured: a unit costs about 1.24 times as much).  The swapped form wins
-// where its finer tiles save a round: 8B sizes 384 to 512 tokens 95 -> 87 and 97 -> 90 us, 32B
-// sizes 256 tokens 131 -> 109 us; at 1,024 tokens of 8B size, where both take as many rounds of
-// work, it loses 166 -> 177 us and is not taken.  g_swiglu_swapped: 0 never, 1 by this rule, 2 always.
+// with the tokens as the M operand a tile is 128 features x 256 tokens (two units), the epilogue
+// overlaps the next tile and the finer tiles fill the last round better: measured at 8B sizes
+// 512 tokens 95.5 -> 78.8 us, 2,048 tokens 294 -> 268 us (1.54 PFLOP/s), 4,096 tokens 551 -> 504 us;
+// at 32B sizes 256 tokens 153 -> 111 us.  It fetches a third more operand bytes per multiply-add,
+// so where both forms need the same rounds of work for ONE token tile (8B sizes up to 256 tokens:
+// 48 tiles in one round against 96 in two) the first form stays ahead, 51.6 against 55.0 us.
+// g_swiglu_swapped: 0 never, 1 by this rule, 2 always.
 static bool swiglu_swapped_wins(int T, int ff) {
     if (g_swiglu_swapped != 1) return g_swiglu_swapped == 2;
     const long long pairs = kestrel_sms() / 2, tt = (T + TCP_BN - 1) / TCP_BN;
-    const long long rounds_m = (((ff + 255) / 256) * tt + pairs - 1) / pairs;       // weights as M
-    const long long rounds_t = (((ff + 127) / 128) * tt + pairs - 1) / pairs;       // tokens as M
-    return rounds_t * 248 < rounds_m * 430;
+    const long long work_m = 4 * ((((ff + 255) / 256) * tt + pairs - 1) / pairs);       // weights as M: rounds of four units
+    const long long work_t = 2 * ((((ff + 127) / 128) * tt + pairs - 1) / pairs);       // tokens as M: rounds of two
+    return work_t < work_m || (work_t == work_m && tt > 1);
 }
 
 template <int MODE>
