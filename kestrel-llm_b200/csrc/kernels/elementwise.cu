@@ -489,10 +489,14 @@ __global__ void attn_prepare_kernel(const float *__restrict__ partial, int S, si
     }
 }
 
-// The same for head size 128 with all 128 dims rotated (the common case): a block of 8 warps
-// takes 8 heads of one token; cos and sin of the token's 64 angles are computed once per block
-// into shared memory; a lane owns 4 consecutive dims (float4 loads, 8- or 16-byte stores) and
-// gets its rotation partner (dim +-64) from lane ^ 16 by shuffle.
+// The same for head size 128 with all 128 dims rotated by rotate-half pairing (the common case).
+// A warp takes FOUR heads of one token: eight lanes a head, sixteen values a lane - dimensions
+// 8 l' .. 8 l' + 7 and 64 + 8 l' .. 64 + 8 l' + 7 for lane l' of the eight, so that both members
+// of every rotation pair sit in the same lane and the sum of squares needs three shuffle steps.
+// With one head a warp and four values a lane the kernel spent about an instruction per value on
+// addresses, shuffles and bookkeeping and ran at 2.5 TB/s, bound by instruction issue; this form
+// needs about a third of the instructions.  A block of 256 threads takes 32 heads of a token
+// (the token's cosines and sines are computed once per block, by 64 threads, into shared memory).
 template <typename T>
 __global__ void __launch_bounds__(256)
 attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice_stride,
@@ -505,28 +509,27 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
     pdl_launch_dependents();
     pdl_wait();
     constexpr int hd = 128;
-    __shared__ float cs_s[64], sn_s[64];
-    int t = blockIdx.x;
-    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int heads = nq + 2 * nkv;
-    int h = blockIdx.y * 8 + warp;
+    __shared__ __align__(16) float cs_s[64], sn_s[64];
+    const int t = blockIdx.x;
+    const int sub = threadIdx.x & 7;                       // lane of the eight that share a head
+    const int heads = nq + 2 * nkv;
+    const int h = blockIdx.y * 32 + (threadIdx.x >> 3);
     const bool live = h < heads;
-    // The head's values are asked for first: their loads are in flight while two warps turn the
-    // token's position into cosines and sines and the block meets at the barrier (the loads do
-    // not depend on the position; issued after the barrier, every block would wait out two
-    // memory latencies one behind the other).
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    // the head's values are asked for first: their loads are in flight while two warps turn the
+    // token's position into cosines and sines and the block meets at the barrier
+    float4 x[4];             // x[0], x[1]: dimensions 8 sub .. 8 sub + 7; x[2], x[3]: the same 64 further
+#pragma unroll
+    for (int v = 0; v < 4; ++v) x[v] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live) {
-        const float4 *row = reinterpret_cast<const float4 *>(partial + (size_t)t * heads * hd + (size_t)h * hd) + lane;
-        size_t st4 = slice_stride >> 2;
-        int s = 0;
-        for (; s + 4 <= S; s += 4) {
-            float4 a = row[(size_t)s * st4], b = row[(size_t)(s + 1) * st4], c = row[(size_t)(s + 2) * st4], e = row[(size_t)(s + 3) * st4];
-            x = add4(add4(add4(add4(x, a), b), c), e);
+        const float4 *row = reinterpret_cast<const float4 *>(partial + (size_t)t * heads * hd + (size_t)h * hd) + 2 * sub;
+        const size_t st4 = slice_stride >> 2;
+        for (int s = 0; s < S; ++s) {
+            const float4 *r = row + (size_t)s * st4;
+            float4 a = r[0], b = r[1], c = r[16], e = r[17];
+            x[0] = add4(x[0], a); x[1] = add4(x[1], b); x[2] = add4(x[2], c); x[3] = add4(x[3], e);
         }
-        for (; s < S; ++s) x = add4(x, row[(size_t)s * st4]);
     }
-    int pos = positions[t];
+    const int pos = positions[t];
     const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
     int page = 0;
     if (live && !is_q && write_kv)          // where the key or value goes: two dependent loads, begun before the barrier too
@@ -539,37 +542,48 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
         sn_s[threadIdx.x] = sn * rot_scale;
     }
     __syncthreads();
-    if (!live) return;
-    if (!is_q && !write_kv) return;
-    if (bias) x = add4(x, reinterpret_cast<const float4 *>(bias + (size_t)h * hd)[lane]);
+    // from here on the eight lanes of a head stay together: shuffles name them by their own mask
+    if (!live || (!is_q && !write_kv)) return;
+    const unsigned mask = 0xffu << (threadIdx.x & 24);
+    if (bias) {
+        const float4 *b4 = reinterpret_cast<const float4 *>(bias + (size_t)h * hd) + 2 * sub;
+        x[0] = add4(x[0], b4[0]); x[1] = add4(x[1], b4[1]); x[2] = add4(x[2], b4[16]); x[3] = add4(x[3], b4[17]);
+    }
     const float *nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
     if (nw) {
-        float ss = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
-        ss = warp_sum(ss);
-        float rinv = 1.0f / sqrtf(ss / (float)hd + norm_eps);
-        float4 g = reinterpret_cast<const float4 *>(nw)[lane];
-        x = make_float4((x.x * rinv) * g.x, (x.y * rinv) * g.y, (x.z * rinv) * g.z, (x.w * rinv) * g.w);
+        float ss = 0.f;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) ss += x[v].x * x[v].x + x[v].y * x[v].y + x[v].z * x[v].z + x[v].w * x[v].w;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(mask, ss, o);
+        const float rinv = 1.0f / sqrtf(ss / (float)hd + norm_eps);
+        const float4 *g4 = reinterpret_cast<const float4 *>(nw) + 2 * sub;
+        const float4 g[4] = {g4[0], g4[1], g4[16], g4[17]};
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+            x[v] = make_float4((x[v].x * rinv) * g[v].x, (x[v].y * rinv) * g[v].y, (x[v].z * rinv) * g[v].z, (x[v].w * rinv) * g[v].w);
     }
     if (is_q || is_k) {
-        float4 o;
-        o.x = __shfl_xor_sync(0xffffffffu, x.x, 16);
-        o.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
-        o.z = __shfl_xor_sync(0xffffffffu, x.z, 16);
-        o.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
-        int j = (4 * lane) & 63;
-        float4 cs = *reinterpret_cast<const float4 *>(cs_s + j), sn = *reinterpret_cast<const float4 *>(sn_s + j);
-        if (lane < 16)      // this lane holds the low half of the pairs: lo * c - hi * s
-            x = make_float4(x.x * cs.x - o.x * sn.x, x.y * cs.y - o.y * sn.y, x.z * cs.z - o.z * sn.z, x.w * cs.w - o.w * sn.w);
-        else                // the high half: hi * c + lo * s
-            x = make_float4(x.x * cs.x + o.x * sn.x, x.y * cs.y + o.y * sn.y, x.z * cs.z + o.z * sn.z, x.w * cs.w + o.w * sn.w);
+        // pair j = 8 sub + i: low member x[i / 4], high member x[2 + i / 4]
+        const float4 *c4 = reinterpret_cast<const float4 *>(cs_s) + 2 * sub, *s4 = reinterpret_cast<const float4 *>(sn_s) + 2 * sub;
+#pragma unroll
+        for (int v = 0; v < 2; ++v) {
+            const float4 cs = c4[v], sn = s4[v], lo = x[v], hi = x[2 + v];
+            x[v] = make_float4(lo.x * cs.x - hi.x * sn.x, lo.y * cs.y - hi.y * sn.y, lo.z * cs.z - hi.z * sn.z, lo.w * cs.w - hi.w * sn.w);
+            x[2 + v] = make_float4(hi.x * cs.x + lo.x * sn.x, hi.y * cs.y + lo.y * sn.y, hi.z * cs.z + lo.z * sn.z, hi.w * cs.w + lo.w * sn.w);
+        }
     }
+    T *o;
     if (is_q) {
-        store4(q_out + ((size_t)t * nq + h) * hd + 4 * lane, x);
+        o = q_out + ((size_t)t * nq + h) * hd;
     } else {
-        int kvh = is_k ? h - nq : h - nq - nkv;
-        T *plane = is_k ? k_cache : v_cache;
-        store4(plane + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd + 4 * lane, x);
+        const int kvh = is_k ? h - nq : h - nq - nkv;
+        o = (is_k ? k_cache : v_cache) + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd;
     }
+    store4(o + 8 * sub, x[0]);
+    store4(o + 8 * sub + 4, x[1]);
+    store4(o + 64 + 8 * sub, x[2]);
+    store4(o + 64 + 8 * sub + 4, x[3]);
 }
 
 KESTREL_API int kestrel_attn_prepare(const float *partial, int S, long long slice_stride,
@@ -587,11 +601,11 @@ KESTREL_API int kestrel_attn_prepare(const float *partial, int S, long long slic
     KESTREL_REQUIRE(page_size > 0, "attn_prepare: page size %d", page_size);
     long long warps = (long long)T * (nq + 2 * nkv);
     unsigned blocks = (unsigned)((warps + 3) / 4);
-    bool fast = hd == 128 && rot == 128 && rot_mode == 0 && slice_stride % 4 == 0 && (nq + 2 * nkv + 7) / 8 <= 65535 &&
+    bool fast = hd == 128 && rot == 128 && rot_mode == 0 && slice_stride % 4 == 0 && (nq + 2 * nkv + 31) / 32 <= 65535 &&
                 ((((uintptr_t)partial | (uintptr_t)bias | (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)q_out |
                    (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0);
     if (fast) {
-        dim3 grid(T, (nq + 2 * nkv + 7) / 8);
+        dim3 grid(T, (nq + 2 * nkv + 31) / 32);
         if (dtype == KESTREL_F32)
             kestrel_launch(attn_prepare_hd128_kernel<float>, grid, dim3(256), 0, stream, partial, S, (size_t)slice_stride, bias, q_norm_w,
                            k_norm_w, norm_eps, inv_freq, rot_scale, positions, seq_of_token, block_table, table_stride, page_size,
