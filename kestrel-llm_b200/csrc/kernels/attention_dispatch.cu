@@ -251,13 +251,32 @@ KESTREL_API int kestrel_attention(void *planner, long long step_serial, const in
     const int gs = nq / nkv;
     const bool use_tc = kestrel_attention_tc_supported(hd, page_size) != 0;
     // The tcgen05 kernel takes two row tiles of 128 a CTA, so that the tensor cores work on one
-    // while the other is in its softmax; with so few rows that CTAs of 256 would leave more than
-    // half of the SMs idle, one row tile a CTA and twice the CTAs is faster (measured, one request
-    // from position 0: 512 tokens 15.7 against 20.2 us, 256 tokens 11.6 against 15.7; 1,024 equal;
-    // 1,024 equal).  Far into a long context the few CTAs of 256 rows cut their key ranges into
-    // slices instead (below), which gains more.
+    // while the other is in its softmax.  Few rows leave SMs idle, one CTA per SM.  Where the keys
+    // are many the key range is cut into slices instead, as many as fill the SMs once, of at least
+    // 512 keys each, merged through scratch (a warp a row; measured alone, 4,096 keys of context:
+    // 512 tokens 86.7 -> 61.1 us with 2 slices, 256 tokens 81.6 -> 36.2 with 4, 64 tokens 78.7 ->
+    // 24.6 with 8; more CTAs than SMs lose again).  Where the keys are too few to cut, one row
+    // tile a CTA and twice the CTAs is the faster form (512 tokens from position 0: 20.2 -> 15.7 us;
+    // behind 1,024 keys 36.8 -> 31.2).
     int rows_large = use_tc ? 256 : kestrel_attention_mma_rows_per_tile(hd);
-    if (use_tc && layout[KB_MAX_KV_LEN] < 4096 && (long long)T * gs * nkv <= 128ll * kestrel_attention_tc_slots()) rows_large = 128;
+    int tc_slices = 1;
+    if (use_tc) {
+        // the portions of this step (requests with more than 16 rows): their rows, their tiles of 256, their longest context
+        const int *cu_h = batch_host + layout[KB_O_CU_SEQLENS], *kv_h = batch_host + layout[KB_O_KV_LENS];
+        long long rows = 0, tiles256 = 0;
+        int kv = 0;
+        for (int i = 0; i < n; ++i) {
+            const long long r = (long long)(cu_h[i + 1] - cu_h[i]) * gs;
+            if (r <= 16) continue;
+            rows += r;
+            tiles256 += (r + 255) / 256;
+            kv = std::max(kv, kv_h[i]);
+        }
+        const int sms = kestrel_attention_tc_slots();
+        const int cand = window > 0 ? 1 : (int)std::min<long long>(std::min<long long>(sms / std::max<long long>(1, tiles256 * nkv), kv / 512), 16);
+        if (cand >= 2 && (cand > 2 || kv >= 2048)) tc_slices = cand;
+        else if (rows * nkv <= 128ll * sms) rows_large = 128;
+    }
     const Plan *plan = nullptr;
     int rc = plan_for(*pl, step_serial, batch_host, batch_dev, layout, gs, rows_large, captured != 0, stream, &plan);
     if (rc) return rc;
@@ -300,14 +319,11 @@ KESTREL_API int kestrel_attention(void *planner, long long step_serial, const in
     }
     if (plan->nl > 0) {
         if (use_tc) {
-            // Few tiles far into a long context (a portion of a long prompt) leave SMs idle, one
-            // CTA per SM: the key range is then cut into slices of at least 2,048 keys, merged
-            // through scratch.
+            // the number of slices was chosen above, with the tile size; here it is fitted to the
+            // longest request among the portions
             int slices = 1, slice_len = NO_SPLIT;
-            const int ctas = plan->nl * nkv, sms = kestrel_attention_tc_slots();
-            if (window <= 0 && 2 * ctas <= sms && plan->large_kv >= 4096) {
-                const int cand = std::min(std::min(sms / ctas, plan->large_kv / 2048), 16);
-                slice_len = round_up(ceil_div(plan->large_kv, cand), 128);
+            if (tc_slices > 1 && plan->large_kv >= 1024) {
+                slice_len = round_up(ceil_div(plan->large_kv, tc_slices), 128);
                 slices = ceil_div(plan->large_kv, slice_len);
                 if (slices <= 1) { slices = 1; slice_len = NO_SPLIT; }
             }

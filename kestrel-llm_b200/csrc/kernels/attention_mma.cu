@@ -443,6 +443,61 @@ attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict
     }
 }
 
+// The same merge for tiles of many rows (prompt portions cut into key-range slices) and up to 32
+// slices: one WARP per row, a lane per slice for the weights and four output dims a lane, every
+// slice's values in flight at once; eight rows a block.  One block per row, with its three block
+// barriers, took some 25 us for the 16,384 rows of a 512-token portion - more than the slices
+// saved.  Slices are added in ascending order, as above.
+#define AMW_MAX_SLICES 32
+__global__ void __launch_bounds__(256)
+attention_merge_rows_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
+                            __nv_bfloat16 *__restrict__ out, const int *__restrict__ tile_seq,
+                            const int *__restrict__ tile_row0, const int *__restrict__ cu_seqlens,
+                            int slices, int hd, int nq, int nkv, int rows_per_tile) {
+    pdl_launch_dependents();
+    const int tile = blockIdx.x, kvh = blockIdx.y, lane = threadIdx.x & 31;
+    const int r = blockIdx.z * 8 + (threadIdx.x >> 5);
+    const int seq = tile_seq[tile], row0 = tile_row0[tile];
+    const int G = nq / nkv;
+    const int tok_begin = cu_seqlens[seq];
+    const int n_rows = (cu_seqlens[seq + 1] - tok_begin) * G;
+    if (r >= min(rows_per_tile, n_rows - row0)) return;
+    const int row = row0 + r;
+    const size_t qrow = (size_t)(tok_begin + row / G) * nq + kvh * G + row % G;
+    pdl_wait();
+    // lane s holds slice s: its maximum and sum
+    float2 ml = lane < slices ? *reinterpret_cast<const float2 *>(part_ml + (qrow * slices + lane) * 2) : make_float2(-INFINITY, 0.f);
+    const float M = warp_max(ml.x);
+    const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
+    const float lf = f != 0.f ? ml.y * f : 0.f;
+    const int d = 4 * lane;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float L = 0.f;
+    const float *po = part_o + qrow * slices * hd + d;
+    float4 v[AMW_MAX_SLICES / 4];
+    for (int s0 = 0; s0 < slices; s0 += AMW_MAX_SLICES / 4) {        // eight slices' values in flight
+#pragma unroll
+        for (int u = 0; u < AMW_MAX_SLICES / 4; ++u)
+            if (s0 + u < slices && d < hd) v[u] = *reinterpret_cast<const float4 *>(po + (size_t)(s0 + u) * hd);
+#pragma unroll
+        for (int u = 0; u < AMW_MAX_SLICES / 4; ++u) {
+            if (s0 + u >= slices) break;
+            const float fs = __shfl_sync(0xffffffffu, f, s0 + u);
+            L += __shfl_sync(0xffffffffu, lf, s0 + u);
+            if (fs != 0.f && d < hd) {
+                acc.x += v[u].x * fs; acc.y += v[u].y * fs; acc.z += v[u].z * fs; acc.w += v[u].w * fs;
+            }
+        }
+    }
+    if (d < hd) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x / L, acc.y / L), hi = __floats2bfloat162_rn(acc.z / L, acc.w / L);
+        uint2 u2;
+        u2.x = *reinterpret_cast<uint32_t *>(&lo);
+        u2.y = *reinterpret_cast<uint32_t *>(&hi);
+        *reinterpret_cast<uint2 *>(out + qrow * hd + d) = u2;
+    }
+}
+
 template <int HD, bool KEYS_MODE, int MT>
 static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream) {
     constexpr int BM = KEYS_MODE ? 16 : 64 * MT;
@@ -468,6 +523,11 @@ KESTREL_API int kestrel_attention_merge(const float *part_o, const float *part_m
     KESTREL_REQUIRE(rows_per_tile >= 1 && rows_per_tile <= 65535, "attention_merge: tiles of %d rows", rows_per_tile);
     KESTREL_REQUIRE(slices >= 1 && slices <= AMG_MAX_SLICES, "attention_merge: %d slices; the kernel merges up to %d", slices, AMG_MAX_SLICES);
     KESTREL_REQUIRE(tiles <= 0x7fffffff && nkv <= 65535, "attention_merge: grid too large");
+    if (rows_per_tile > 16 && slices <= AMW_MAX_SLICES && hd % 4 == 0 && hd <= 128 && (((uintptr_t)part_o | (uintptr_t)out) & 15) == 0) {
+        kestrel_launch(attention_merge_rows_kernel, dim3(tiles, nkv, (rows_per_tile + 7) / 8), dim3(256), 0, stream, part_o, part_ml,
+                       (__nv_bfloat16 *)out, tile_seq, tile_row0, cu_seqlens, slices, hd, nq, nkv, rows_per_tile);
+        return kestrel_check_launch("attention_merge");
+    }
     kestrel_launch(attention_merge_kernel, dim3(tiles, nkv, rows_per_tile), dim3(AMG_THREADS), 0, stream, part_o, part_ml, (__nv_bfloat16 *)out,
                    tile_seq, tile_row0, cu_seqlens, slices, hd, nq, nkv);
     return kestrel_check_launch("attention_merge");
