@@ -15,7 +15,7 @@ both numbers); layer sizes never shrink.
 
 `--workload mix14b`: 32 requests with prompts of 128 to 2,048 tokens (seed-fixed) and 256 greedy
 tokens each at the sizes of Qwen3-14B, through `LLM.add_request` / `LLM.step`, prompt portions
-of 512 tokens mixed with decode tokens.  `--workload 32b`: 16 requests of 1,024 + 128 tokens at
+mixed with decode tokens under a budget of 512 tokens a step (two token tiles of the products).  `--workload 32b`: 16 requests of 1,024 + 128 tokens at
 the sizes of Qwen3-32B (64 query heads of 128 on a width of 5,120).  Each prints one JSON line
 with total, prompt and generated tokens a second, the time of all steps on the device, the
 wall-clock time over it, and the steps' fraction of their roofline.
@@ -164,7 +164,7 @@ def run_workload(args) -> int:
     fill_random_(model, 0)
     longest = max(lengths) + gen + 64
     opts = EngineOptions(dtype="bfloat16", page_size=args.page_size, batch_max=n_req, max_model_len=longest,
-                         max_tokens=sum(l + gen + 64 for l in lengths), max_step_tokens=chunk + n_req, prefill_batch=chunk)
+                         max_tokens=sum(l + gen + 64 for l in lengths), max_step_tokens=chunk, prefill_batch=chunk)
     llm = LLM(model, dtype="bfloat16", options=opts)
     llm.engine.cache.shuffle_free(0)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lengths]
