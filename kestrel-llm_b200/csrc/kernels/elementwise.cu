@@ -175,6 +175,16 @@ add_rmsnorm_vec_kernel(float *__restrict__ residual, const float *__restrict__ p
 // z, w, virtual lanes 32 g .. 32 g + 31 are combined by the same shuffle tree and the 32 group
 // sums in ascending order - so a row's bits do not depend on which variant ran.
 // NV: vectors per lane, 32 NV >= d / 4.
+// Rows from which the norm takes a warp a row, where it only reads the stream (the products
+// added themselves already).  With slices to add and the stream to write back the block-a-row
+// kernel is twice as fast (measured, 4,096 rows of two slices: 52 against 106 us; 1,536 rows of
+// three: 29 against 58), so the warp kernel is not taken then unless a test asks for it.
+static int g_norm_warp_rows = 1024, g_norm_warp_slices = 0;
+KESTREL_API void kestrel_set_norm_warp_rows(int rows, int with_slices) {
+    g_norm_warp_rows = rows > 0 ? rows : 1024;
+    g_norm_warp_slices = with_slices ? 1 : 0;
+}
+
 template <typename TOut, int NV>
 __global__ void __launch_bounds__(128)
 add_rmsnorm_warp_kernel(float *__restrict__ residual, const float *__restrict__ partial, int S, size_t slice_stride,
@@ -189,24 +199,47 @@ add_rmsnorm_warp_kernel(float *__restrict__ residual, const float *__restrict__ 
     const int d4 = d >> 2;
     float4 *res = reinterpret_cast<float4 *>(residual + (size_t)t * d);
     float4 x[NV];
-#pragma unroll
-    for (int j = 0; j < NV; ++j) {
-        const int i = 32 * j + lane;
-        x[j] = i < d4 ? res[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
     if (partial) {
+        // delta = ((0 + P[0]) + P[1]) + ... + bias, then residual + delta: the other norm kernels'
+        // order.  A pass over the row per slice, so that all of a pass's loads are in flight at
+        // once (one element's slices one after the other is a chain of S load latencies, thirty-two
+        // times over: measured 80 us instead of 20 for 1,536 rows of three slices).
         const float4 *p4 = reinterpret_cast<const float4 *>(partial + (size_t)t * d);
         const float4 *bias4 = reinterpret_cast<const float4 *>(bias);
         const size_t st4 = slice_stride >> 2;
+        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = 32 * j + lane;
+            x[j] = i < d4 ? add4(zero, p4[i]) : zero;
+        }
+        for (int s = 1; s < S; ++s) {
+            const float4 *ps = p4 + (size_t)s * st4;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int i = 32 * j + lane;
+                if (i < d4) x[j] = add4(x[j], ps[i]);
+            }
+        }
+        if (bias) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int i = 32 * j + lane;
+                if (i < d4) x[j] = add4(x[j], bias4[i]);
+            }
+        }
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             const int i = 32 * j + lane;
             if (i >= d4) continue;
-            float4 delta = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s = 0; s < S; ++s) delta = add4(delta, p4[(size_t)s * st4 + i]);
-            if (bias) delta = add4(delta, bias4[i]);
-            x[j] = add4(x[j], delta);
+            x[j] = add4(res[i], x[j]);
             if (write_back) res[i] = x[j];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = 32 * j + lane;
+            x[j] = i < d4 ? res[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
     float tot = 0.f;
@@ -249,7 +282,7 @@ static void launch_add_rmsnorm(float *residual, const float *partial, int S, lon
     bool vec = d % 4 == 0 && d >= 2048 && slice_stride % 4 == 0 &&
                ((((uintptr_t)residual | (uintptr_t)partial | (uintptr_t)bias | (uintptr_t)w) & 15) == 0) &&
                (((uintptr_t)out & 7) == 0);
-    if (vec && R >= 1024 && d <= 48 * 128) {
+    if (vec && R >= g_norm_warp_rows && d <= 48 * 128 && (!partial || g_norm_warp_slices)) {
         // very many rows: a warp a row (widths up to 6144 fit a lane's registers; measured faster from about a thousand rows on)
         const dim3 grid((R + 3) / 4), block(128);
         if (d <= 16 * 128)
@@ -282,6 +315,7 @@ KESTREL_API int kestrel_add_rmsnorm(float *residual, const float *partial, int S
     if (R == 0) return 0;
     KESTREL_REQUIRE(R > 0 && d > 0, "add_rmsnorm: bad sizes R=%d d=%d", R, d);
     KESTREL_REQUIRE(!(rows && write_back), "add_rmsnorm: write_back with gathered rows");
+    KESTREL_REQUIRE(!partial || S >= 1, "add_rmsnorm: a product of %d slices", S);
     size_t smem = (size_t)d * sizeof(float);
     KESTREL_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: width %d exceeds the 51200 the kernel holds in shared memory", d);
     if (out_dtype == KESTREL_F32)

@@ -30,7 +30,13 @@
 #define TC_BK 64
 #define TC_THREADS 192
 
-enum { TC_PARTIAL = 0, TC_SWIGLU = 1, TC_PARTIAL2 = 2, TC_SWIGLU_T = 3 };     // PARTIAL2: two weight tiles a CTA, as SWIGLU, both written as float32 slices
+enum { TC_PARTIAL = 0, TC_SWIGLU = 1, TC_PARTIAL2 = 2, TC_SWIGLU_T = 3, TC_QKV_PREP = 4 };     // PARTIAL2: two weight tiles a CTA, as SWIGLU, both written as float32 slices
+// QKV_PREP (CTA pairs only): the q, k, v product with the tokens as the M operand and, in its
+// epilogue, everything the prepare kernel does between that product and attention for head
+// size 128: bias, per-head RMSNorm, rotate-half rotation, queries out, keys and values into their
+// cache pages.  A tile is 256 tokens x 2 heads (one head's 128 weight rows from each rank), so a
+// TMEM lane holds one token's whole head: the product's float32 plane (50 MB at 2,048 tokens of
+// 8B size) is neither written nor read back, and the prepare kernel's 20 us a layer go.
 // SWIGLU_T (CTA pairs only): the roles of the operands swapped - tokens are the MMA's M operand,
 // the weights its N operand (128 gate rows from one rank, the 128 up rows of the same features
 // from the other) - so that ONE accumulator of 256 columns holds gate and up of a (token,
@@ -39,6 +45,16 @@ enum { TC_PARTIAL = 0, TC_SWIGLU = 1, TC_PARTIAL2 = 2, TC_SWIGLU_T = 3 };     //
 // large, which fills the last round of tiles better.
 
 __device__ int g_tc_error = 0;
+
+// what the QKV_PREP epilogue needs beside the product's own arguments
+struct QkvPrepParams {
+    const float *bias, *q_norm_w, *k_norm_w, *inv_freq;
+    float norm_eps, rot_scale;
+    const int *positions, *seq_of_token, *block_table;
+    int table_stride, page_size;
+    __nv_bfloat16 *k_cache, *v_cache, *q_out;
+    int nq, nkv, write_kv;
+};
 
 // ------------------------------------------------------------------------------- kernel
 template <int BN, int MODE>
@@ -428,9 +444,10 @@ template <int MODE>
 __global__ void __launch_bounds__(TCP_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     void *__restrict__ out, int T, int N, int K, long long ldo, int stages, int tiles_n, int tiles_total,
-                    int up_row_offset, int accumulate, int tiles_nt, int kb_per_split, long long slice_stride) {
+                    int up_row_offset, int accumulate, int tiles_nt, int kb_per_split, long long slice_stride,
+                    const QkvPrepParams prep) {
     pdl_launch_dependents();
-    constexpr bool SWAP = MODE == TC_SWIGLU_T;
+    constexpr bool SWAP = MODE == TC_SWIGLU_T || MODE == TC_QKV_PREP;      // tokens are the M operand
     constexpr int A_TILES = MODE == TC_SWIGLU ? 2 : 1;
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = (TCP_BN / 2) * TC_BK * 2;
@@ -493,7 +510,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const int split = tile / tiles_nt, tw = tile % tiles_nt;       // a tile of the output and its slice of K
                 int n0 = tile_n(tw) * 256 + (int)rank * TC_BM;
                 int t0 = tile_t(tw) * TCP_BN + (int)rank * (TCP_BN / 2);
-                if (SWAP) n0 = tile_n(tw) * TC_BM + (rank ? up_row_offset : 0);     // this rank's half of the N operand: gate rows, or up rows
+                if (MODE == TC_SWIGLU_T) n0 = tile_n(tw) * TC_BM + (rank ? up_row_offset : 0);     // this rank's half of the N operand: gate rows, or up rows
+                if (MODE == TC_QKV_PREP) n0 = (2 * tile_n(tw) + (int)rank) * TC_BM;                  // one head's rows from each rank
                 const int kb_end = min(num_kb, (split + 1) * kb_per_split);
                 for (int kb = split * kb_per_split; kb < kb_end; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1)) { atomicExch(&g_tc_error, 1); ok = false; break; }
@@ -556,6 +574,103 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (!mbar_wait(acc_full(b), acc_phase)) { if (lane == 0) atomicExch(&g_tc_error, 3); break; }
             tc_fence_after();
             uint32_t d = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)b * ACC_COLS;
+            if (MODE == TC_QKV_PREP) {
+                // lane = token, columns 0..127 = head 2 fn, 128..255 = head 2 fn + 1.  The four warps that
+                // share a lane quarter each take sixteen rotation pairs (dimensions 16 g.. and 64 + 16 g..)
+                // of both heads; they exchange their parts of the sums of squares through shared memory.
+                __shared__ float ss_x[2][2][4][128];                     // [tile parity][head of the tile][group][token]
+                const int grp = (warp - 2) >> 2, tl = 32 * q + lane;
+                const int t = t0 + (int)rank * (TCP_BN / 2) + tl;
+                const bool t_ok = t < T;
+                const int heads = prep.nq + 2 * prep.nkv, head0 = 2 * tile_n(tw);
+                const int pos = t_ok ? prep.positions[t] : 0;
+                int page = 0;
+                if (t_ok && prep.write_kv) page = prep.block_table[(size_t)prep.seq_of_token[t] * prep.table_stride + pos / prep.page_size];
+                float cs[16], sn[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    sincosf((float)pos * prep.inv_freq[16 * grp + c], &sn[c], &cs[c]);
+                    cs[c] *= prep.rot_scale;
+                    sn[c] *= prep.rot_scale;
+                }
+                float (*ssb)[4][128] = ss_x[j & 1];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int head = head0 + hh;
+                    float lo[16], hi[16];
+                    tc_ld16(d + hh * TC_BM + 16 * grp, lo);
+                    tc_ld16(d + hh * TC_BM + 64 + 16 * grp, hi);
+                    float ss = 0.f;
+                    if (head < heads) {
+                        const float *b = prep.bias ? prep.bias + (size_t)head * TC_BM : nullptr;
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            if (b) { lo[c] += b[16 * grp + c]; hi[c] += b[64 + 16 * grp + c]; }
+                            ss += lo[c] * lo[c] + hi[c] * hi[c];
+                        }
+                    }
+                    ssb[hh][grp][tl] = ss;
+                }
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + q) : "memory");       // the four warps of this lane quarter
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int head = head0 + hh;
+                    if (head >= heads) continue;
+                    const bool is_q = head < prep.nq, is_k = !is_q && head < prep.nq + prep.nkv;
+                    if (!is_q && !prep.write_kv) continue;
+                    float lo[16], hi[16];
+                    tc_ld16(d + hh * TC_BM + 16 * grp, lo);
+                    tc_ld16(d + hh * TC_BM + 64 + 16 * grp, hi);
+                    if (prep.bias) {
+                        const float *b = prep.bias + (size_t)head * TC_BM;
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) { lo[c] += b[16 * grp + c]; hi[c] += b[64 + 16 * grp + c]; }
+                    }
+                    const float *nw = is_q ? prep.q_norm_w : (is_k ? prep.k_norm_w : nullptr);
+                    if (nw) {
+                        const float tot = ((ssb[hh][0][tl] + ssb[hh][1][tl]) + ssb[hh][2][tl]) + ssb[hh][3][tl];
+                        const float rinv = 1.0f / sqrtf(tot / (float)TC_BM + prep.norm_eps);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            lo[c] = (lo[c] * rinv) * nw[16 * grp + c];
+                            hi[c] = (hi[c] * rinv) * nw[64 + 16 * grp + c];
+                        }
+                    }
+                    if (is_q || is_k) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const float a = lo[c], b2 = hi[c];
+                            lo[c] = a * cs[c] - b2 * sn[c];
+                            hi[c] = b2 * cs[c] + a * sn[c];
+                        }
+                    }
+                    if (t_ok) {
+                        __nv_bfloat16 *o;
+                        if (is_q) {
+                            o = prep.q_out + ((size_t)t * prep.nq + head) * TC_BM;
+                        } else {
+                            const int kvh = is_k ? head - prep.nq : head - prep.nq - prep.nkv;
+                            o = (is_k ? prep.k_cache : prep.v_cache) + (((size_t)page * prep.nkv + kvh) * prep.page_size + pos % prep.page_size) * TC_BM;
+                        }
+                        uint32_t pl[8], ph[8];
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            __nv_bfloat162 a = __floats2bfloat162_rn(lo[2 * c], lo[2 * c + 1]), b2 = __floats2bfloat162_rn(hi[2 * c], hi[2 * c + 1]);
+                            pl[c] = *reinterpret_cast<uint32_t *>(&a);
+                            ph[c] = *reinterpret_cast<uint32_t *>(&b2);
+                        }
+                        uint4 *dl = reinterpret_cast<uint4 *>(o + 16 * grp), *dh = reinterpret_cast<uint4 *>(o + 64 + 16 * grp);
+                        dl[0] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                        dl[1] = make_uint4(pl[4], pl[5], pl[6], pl[7]);
+                        dh[0] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                        dh[1] = make_uint4(ph[4], ph[5], ph[6], ph[7]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_rank(acc_empty(b), 0));
+                continue;
+            }
             if (SWAP) {
                 // lane = token, columns 0..127 = gate of 128 features, 128..255 = up of the same features;
                 // each group of four warps takes a quarter of the features
@@ -709,6 +824,7 @@ KESTREL_API int kestrel_gemm_tc_supported(const void *x, const void *w, int T, i
 // g_ctas_per_sm CTAs share an SM's shared memory for their stages; a CTA costs about
 // g_overhead_kb k-blocks of time beyond its own k-blocks (launch, barrier set-up, TMEM
 // allocation, first tensor-map fetch, pipeline fill, epilogue).
+static int g_qkv_fused = 1;        // the q, k, v product of many tokens does the prepare kernel's work in its epilogue
 static int g_swiglu_swapped = 1;   // the SwiGLU product on CTA pairs with tokens as the M operand (TC_SWIGLU_T)
 static int g_swiglu_bn = 256;      // token tile of the persistent SwiGLU product: 256 (one accumulator pair) or 128 (two)
 static int g_pairs = 1;            // many-token PARTIAL products on CTA pairs (cta_group::2)
@@ -745,22 +861,35 @@ static int g_wide = 1, g_wide_min = 32;
 KESTREL_API void kestrel_gemm_tc_set_wide(int on, int more_than_tokens) { g_wide = on ? 1 : 0; if (more_than_tokens >= 0) g_wide_min = more_than_tokens; }
 static bool tc_wide(int T, int N) { return g_wide && T > g_wide_min && T <= 128 && T <= g_pair_min_tokens && N % (2 * TC_BM) == 0; }
 
+// Cost of a many-token product on CTA pairs cut into s slices along K, in k-blocks of one
+// pair's time (about 0.42 us at these sizes); -1 where s does not divide the k-blocks into slices
+// of at least sixteen.  A slice costs about g_pair_overhead_kb k-blocks beyond its own (pipeline
+// fill, the last tile's epilogue); the slices' float32 planes cost their write and their read
+// by the consumer as far as they no longer fit L2 (measured at 3,072 tokens: the down product in
+// three slices 227 + 89 us with its norm, whole 251 + 47).
+static long long pair_cost(int T, int N, int K, int s, long long *waves_out = nullptr) {
+    const long long tiles = (long long)((N + 255) / 256) * ((T + TCP_BN - 1) / TCP_BN);
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    const int pairs = kestrel_sms() / 2;
+    const int per = (total_kb + s - 1) / s;
+    if (s > 1 && (per < 16 || (total_kb + per - 1) / per != s)) return -1;
+    const long long waves = (tiles * s + pairs - 1) / pairs;
+    if (waves_out) *waves_out = waves;
+    long long planes = 8ll * T * N * (s - 1) - (64ll << 20);
+    if (planes < 0) planes = 0;
+    return waves * (g_pair_overhead_kb + per) + planes / 2100000;
+}
+
 KESTREL_API int kestrel_gemm_tc_splits(int T, int N, int K) {
     if (T > g_pair_min_tokens) {
-        // many tokens on CTA pairs: tiles of 256 x 256 over the pairs of SMs.  A slice costs about
-        // g_pair_overhead_kb k-blocks beyond its own (pipeline fill, the last tile's epilogue, its
-        // float32 plane written and read back); K is cut only where that fills idle pairs.
+        // many tokens on CTA pairs: tiles of 256 x 256 over the pairs of SMs; K is cut only where
+        // that fills idle pairs
         if (!g_pairs || !g_persistent) return 1;
-        long long tiles = (long long)((N + 255) / 256) * ((T + TCP_BN - 1) / TCP_BN);
-        int total_kb = (K + TC_BK - 1) / TC_BK;
-        const int pairs = kestrel_sms() / 2;
         int best = 1;
         long long best_cost = -1;
         for (int s = 1; s <= 8; ++s) {
-            int per = (total_kb + s - 1) / s;
-            if (s > 1 && (per < 16 || (total_kb + per - 1) / per != s)) continue;
-            long long waves = (tiles * s + pairs - 1) / pairs;
-            long long cost = waves * (g_pair_overhead_kb + per);
+            long long cost = pair_cost(T, N, K, s);
+            if (cost < 0) continue;
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
         }
         return best;
@@ -846,7 +975,8 @@ static int launch_tc_persistent(const CUtensorMap &mw, const CUtensorMap &mx, vo
 
 template <int MODE>
 static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *out, int T, int N, int K, long long ldo,
-                          int up_off, int accumulate, int splits, long long slice_stride, cudaStream_t stream) {
+                          int up_off, int accumulate, int splits, long long slice_stride, cudaStream_t stream,
+                          const QkvPrepParams &prep = QkvPrepParams()) {
     const int STAGE_BYTES = (MODE == TC_SWIGLU ? 2 : 1) * TC_BM * TC_BK * 2 + (TCP_BN / 2) * TC_BK * 2;
     int stages = (200 * 1024) / STAGE_BYTES;
     if (stages > 8) stages = 8;
@@ -864,7 +994,7 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (max_clusters < 0) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return kestrel_fail(-3, "gemm_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
         cfg.gridDim = dim3(kestrel_sms());
         int n = 0;
@@ -878,6 +1008,7 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
     }
     if (max_clusters == 0) return 1;       // not an error: tells the caller to fall back
     // output tiles: 256 features x 256 tokens; with the operands swapped 128 features x 256 tokens
+    // (QKV_PREP: 256 features = two heads of 128 x 256 tokens, N = all heads' rows)
     int tiles_n = MODE == TC_SWIGLU_T ? (N + TC_BM - 1) / TC_BM : (N + 255) / 256, tiles_t = (T + TCP_BN - 1) / TCP_BN;
     long long tiles_nt = (long long)tiles_n * tiles_t, total = tiles_nt * splits;
     if (total > 0x7fffffff) return kestrel_fail(-2, "gemm_tc: too many tiles");
@@ -887,7 +1018,7 @@ static int launch_tc_pair(const CUtensorMap &mw, const CUtensorMap &mx, void *ou
     int pairs = total < max_clusters ? (int)total : max_clusters;
     cfg.gridDim = dim3(2 * pairs);
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<MODE>, mw, mx, out, T, N, K, ldo, stages, tiles_n, (int)total, up_off, accumulate,
-                                       (int)tiles_nt, per, slice_stride);
+                                       (int)tiles_nt, per, slice_stride, prep);
     if (e != cudaSuccess) return kestrel_fail(-3, "gemm_tc_pair: %s", cudaGetErrorString(e));
     return kestrel_check_launch("gemm_tc_pair");
 }
@@ -983,6 +1114,48 @@ KESTREL_API int kestrel_gemm_tc_add(const void *x, const void *w, float *residua
     if (rc) return rc;
     return launch_tc_pair<TC_PARTIAL>(mw, mx, residual, T, N, K, ldo, 0, 1, 1, 0, stream);
 }
+
+// The q, k, v product of a prompt portion and everything between it and attention in one kernel
+// (QKV_PREP above): x bf16 [T, K], w bf16 [(nq + 2 nkv) * 128, K]; the other arguments as
+// kestrel_attn_prepare's.  Returns 0 when done; 1 when this form does not apply - few tokens, a
+// product that is better cut along K (a few hundred tokens), another head size or rotation,
+// pairs that cannot be scheduled - and nothing was launched: the caller then runs the product and
+// the prepare kernel.
+KESTREL_API int kestrel_gemm_tc_qkv_prepare(const void *x, const void *w, int T, int K, long long ldx, long long ldw, const float *bias,
+                                            const float *q_norm_w, const float *k_norm_w, float norm_eps, const float *inv_freq, int rot,
+                                            int rot_mode, float rot_scale, const int *positions, const int *seq_of_token,
+                                            const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache,
+                                            void *q_out, int nq, int nkv, int hd, int write_kv, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!g_qkv_fused || hd != TC_BM || rot != TC_BM || rot_mode != 0 || !inv_freq || nq <= 0 || nkv <= 0 || page_size <= 0) return 1;
+    const int N = (nq + 2 * nkv) * TC_BM;
+    if (T <= g_pair_min_tokens || !g_persistent || !g_pairs || !kestrel_gemm_tc_supported(x, w, T, N, K, ldx, ldw)) return 1;
+    if (g_qkv_fused < 2) {
+        // uncut where cutting along K gains nothing, or little while the tiles come in three rounds
+        // or more, so that all but the last epilogue run under the next tile's products (measured:
+        // 1,792 tokens 98 us uncut and fused against 117 us in two slices with the prepare kernel;
+        // 512 tokens, one round, 44 against 36)
+        const int S = kestrel_gemm_tc_splits(T, N, K);
+        long long waves = 0;
+        const long long whole = pair_cost(T, N, K, 1, &waves);
+        if (S > 1 && !(waves >= 3 && whole * 10 <= pair_cost(T, N, K, S) * 11)) return 1;
+    }
+    if ((((uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) != 0) return 1;
+    CUtensorMap mw, mx;
+    int rc = kestrel_tensor_map_bf16(&mw, w, N, K, ldw, TC_BM);
+    if (rc) return rc;
+    rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, TCP_BN / 2);
+    if (rc) return rc;
+    QkvPrepParams prep;
+    prep.bias = bias; prep.q_norm_w = q_norm_w; prep.k_norm_w = k_norm_w; prep.inv_freq = inv_freq;
+    prep.norm_eps = norm_eps; prep.rot_scale = rot_scale; prep.positions = positions; prep.seq_of_token = seq_of_token;
+    prep.block_table = block_table; prep.table_stride = table_stride; prep.page_size = page_size;
+    prep.k_cache = (__nv_bfloat16 *)k_cache; prep.v_cache = (__nv_bfloat16 *)v_cache; prep.q_out = (__nv_bfloat16 *)q_out;
+    prep.nq = nq; prep.nkv = nkv; prep.write_kv = write_kv ? 1 : 0;
+    return launch_tc_pair<TC_QKV_PREP>(mw, mx, nullptr, T, N, K, 0, 0, 0, 1, 0, stream, prep);
+}
+
+KESTREL_API void kestrel_gemm_tc_set_qkv_fused(int mode) { g_qkv_fused = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 
 // out bf16 [T, ff] = silu(x Wg^T) * (x Wu^T), w bf16 [2 ff, K] with the gate rows first;
 // weights_static as in kestrel_gemm_tc_w

@@ -58,6 +58,8 @@ struct Reg {
     int dtype = KESTREL_F32;      // element type of a plain tensor
     int slices = -1;              // >= 0: float32 slices [slices, rows, cols] still to be summed (0: added already, nothing pending)
     const float *bias = nullptr;  // still to be added by the consumer of the slices
+    void *prepared = nullptr;     // a q, k, v product whose kernel did the prepare op's work too: the queries it wrote
+    void *q_room = nullptr;       // room taken for the queries when that kernel was tried and did not take the case
     bool persistent = false;
 };
 
@@ -193,6 +195,29 @@ struct Walk {
                             break;
                         }
                     }
+                    if (!dry && bf16 && op.b < 0 && oi + 1 < pg.ops.size() && pg.ops[oi + 1].kind == OP_ATTN_PREPARE && pg.ops[oi + 1].a == op.out) {
+                        // a q, k, v product of many tokens does its consumer's work in its epilogue, where
+                        // that kernel takes the sizes; the product's float32 plane is then never made (a
+                        // dry walk counts both the plane and the queries: an upper bound)
+                        const Op &pp = pg.ops[oi + 1];
+                        if (op.N == (pp.nq + 2 * pp.nkv) * pp.hd && pp.group >= 0 && pp.group < layout[KB_NUM_GROUPS]) {
+                            void *q_out = take((size_t)T * pp.nq * pp.hd * elem_size(pg.dtype), false);
+                            int fused = kestrel_gemm_tc_qkv_prepare(xp, op.w, T, op.K, op.K, op.ldw, op.bias, pp.w2, pp.w3, pp.eps, (const float *)pp.w,
+                                                                    pp.rot, pp.rot_mode, pp.rot_scale, dev + layout[KB_O_POSITIONS],
+                                                                    dev + layout[KB_O_SEQ_OF_TOKEN], dev + layout[KB_O_TABLES] + (size_t)pp.group * n * W, W,
+                                                                    pp.page_size, (void *)pp.k_cache, (void *)pp.v_cache, q_out, pp.nq, pp.nkv, pp.hd,
+                                                                    pp.flag, stream);
+                            if (fused < 0) return fused;
+                            if (fused == 0) {
+                                launches++;
+                                o.slices = 0;
+                                o.ptr = nullptr;
+                                o.prepared = q_out;
+                                break;
+                            }
+                            o.q_room = q_out;              // the prepare op writes its queries there
+                        }
+                    }
                     const int S = bf16 ? kestrel_gemm_tc_plan(xp, op.w, T, op.N, op.K, op.K, op.ldw) : 0;
                     o.slices = S > 0 ? S : 1;
                     o.ptr = take((size_t)o.slices * T * op.N * 4, false);
@@ -240,7 +265,11 @@ struct Walk {
                     const Reg &qkv = regs[op.a];
                     Reg &o = regs[op.out];
                     o.rows = T; o.cols = op.nq * op.hd; o.dtype = pg.dtype;
-                    o.ptr = take((size_t)T * o.cols * elem_size(pg.dtype), false);
+                    if (!dry && qkv.prepared) {
+                        o.ptr = qkv.prepared;
+                        break;
+                    }
+                    o.ptr = (!dry && qkv.q_room) ? qkv.q_room : take((size_t)T * o.cols * elem_size(pg.dtype), false);
                     if (!dry) {
                         if (qkv.slices < 1 || qkv.cols != (op.nq + 2 * op.nkv) * op.hd)
                             return kestrel_fail(-2, "step program: op %zu: the register is not a q, k, v product of %d + 2 x %d heads", oi, op.nq, op.nkv);

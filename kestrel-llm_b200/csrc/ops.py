@@ -163,6 +163,13 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
                                    out.data_ptr(), T, d, _stream()))
 
 
+def norm_set_warp_rows(rows: int = 0, with_slices: bool = False) -> None:
+    """From how many rows on a norm that only reads the stream takes the kernel with a warp a row
+    (0: the default, 1024), and whether a norm that adds slices takes it too (by default it does
+    not: the block-a-row kernel is faster there).  For tests of both kernels."""
+    library().kestrel_set_norm_warp_rows(int(rows), 1 if with_slices else 0)
+
+
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[Partials], weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
     """x = residual[t] + delta[t]; residual[t] = x if write_back; out[r] = rmsnorm(x) * weight,
@@ -225,6 +232,39 @@ def attn_prepare(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: Opti
         block_table.data_ptr(), block_table.stride(0), int(page_size), k_cache.data_ptr(),
         v_cache.data_ptr(), q_out.data_ptr(), _code(q_out, "attn_prepare.q_out"), T, nq, nkv, hd,
         1 if write_kv else 0, _stream()))
+
+
+def qkv_prepare_fused(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_norm_w: Optional[torch.Tensor],
+                      k_norm_w: Optional[torch.Tensor], norm_eps: float, inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                      positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                      k_cache: torch.Tensor, v_cache: torch.Tensor, q_out: torch.Tensor, nq: int, nkv: int, hd: int,
+                      write_kv: bool = True, rot_mode: int = 0, rot_scale: float = 1.0) -> bool:
+    """The q, k, v product of x [T, K] with w [(nq + 2 nkv) hd, K] and all of ``attn_prepare`` in
+    one tcgen05 kernel.  False, and nothing launched, where that kernel does not take the case
+    (float32, few tokens, a head size or rotation other than 128 / rotate-half over the whole
+    head): the caller then runs the product and ``attn_prepare``."""
+    if x.dtype != torch.bfloat16 or inv_freq is None or x.stride(1) != 1 or w.stride(1) != 1:
+        return False
+    _need(x, "qkv_prepare.x", torch.bfloat16, 2)
+    _need(w, "qkv_prepare.w", torch.bfloat16, 2)
+    _need(q_out, "qkv_prepare.q_out", torch.bfloat16, 2)
+    _need(positions, "qkv_prepare.positions", torch.int32, 1)
+    _need(seq_of_token, "qkv_prepare.seq_of_token", torch.int32, 1)
+    _need(block_table, "qkv_prepare.block_table", torch.int32, 2)
+    _need(k_cache, "qkv_prepare.k_cache", torch.bfloat16)
+    _need(v_cache, "qkv_prepare.v_cache", torch.bfloat16)
+    T, K = x.shape
+    if w.shape != ((nq + 2 * nkv) * hd, K) or q_out.shape != (T, nq * hd) or not q_out.is_contiguous():
+        raise KernelError("qkv_prepare: shapes differ")
+    rc = library().kestrel_gemm_tc_qkv_prepare(
+        x.data_ptr(), w.data_ptr(), T, K, x.stride(0), w.stride(0), _p(bias), _p(q_norm_w), _p(k_norm_w), float(norm_eps),
+        _p(inv_freq), int(rotary_dim), int(rot_mode), float(rot_scale), positions.data_ptr(), seq_of_token.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), int(page_size), k_cache.data_ptr(), v_cache.data_ptr(),
+        q_out.data_ptr(), nq, nkv, hd, 1 if write_kv else 0, _stream())
+    if rc == 1:
+        return False
+    _check(rc)
+    return True
 
 
 def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -395,6 +435,13 @@ def gemm_tc_set_many_token_path(pairs: bool = True, persistent: bool = True, swi
                     ("kestrel_gemm_tc_set_swiglu_tile", int(swiglu_tile)), ("kestrel_gemm_tc_set_swiglu_swapped", 1 if swiglu_swapped is None else (2 if swiglu_swapped else 0))):
         fn = getattr(lib, name)
         fn(v)
+
+
+def gemm_tc_set_qkv_fused(on: Optional[bool] = None) -> None:
+    """Whether a q, k, v product of many tokens does ``attn_prepare``'s work in its epilogue: where
+    the product would not be cut along K (None, the default), wherever the kernel takes the
+    sizes (True), never (False).  For tests of both paths."""
+    library().kestrel_gemm_tc_set_qkv_fused(1 if on is None else (2 if on else 0))
 
 
 def gemm_tc_error() -> int:

@@ -144,6 +144,7 @@ KESTREL_API int kestrel_kernel_errors(void);
 
 /* ---- elementwise kernels ---- */
 KESTREL_API int kestrel_embed(const void *table, int dtype, const int *ids, float *out, int T, int d, kestrel_stream_t stream);
+KESTREL_API void kestrel_set_norm_warp_rows(int rows, int with_slices);   /* rows from which a norm that only reads the stream takes a warp a row (0: the default), and whether one that adds slices does too; for tests of both kernels */
 KESTREL_API int kestrel_add_rmsnorm(float *residual, const float *partial, int S, long long slice_stride, const float *bias, const int *rows, const float *w, float eps, void *out, int out_dtype, int R, int d, int write_back, kestrel_stream_t stream);
 KESTREL_API int kestrel_swiglu(const float *partial, int S, long long slice_stride, void *out, int out_dtype, int T, int ff, kestrel_stream_t stream);
 /* rot_mode: 0 pairs dimension j with j + rot/2 (rotate-half), 1 pairs 2j with 2j + 1 (interleaved); rot_scale multiplies cos and sin */
@@ -160,6 +161,9 @@ KESTREL_API int kestrel_gemm_tc(const void *x, const void *w, float *out, int T,
 KESTREL_API int kestrel_gemm_tc_add(const void *x, const void *w, float *residual, int T, int N, int K, long long ldx, long long ldw, long long ldo, kestrel_stream_t stream);
 KESTREL_API int kestrel_gemm_tc_swiglu_w(const void *x, const void *w, void *out, int T, int ff, int K, long long ldx, long long ldw, long long ldo, int weights_static, kestrel_stream_t stream);
 KESTREL_API int kestrel_gemm_tc_swiglu(const void *x, const void *w, void *out, int T, int ff, int K, long long ldx, long long ldw, long long ldo, kestrel_stream_t stream);
+/* the q, k, v product of many tokens with the prepare kernel's work in its epilogue (head size 128, rotate-half over the whole head); 0 done, 1 this form does not apply and nothing ran */
+KESTREL_API int kestrel_gemm_tc_qkv_prepare(const void *x, const void *w, int T, int K, long long ldx, long long ldw, const float *bias, const float *q_norm_w, const float *k_norm_w, float norm_eps, const float *inv_freq, int rot, int rot_mode, float rot_scale, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, int nq, int nkv, int hd, int write_kv, kestrel_stream_t stream);
+KESTREL_API void kestrel_gemm_tc_set_qkv_fused(int mode);   /* 0 never, 1 where the product is not cut along K (default), 2 wherever the kernel takes the sizes */
 KESTREL_API int kestrel_gemm_tc_error(void);
 KESTREL_API int kestrel_linear_bf16_noalloc(const void *x, const void *w, const float *bias, void *out, int out_dtype, int T, int N, int K, long long ldx, long long ldw, kestrel_stream_t stream);
 /* tuning and test hooks of the products */

@@ -71,14 +71,17 @@ class GroupedQueryAttention(Mixer):
 
     def forward(self, x: torch.Tensor, batch, cache, residual: Optional[torch.Tensor] = None) -> Optional[ops.Partials]:
         T = x.shape[0]
-        qkv = self.qkv.forward(x)
         q = torch.empty((T, self.heads * self.head_dim), dtype=self.dtype, device=x.device)
         rot = self.position.rotary() if self.position is not None else None
         table = batch.block_table(cache.group)
-        ops.attn_prepare(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, rot.inv_freq if rot else None,
-                         rot.dim if rot else 0, batch.positions, batch.seq_of_token, table, cache.page_size, cache.k, cache.v,
-                         q, self.heads, self.kv_heads, self.head_dim, write_kv=cache.writable,
-                         rot_mode=rot.mode if rot else 0, rot_scale=rot.scale if rot else 1.0)
+        prepare = dict(q_norm_w=self.q_norm, k_norm_w=self.k_norm, norm_eps=self.qk_norm_eps or 0.0,
+                       inv_freq=rot.inv_freq if rot else None, rotary_dim=rot.dim if rot else 0, positions=batch.positions,
+                       seq_of_token=batch.seq_of_token, block_table=table, page_size=cache.page_size, k_cache=cache.k,
+                       v_cache=cache.v, q_out=q, nq=self.heads, nkv=self.kv_heads, hd=self.head_dim, write_kv=cache.writable,
+                       rot_mode=rot.mode if rot else 0, rot_scale=rot.scale if rot else 1.0)
+        # many tokens of head size 128: one kernel for the product and everything up to attention
+        if not ops.qkv_prepare_fused(x, self.qkv.weight, self.qkv.bias, **prepare):
+            ops.attn_prepare(self.qkv.forward(x), **prepare)
         a = torch.empty_like(q)
         ops.attention(self.planner, q, cache.k, cache.v, batch, cache.group, cache.page_size, a, self.heads, self.kv_heads,
                       self.head_dim, self.window, self.scale)

@@ -293,6 +293,15 @@ def test_add_rmsnorm_row_does_not_depend_on_the_batch(d, S, with_bias):
         gathered = torch.empty((400, d), dtype=dt, device=DEV)
         ops.add_rmsnorm(res.clone(), delta, w, 1e-6, gathered, rows=rows)
         assert torch.equal(gathered[399 - 123], many[123])
+        # the kernel with a warp a row, which is otherwise taken from 1,024 rows on and without slices
+        ops.norm_set_warp_rows(100, with_slices=True)
+        try:
+            warp = torch.empty((400, d), dtype=dt, device=DEV)
+            r3 = res.clone()
+            ops.add_rmsnorm(r3, delta, w, 1e-6, warp)
+        finally:
+            ops.norm_set_warp_rows()
+        assert torch.equal(warp, many) and torch.equal(r3, r1)
 
 
 def test_add_rmsnorm_refuses_what_it_cannot_hold():
@@ -908,6 +917,97 @@ def test_attn_prepare_token_does_not_depend_on_the_batch(dtype, nq, nkv, S, bias
         ref = P.rope(qr, cos, sin)
     tol = 1e-5 if dtype == "float32" else 1e-2
     np.testing.assert_allclose(q_all.float().cpu().numpy().reshape(T, nq, hd), ref, rtol=tol, atol=tol * 4)
+
+
+@pytest.mark.parametrize("nq,nkv,bias,norm,T,K,write_kv", [(5, 2, True, True, 300, 192, True), (32, 8, False, True, 1100, 256, True),
+                                                           (3, 1, True, False, 513, 128, True), (4, 2, False, True, 257, 320, False)])
+def test_qkv_product_with_prepare_in_its_epilogue(nq, nkv, bias, norm, T, K, write_kv):
+    """The q, k, v product of many tokens at head size 128 with bias, head norms, rotation and the
+    cache write in its epilogue, against the plain parts and against the two kernels it
+    replaces; head counts that leave a tile half empty, token counts that are no multiple of a
+    tile, two requests at far positions, pages in random order."""
+    ops = _ops()
+    hd, page = 128, 16
+    heads = nq + 2 * nkv
+    x, xr = _rand((T, K), torch.bfloat16, 41)
+    w, wr = _rand((heads * hd, K), torch.bfloat16, 42, K ** -0.5)
+    b, br = _rand((heads * hd,), torch.float32, 43, 0.2) if bias else (None, None)
+    qw, qwr = _rand((hd,), torch.float32, 44) if norm else (None, None)
+    kw, kwr = _rand((hd,), torch.float32, 45) if norm else (None, None)
+    inv = (np.float32(1) / np.power(np.float32(1e6), np.arange(hd // 2, dtype=np.float32) / np.float32(hd // 2))).astype(np.float32)
+    inv_d = torch.from_numpy(inv).to(DEV)
+    first = T // 3
+    positions = np.concatenate([np.arange(first) + 30000, np.arange(T - first) + 5]).astype(np.int32)
+    seqs = np.concatenate([np.zeros(first), np.ones(T - first)]).astype(np.int32)
+    width = (30000 + T) // page + 1
+    num_pages = 2 * (T // page + 3)
+    order = np.random.default_rng(2).permutation(num_pages).astype(np.int32)
+    table = np.full((2, width), -1, dtype=np.int32)
+    used = 0
+    for r, (lo, n) in enumerate(((30000, first), (5, T - first))):
+        for col in range(lo // page, (lo + n - 1) // page + 1):
+            table[r, col] = order[used]
+            used += 1
+    args = dict(q_norm_w=qw, k_norm_w=kw, norm_eps=1e-6, inv_freq=inv_d, rotary_dim=hd, positions=torch.from_numpy(positions).to(DEV),
+                seq_of_token=torch.from_numpy(seqs).to(DEV), block_table=torch.from_numpy(table).to(DEV), page_size=page, nq=nq,
+                nkv=nkv, hd=hd, write_kv=write_kv)
+
+    def caches():
+        kc = torch.zeros((num_pages, nkv, page, hd), dtype=torch.bfloat16, device=DEV)
+        return kc, torch.zeros_like(kc), torch.empty((T, nq * hd), dtype=torch.bfloat16, device=DEV)
+
+    kc, vc, q_out = caches()
+    assert ops.qkv_prepare_fused(x, w, b, k_cache=kc, v_cache=vc, q_out=q_out, **args)
+    assert ops.gemm_tc_error() == 0
+    kc2, vc2, q2 = caches()
+    ops.attn_prepare(ops.Partials(ops.linear(x, w), b), k_cache=kc2, v_cache=vc2, q_out=q2, **args)
+    # the plain parts, from the same bfloat16 operands
+    y = (xr.astype(np.float64) @ wr.astype(np.float64).T).astype(np.float32) + (br if bias else 0)
+    q = y[:, :nq * hd].reshape(T, nq, hd)
+    k = y[:, nq * hd:(nq + nkv) * hd].reshape(T, nkv, hd)
+    v = y[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+    if norm:
+        q, k = P.head_rms_norm(q, qwr, 1e-6), P.head_rms_norm(k, kwr, 1e-6)
+    ang = positions.astype(np.float32)[:, None] * inv[None, :]
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    q, k = P.rope(q, cos, sin), P.rope(k, cos, sin)
+    tol = 1e-2
+    np.testing.assert_allclose(q_out.float().cpu().numpy().reshape(T, nq, hd), q, rtol=tol, atol=tol * 4)
+    np.testing.assert_allclose(q_out.float().cpu().numpy(), q2.float().cpu().numpy(), rtol=tol, atol=tol * 4)
+    kcn, vcn = kc.float().cpu().numpy(), vc.float().cpu().numpy()
+    if not write_kv:
+        assert not kcn.any() and not vcn.any()
+        return
+    written = np.zeros((num_pages, page), dtype=bool)
+    for t in range(T):
+        pg, sl = table[seqs[t], positions[t] // page], positions[t] % page
+        written[pg, sl] = True
+        np.testing.assert_allclose(kcn[pg, :, sl, :], k[t], rtol=tol, atol=tol * 4)
+        np.testing.assert_allclose(vcn[pg, :, sl, :], v[t], rtol=tol, atol=tol * 4)
+    assert not kcn.transpose(0, 2, 1, 3)[~written].any() and not vcn.transpose(0, 2, 1, 3)[~written].any(), \
+        "a cache row of no token was written"
+    np.testing.assert_allclose(kcn, kc2.float().cpu().numpy(), rtol=tol, atol=tol * 4)
+
+
+def test_qkv_product_with_prepare_leaves_other_cases_alone():
+    """Few tokens, float32, another head size, a partial rotation: nothing is launched and the
+    caller is told so."""
+    ops = _ops()
+    i32 = torch.zeros(300, dtype=torch.int32, device=DEV)
+    inv = torch.ones(64, device=DEV)
+
+    def tried(T, hd, dtype, rot):
+        x = torch.zeros((T, 128), dtype=dtype, device=DEV)
+        w = torch.zeros((3 * hd, 128), dtype=dtype, device=DEV)
+        kc = torch.zeros((32, 1, 16, hd), dtype=dtype, device=DEV)
+        return ops.qkv_prepare_fused(x, w, None, None, None, 0.0, inv[:max(rot // 2, 1)], rot, i32[:T], i32[:T], i32[None, :32].contiguous(), 16,
+                                     kc, kc.clone(), torch.empty((T, hd), dtype=dtype, device=DEV), 1, 1, hd)
+
+    assert not tried(100, 128, torch.bfloat16, 128)
+    assert not tried(300, 64, torch.bfloat16, 64)
+    assert not tried(300, 128, torch.bfloat16, 64)
+    assert not tried(300, 128, torch.float32, 128)
+    assert tried(300, 128, torch.bfloat16, 128)
 
 
 def test_attn_prepare_refuses_odd_sizes():
