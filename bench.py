@@ -164,7 +164,7 @@ def run_workload(args) -> int:
     fill_random_(model, 0)
     longest = max(lengths) + gen + 64
     opts = EngineOptions(dtype="bfloat16", page_size=args.page_size, batch_max=n_req, max_model_len=longest,
-                         max_tokens=sum(l + gen + 64 for l in lengths), max_step_tokens=chunk, prefill_batch=chunk)
+                         max_tokens=sum(l + gen + 64 for l in lengths), max_step_tokens=max(args.step_tokens, chunk), prefill_batch=chunk)
     llm = LLM(model, dtype="bfloat16", options=opts)
     llm.engine.cache.shuffle_free(0)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lengths]
@@ -262,6 +262,8 @@ def main() -> int:
                     help="decode8b: the headline run; mix14b / 32b: whole workloads through the scheduler")
     ap.add_argument("--requests", type=int, default=0, help="requests of a workload (0: 32 for mix14b, 16 for 32b)")
     ap.add_argument("--generate", type=int, default=0, help="tokens to generate per request of a workload (0: 256 / 128)")
+    ap.add_argument("--step-tokens", type=int, default=2048,
+                    help="token budget of a workload's step (the engine's default 2,048: up to four portions of 512 beside the decode tokens)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
