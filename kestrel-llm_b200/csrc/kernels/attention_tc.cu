@@ -3,20 +3,22 @@
 // A CTA owns up to 256 rows - (token, query head of one kv group) pairs, token-major, as in
 // attention_mma.cu - as two row tiles A and B of 128, and walks the keys its rows may see in
 // tiles of 128, anchored at multiples of 128 of the absolute position.  Both row tiles use the
-// same K and V tiles, so a key tile is fetched once per 256 rows.  Nineteen warps in three roles,
+// same K and V tiles, so a key tile is fetched once per 256 rows.  Eleven warps in three roles,
 // coupled by mbarriers:
-//   loaders  (warp 16 for K, warp 18 for V)  look the tile's pages up in the block table and
+//   loaders  (warp 8 for K, warp 10 for V)  look the tile's pages up in the block table and
 //            fetch K(t) or V(t) with TMA (boxes of one page, or of 128 keys of a larger page, by
 //            64 dims; 128-byte swizzle) into two-stage rings, each as far ahead as its ring allows;
-//   issuer   (warp 17, one thread)  S_X(t) = Q_X K(t)^T and O_X += P_X(t) V(t) for X = A, B in the
+//   issuer   (warp 9, one thread)  S_X(t) = Q_X K(t)^T and O_X += P_X(t) V(t) for X = A, B in the
 //            order S_A S_B | PV_A S_A' PV_B S_B' | ..., so that the tensor cores work on one row
 //            tile while the other is softmaxed: tcgen05.mma M=128 N=128, 8 steps of K=16.  Q and K
 //            are K-major operands in shared memory (two panels of 64 elements, rows of 128
 //            bytes), V an MN-major one (its rows are keys); P is read from TMEM;
-//   softmax  (warps 0-7 for A, 8-15 for B)  two threads own a row, 64 keys each: row maximum (the
-//            halves exchange it), exp2 and sum in float32, P written as packed bfloat16 over the
-//            first 64 columns of S in TMEM.  Four softmax warps per scheduler hide each other's
-//            TMEM and MUFU latencies.
+//   softmax  (warps 0-3 for A, 4-7 for B)  a thread owns a row: its 128 scores come out of TMEM
+//            once, into registers; row maximum, exp2 and sum in float32, P written as packed
+//            bfloat16 over the first 64 columns of S in TMEM.  Nothing is exchanged between
+//            threads and no barrier stands between S and P (with two threads a row and the
+//            scores read twice, once for the maximum and once for the exponentials, the two
+//            hand-overs between the halves were on every tile's critical path).
 // TMEM (512 columns): S_A, S_B, O_A, O_B.  The output accumulates in TMEM; it is rescaled by
 // 2^(m_old - m_new) only when a row's maximum has grown by more than 8 (in log2 units) since the
 // reference it was accumulated against - P then stays below 2^8, which costs bfloat16 and the
@@ -31,7 +33,7 @@
 #include "tcgen05.cuh"
 #include <math.h>
 
-#define AT_THREADS 608           // 16 softmax warps, two loaders, the issuer
+#define AT_THREADS 352           // 8 softmax warps, two loaders, the issuer
 #define AT_BM 128
 #define AT_BN 128
 #define AT_HD 128
@@ -48,21 +50,22 @@ __device__ __forceinline__ float at_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// 32 consecutive TMEM columns of this thread's lane: two loads in flight, one wait
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float *v) {
-    uint32_t r[32];
-#pragma unroll
-    for (int q = 0; q < 2; ++q)
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-            : "=r"(r[16 * q + 0]), "=r"(r[16 * q + 1]), "=r"(r[16 * q + 2]), "=r"(r[16 * q + 3]), "=r"(r[16 * q + 4]),
-              "=r"(r[16 * q + 5]), "=r"(r[16 * q + 6]), "=r"(r[16 * q + 7]), "=r"(r[16 * q + 8]), "=r"(r[16 * q + 9]),
-              "=r"(r[16 * q + 10]), "=r"(r[16 * q + 11]), "=r"(r[16 * q + 12]), "=r"(r[16 * q + 13]), "=r"(r[16 * q + 14]),
-              "=r"(r[16 * q + 15])
-            : "r"(taddr + 16 * q));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+// 32 consecutive TMEM columns of this thread's lane into registers; at_ld_wait() before they are used
+__device__ __forceinline__ void at_ld32(uint32_t taddr, uint32_t *r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void at_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 // 16 packed words into 16 consecutive TMEM columns of this thread's lane
@@ -105,21 +108,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const uint32_t bars = base + 6 * TILE_BYTES, tmem_slot = bars + 8 * B_COUNT;
     volatile uint32_t *tmem_slot_ptr = (volatile uint32_t *)(aligned + 6 * TILE_BYTES + 8 * B_COUNT);
     uint8_t *v_ptr = aligned + 4 * TILE_BYTES;
-    float *xchg = (float *)(aligned + 6 * TILE_BYTES + 8 * B_COUNT + 16);       // [2 row tiles][768]
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        mbar_init(bar(B_Q_FULL), 16);
+        mbar_init(bar(B_Q_FULL), 8);
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(B_K_FULL + b), 1);  mbar_init(bar(B_K_EMPTY + b), 1);
             mbar_init(bar(B_V_FULL + b), 1);  mbar_init(bar(B_V_EMPTY + b), 1);
-            mbar_init(bar(B_S_FULL + b), 1);  mbar_init(bar(B_P_FULL + b), 8);
+            mbar_init(bar(B_S_FULL + b), 1);  mbar_init(bar(B_P_FULL + b), 4);
             mbar_init(bar(B_PV_DONE + b), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 17) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -152,11 +154,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int k_hi_a = min(pos_begin + (row0 + rows_a - 1) / G + 1, (slice + 1) * slice_len);
     const int n_tiles_a = has_b ? (k_hi_a > k_lo ? (k_hi_a - k_lo + AT_BN - 1) / AT_BN : 0) : n_tiles;
 
-    if (warp == 16 || warp == 18) {
+    if (warp == 8 || warp == 10) {
         // ------------------------------------------------------------------ loaders
-        // warp 16 fetches the K tiles, warp 18 the V tiles, each as far ahead as its ring allows;
+        // warp 8 fetches the K tiles, warp 10 the V tiles, each as far ahead as its ring allows;
         // lane l fetches the l-th page of a tile (both panels)
-        const bool is_v = warp == 18;
+        const bool is_v = warp == 10;
         const CUtensorMap *map = is_v ? &map_v : &map_k;
         const int full0 = is_v ? B_V_FULL : B_K_FULL, empty0 = is_v ? B_V_EMPTY : B_K_EMPTY;
         const uint32_t ring = is_v ? v_s : k_s;
@@ -182,7 +184,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 tma_load_2d(dst + AT_PANEL, map, bar(full0 + b), 64, row);
             }
         }
-    } else if (warp == 17) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------------ issuer
         if (lane == 0 && n_tiles > 0) {
             bool ok = mbar_wait(bar(B_Q_FULL), 0);
@@ -238,26 +240,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
     } else {
         // ------------------------------------------------------------------ softmax
-        // warps 0-7: row tile A, warps 8-15: row tile B.  Two threads own a row: thread (r, h) of a
-        // tile takes 64 h .. + 63 of the tile's 128 keys in the softmax and the same 64 of the 128
-        // output dims.  Warps w and w + 4 of a tile share TMEM lanes 32 (w % 4)...; the halves
-        // exchange their maxima (and at the end their sums) through shared memory.
-        const int x = warp >> 3, h = (warp >> 2) & 1, r = tid & 127;
+        // warps 0-3: row tile A, warps 4-7: row tile B; thread r of a tile owns row r (TMEM lane r)
+        const int x = warp >> 2, r = tid & 127;
         {
-            // Q: thread t moves 16-byte chunk t % 16 of rows (t / 16) * 8 .. + 7 of row tile t / 256
-            const int xt = tid >> 8, lt = tid & 255;
-            const int ld_c = lt & 15, ld_r0 = (lt >> 4) * 8;
+            // Q: thread t moves 16-byte chunk t % 16 of rows (t / 16) * 8 .. + 7 of both row tiles
+            const int ld_c = tid & 15, ld_r0 = (tid >> 4) * 8;
             const uint32_t ld_panel = (uint32_t)(ld_c >> 3) * AT_PANEL;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                int rr = ld_r0 + j;
-                bool valid = xt * AT_BM + rr < rows_here;
-                size_t off = 0;
-                if (valid) {
-                    int row = row0 + xt * AT_BM + rr;
-                    off = ((size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G) * AT_HD + ld_c * 8;
+            for (int xt = 0; xt < 2; ++xt) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    int rr = ld_r0 + j;
+                    bool valid = xt * AT_BM + rr < rows_here;
+                    size_t off = 0;
+                    if (valid) {
+                        int row = row0 + xt * AT_BM + rr;
+                        off = ((size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G) * AT_HD + ld_c * 8;
+                    }
+                    at_cp_async16(q_s + xt * TILE_BYTES + ld_panel + swizzle128(rr, ld_c & 7), p.q + off, valid);
                 }
-                at_cp_async16(q_s + xt * TILE_BYTES + ld_panel + swizzle128(rr, ld_c & 7), p.q + off, valid);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -274,12 +275,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         // warps none of whose 32 rows exist (decode: a few rows per request) skip the arithmetic
         const bool warp_has_rows = 32 * (warp & 3) < rows_x;
         const uint32_t lane_base = ((uint32_t)(32 * (warp & 3))) << 16;
-        const int col0 = 64 * h;
-        const uint32_t s_addr = tmem + lane_base + x * 128 + col0, o_addr = tmem + lane_base + 256 + x * 128 + col0;
-        const uint32_t p_addr = tmem + lane_base + x * 128 + 32 * h;     // P: two keys to a column
-        float *xch = xchg + x * 768;                                     // [2 tile parities + sums][2 halves][128 rows]
-        const int pair_bar = 1 + 4 * x + (warp & 3);                     // the two warps that share these rows
-        float m_ref = -INFINITY, l_run = 0.f;       // the reference the output is accumulated against, and this half's sum
+        const uint32_t s_addr = tmem + lane_base + x * 128, o_addr = tmem + lane_base + 256 + x * 128;
+        float m_ref = -INFINITY, l_run = 0.f;       // the reference the output is accumulated against, and the row's sum
         bool ok = true;             // after a wait gave up the loop runs on without waiting, so that the warps still meet
 
         for (int t = 0; t < n_tiles_x; ++t) {
@@ -289,84 +286,65 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             if (ok && !mbar_wait(bar(B_S_FULL + x), (uint32_t)t & 1u)) { atomicExch(&g_at_error, 7); ok = false; }
             tc_fence_after();
             if (warp_has_rows) {
+                uint32_t sr[128];
+#pragma unroll
+                for (int c = 0; c < 128; c += 32) at_ld32(s_addr + c, sr + c);
+                at_ld_wait();
                 const bool whole = kbase >= k_first && kbase + AT_BN <= k_hi_x && kbase + AT_BN - 1 <= my_pos && kbase >= my_lo;
-                const bool warp_whole = __all_sync(0xffffffffu, whole);
+                if (!__all_sync(0xffffffffu, whole)) {
+                    // keys this row may not see count as minus infinity: no maximum, a weight of zero
+#pragma unroll
+                    for (int j = 0; j < 128; ++j) {
+                        int key = kbase + j;
+                        bool vis = key <= my_pos && key >= my_lo && key < k_hi_x && key >= k_first;
+                        if (!vis) sr[j] = 0xff800000u;
+                    }
+                }
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int c = 0; c < 64; c += 32) {
-                    float s[32];
-                    tc_ld32(s_addr + c, s);
-                    if (warp_whole) {
+                for (int j = 0; j < 128; j += 8) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], s[j]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            int key = kbase + col0 + c + j;
-                            bool vis = key <= my_pos && key >= my_lo && key < k_hi_x && key >= k_first;
-                            m4[j & 3] = fmaxf(m4[j & 3], vis ? s[j] : -INFINITY);
-                        }
-                    }
+                    for (int k = 0; k < 4; ++k)
+                        m4[k] = at_max3(m4[k], __uint_as_float(sr[j + 2 * k]), __uint_as_float(sr[j + 2 * k + 1]));
                 }
-                float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;   // the scale is positive
-                float *xm = xch + b * 256;              // by tile parity: the other warp may still read the tile before
-                xm[h * 128 + r] = mx;
-                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-                mx = fmaxf(mx, xm[(h ^ 1) * 128 + r]);
-                // the reference moves only when the maximum has outgrown it by more than the step;
-                // both halves of a row see the same maximum and decide alike
+                const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;   // the scale is positive
+                // the reference moves only when the maximum has outgrown it by more than the step
                 const bool grow = mx > m_ref + AT_RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
-                if (__any_sync(0xffffffffu, grow && m_ref != -INFINITY && t > 0)) {
-                    // the whole warp walks its rows' outputs (tcgen05.ld / st are warp-wide); rows
-                    // whose reference stays are multiplied by one
-                    const float alpha = (grow && m_ref != -INFINITY) ? at_exp2(m_ref - mx) : 1.f;
-                    l_run *= alpha;
-#pragma unroll
-                    for (int c = 0; c < 64; c += 32) {
-                        float o[32];
-                        tc_ld32(o_addr + c, o);
-                        uint32_t w[32];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(o[j] * alpha);
-                        tc_st16(o_addr + c, w);
-                        tc_st16(o_addr + c + 16, w + 16);
-                    }
+                float alpha = 1.f;
+                if (grow) {
+                    if (m_ref != -INFINITY) alpha = at_exp2(m_ref - mx);
+                    m_ref = mx;
                 }
-                if (grow) m_ref = mx;
+                l_run *= alpha;
                 const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
                 float l4[4] = {0.f, 0.f, 0.f, 0.f};
-                // P may overwrite S only when BOTH halves have read their scores: half 1's P (columns
-                // 32..63) lies over scores of half 0
-                uint32_t w[32];
+                uint32_t w[64];
 #pragma unroll
-                for (int c = 0; c < 64; c += 32) {
-                    float s[32];
-                    tc_ld32(s_addr + c, s);
-                    if (warp_whole) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            s[j] = at_exp2(fmaf(s[j], p.scale_log2, -m_use));
-                            l4[j & 3] += s[j];
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            int key = kbase + col0 + c + j;
-                            bool vis = key <= my_pos && key >= my_lo && key < k_hi_x && key >= k_first;
-                            s[j] = vis ? at_exp2(fmaf(s[j], p.scale_log2, -m_use)) : 0.f;
-                            l4[j & 3] += s[j];
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(s[2 * j], s[2 * j + 1]);
-                        w[(c >> 1) + j] = *reinterpret_cast<uint32_t *>(&b2);
-                    }
+                for (int j = 0; j < 64; ++j) {
+                    float e0 = at_exp2(fmaf(__uint_as_float(sr[2 * j]), p.scale_log2, -m_use));
+                    float e1 = at_exp2(fmaf(__uint_as_float(sr[2 * j + 1]), p.scale_log2, -m_use));
+                    l4[j & 3] += e0 + e1;
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+                    w[j] = *reinterpret_cast<uint32_t *>(&b2);
                 }
                 l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");     // both halves hold their scores in registers now
-                tc_st16(p_addr, w);
-                tc_st16(p_addr + 16, w + 16);
+                // P over this row's own scores, which are all in registers
+#pragma unroll
+                for (int c = 0; c < 64; c += 16) tc_st16(s_addr + c, w + c);
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+                    // the whole warp walks its rows' outputs (tcgen05.ld / st are warp-wide); rows whose
+                    // reference stays are multiplied by one.  O_X is idle: its last product is done.
+#pragma unroll
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t o[32];
+                        at_ld32(o_addr + c, o);
+                        at_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                        tc_st16(o_addr + c, o);
+                        tc_st16(o_addr + c + 16, o + 16);
+                    }
+                }
                 tc_wait_st();
             }
             if (kbase < k_first || kbase + AT_BN > k_hi) {
@@ -374,7 +352,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 // reads them (both row tiles write the same zeros: either may be the only one at a tile)
                 if (ok && !mbar_wait(bar(B_V_FULL + b), (uint32_t)(t >> 1) & 1u)) { atomicExch(&g_at_error, 8); ok = false; }
                 const int lo_rows = max(0, k_first - kbase), hi_row = min(AT_BN, k_hi - kbase);
-                for (int idx = (tid & 255); idx < AT_BN * 16; idx += 256) {
+                for (int idx = r; idx < AT_BN * 16; idx += 128) {
                     int row = idx >> 4, c = idx & 15;
                     if (row < lo_rows || row >= hi_row)
                         *reinterpret_cast<uint4 *>(v_ptr + b * TILE_BYTES + (c >> 3) * AT_PANEL + row * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
@@ -390,38 +368,36 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         if (n_tiles_x > 0 && ok && !mbar_wait(bar(B_PV_DONE + x), (uint32_t)(n_tiles_x - 1) & 1u)) { atomicExch(&g_at_error, 9); ok = false; }
         tc_fence_after();
         if (warp_has_rows) {
-            // the row's sum is the sum of its halves
-            xch[512 + h * 128 + r] = l_run;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            const float l_tot = l_run + xch[512 + (h ^ 1) * 128 + r];
             const bool write = row_ok && ok;
             int row = row0 + x * AT_BM + r;
             size_t qrow = write ? (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G : 0;
-            const float inv = p.slices > 1 ? 1.f : 1.0f / l_tot;
+            const float inv = p.slices > 1 ? 1.f : 1.0f / l_run;
 #pragma unroll
-            for (int c = 0; c < 64; c += 32) {
-                float o[32];
+            for (int c = 0; c < 128; c += 32) {
+                uint32_t o[32];
                 if (n_tiles_x > 0) {
-                    tc_ld32(o_addr + c, o);             // warp-wide, whatever rows exist
+                    at_ld32(o_addr + c, o);             // warp-wide, whatever rows exist
+                    at_ld_wait();
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) o[j] = 0.f;
+                    for (int j = 0; j < 32; ++j) o[j] = 0u;
                 }
                 if (!write) continue;
                 if (p.slices > 1) {
                     // this slice's unnormalised out; attention_merge_kernel combines the slices
-                    float *po = p.part_o + (qrow * p.slices + slice) * AT_HD + col0 + c;
+                    float *po = p.part_o + (qrow * p.slices + slice) * AT_HD + c;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(po + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<uint4 *>(po + j) = make_uint4(o[j], o[j + 1], o[j + 2], o[j + 3]);
                 } else {
-                    __nv_bfloat16 *po = p.out + qrow * AT_HD + col0 + c;
+                    __nv_bfloat16 *po = p.out + qrow * AT_HD + c;
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
                         uint4 u;
-                        __nv_bfloat162 b0 = __floats2bfloat162_rn(o[j] * inv, o[j + 1] * inv);
-                        __nv_bfloat162 b1 = __floats2bfloat162_rn(o[j + 2] * inv, o[j + 3] * inv);
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(o[j + 4] * inv, o[j + 5] * inv);
-                        __nv_bfloat162 b3 = __floats2bfloat162_rn(o[j + 6] * inv, o[j + 7] * inv);
+                        __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
+                        __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+                        __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
                         u.x = *reinterpret_cast<uint32_t *>(&b0);
                         u.y = *reinterpret_cast<uint32_t *>(&b1);
                         u.z = *reinterpret_cast<uint32_t *>(&b2);
@@ -430,15 +406,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                     }
                 }
             }
-            if (write && p.slices > 1 && h == 0) {
+            if (write && p.slices > 1) {
                 p.part_ml[(qrow * p.slices + slice) * 2] = m_ref;
-                p.part_ml[(qrow * p.slices + slice) * 2 + 1] = l_tot;
+                p.part_ml[(qrow * p.slices + slice) * 2 + 1] = l_run;
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 17) {
+    if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
@@ -485,7 +461,7 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
     p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = slices; p.slice_len = slice_len;
     p.max_kv_ptr = max_kv_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
-    size_t smem = 12 * AT_PANEL + 8 * B_COUNT + 16 + 2 * 768 * 4 + 1024;
+    size_t smem = 12 * AT_PANEL + 8 * B_COUNT + 16 + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
