@@ -28,7 +28,7 @@ constexpr int RING = 8;                  // tile lists of this many plans may be
 constexpr int NO_SPLIT = (1 << 30) / 128 * 128;
 
 struct Plan {
-    int group_size = 0, rows_large = 0;
+    int group_size = 0, rows_large = 0, small_rows = 16;
     int ns = 0, nl = 0;                  // tiles of at most 16 rows; tiles of rows_large rows
     int small_kv = 0, large_kv = 0;      // longest request among each kind
     const int *small_seq = nullptr, *small_row0 = nullptr, *large_seq = nullptr, *large_row0 = nullptr;   // device
@@ -92,20 +92,32 @@ int grow_identity(Planner &pl, int seqs, cudaStream_t stream) {
 }
 
 // tile lists of this step for mixers with `gs` query heads per kv head and tiles of `rl` rows
-int plan_for(Planner &pl, long long serial, const int *host, const int *dev, const int *layout, int gs, int rl,
+// Requests of at most 16 rows are one small tile each.  A short portion near the start of its
+// request (at most small_rows rows, at most SMALL_PORTION_KEYS keys) is cut into small tiles too
+// where small_rows > 16: the kernel for decode tokens has a lower floor than the one for prompt
+// portions (measured alone, from position 0: 16 tokens 4.7 against 8.5 us, 128 tokens 6.7 against
+// 9.4; from 256 tokens on, or with thousands of keys that every small tile would read again, the
+// portion kernel wins).
+constexpr int SMALL_PORTION_KEYS = 512;
+inline bool small_request(long long rows, int kv, int small_rows) {
+    return rows <= 16 || (rows <= small_rows && kv <= SMALL_PORTION_KEYS);
+}
+
+int plan_for(Planner &pl, long long serial, const int *host, const int *dev, const int *layout, int gs, int rl, int small_rows,
              bool captured, cudaStream_t stream, const Plan **out) {
     if (serial != pl.serial) {
         pl.plans.clear();
         pl.serial = serial;
     }
     for (const Plan &p : pl.plans)
-        if (p.group_size == gs && p.rows_large == rl) { *out = &p; return 0; }
+        if (p.group_size == gs && p.rows_large == rl && p.small_rows == small_rows) { *out = &p; return 0; }
     const int n = layout[KB_NUM_SEQS];
     const int *cu = host + layout[KB_O_CU_SEQLENS];
     const int *kv = host + layout[KB_O_KV_LENS];
     Plan p;
     p.group_size = gs;
     p.rows_large = rl;
+    p.small_rows = small_rows;
     if ((long long)layout[KB_MAX_COUNT] * gs <= 16) {
         // every request fits one tile of 16 rows: tile i is request i, first row 0
         if (n > pl.max_seqs) {
@@ -124,9 +136,11 @@ int plan_for(Planner &pl, long long serial, const int *host, const int *dev, con
     std::vector<int> ss, sr, ls, lr;
     for (int i = 0; i < n; ++i) {
         const long long rows = (long long)(cu[i + 1] - cu[i]) * gs;
-        if (rows <= 16) {
-            ss.push_back(i);
-            sr.push_back(0);
+        if (small_request(rows, kv[i], small_rows)) {
+            for (long long r0 = 0; r0 < rows; r0 += 16) {
+                ss.push_back(i);
+                sr.push_back((int)r0);
+            }
             p.small_kv = std::max(p.small_kv, kv[i]);
         } else {
             for (long long r0 = 0; r0 < rows; r0 += rl) {
@@ -260,14 +274,16 @@ KESTREL_API int kestrel_attention(void *planner, long long step_serial, const in
     // behind 1,024 keys 36.8 -> 31.2).
     int rows_large = use_tc ? 256 : kestrel_attention_mma_rows_per_tile(hd);
     int tc_slices = 1;
+    const bool use_decode = kestrel_attention_decode_supported(hd, page_size) && gs <= 16;
+    const int small_rows = use_decode ? 512 : 16;
     if (use_tc) {
-        // the portions of this step (requests with more than 16 rows): their rows, their tiles of 256, their longest context
+        // the portions of this step that go to this kernel: their rows, their tiles of 256, their longest context
         const int *cu_h = batch_host + layout[KB_O_CU_SEQLENS], *kv_h = batch_host + layout[KB_O_KV_LENS];
         long long rows = 0, tiles256 = 0;
         int kv = 0;
         for (int i = 0; i < n; ++i) {
             const long long r = (long long)(cu_h[i + 1] - cu_h[i]) * gs;
-            if (r <= 16) continue;
+            if (small_request(r, kv_h[i], small_rows)) continue;
             rows += r;
             tiles256 += (r + 255) / 256;
             kv = std::max(kv, kv_h[i]);
@@ -278,7 +294,7 @@ KESTREL_API int kestrel_attention(void *planner, long long step_serial, const in
         else if (rows * nkv <= 128ll * sms) rows_large = 128;
     }
     const Plan *plan = nullptr;
-    int rc = plan_for(*pl, step_serial, batch_host, batch_dev, layout, gs, rows_large, captured != 0, stream, &plan);
+    int rc = plan_for(*pl, step_serial, batch_host, batch_dev, layout, gs, rows_large, small_rows, captured != 0, stream, &plan);
     if (rc) return rc;
     int launches = 0;
     if (plan->ns > 0) {
@@ -288,7 +304,6 @@ KESTREL_API int kestrel_attention(void *planner, long long step_serial, const in
         // is short; only full-length key ranges are cut.  The decode kernel merges up to 4 slices
         // inside a cluster, more through scratch and a second kernel of a few microseconds
         // (measured, one request: 8,192 keys 21.7 us with 8 slices, 12.2 us with 32).
-        const bool use_decode = kestrel_attention_decode_supported(hd, page_size) && gs <= 16;
         int slices = 1, slice_len = NO_SPLIT;
         if (window <= 0) {
             const int slots = use_decode ? kestrel_attention_decode_slots(hd) : kestrel_attention_mma_slots(hd);
