@@ -613,6 +613,17 @@ def test_attention_decode_takes_short_portions_too():
               seed=3, decode=True)
 
 
+@pytest.mark.parametrize("nq,nkv,hd,window,slices,slice_len", [(8, 2, 128, 0, 1, 1 << 24), (10, 2, 128, 0, 3, 128), (6, 2, 64, 40, 1, 1 << 24),
+                                                               (3, 1, 128, 0, 5, 64)])
+def test_attention_decode_takes_portions_of_many_tiles(nq, nkv, hd, window, slices, slice_len):
+    """What the dispatcher hands this kernel since short portions near a request's start go to it:
+    portions of tens of tokens cut into tiles of 16 rows, a token's heads split over two tiles
+    where the group size does not divide 16, beside single tokens; tiles whose first row is not
+    the request's first."""
+    _mma_case(nq, nkv, hd, window, 16, lens_new=(40, 1, 100, 7, 1), lens_ctx=(100, 300, 0, 0, 9), rows_per_tile=16, slices=slices,
+              slice_len=slice_len, seed=21, decode=True)
+
+
 @pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 255, 256, 299])
 @pytest.mark.parametrize("sliced", [False, True])
 def test_attention_decode_finds_one_far_key(far, sliced):
