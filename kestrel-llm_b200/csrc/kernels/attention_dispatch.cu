@@ -92,17 +92,25 @@ int grow_identity(Planner &pl, int seqs, cudaStream_t stream) {
 }
 
 // tile lists of this step for mixers with `gs` query heads per kv head and tiles of `rl` rows
-// Requests of at most 16 rows are one small tile each.  A short portion near the start of its
-// request (at most small_rows rows, at most SMALL_PORTION_KEYS keys) is cut into small tiles too
-// where small_rows > 16: the kernel for decode tokens has a lower floor than the one for prompt
-// portions (measured alone, from position 0: 16 tokens 4.7 against 8.5 us, 128 tokens 6.7 against
-// 9.4; from 256 tokens on, or with thousands of keys that every small tile would read again, the
-// portion kernel wins).
-constexpr int SMALL_PORTION_KEYS = 512;
+// Requests of at most 16 rows are one small tile each.  A short portion (at most small_rows rows,
+// where small_rows > 16) is cut into small tiles too while its keys are few enough: the kernel for
+// decode tokens has a lower floor than the one for prompt portions, but every tile of 16 rows reads
+// the request's keys again (measured inside steps of 36 layers, new tokens / keys before them:
+// 16 / 0 3.78 -> 3.44 ms, 16 / 1,024 4.40 -> 3.65, 16 / 4,096 4.01 -> 3.86, 64 / 1,024 4.92 -> 4.30,
+// 64 / 2,048 4.77 -> 4.61, 128 / 0 4.88 -> 4.46, 128 / 1,024 5.58 -> 5.01; the portion kernel wins at
+// 32 / 4,096 4.36 against 4.50, 64 / 4,096 4.93 against 5.21, 128 / 2,048 5.47 against 5.59, and
+// from 256 tokens on).  g_small_portion_scale stretches the limits (0: no short portion goes there).
+int g_small_portion_scale = 100;       // per cent
 inline bool small_request(long long rows, int kv, int small_rows) {
-    return rows <= 16 || (rows <= small_rows && kv <= SMALL_PORTION_KEYS);
+    if (rows <= 16) return true;
+    if (rows > small_rows) return false;
+    const long long limit = rows <= 64 ? 4352 : rows <= 256 ? 2304 : 1664;
+    return (long long)kv * 100 <= limit * g_small_portion_scale;
 }
 
+}  // namespace
+KESTREL_API void kestrel_attention_set_small_portions(int per_cent) { g_small_portion_scale = per_cent >= 0 ? per_cent : 100; }
+namespace {
 int plan_for(Planner &pl, long long serial, const int *host, const int *dev, const int *layout, int gs, int rl, int small_rows,
              bool captured, cudaStream_t stream, const Plan **out) {
     if (serial != pl.serial) {

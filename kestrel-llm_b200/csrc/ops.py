@@ -662,6 +662,13 @@ def attention_tc_error() -> int:
     return library().kestrel_attention_tc_error()
 
 
+def attention_set_small_portions(per_cent: int = -1) -> None:
+    """Short prompt portions (at most 512 rows of (token, head) per kv head) go to the attention
+    kernel for decode tokens while their keys stay under limits by row count; ``per_cent`` scales
+    those limits (0: never, negative: the default).  For tests of both routes."""
+    library().kestrel_attention_set_small_portions(int(per_cent))
+
+
 class AttentionPlanner:
     """What the attention kernels keep between the layers of a step: the tile lists of the
     step's requests on the device (made once per step from the step's host description) and

@@ -203,6 +203,8 @@ KESTREL_API int kestrel_attention_decode_error(void);
  * the device, `layout` its layout; `step_serial` changes with every step.  captured != 0: the
  * launch is being recorded for replay with other contents, so the number of slices follows
  * layout[KB_MAX_KV_LEN] (a nominal context) and their length is read on the device. */
+/* short prompt portions on the kernel for decode tokens: the key limits in per cent of the defaults (0: never, negative: the default); for tests and tuning */
+KESTREL_API void kestrel_attention_set_small_portions(int per_cent);
 KESTREL_API void *kestrel_attn_planner_create(int max_tokens, int max_seqs);
 KESTREL_API void kestrel_attn_planner_destroy(void *planner);
 KESTREL_API int kestrel_attention(void *planner, long long step_serial, const int *batch_host, const int *batch_dev, const int *layout, int group, int captured, const void *q, const void *k_cache, const void *v_cache, void *out, int dtype, int cache_pages, int page_size, int nq, int nkv, int hd, int window, float scale, kestrel_stream_t stream);

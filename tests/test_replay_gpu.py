@@ -103,6 +103,20 @@ def test_other_page_sizes(model_dirs, name, page_size, family, dtype, record_pro
         assert engine.cache.pages_handed_out() > engine.cache.num_pages(0)
 
 
+@pytest.mark.parametrize("per_cent", [0, 100, 1000])
+@pytest.mark.parametrize("family", [R.trace_portions, R.trace_mixed])
+def test_short_portions_on_either_attention_kernel(model_dirs, per_cent, family, record_property):
+    """Head size 128 in bfloat16: short portions go to the attention kernel for decode tokens
+    while their keys are few (the default), never (0), or whatever their keys (1000); every
+    route against the plain implementation."""
+    from kestrel_llm_b200.csrc import ops
+    ops.attention_set_small_portions(per_cent)
+    try:
+        _run(model_dirs, "D", "bfloat16", family, record_property, lengths=LENGTHS_MIXED["D"] if family is R.trace_mixed else None)
+    finally:
+        ops.attention_set_small_portions()
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_cuttings_agree_with_each_other(model_dirs, name, dtype):
