@@ -62,6 +62,26 @@ __device__ __forceinline__ void at_ld32(uint32_t taddr, uint32_t *r) {
         : "r"(taddr));
 }
 __device__ __forceinline__ void at_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// two float32 lanes in one instruction (fma.rn.f32x2, add.rn.f32x2): half the issue slots of the
+// softmax's multiply-adds and sums
+__device__ __forceinline__ uint64_t at_pack2(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void at_unpack2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t at_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t at_add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ float at_max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -317,17 +337,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 }
                 l_run *= alpha;
                 const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint64_t scale2 = at_pack2(p.scale_log2, p.scale_log2), shift2 = at_pack2(-m_use, -m_use);
+                uint64_t l2[4] = {0ull, 0ull, 0ull, 0ull};          // four pairs of partial sums
                 uint32_t w[64];
 #pragma unroll
                 for (int j = 0; j < 64; ++j) {
-                    float e0 = at_exp2(fmaf(__uint_as_float(sr[2 * j]), p.scale_log2, -m_use));
-                    float e1 = at_exp2(fmaf(__uint_as_float(sr[2 * j + 1]), p.scale_log2, -m_use));
-                    l4[j & 3] += e0 + e1;
+                    float x0, x1;
+                    at_unpack2(at_fma2(at_pack2(__uint_as_float(sr[2 * j]), __uint_as_float(sr[2 * j + 1])), scale2, shift2), x0, x1);
+                    const float e0 = at_exp2(x0), e1 = at_exp2(x1);
+                    l2[j & 3] = at_add2(l2[j & 3], at_pack2(e0, e1));
                     __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
                     w[j] = *reinterpret_cast<uint32_t *>(&b2);
                 }
-                l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                {
+                    float a0, a1, b0, b1;
+                    at_unpack2(at_add2(at_add2(l2[0], l2[1]), at_add2(l2[2], l2[3])), a0, a1);
+                    b0 = a0 + a1;
+                    (void)b1;
+                    l_run += b0;
+                }
                 // P over this row's own scores, which are all in registers
 #pragma unroll
                 for (int c = 0; c < 64; c += 16) tc_st16(s_addr + c, w + c);
