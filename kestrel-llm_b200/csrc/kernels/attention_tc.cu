@@ -339,26 +339,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
                 const uint64_t scale2 = at_pack2(p.scale_log2, p.scale_log2), shift2 = at_pack2(-m_use, -m_use);
                 uint64_t l2[4] = {0ull, 0ull, 0ull, 0ull};          // four pairs of partial sums
-                uint32_t w[64];
+                // P over this row's own scores, which are all in registers; sixteen columns are stored
+                // while the next sixteen are computed
 #pragma unroll
-                for (int j = 0; j < 64; ++j) {
-                    float x0, x1;
-                    at_unpack2(at_fma2(at_pack2(__uint_as_float(sr[2 * j]), __uint_as_float(sr[2 * j + 1])), scale2, shift2), x0, x1);
-                    const float e0 = at_exp2(x0), e1 = at_exp2(x1);
-                    l2[j & 3] = at_add2(l2[j & 3], at_pack2(e0, e1));
-                    __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-                    w[j] = *reinterpret_cast<uint32_t *>(&b2);
+                for (int c = 0; c < 64; c += 16) {
+                    uint32_t w[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float x0, x1;
+                        at_unpack2(at_fma2(at_pack2(__uint_as_float(sr[2 * (c + j)]), __uint_as_float(sr[2 * (c + j) + 1])), scale2, shift2), x0, x1);
+                        const float e0 = at_exp2(x0), e1 = at_exp2(x1);
+                        l2[j & 3] = at_add2(l2[j & 3], at_pack2(e0, e1));
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+                        w[j] = *reinterpret_cast<uint32_t *>(&b2);
+                    }
+                    tc_st16(s_addr + c, w);
                 }
                 {
-                    float a0, a1, b0, b1;
+                    float a0, a1;
                     at_unpack2(at_add2(at_add2(l2[0], l2[1]), at_add2(l2[2], l2[3])), a0, a1);
-                    b0 = a0 + a1;
-                    (void)b1;
-                    l_run += b0;
+                    l_run += a0 + a1;
                 }
-                // P over this row's own scores, which are all in registers
-#pragma unroll
-                for (int c = 0; c < 64; c += 16) tc_st16(s_addr + c, w + c);
                 if (__any_sync(0xffffffffu, alpha != 1.f)) {
                     // the whole warp walks its rows' outputs (tcgen05.ld / st are warp-wide); rows whose
                     // reference stays are multiplied by one.  O_X is idle: its last product is done.
