@@ -110,6 +110,10 @@ add_rmsnorm_vec_kernel(float *__restrict__ residual, const float *__restrict__ p
                        const float *__restrict__ bias, const int *__restrict__ rows, const float *__restrict__ w,
                        float eps, TOut *__restrict__ out, int d, int write_back) {
     pdl_launch_dependents();
+    // the norm's weight is a model weight: this thread's first vector of it is fetched while the
+    // kernel before this one still runs, not after the row's sum is known
+    const float4 *w4 = reinterpret_cast<const float4 *>(w);
+    const float4 g0 = (int)threadIdx.x < (d >> 2) ? w4[threadIdx.x] : make_float4(0.f, 0.f, 0.f, 0.f);
     pdl_wait();
     constexpr int VL = NORMV_THREADS / THREADS;
     extern __shared__ float xs[];
@@ -160,9 +164,8 @@ add_rmsnorm_vec_kernel(float *__restrict__ residual, const float *__restrict__ p
     for (int k = 0; k < NORMV_THREADS / 32; ++k) tot += red[k];
     float rinv = 1.0f / sqrtf(tot / (float)d + eps);
     TOut *o = out + (size_t)r * d;
-    const float4 *w4 = reinterpret_cast<const float4 *>(w);
     for (int i = threadIdx.x; i < d4; i += THREADS) {
-        float4 x = reinterpret_cast<float4 *>(xs)[i], g = w4[i];
+        float4 x = reinterpret_cast<float4 *>(xs)[i], g = i == (int)threadIdx.x ? g0 : w4[i];
         store4(o + 4 * i, make_float4((x.x * rinv) * g.x, (x.y * rinv) * g.y, (x.z * rinv) * g.z, (x.w * rinv) * g.w));
     }
 }
@@ -541,7 +544,6 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
                           T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out,
                           int nq, int nkv, int write_kv) {
     pdl_launch_dependents();
-    pdl_wait();
     constexpr int hd = 128;
     __shared__ __align__(16) float cs_s[64], sn_s[64];
     const int t = blockIdx.x;
@@ -549,8 +551,35 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
     const int heads = nq + 2 * nkv;
     const int h = blockIdx.y * 32 + (threadIdx.x >> 3);
     const bool live = h < heads;
-    // the head's values are asked for first: their loads are in flight while two warps turn the
-    // token's position into cosines and sines and the block meets at the barrier
+    // What does not come from the kernel before this one - the step's description (positions, block
+    // tables: copied before the step's first kernel), the rotation's frequencies, norm weights and
+    // bias - is read, and the cosines and sines are made, while that kernel still runs.
+    const int pos = positions[t];
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    int page = 0;
+    if (live && !is_q && write_kv)          // where the key or value goes: two dependent loads
+        page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
+    if (threadIdx.x < 64) {
+        float ang = (float)pos * inv_freq[threadIdx.x];
+        float sn, cs;
+        sincosf(ang, &sn, &cs);
+        cs_s[threadIdx.x] = cs * rot_scale;
+        sn_s[threadIdx.x] = sn * rot_scale;
+    }
+    const float *nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    float4 g[4], bv[4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) g[v] = bv[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live && nw) {
+        const float4 *g4 = reinterpret_cast<const float4 *>(nw) + 2 * sub;
+        g[0] = g4[0]; g[1] = g4[1]; g[2] = g4[16]; g[3] = g4[17];
+    }
+    if (live && bias) {
+        const float4 *b4 = reinterpret_cast<const float4 *>(bias + (size_t)h * hd) + 2 * sub;
+        bv[0] = b4[0]; bv[1] = b4[1]; bv[2] = b4[16]; bv[3] = b4[17];
+    }
+    pdl_wait();
+    // the head's values: their loads are in flight while the block meets at the barrier
     float4 x[4];             // x[0], x[1]: dimensions 8 sub .. 8 sub + 7; x[2], x[3]: the same 64 further
 #pragma unroll
     for (int v = 0; v < 4; ++v) x[v] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -563,27 +592,14 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
             x[0] = add4(x[0], a); x[1] = add4(x[1], b); x[2] = add4(x[2], c); x[3] = add4(x[3], e);
         }
     }
-    const int pos = positions[t];
-    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
-    int page = 0;
-    if (live && !is_q && write_kv)          // where the key or value goes: two dependent loads, begun before the barrier too
-        page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
-    if (threadIdx.x < 64) {
-        float ang = (float)pos * inv_freq[threadIdx.x];
-        float sn, cs;
-        sincosf(ang, &sn, &cs);
-        cs_s[threadIdx.x] = cs * rot_scale;
-        sn_s[threadIdx.x] = sn * rot_scale;
-    }
     __syncthreads();
     // from here on the eight lanes of a head stay together: shuffles name them by their own mask
     if (!live || (!is_q && !write_kv)) return;
     const unsigned mask = 0xffu << (threadIdx.x & 24);
     if (bias) {
-        const float4 *b4 = reinterpret_cast<const float4 *>(bias + (size_t)h * hd) + 2 * sub;
-        x[0] = add4(x[0], b4[0]); x[1] = add4(x[1], b4[1]); x[2] = add4(x[2], b4[16]); x[3] = add4(x[3], b4[17]);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) x[v] = add4(x[v], bv[v]);
     }
-    const float *nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
     if (nw) {
         float ss = 0.f;
 #pragma unroll
@@ -591,8 +607,6 @@ attn_prepare_hd128_kernel(const float *__restrict__ partial, int S, size_t slice
 #pragma unroll
         for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(mask, ss, o);
         const float rinv = 1.0f / sqrtf(ss / (float)hd + norm_eps);
-        const float4 *g4 = reinterpret_cast<const float4 *>(nw) + 2 * sub;
-        const float4 g[4] = {g4[0], g4[1], g4[16], g4[17]};
 #pragma unroll
         for (int v = 0; v < 4; ++v)
             x[v] = make_float4((x[v].x * rinv) * g[v].x, (x[v].y * rinv) * g[v].y, (x[v].z * rinv) * g[v].z, (x[v].w * rinv) * g[v].w);
